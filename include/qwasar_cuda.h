@@ -1,0 +1,277 @@
+/* qwasar_cuda.h -- C ABI of the B200 (sm_100a) backend for qwasar's gated GQA
+ * full-attention path.
+ *
+ * The first part re-declares, with unchanged names, argument order and
+ * meaning, the subset of the reference's backend boundary (qwasar_gpu.h) that
+ * the attention node uses; each declaration cites the reference declaration it
+ * implements.  A translation unit that already includes the reference's
+ * qwasar_gpu.h may define QWASAR_GPU_H's types first: the typedefs below are
+ * skipped when QWASAR_GPU_H is defined.  The second part is additive: entry
+ * points the reference does not have (device-resident buffers, the paged K/V
+ * arena, the fused node, batched decode, partials for the exchange between
+ * GPUs).  Plain C99; no CUDA or torch types appear in any signature.
+ *
+ * Cache element type: bfloat16 (the reference stores IEEE half,
+ * qwasar_gpu.h:395-400).  Activations are fp32 in the reference signatures;
+ * the additive entry points take a qw_dtype. */
+#ifndef QWASAR_CUDA_H
+#define QWASAR_CUDA_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ======================================================================== *
+ *  Part 1 -- the reference boundary (qwasar_gpu.h)                          *
+ * ======================================================================== */
+
+#ifndef QWASAR_GPU_H
+/* qwasar_gpu.h:13-16 -- opaque buffer handle. */
+typedef struct qw_buf_s *qw_buf;
+/* qwasar_gpu.h:45-52 -- a tensor argument: buffer + byte offset, by value.
+ * {NULL, 0} means "operand absent" (qwasar_gpu.h:269-272). */
+typedef struct { qw_buf buf; size_t off; } qw_ref;
+static inline qw_ref qw_ref_at(qw_buf b, size_t off) { qw_ref r = { b, off }; return r; }
+static inline qw_ref qw_ref_offset(qw_ref r, size_t off) { r.off += off; return r; }
+/* qwasar_gpu.h:54 -- one command buffer under construction. */
+typedef struct qw_cmd_s *qw_cmd;
+#endif
+
+/* qwasar_gpu.h:18-23.  Idempotent; false + message in err on failure (no
+ * CUDA device, not compute capability 10.x, driver entry points missing). */
+bool qw_gpu_init(char *err, size_t errcap);
+void qw_gpu_shutdown(void);
+/* qwasar_gpu.h:25-28. */
+const char *qw_gpu_name(void);
+uint64_t    qw_gpu_working_set_limit(void);   /* bytes of device memory */
+uint64_t    qw_gpu_max_buffer_length(void);
+
+/* qwasar_gpu.h:30-37.  A buffer from qw_buf_alloc is "shared": qw_buf_contents
+ * returns pinned host memory the CPU reads and writes directly, mirrored in
+ * device memory.  The mirror is refreshed from the host copy the first time a
+ * command buffer touches a byte range, and ranges an op wrote are copied back
+ * by qw_cmd_wait; so host writes must precede the encoding of the op that
+ * reads them, and results are read after qw_cmd_wait -- the order every
+ * caller in the reference already follows (qwasar_graph.c:1525-1570).
+ * New buffers are zero-filled.  qw_buf_wrap mirrors caller-owned host memory
+ * the same way (it is page-locked when the platform allows). */
+qw_buf qw_buf_wrap(void *ptr, size_t len);
+qw_buf qw_buf_alloc(size_t len);
+void   qw_buf_free(qw_buf b);                 /* NULL-safe */
+void  *qw_buf_contents(qw_buf b);             /* NULL for device-only buffers and arenas */
+size_t qw_buf_length(qw_buf b);
+
+/* qwasar_gpu.h:56-69.  One qw_cmd is one CUDA stream: ops are launched as
+ * they are encoded and run in encoding order, so "each dispatch sees
+ * everything before it" holds; qw_cmd_parallel regions are accepted and run
+ * serially (same results).  qw_cmd_commit and qw_cmd_flush are submission
+ * hints; qw_cmd_wait blocks until everything encoded has finished, copies
+ * written ranges of shared buffers back to the host, and latches the first
+ * error, which qw_cmd_error then returns (NULL when there was none). */
+qw_cmd qw_cmd_begin(void);
+void   qw_cmd_commit(qw_cmd c);
+void   qw_cmd_wait(qw_cmd c);
+void   qw_cmd_flush(qw_cmd c);
+void   qw_cmd_parallel(qw_cmd c, bool on);
+void   qw_cmd_free(qw_cmd c);
+const char *qw_cmd_error(qw_cmd c);
+
+/* qwasar_gpu.h:77-81.  QWASAR_PROFILE=1: qw_cmd_mark times the work since the
+ * previous mark with a pair of CUDA events and charges it to `label`;
+ * qw_prof_report prints the table to stderr (qwasar_metal.m:396-450). */
+bool qw_prof_enabled(void);
+void qw_cmd_mark(qw_cmd c, const char *label);
+void qw_prof_report(void);
+
+/* qwasar_gpu.h:391-393.  [rows, heads, 2*dim] f32 -> two [rows, heads, dim]. */
+void qw_op_split_heads2(qw_cmd c, qw_ref a, qw_ref b, qw_ref src,
+                        int32_t rows, int32_t heads, int32_t dim);
+/* qwasar_gpu.h:269-276.  weight: bf16 [dim] or a null ref. */
+void qw_op_rms_norm(qw_cmd c, qw_ref y, qw_ref x, qw_ref weight,
+                    int32_t dim, int32_t rows, float eps, float out_scale);
+/* qwasar_gpu.h:366-377.  In place; pos int32 [3, rows], axis uint8
+ * [rotary_dim/2], inv_freq f32 [rotary_dim/2]. */
+void qw_op_rope_partial(qw_cmd c, qw_ref x, qw_ref pos, qw_ref axis, qw_ref inv_freq,
+                        int32_t rows, int32_t heads, int32_t head_dim, int32_t rotary_dim);
+/* qwasar_gpu.h:379-382 (host function; qwasar_cpu.c:284-302). */
+void qw_rope_tables(uint8_t *axis, float *inv_freq, int32_t rotary_dim,
+                    float theta, const int32_t mrope_section[3]);
+/* qwasar_gpu.h:385.  y[i] *= sigmoid(gate[i]). */
+void qw_op_mul_sigmoid(qw_cmd c, qw_ref y, qw_ref gate, int32_t n);
+
+/* qwasar_gpu.h:402-406.  Appends rows of K and V at base_pos, rounding to the
+ * cache type (bf16, round-to-nearest-even).  The cache refs address one layer:
+ * either a plain buffer holding the reference's head-major
+ * [kv_heads, max_ctx, head_dim] array, or an arena from qw_kv_arena_alloc
+ * addressed exactly as the reference addresses its cache -- byte offset
+ * layer * kv_heads * max_ctx * head_dim * 2 (qwasar_graph.c:624,646-653). */
+void qw_op_kv_write(qw_cmd c, qw_ref kcache, qw_ref vcache, qw_ref k, qw_ref v,
+                    int32_t rows, int32_t kv_heads, int32_t head_dim,
+                    int32_t max_ctx, int32_t base_pos);
+
+/* qwasar_gpu.h:408-413.  The per-query kernel: fp32 throughout. */
+void qw_op_attn_decode(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                       int32_t rows, int32_t q_heads, int32_t kv_heads,
+                       int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+/* qwasar_gpu.h:415-422.  The tiled kernel for many query rows.  Returns
+ * false, encoding nothing, when head_dim != 256 or the grouping does not fit. */
+bool qw_op_attn_prefill(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                        int32_t rows, int32_t q_heads, int32_t kv_heads,
+                        int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+/* qwasar_gpu.h:424-428.  half_form is accepted and ignored: this backend has
+ * one form (bf16 operands, fp32 accumulation). */
+bool qw_op_attn_prefill_as(qw_cmd c, bool half_form, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                           int32_t rows, int32_t q_heads, int32_t kv_heads,
+                           int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+/* qwasar_gpu.h:430-437 and :509-515.  Both names reach the same split-KV
+ * tensor-op kernel, which takes any q_heads / kv_heads grouping with
+ * rows * grouping <= 64 (the reference's split kernel is fixed at 6:1). */
+bool qw_op_attn_decode_split(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                             int32_t rows, int32_t q_heads, int32_t kv_heads,
+                             int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                              int32_t rows, int32_t q_heads, int32_t kv_heads,
+                              int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+/* qwasar_gpu.h:439-446.  What the graph calls: rows >= 16 -> the tiled
+ * kernel; fewer -> the split-KV kernel; the per-query kernel where those
+ * decline. */
+void qw_op_attn(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                int32_t rows, int32_t q_heads, int32_t kv_heads,
+                int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+
+/* ======================================================================== *
+ *  Part 2 -- additive entry points (no counterpart in the reference)        *
+ * ======================================================================== */
+
+typedef enum { QW_F32 = 0, QW_BF16 = 1 } qw_dtype;
+
+/* Last error of a call that has no qw_cmd to report through (allocation,
+ * arena, init), or NULL. */
+const char *qw_gpu_last_error(void);
+int32_t     qw_gpu_sm_count(void);
+
+/* Kernels this library has launched since qw_gpu_init (every __global__ launch counts one). */
+uint64_t    qw_gpu_launch_count(void);
+/* Per-kernel device timing for roofline figures: while on, every launch of an attention
+ * kernel ("qw_attn_split", "qw_attn_prefill") is bracketed by a pair of CUDA events on its
+ * stream; qw_cmd_wait folds the elapsed times into per-kernel totals that
+ * qw_prof_kernel_read returns (false for an unknown name). */
+void        qw_prof_kernels(bool on);
+bool        qw_prof_kernel_read(const char *kernel, double *ms_total, int64_t *launches, bool reset);
+
+/* Device-only buffers: no host mirror, qw_buf_contents returns NULL. */
+qw_buf qw_buf_alloc_device(size_t len);                /* zero-filled */
+qw_buf qw_buf_wrap_device(void *device_ptr, size_t len); /* caller keeps ownership */
+void  *qw_buf_device_ptr(qw_buf b);
+/* Blocking copies between host memory and any buffer's device side. */
+bool   qw_buf_upload(qw_buf b, size_t off, const void *src, size_t len);
+bool   qw_buf_download(qw_buf b, size_t off, void *dst, size_t len);
+
+/* A command buffer on a stream the caller owns (a cudaStream_t passed as
+ * void*), so that ops order with the caller's other work on that stream. */
+qw_cmd qw_cmd_begin_on_stream(void *cuda_stream);
+/* dst[0:n] = src[0:n] bytes, in stream order; either side may be a shared,
+ * device or wrapped buffer. */
+void   qw_op_copy(qw_cmd c, qw_ref dst, qw_ref src, size_t n);
+
+/* ---- the paged K/V arena -------------------------------------------------
+ * One arena replaces one of the reference's cache buffers (kcache or vcache:
+ * [n_layers, kv_heads, max_ctx, head_dim], qwasar_graph.c:79-86).  Storage is
+ * a pool of 32 KB pages (64 tokens x 256 dims x bf16, rows 512 B, so every row
+ * is 128 B-aligned) mapped on demand; a device page table per (layer, head)
+ * gives logical page -> pool page.  The arena's *logical* contents are those
+ * of the head-major array, bit for bit, and callers keep addressing it with
+ * the reference's byte offsets (layer stride kv_heads*max_ctx*head_dim*2).
+ * Physical memory is committed as tokens are appended (growth in 64 MB steps
+ * of a reserved virtual range), which is what the reference gets from lazily
+ * committed shared buffers.  shuffle_seed != 0 hands pages out in a permuted
+ * order (tests use it so that the mapping is never the identity). */
+qw_buf  qw_kv_arena_alloc(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
+qw_buf  qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                             uint32_t shuffle_seed);
+/* Gather / scatter of n token rows of one (layer, head) starting at pos0,
+ * to / from packed host memory (n * head_dim * 2 bytes) -- what
+ * qw_session_pack / qw_session_unpack (qwasar_graph.c:320-393) need in place
+ * of memcpy through qw_buf_contents.  Blocking.  Also accept a plain cache
+ * buffer, for which they are strided copies. */
+bool    qw_kv_read(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, void *dst,
+                   int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
+bool    qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, const void *src,
+                    int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
+/* Returns to the pool every page that lies wholly at or past n_tokens
+ * (a rewind, qwasar_graph.c:407-463, needs no undo of KV rows; this only
+ * gives memory back). */
+void    qw_kv_arena_trim(qw_buf cache, int32_t n_tokens);
+int64_t qw_kv_arena_pages_in_use(qw_buf cache);
+int64_t qw_kv_arena_bytes_committed(qw_buf cache);
+
+/* ---- the fused node ------------------------------------------------------
+ * Everything qw_encode_attention_layer encodes between the q/k/v projections
+ * and o_proj (qwasar_graph.c:630-659), in two or three launches: split of
+ * [q|gate], RMS norm of q and k (bf16 weights or null refs), partial RoPE,
+ * K/V append at base_pos, causal attention of the rows against
+ * [0, base_pos + r], sigmoid output gate.
+ *   qg   [rows, q_heads, 2*head_dim]   k, v  [rows, kv_heads, head_dim]   (io)
+ *   out  [rows, q_heads, head_dim]                                        (io)
+ * io = QW_F32 or QW_BF16 for qg, k, v and out alike.  Returns false, encoding
+ * nothing, for head_dim != 256, rotary_dim != 64 or q_heads % kv_heads != 0. */
+bool qw_op_attn_layer_fused(qw_cmd c, qw_ref out, qw_ref qg, qw_ref k, qw_ref v,
+                            qw_ref q_norm_w, qw_ref k_norm_w, qw_ref pos, qw_ref axis, qw_ref inv_freq,
+                            qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                            int32_t head_dim, int32_t rotary_dim, int32_t max_ctx, int32_t base_pos,
+                            float eps, float scale, qw_dtype io);
+
+/* The same for n_seq independent sequences (one qw_session each in the
+ * reference, which has no batch dimension): arrays of n_seq refs and base
+ * positions; every sequence has `rows` rows.  Sequences are processed by one
+ * launch per 16. */
+bool qw_op_attn_layer_fused_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *qg,
+                                  const qw_ref *k, const qw_ref *v, qw_ref q_norm_w, qw_ref k_norm_w,
+                                  const qw_ref *pos, qw_ref axis, qw_ref inv_freq,
+                                  const qw_ref *kcache, const qw_ref *vcache, const int32_t *base_pos,
+                                  int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                                  int32_t rotary_dim, int32_t max_ctx, float eps, float scale, qw_dtype io);
+
+/* Batched form of qw_op_attn (attention only; q/out fp32 or bf16 per `io`). */
+bool qw_op_attn_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *q,
+                      const qw_ref *kcache, const qw_ref *vcache, const int32_t *base_pos,
+                      int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                      int32_t max_ctx, float scale, qw_dtype io);
+
+/* ---- partials, for a sequence split across GPUs ---------------------------
+ * qw_op_attn_partial attends the rows to the cache positions
+ * [key_lo, key_hi) only (key_lo a multiple of 64; causality still applies) and
+ * leaves, per (row, query head), the un-normalised partial softmax:
+ *   pacc  f32 [rows, q_heads, head_dim]   sum_t exp(s_t - m) V_t
+ *   pstat f32 [rows, q_heads, 2]          (m, sum_t exp(s_t - m)); sum 0 = no keys
+ * -- the (max, sum, acc) triple of the reference's split kernels
+ * (metal/attn.metal:198-259).  qw_op_attn_merge combines `parts` such sets,
+ * laid out [parts, rows*q_heads, ...] (what an all-gather of the ranks'
+ * partials produces), by log-sum-exp exactly as qw_attn_merge_gated does
+ * (metal/attn.metal:273-331), applying sigmoid(gate) when gate is not a null
+ * ref; gate element (r, h, d) is read at gate[(r*q_heads + h)*gate_stride + d]. */
+bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q, qw_ref kcache, qw_ref vcache,
+                        int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                        int32_t max_ctx, int32_t base_pos, int32_t key_lo, int32_t key_hi,
+                        float scale, qw_dtype q_dtype);
+void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate,
+                      int32_t rows, int32_t q_heads, int32_t head_dim, int32_t parts,
+                      int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype);
+
+/* The pre-op half of the fused node alone (split, norm, RoPE, append; q_out
+ * receives the normed + roped query as bf16 [rows, q_heads, head_dim]), for
+ * callers that run the attention half per rank (sequence split). */
+bool qw_op_attn_preop(qw_cmd c, qw_ref q_out, qw_ref qg, qw_ref k, qw_ref v,
+                      qw_ref q_norm_w, qw_ref k_norm_w, qw_ref pos, qw_ref axis, qw_ref inv_freq,
+                      qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                      int32_t head_dim, int32_t rotary_dim, int32_t max_ctx, int32_t base_pos,
+                      float eps, qw_dtype io, bool append);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QWASAR_CUDA_H */

@@ -1,0 +1,129 @@
+// Shared device-side helpers for the attention kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include <stdint.h>
+
+#define QW_HEAD_DIM 256          // the only head width the reference builds for (qwasar_metal.m:1359-1363)
+#define QW_PAGE_TOKENS 64        // tokens per arena page: 64 x 512 B = 32 KB, 128 B-aligned rows
+#define QW_MAX_SEQ 16            // sequences (or row chunks) one launch carries
+
+// Status codes a kernel leaves in the backend's status word (first one wins).
+enum : int {
+    QW_ST_OK = 0,
+    QW_ST_TMA_TIMEOUT = 1,       // a wait on a TMA "full" barrier ran out
+    QW_ST_SLOT_TIMEOUT = 2,      // a wait on an "empty" barrier ran out
+    QW_ST_MMA_TIMEOUT = 3,       // a wait on a tcgen05 commit barrier ran out
+    QW_ST_BAD_PAGE = 4,          // a page-table entry was unmapped where a key was needed
+};
+
+namespace qw {
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// The status word lives in page-locked host memory mapped into the device: a plain store
+// (no atomics across the bus); the first code is kept unless two arrive at once.
+__device__ __forceinline__ void report(int *status, int code) {
+    volatile int *s = status;
+    if (s && *s == 0) *s = code;
+}
+
+// ---- mbarrier -----------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (seconds), records `code`, raises the
+// CTA-wide abort flag so that every later wait returns at once, and returns false.
+// Control flow never depends on the outcome, so all warps still meet at the same
+// named barriers and the kernel ends.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                          int *status, int code) {
+    if (*abort_flag) return false;
+    for (uint32_t spin = 0; spin < (1u << 22); ++spin) {
+        if (mbar_try(bar, parity)) return true;
+        if (spin > 64) __nanosleep(spin > 4096 ? 256 : 32);
+        if ((spin & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    report(status, code);
+    return false;
+}
+
+// ---- TMA (tiled, no multicast anywhere in this library) -------------------------
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int32_t x, int32_t y,
+                                            uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+// Generic-proxy writes to shared memory made visible to the async proxy (TMA / tcgen05).
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- warp-level tensor ops (m16n8k16, bf16 in, fp32 accumulate) ----------------------
+__device__ __forceinline__ void ldsm_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+// Byte offset of element (row, col) inside one 128B-swizzled box whose rows are 64
+// bf16 (128 B) wide; the box base is 1024 B-aligned.  16-byte chunk c of row r sits
+// at chunk c ^ (r & 7) -- the layout TMA's SWIZZLE_128B writes.
+__device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t col) {
+    return row * 128u + ((((col >> 3) ^ row) & 7u) << 4) + ((col & 7u) << 1);
+}
+
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace qw

@@ -1,0 +1,625 @@
+// Decode / speculative-verify attention over the bf16 KV cache (sm_100a).
+//
+// qw_attn_split_kernel -- the split-KV kernel.  All (sequence, kv head) groups of a
+// launch are laid end to end as one line of 32-key tiles, and that line is cut into
+// one equal share per CTA (one CTA per SM), so every SM streams the same number of
+// bytes whatever the batch, head count or depth.  A share that crosses a group
+// boundary is processed as two segments.  Per CTA:
+//   * one producer warp walks the share and issues TMA loads (SWIZZLE_128B boxes of
+//     32 keys x 64 dims) of K and V into a ring of 32 KB stages, mbarrier-tracked;
+//   * MT x KG consumer warps: warp (mt, kg) owns query rows [16 mt, 16 mt + 16) of
+//     the group (row i = r * gqa + g: all query heads of the kv head, all rows) and
+//     every KG-th 16-key block; S = Q K^T and O += P V run on m16n8k16 bf16 tensor
+//     ops with fp32 accumulators, the softmax is online in fp32 (exp2 domain), quad
+//     reductions by shuffle;
+//   * at a segment's end the warps' (m, l, O) are merged through shared memory and
+//     written either as the final gated output (the segment was the whole group) or
+//     as one partial (max, sum, un-normalised acc) per row.
+// qw_attn_merge_kernel combines a group's partials by log-sum-exp and applies the
+// sigmoid output gate, the arithmetic of the reference's qw_attn_merge_gated
+// (metal/attn.metal:273-331).
+//
+// Bytes moved per key: 512 B of K + 512 B of V, once (the algorithmic minimum);
+// partials add (n_cta + groups) x rows x 1 KB.
+#include "qw_kernels.h"
+#include <algorithm>
+
+namespace qw {
+
+namespace {
+
+constexpr int TILE_KEYS = 32;
+constexpr int STAGE_BYTES = TILE_KEYS * 512 * 2;          // K then V
+constexpr int BOX_BYTES = TILE_KEYS * 128;                // 32 keys x 64 dims bf16
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr float LN2 = 0.6931471805599453f;
+constexpr float NEG_BIG = -1.0e30f;
+
+template <int MT>
+struct SplitCfg {
+    static constexpr int KG = (MT == 4) ? 2 : 4;
+    static constexpr int NW = MT * KG;                    // consumer warps
+    static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 4);
+    static constexpr int THREADS = (NW + 1) * 32;
+    static constexpr int Q_BYTES = MT * 16 * 512;
+    static constexpr int RED_BYTES = MT * 16 * 256 * 4;
+    static constexpr int OFF_Q = NST * STAGE_BYTES;
+    static constexpr int OFF_RED = OFF_Q + Q_BYTES;
+    static constexpr int OFF_M = OFF_RED + RED_BYTES;     // [MT][KG][16] floats
+    static constexpr int OFF_L = OFF_M + MT * KG * 16 * 4;  // [MT][16] floats
+    static constexpr int OFF_BAR = OFF_L + MT * 16 * 4;   // full[NST], empty[NST], abort
+    static constexpr int SMEM = OFF_BAR + (2 * NST + 1) * 8 + 1024;  // + alignment slack
+};
+
+struct Cursor {      // position on the flattened tile line
+    int s, h, t;     // sequence, kv head, tile within the group
+};
+
+__device__ __forceinline__ Cursor locate(const AttnParams &p, int T) {
+    Cursor c;
+    int s = 0;
+    while (s + 1 < p.n_seq && p.seq[s + 1].cum_tiles <= T) s++;
+    const int rel = T - p.seq[s].cum_tiles;
+    c.s = s;
+    c.h = rel / p.seq[s].n_tiles;
+    c.t = rel - c.h * p.seq[s].n_tiles;
+    return c;
+}
+__device__ __forceinline__ void advance(const AttnParams &p, Cursor &c) {
+    if (++c.t == p.seq[c.s].n_tiles) {
+        c.t = 0;
+        if (++c.h == p.kv_heads) { c.h = 0; c.s++; }
+    }
+}
+__device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
+    return (int)(((int64_t)cta * p.total_tiles) / p.n_cta);
+}
+
+__device__ __forceinline__ float load_gate(const void *g, size_t i, int dtype) {
+    return dtype == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(g)[i])
+                            : reinterpret_cast<const float *>(g)[i];
+}
+__device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+template <int MT>
+__global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel(const __grid_constant__ AttnParams p) {
+    using Cfg = SplitCfg<MT>;
+    constexpr int KG = Cfg::KG, NW = Cfg::NW, NST = Cfg::NST;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem + Cfg::OFF_Q;
+    float *red = reinterpret_cast<float *>(smem + Cfg::OFF_RED);
+    float *sm_m = reinterpret_cast<float *>(smem + Cfg::OFF_M);
+    float *sm_l = reinterpret_cast<float *>(smem + Cfg::OFF_L);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + Cfg::OFF_BAR);
+    uint64_t *empty = full + NST;
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(empty + NST);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lo = share_lo(p, blockIdx.x), hi = share_lo(p, blockIdx.x + 1);
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < NST; i++) {
+            mbar_init(&full[i], 1);
+            mbar_init(&empty[i], MT * (KG >= 2 ? 2 : 1));
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (lo >= hi) return;
+
+    if (warp == NW) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            Cursor c = locate(p, lo);
+            for (int T = lo; T < hi; T++) {
+                const int i = T - lo, slot = i % NST;
+                const AttnSeq &sq = p.seq[c.s];
+                const int t_abs = (sq.tile0 + c.t) * TILE_KEYS;
+                int64_t kr, vr;
+                if (sq.kc.table) {
+                    const int kp = __ldg(sq.kc.table + (size_t)c.h * sq.kc.pt_stride + (t_abs >> 6));
+                    const int vp = __ldg(sq.vc.table + (size_t)c.h * sq.vc.pt_stride + (t_abs >> 6));
+                    if (kp < 0 || vp < 0) report(p.status, QW_ST_BAD_PAGE);
+                    kr = (int64_t)max(kp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
+                    vr = (int64_t)max(vp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
+                } else {
+                    kr = (int64_t)c.h * sq.kc.max_ctx + t_abs;
+                    vr = (int64_t)c.h * sq.vc.max_ctx + t_abs;
+                }
+                if (i >= NST) mbar_wait(&empty[slot], ((i / NST) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                uint8_t *st = smem + slot * STAGE_BYTES;
+                mbar_expect_tx(&full[slot], STAGE_BYTES);
+#pragma unroll
+                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.kmap[c.s], b * 64, (int32_t)kr, &full[slot]);
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.vmap[c.s], b * 64, (int32_t)vr, &full[slot]);
+                advance(p, c);
+            }
+        }
+        // falls through to the end: consumers wait for every stage that was issued.
+    } else {
+        // ---------------- consumers ----------------
+        const int mt = warp / KG, kg = warp % KG;
+        const int gid = lane >> 2, tig = lane & 3;
+        const uint32_t q_base = smem_u32(q_s);
+        const float sc2 = p.scale * LOG2E;
+
+        float o[32][4];
+        float m0, m1, l0, l1;
+        Cursor c = locate(p, lo);
+        int T = lo;
+        while (T < hi) {
+            // ---- segment start ----
+            const AttnSeq &sq = p.seq[c.s];
+            const int seg_t0 = c.t;
+            const int seg_n = min(sq.n_tiles - c.t, hi - T);
+            const int valid_rows = sq.rows * p.gqa;
+            const int head0 = c.h * p.gqa;
+
+            // Q of this group -> bf16, swizzled: 4 boxes of [MT*16 rows, 64 dims].
+            for (int idx = warp * 32 + lane; idx < MT * 16 * 32; idx += NW * 32) {
+                const int row = idx >> 5, chunk = idx & 31;           // 16-byte chunk = 8 dims
+                uint4 val = make_uint4(0, 0, 0, 0);
+                if (row < valid_rows) {
+                    const int r = row / p.gqa, g = row - r * p.gqa;
+                    const size_t src = ((size_t)r * p.q_heads + head0 + g) * 256 + chunk * 8;
+                    if (p.q_dtype == DT_BF16) {
+                        val = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(sq.q) + src);
+                    } else {
+                        const float4 a = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src);
+                        const float4 b = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src + 4);
+                        val.x = pack_bf16(a.x, a.y); val.y = pack_bf16(a.z, a.w);
+                        val.z = pack_bf16(b.x, b.y); val.w = pack_bf16(b.z, b.w);
+                    }
+                }
+                *reinterpret_cast<uint4 *>(q_s + (chunk >> 3) * (MT * 16 * 128) + swz128(row, (chunk & 7) * 8)) = val;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+
+#pragma unroll
+            for (int n = 0; n < 32; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+            m0 = m1 = NEG_BIG;
+            l0 = l1 = 0.0f;
+
+            // causal limits of this thread's two rows (last readable key index)
+            const int row0 = mt * 16 + gid, row1 = row0 + 8;
+            const int lim0 = min(sq.key_hi - 1, row0 < valid_rows ? sq.base_pos + row0 / p.gqa : 0x7fffffff);
+            const int lim1 = min(sq.key_hi - 1, row1 < valid_rows ? sq.base_pos + row1 / p.gqa : 0x7fffffff);
+            const int mask_from = min(sq.key_hi, sq.base_pos + 1);   // blocks reaching this key need masking
+
+            for (int tt = 0; tt < seg_n; tt++, T++) {
+                const int i = T - lo, slot = i % NST;
+                bool uses = false;
+#pragma unroll
+                for (int j = 0; j < 2; j++) uses |= ((2 * i + j) % KG) == kg;
+                if (!uses) continue;
+                mbar_wait(&full[slot], (i / NST) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                const uint32_t k_base = smem_u32(smem + slot * STAGE_BYTES);
+                const uint32_t v_base = k_base + 4 * BOX_BYTES;
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    if (((2 * i + j) % KG) != kg) continue;
+                    const int blk_t0 = (sq.tile0 + seg_t0 + tt) * TILE_KEYS + j * 16;
+                    if (blk_t0 >= sq.key_hi) continue;
+
+                    // ---- S = Q K^T for 16 keys ----
+                    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+                    float s2[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+                    {
+                        const int mi = lane >> 3;
+                        const uint32_t q_row = mt * 16 + (mi & 1) * 8 + (lane & 7);
+                        const uint32_t k_row = j * 16 + (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+                        for (int ks = 0; ks < 16; ks++) {
+                            const uint32_t qc = ks * 2 + (mi >> 1), kc = ks * 2 + (mi & 1);
+                            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                            ldsm_x4(a0, a1, a2, a3, q_base + (qc >> 3) * (MT * 16 * 128) + swz128(q_row, (qc & 7) * 8));
+                            ldsm_x4(b0, b1, b2, b3, k_base + (kc >> 3) * BOX_BYTES + swz128(k_row, (kc & 7) * 8));
+                            if (ks & 1) {
+                                mma_bf16(s2[0], a0, a1, a2, a3, b0, b1);
+                                mma_bf16(s2[1], a0, a1, a2, a3, b2, b3);
+                            } else {
+                                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+                                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int n = 0; n < 2; n++)
+#pragma unroll
+                        for (int e = 0; e < 4; e++) s[n][e] = (s[n][e] + s2[n][e]) * sc2;
+
+                    if (blk_t0 + 16 > mask_from) {
+#pragma unroll
+                        for (int n = 0; n < 2; n++)
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int key = blk_t0 + n * 8 + tig * 2 + (e & 1);
+                                if (key > ((e & 2) ? lim1 : lim0)) s[n][e] = -INFINITY;
+                            }
+                    }
+
+                    // ---- online softmax ----
+                    float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+                    float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                    if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
+                        const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+                        l0 *= al0; l1 *= al1;
+#pragma unroll
+                        for (int n = 0; n < 32; n++) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
+                        m0 = mn0; m1 = mn1;
+                    }
+                    uint32_t pa[4];
+                    {
+                        const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
+                        const float p02 = exp2f(s[0][2] - m1), p03 = exp2f(s[0][3] - m1);
+                        const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
+                        const float p12 = exp2f(s[1][2] - m1), p13 = exp2f(s[1][3] - m1);
+                        l0 += (p00 + p01) + (p10 + p11);
+                        l1 += (p02 + p03) + (p12 + p13);
+                        pa[0] = pack_bf16(p00, p01); pa[1] = pack_bf16(p02, p03);
+                        pa[2] = pack_bf16(p10, p11); pa[3] = pack_bf16(p12, p13);
+                    }
+
+                    // ---- O += P V ----
+                    {
+                        const int mi = lane >> 3;
+                        const uint32_t v_row = j * 16 + (mi & 1) * 8 + (lane & 7);
+                        const bool ragged = blk_t0 + 16 > sq.key_hi;   // keys past the end may hold anything
+                        const int k_a = blk_t0 + tig * 2;              // key of a b-register's low half (b0); +8 for b1
+#pragma unroll
+                        for (int np = 0; np < 16; np++) {
+                            const uint32_t vc = np * 2 + (mi >> 1);
+                            uint32_t b0, b1, b2, b3;
+                            ldsm_x4_t(b0, b1, b2, b3, v_base + (vc >> 3) * BOX_BYTES + swz128(v_row, (vc & 7) * 8));
+                            if (ragged) {
+                                const uint32_t keep_a = (k_a < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 1 < sq.key_hi ? 0xffff0000u : 0u);
+                                const uint32_t keep_b = (k_a + 8 < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 9 < sq.key_hi ? 0xffff0000u : 0u);
+                                b0 &= keep_a; b2 &= keep_a; b1 &= keep_b; b3 &= keep_b;
+                            }
+                            mma_bf16(o[np * 2], pa[0], pa[1], pa[2], pa[3], b0, b1);
+                            mma_bf16(o[np * 2 + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+            }
+
+            // ---- segment end: merge the KG warps of each row tile ----
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+            if (tig == 0) {
+                sm_m[(mt * KG + kg) * 16 + gid] = m0;
+                sm_m[(mt * KG + kg) * 16 + gid + 8] = m1;
+            }
+            if (threadIdx.x < MT * 16) sm_l[threadIdx.x] = 0.0f;
+            for (int idx = warp * 32 + lane; idx < MT * 16 * 64; idx += NW * 32)
+                reinterpret_cast<float4 *>(red)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+            float M0 = NEG_BIG, M1 = NEG_BIG;
+#pragma unroll
+            for (int g2 = 0; g2 < KG; g2++) {
+                M0 = fmaxf(M0, sm_m[(mt * KG + g2) * 16 + gid]);
+                M1 = fmaxf(M1, sm_m[(mt * KG + g2) * 16 + gid + 8]);
+            }
+            {
+                const float f0 = exp2f(m0 - M0), f1 = exp2f(m1 - M1);
+                float *r0 = red + (size_t)(mt * 16 + gid) * 256 + tig * 2;
+                float *r1 = r0 + 8 * 256;
+#pragma unroll
+                for (int n = 0; n < 32; n++) {
+                    atomicAdd(r0 + n * 8, o[n][0] * f0);
+                    atomicAdd(r0 + n * 8 + 1, o[n][1] * f0);
+                    atomicAdd(r1 + n * 8, o[n][2] * f1);
+                    atomicAdd(r1 + n * 8 + 1, o[n][3] * f1);
+                }
+                if (tig == 0) {
+                    atomicAdd(&sm_l[mt * 16 + gid], l0 * f0);
+                    atomicAdd(&sm_l[mt * 16 + gid + 8], l1 * f1);
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+
+            const bool whole = (seg_t0 == 0) && (seg_n == sq.n_tiles) && (p.mode == 0);
+            const int slot_id = blockIdx.x + c.s * p.kv_heads + c.h;   // partial slot of (cta, group)
+            for (int idx = warp * 32 + lane; idx < valid_rows * 64; idx += NW * 32) {
+                const int row = idx >> 6, d4 = (idx & 63) * 4;
+                float4 acc = *reinterpret_cast<const float4 *>(red + (size_t)row * 256 + d4);
+                float Mrow = NEG_BIG;
+#pragma unroll
+                for (int g2 = 0; g2 < KG; g2++) Mrow = fmaxf(Mrow, sm_m[((row >> 4) * KG + g2) * 16 + (row & 15)]);
+                const float L = sm_l[row];
+                if (whole) {
+                    const int r = row / p.gqa, g = row - r * p.gqa;
+                    const size_t oi = ((size_t)r * p.q_heads + head0 + g) * 256 + d4;
+                    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+                    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+                    if (sq.gate) {
+                        const size_t gi = ((size_t)r * p.q_heads + head0 + g) * p.gate_stride + d4;
+                        acc.x *= sigmoidf(load_gate(sq.gate, gi, p.gate_dtype));
+                        acc.y *= sigmoidf(load_gate(sq.gate, gi + 1, p.gate_dtype));
+                        acc.z *= sigmoidf(load_gate(sq.gate, gi + 2, p.gate_dtype));
+                        acc.w *= sigmoidf(load_gate(sq.gate, gi + 3, p.gate_dtype));
+                    }
+                    if (p.out_dtype == DT_BF16) {
+                        uint2 v;
+                        v.x = pack_bf16(acc.x, acc.y); v.y = pack_bf16(acc.z, acc.w);
+                        *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(sq.out) + oi) = v;
+                    } else {
+                        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(sq.out) + oi) = acc;
+                    }
+                } else {
+                    const size_t pi = (size_t)slot_id * (MT * 16) + row;
+                    *reinterpret_cast<float4 *>(p.pacc + pi * 256 + d4) = acc;
+                    if ((idx & 63) == 0) {
+                        p.pstat[pi * 2] = Mrow * LN2;
+                        p.pstat[pi * 2 + 1] = L;
+                    }
+                }
+            }
+            // next segment (if any) begins with the next group
+            for (int k2 = 0; k2 < seg_n; k2++) advance(p, c);
+            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+        }
+    }
+}
+
+// One block per (group, row i): combine the group's partials.  64 threads x float4.
+template <int MT>
+__global__ void __launch_bounds__(64) qw_attn_merge_kernel(const __grid_constant__ AttnParams p, int max_valid_rows) {
+    const int gidx = blockIdx.x / max_valid_rows;            // sequence * kv_heads + head
+    const int row = blockIdx.x - gidx * max_valid_rows;
+    const int s = gidx / p.kv_heads, h = gidx - s * p.kv_heads;
+    if (s >= p.n_seq) return;
+    const AttnSeq &sq = p.seq[s];
+    if (row >= sq.rows * p.gqa) return;
+    const int64_t G0 = (int64_t)sq.cum_tiles + (int64_t)h * sq.n_tiles, G1 = G0 + sq.n_tiles;
+    const int64_t Tt = p.total_tiles, C = p.n_cta;
+    int c_first = (int)((G0 * C) / Tt);
+    while (c_first + 1 < C && ((int64_t)(c_first + 1) * Tt) / C <= G0) c_first++;
+    int c_last = (int)(((G1 - 1) * C) / Tt);
+    while (c_last + 1 < C && ((int64_t)(c_last + 1) * Tt) / C <= G1 - 1) c_last++;
+    const int parts = c_last - c_first + 1;
+    if (parts == 1 && p.mode == 0) return;                     // the split kernel wrote the output itself
+
+    const int d4 = threadIdx.x * 4;
+    float m = -3.0e38f;
+    for (int q = 0; q < parts; q++) {
+        const size_t pi = (size_t)(c_first + q + gidx) * (MT * 16) + row;
+        if (p.pstat[pi * 2 + 1] > 0.0f) m = fmaxf(m, p.pstat[pi * 2]);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.0f;
+    for (int q = 0; q < parts; q++) {
+        const size_t pi = (size_t)(c_first + q + gidx) * (MT * 16) + row;
+        const float l = p.pstat[pi * 2 + 1];
+        const float w = l > 0.0f ? __expf(p.pstat[pi * 2] - m) : 0.0f;
+        const float4 a = *reinterpret_cast<const float4 *>(p.pacc + pi * 256 + d4);
+        den += l * w;
+        acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+    }
+    const int r = row / p.gqa, g = row - r * p.gqa;
+    const size_t rh = (size_t)r * p.q_heads + h * p.gqa + g;
+    if (p.mode == 1) {
+        // leave one combined partial per (row, head) for the exchange between GPUs
+        const size_t ci = (size_t)sq.row_slot0 * p.q_heads + rh;
+        float *ca = p.pacc + (size_t)attn_split_slots(p) * (MT * 16) * 256;      // combined area follows the slots
+        float *cs = p.pstat + (size_t)attn_split_slots(p) * (MT * 16) * 2;
+        *reinterpret_cast<float4 *>(ca + ci * 256 + d4) = acc;
+        if (threadIdx.x == 0) { cs[ci * 2] = den > 0.0f ? m : -3.0e38f; cs[ci * 2 + 1] = den; }
+        return;
+    }
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    if (sq.gate) {
+        const size_t gi = rh * p.gate_stride + d4;
+        acc.x *= sigmoidf(load_gate(sq.gate, gi, p.gate_dtype));
+        acc.y *= sigmoidf(load_gate(sq.gate, gi + 1, p.gate_dtype));
+        acc.z *= sigmoidf(load_gate(sq.gate, gi + 2, p.gate_dtype));
+        acc.w *= sigmoidf(load_gate(sq.gate, gi + 3, p.gate_dtype));
+    }
+    if (p.out_dtype == DT_BF16) {
+        uint2 v;
+        v.x = pack_bf16(acc.x, acc.y); v.y = pack_bf16(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(sq.out) + rh * 256 + d4) = v;
+    } else {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(sq.out) + rh * 256 + d4) = acc;
+    }
+}
+
+// ---- merge of partials that arrive from outside (other GPUs) ---------------------------
+// pacc [parts, n_rh, 256], pstat [parts, n_rh, 2] (max in natural units, sum).
+__global__ void __launch_bounds__(64) merge_parts_kernel(void *out, int out_dtype, const float *__restrict__ pacc,
+                                                         const float *__restrict__ pstat, const void *gate,
+                                                         int gate_dtype, int gate_stride, int n_rh, int parts,
+                                                         float *pacc_out, float *pstat_out) {
+    const int rh = blockIdx.x;
+    const int d4 = threadIdx.x * 4;
+    float m = -3.0e38f;
+    for (int q = 0; q < parts; q++) {
+        const size_t pi = (size_t)q * n_rh + rh;
+        if (pstat[pi * 2 + 1] > 0.0f) m = fmaxf(m, pstat[pi * 2]);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.0f;
+    for (int q = 0; q < parts; q++) {
+        const size_t pi = (size_t)q * n_rh + rh;
+        const float l = pstat[pi * 2 + 1];
+        const float w = l > 0.0f ? __expf(pstat[pi * 2] - m) : 0.0f;
+        const float4 a = *reinterpret_cast<const float4 *>(pacc + pi * 256 + d4);
+        den += l * w;
+        acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+    }
+    if (pacc_out) {
+        *reinterpret_cast<float4 *>(pacc_out + (size_t)rh * 256 + d4) = acc;
+        if (threadIdx.x == 0) { pstat_out[rh * 2] = den > 0.0f ? m : -3.0e38f; pstat_out[rh * 2 + 1] = den; }
+        return;
+    }
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    if (gate) {
+        const size_t gi = (size_t)rh * gate_stride + d4;
+        acc.x *= sigmoidf(load_gate(gate, gi, gate_dtype));
+        acc.y *= sigmoidf(load_gate(gate, gi + 1, gate_dtype));
+        acc.z *= sigmoidf(load_gate(gate, gi + 2, gate_dtype));
+        acc.w *= sigmoidf(load_gate(gate, gi + 3, gate_dtype));
+    }
+    if (out_dtype == DT_BF16) {
+        uint2 v;
+        v.x = pack_bf16(acc.x, acc.y); v.y = pack_bf16(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + (size_t)rh * 256 + d4) = v;
+    } else {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)rh * 256 + d4) = acc;
+    }
+}
+
+// ---- per-query kernel: fp32 throughout (CUDA cores) ----------------------------------------
+// The counterpart of the reference's qw_attn_decode (metal/attn.metal:32-129): no rounding
+// of q or of the softmax weights, so it tracks the CPU twin to float rounding.  One block
+// per (key slice, row, query head); 8 warps stride the slice's keys, a lane owns 8 dims.
+__global__ void __launch_bounds__(256) attn_per_query_kernel(AttnSeq sq, int q_heads, int kv_heads, float scale,
+                                                             float *pacc, float *pstat, int splits) {
+    const int split = blockIdx.y, rh = blockIdx.x;
+    const int r = rh / q_heads, h = rh - r * q_heads;
+    const int kvh = h / (q_heads / kv_heads);
+    const int n = min(sq.key_hi, sq.base_pos + r + 1);
+    const int per = max(1, (n - sq.key_lo + splits - 1) / splits);
+    const int t0 = sq.key_lo + split * per, t1 = min(n, t0 + per);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *qv = reinterpret_cast<const float *>(sq.q) + (size_t)rh * 256 + lane * 8;
+    float q[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = qv[i] * scale;
+    float m = -3.0e38f, l = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int t = t0 + warp; t < t1; t += 8) {
+        const int64_t kr = kv_row(sq.kc, kvh, t), vr = kv_row(sq.vc, kvh, t);
+        const uint4 kk = reinterpret_cast<const uint4 *>(sq.kc.base + kr * 256)[lane];
+        const uint4 vv = reinterpret_cast<const uint4 *>(sq.vc.base + vr * 256)[lane];
+        const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            s += q[2 * i] * __uint_as_float(kw[i] << 16);
+            s += q[2 * i + 1] * __uint_as_float(kw[i] & 0xffff0000u);
+        }
+        s = warp_sum(s);
+        const float mn = fmaxf(m, s);
+        const float a = expf(m - mn), pe = expf(s - mn);
+        l = l * a + pe;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            acc[2 * i] = acc[2 * i] * a + pe * __uint_as_float(vw[i] << 16);
+            acc[2 * i + 1] = acc[2 * i + 1] * a + pe * __uint_as_float(vw[i] & 0xffff0000u);
+        }
+        m = mn;
+    }
+    __shared__ float s_m[8], s_l[8], s_acc[8][256];
+    if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < 8; i++) s_acc[warp][lane * 8 + i] = acc[i];
+    __syncthreads();
+    float M = -3.0e38f;
+    for (int w = 0; w < 8; w++) if (s_l[w] > 0.0f) M = fmaxf(M, s_m[w]);
+    float L = 0.0f, o = 0.0f;
+    for (int w = 0; w < 8; w++) {
+        const float f = s_l[w] > 0.0f ? expf(s_m[w] - M) : 0.0f;
+        L += s_l[w] * f;
+        o += s_acc[w][threadIdx.x] * f;
+    }
+    const size_t pi = (size_t)split * gridDim.x + rh;
+    pacc[pi * 256 + threadIdx.x] = o;
+    if (threadIdx.x == 0) { pstat[pi * 2] = M; pstat[pi * 2 + 1] = L; }
+}
+
+template <int MT>
+void launch_split_t(cudaStream_t s, const AttnParams &p) {
+    using Cfg = SplitCfg<MT>;
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(qw_attn_split_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+        configured = true;
+    }
+    qw_attn_split_kernel<MT><<<p.n_cta, Cfg::THREADS, Cfg::SMEM, s>>>(p);
+    g_launches++;
+}
+
+int row_tiles(int max_rows, int gqa) {
+    const int need = (max_rows * gqa + 15) / 16;
+    return need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+}
+
+}  // namespace
+
+unsigned long long g_launches = 0;
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows) {
+    const int mt = row_tiles(max_rows, p.gqa);
+    size_t rows_total = 0;
+    for (int i = 0; i < p.n_seq; i++) rows_total += p.seq[i].rows;
+    // slots, then (mode 1) one combined partial per (row, head)
+    return ((size_t)attn_split_slots(p) * mt * 16 + rows_total * p.q_heads) * 258 * sizeof(float);
+}
+
+void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
+    switch (row_tiles(max_rows, p.gqa)) {
+        case 1: launch_split_t<1>(s, p); break;
+        case 2: launch_split_t<2>(s, p); break;
+        default: launch_split_t<4>(s, p); break;
+    }
+}
+
+void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows) {
+    const int vr = max_rows * p.gqa;
+    const unsigned blocks = (unsigned)(p.n_seq * p.kv_heads * vr);
+    switch (row_tiles(max_rows, p.gqa)) {
+        case 1: qw_attn_merge_kernel<1><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
+        case 2: qw_attn_merge_kernel<2><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
+        default: qw_attn_merge_kernel<4><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
+    }
+}
+
+void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,
+                        const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
+                        float *pacc_out, float *pstat_out) {
+    if (n_rows_heads <= 0) return;
+    merge_parts_kernel<<<n_rows_heads, 64, 0, s>>>(out, out_dtype, pacc, pstat, gate, gate_dtype, gate_stride,
+                                                   n_rows_heads, parts, pacc_out, pstat_out);
+    g_launches++;
+}
+
+int attn_per_query_splits(int rows, int q_heads, int n_keys) {
+    int want = (2 * sm_count() + rows * q_heads - 1) / (rows * q_heads);
+    int cap = (n_keys + 255) / 256;
+    return std::max(1, std::min(want, cap));
+}
+size_t attn_per_query_scratch_bytes(int rows, int q_heads, int splits) {
+    return (size_t)splits * rows * q_heads * 258 * sizeof(float);
+}
+void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, float *pacc,
+                           float *pstat, int splits) {
+    dim3 grid(seq.rows * q_heads, splits);
+    attn_per_query_kernel<<<grid, 256, 0, s>>>(seq, q_heads, kv_heads, scale, pacc, pstat, splits);
+    g_launches++;
+}
+
+}  // namespace qw

@@ -1,0 +1,109 @@
+// Internal launch interface between the C-ABI backend (qwasar_cuda.cu) and the
+// kernel translation units.  Not part of the public boundary.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda.h>
+#include <stdint.h>
+#include "qw_common.cuh"
+
+namespace qw {
+
+enum Dtype : int { DT_F32 = 0, DT_BF16 = 1 };
+
+// Where one layer's K (or V) rows live.  Row index `row(h, t)` addresses a 512-byte
+// row of a 2-D [total_rows, 256] bf16 array:
+//   linear (reference layout, qwasar_gpu.h:395-400): row = h * max_ctx + t
+//   paged  (arena):  row = table[h * pt_stride + t / 64] * 64 + t % 64
+struct KvLayer {
+    __nv_bfloat16 *base;     // row 0 of the 2-D array (linear: the layer's first row; paged: the pool)
+    const int32_t *table;    // paged: this layer's page table [kv_heads, pt_stride]; linear: nullptr
+    int32_t pt_stride;
+    int32_t max_ctx;
+};
+
+__host__ __device__ __forceinline__ int64_t kv_row(const KvLayer &L, int32_t h, int32_t t) {
+#ifdef __CUDA_ARCH__
+    if (L.table) return (int64_t)__ldg(L.table + (size_t)h * L.pt_stride + (t >> 6)) * QW_PAGE_TOKENS + (t & 63);
+#endif
+    return (int64_t)h * L.max_ctx + t;
+}
+
+// ---- pre-ops -------------------------------------------------------------------------
+void launch_split_heads2(cudaStream_t s, float *a, float *b, const float *src, int rows, int heads, int dim);
+void launch_rms_norm(cudaStream_t s, float *y, const float *x, const uint16_t *w, int dim, int rows, float eps,
+                     float out_scale);
+void launch_rope_partial(cudaStream_t s, float *x, const int32_t *pos, const uint8_t *axis, const float *inv_freq,
+                         int rows, int heads, int head_dim, int rotary_dim);
+void launch_kv_write(cudaStream_t s, KvLayer kc, KvLayer vc, const float *k, const float *v, int rows, int kv_heads,
+                     int base_pos);
+void launch_mul_sigmoid(cudaStream_t s, float *y, const float *gate, int64_t n);
+void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, int64_t n);
+
+// One sequence of the fused pre-op: split [q|gate], RMS-norm q and k, partial RoPE,
+// round and append K/V, leave the normed+roped query as bf16.
+struct PreopSeq {
+    const void *qg;          // [rows, q_heads, 512]   (io dtype)
+    const void *k, *v;       // [rows, kv_heads, 256]  (io dtype)
+    const int32_t *pos;      // [3, rows]
+    __nv_bfloat16 *q_out;    // [rows, q_heads, 256]
+    KvLayer kc, vc;
+    int32_t rows, base_pos;
+};
+struct PreopParams {
+    PreopSeq seq[QW_MAX_SEQ];
+    int32_t n_seq, q_heads, kv_heads, rotary_dim, io_dtype;
+    const uint16_t *q_norm_w, *k_norm_w;   // bf16 [256] or nullptr
+    const uint8_t *axis;
+    const float *inv_freq;
+    float eps;
+};
+void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows);
+
+// ---- attention ------------------------------------------------------------------------
+struct AttnSeq {
+    const void *q;           // [rows, q_heads, 256] f32 or bf16
+    void *out;               // [rows, q_heads, 256] f32 or bf16
+    const void *gate;        // nullptr, or element (r, h, d) at gate[(r*q_heads + h)*gate_stride + d]
+    KvLayer kc, vc;
+    int32_t rows, base_pos;  // row r reads keys [key_lo, min(key_hi, base_pos + r + 1))
+    int32_t key_lo, key_hi;  // this launch's share of the sequence (whole: 0, base_pos + rows)
+    int32_t tile0, n_tiles;  // first 32-key tile and tile count per kv head, from key_lo/key_hi
+    int32_t cum_tiles;       // tiles of all earlier sequences times kv_heads
+    int32_t row_slot0;       // first row of this sequence in the partial buffers
+};
+struct AttnParams {
+    AttnSeq seq[QW_MAX_SEQ];
+    CUtensorMap kmap[QW_MAX_SEQ], vmap[QW_MAX_SEQ];
+    int32_t n_seq, q_heads, kv_heads, gqa;
+    int32_t q_dtype, out_dtype, gate_dtype, gate_stride;
+    int32_t total_tiles, n_cta;
+    int32_t mode;            // 0: write normalised (gated) output; 1: always leave partials (m, l, acc)
+    float scale;
+    float *pacc, *pstat;     // partial scratch: [slot, MT*16, 256] and [slot, MT*16, 2]
+    int *status;
+};
+// rows_per_seq * gqa <= 64.  The number of partial slots a launch may write: a (CTA, group)
+// segment uses slot cta + group.
+__host__ __device__ inline int attn_split_slots(const AttnParams &p) { return p.n_cta + p.n_seq * p.kv_heads; }
+size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows);
+void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows);
+void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
+
+// Per-query fp32 kernel (CUDA cores, no rounding of q or of the weights).
+void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale,
+                           float *pacc, float *pstat, int splits);
+size_t attn_per_query_scratch_bytes(int rows, int q_heads, int splits);
+int attn_per_query_splits(int rows, int q_heads, int n_keys);
+
+// Merge of externally supplied partials (the cross-GPU exchange): pacc [parts, rows*q_heads, 256],
+// pstat [parts, rows*q_heads, 2] -> out (gated when gate != nullptr).
+void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,
+                        const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
+                        float *pacc_out, float *pstat_out);
+
+int sm_count();
+
+// Launch accounting: every launcher adds the kernels it launched.
+extern unsigned long long g_launches;
+
+}  // namespace qw

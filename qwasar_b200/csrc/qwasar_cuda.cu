@@ -1,0 +1,1178 @@
+// qwasar_cuda.cu -- the C-ABI CUDA backend for the gated attention path (sm_100a).
+//
+// The sibling of the reference's qwasar_metal.m for the subset of qwasar_gpu.h that
+// the attention node uses: device bring-up, buffers, command buffers (one CUDA
+// stream each), the paged K/V arena, and host dispatch of the kernels in
+// qw_preops.cu / qw_decode.cu / qw_prefill.cu.  Error convention of the
+// reference: void ops encode nothing on a bad argument, bool ops return false
+// "encoding nothing", device errors surface as a string from qw_cmd_error after
+// qw_cmd_wait.  There is no CPU path: without a CUDA device qw_gpu_init fails
+// and every op declines.
+#include "../../include/qwasar_cuda.h"
+#include "qw_kernels.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <string>
+#include <vector>
+
+using namespace qw;
+
+// ---------------------------------------------------------------------------------------
+// state
+// ---------------------------------------------------------------------------------------
+namespace {
+
+enum BufKind { BUF_SHARED, BUF_DEVICE, BUF_ARENA };
+
+struct Arena;
+
+}  // namespace
+
+struct qw_buf_s {
+    BufKind kind;
+    size_t len;
+    void *host;          // shared: pinned (or caller's) host memory
+    void *dev;           // device side (shared mirror, device buffer, or arena pool)
+    bool own_host, own_dev, registered;
+    Arena *arena;
+};
+
+namespace {
+
+struct Touch {
+    qw_buf b;
+    size_t lo, hi;       // byte range whose device mirror is current in this command buffer
+    size_t wlo, whi;     // hull of the ranges ops wrote (whi == 0: none)
+};
+struct Scratch { void *p; size_t n; };
+struct Mark { cudaEvent_t ev; const char *label; };
+struct KTime { cudaEvent_t t0, t1; const char *kernel; };
+
+}  // namespace
+
+struct qw_cmd_s {
+    cudaStream_t stream;
+    bool own_stream;
+    bool failed;
+    char err[256];
+    int parallel;
+    std::vector<Touch> touched;
+    std::vector<Scratch> scratch;   // last one is current; earlier ones may still be in flight
+    std::vector<Mark> marks;
+    std::vector<KTime> ktimes;
+};
+
+namespace {
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*PFN_memAddressReserve)(CUdeviceptr *, size_t, size_t, CUdeviceptr, unsigned long long);
+typedef CUresult (*PFN_memAddressFree)(CUdeviceptr, size_t);
+typedef CUresult (*PFN_memCreate)(CUmemGenericAllocationHandle *, size_t, const CUmemAllocationProp *, unsigned long long);
+typedef CUresult (*PFN_memRelease)(CUmemGenericAllocationHandle);
+typedef CUresult (*PFN_memMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+typedef CUresult (*PFN_memUnmap)(CUdeviceptr, size_t);
+typedef CUresult (*PFN_memSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc *, size_t);
+typedef CUresult (*PFN_memGetGranularity)(size_t *, const CUmemAllocationProp *, CUmemAllocationGranularity_flags);
+
+struct Globals {
+    bool up = false;
+    int device = 0;
+    cudaDeviceProp prop;
+    char name[300] = "";
+    int *status_host = nullptr;    // pinned + mapped: kernels record a status code here
+    int *status_dev = nullptr;
+    PFN_encodeTiled encodeTiled = nullptr;
+    PFN_memAddressReserve memAddressReserve = nullptr;
+    PFN_memAddressFree memAddressFree = nullptr;
+    PFN_memCreate memCreate = nullptr;
+    PFN_memRelease memRelease = nullptr;
+    PFN_memMap memMap = nullptr;
+    PFN_memUnmap memUnmap = nullptr;
+    PFN_memSetAccess memSetAccess = nullptr;
+    PFN_memGetGranularity memGetGranularity = nullptr;
+    std::vector<Scratch> scratch_pool;
+    std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows) -> map
+    char last_error[256] = "";
+    bool has_error = false;
+    int prof = -1;
+    std::map<std::string, std::pair<double, long>> prof_ms;
+    bool time_kernels = false;
+    std::map<std::string, std::pair<double, long long>> kernel_ms;
+} G;
+
+void set_error(const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(G.last_error, sizeof G.last_error, fmt, ap);
+    va_end(ap);
+    G.has_error = true;
+}
+
+void cmd_fail(qw_cmd c, const char *fmt, ...) {
+    if (!c || c->failed) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(c->err, sizeof c->err, fmt, ap);
+    va_end(ap);
+    c->failed = true;
+}
+
+bool cuda_ok(qw_cmd c, cudaError_t e, const char *what) {
+    if (e == cudaSuccess) return true;
+    cmd_fail(c, "%s: %s", what, cudaGetErrorString(e));
+    return false;
+}
+
+template <typename T>
+bool entry(const char *name, T *fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p)
+        return false;
+    *fn = reinterpret_cast<T>(p);
+    return true;
+}
+
+const char *status_text(int code) {
+    switch (code) {
+        case QW_ST_TMA_TIMEOUT: return "kernel gave up waiting for a TMA load";
+        case QW_ST_SLOT_TIMEOUT: return "kernel gave up waiting for a free pipeline stage";
+        case QW_ST_MMA_TIMEOUT: return "kernel gave up waiting for a tensor-core commit";
+        case QW_ST_BAD_PAGE: return "attention reached a cache position whose page was never mapped";
+        default: return "unknown kernel status";
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// the paged arena
+// ---------------------------------------------------------------------------------------
+constexpr size_t PAGE_BYTES = (size_t)QW_PAGE_TOKENS * QW_HEAD_DIM * 2;   // 32 KB
+constexpr size_t CHUNK_BYTES = (size_t)64 << 20;                           // physical growth step
+constexpr int PAGES_PER_CHUNK = (int)(CHUNK_BYTES / PAGE_BYTES);
+
+struct Arena {
+    int n_layers, kv_heads, max_ctx, head_dim;
+    int pages_per_head;
+    int64_t max_pages;
+    bool vmm;
+    CUdeviceptr va;
+    size_t va_size;
+    std::vector<CUmemGenericAllocationHandle> chunks;
+    int64_t mapped_pages;                 // pool pages backed by physical memory
+    std::vector<int32_t> table_host;      // [n_layers, kv_heads, pages_per_head], -1 = unmapped
+    int32_t *table_dev;
+    std::vector<int32_t> free_pages;
+    int64_t in_use;
+    uint32_t shuffle;
+    CUtensorMap map;
+};
+
+bool encode_rows_map(CUtensorMap *m, void *base, uint64_t rows, uint32_t box_rows) {
+    cuuint64_t dims[2] = {QW_HEAD_DIM, rows};
+    cuuint64_t strides[1] = {QW_HEAD_DIM * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = G.encodeTiled(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return false; }
+    return true;
+}
+
+bool arena_grow(Arena *a) {
+    if (a->mapped_pages >= a->max_pages) return false;
+    const int64_t first = a->mapped_pages;
+    const int64_t n = std::min<int64_t>(PAGES_PER_CHUNK, a->max_pages - first);
+    if (a->vmm) {
+        CUmemAllocationProp prop = {};
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = G.device;
+        CUmemGenericAllocationHandle h;
+        // the reserved range is a whole number of chunks, so a full chunk is always mapped
+        if (G.memCreate(&h, CHUNK_BYTES, &prop, 0) != CUDA_SUCCESS) { set_error("arena: out of device memory"); return false; }
+        const CUdeviceptr at = a->va + (size_t)first * PAGE_BYTES;
+        if (G.memMap(at, CHUNK_BYTES, 0, h, 0) != CUDA_SUCCESS) { G.memRelease(h); set_error("arena: cuMemMap failed"); return false; }
+        CUmemAccessDesc acc = {};
+        acc.location = prop.location;
+        acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        if (G.memSetAccess(at, CHUNK_BYTES, &acc, 1) != CUDA_SUCCESS) {
+            G.memUnmap(at, CHUNK_BYTES); G.memRelease(h); set_error("arena: cuMemSetAccess failed"); return false;
+        }
+        a->chunks.push_back(h);
+        cudaMemset(reinterpret_cast<void *>(at), 0, CHUNK_BYTES);
+    }
+    // hand the new pages to the free list, permuted when asked to
+    std::vector<int32_t> ids((size_t)n);
+    for (int64_t i = 0; i < n; i++) ids[(size_t)i] = (int32_t)(first + i);
+    if (a->shuffle) {
+        uint32_t s = a->shuffle ^ (uint32_t)first ^ 0x9e3779b9u;
+        for (int64_t i = n - 1; i > 0; i--) {
+            s ^= s << 13; s ^= s >> 17; s ^= s << 5;
+            std::swap(ids[(size_t)i], ids[(size_t)(s % (uint32_t)(i + 1))]);
+        }
+    }
+    // free_pages is popped from the back: keep ascending order there when not shuffling
+    for (int64_t i = n - 1; i >= 0; i--) a->free_pages.push_back(ids[(size_t)i]);
+    a->mapped_pages += n;
+    return true;
+}
+
+// Makes sure the pages that hold tokens [0, n_tokens) of `layer` exist, and pushes new
+// page-table entries to the device in stream order.
+bool arena_ensure(Arena *a, int layer, int n_tokens, cudaStream_t stream) {
+    const int need = (n_tokens + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
+    if (need > a->pages_per_head) { set_error("arena: %d tokens exceed max_ctx %d", n_tokens, a->max_ctx); return false; }
+    for (int h = 0; h < a->kv_heads; h++) {
+        int32_t *row = a->table_host.data() + ((size_t)layer * a->kv_heads + h) * a->pages_per_head;
+        int first_new = -1, last_new = -1;
+        for (int pg = 0; pg < need; pg++) {
+            if (row[pg] >= 0) continue;
+            if (a->free_pages.empty() && !arena_grow(a)) return false;
+            row[pg] = a->free_pages.back();
+            a->free_pages.pop_back();
+            a->in_use++;
+            if (first_new < 0) first_new = pg;
+            last_new = pg;
+        }
+        if (first_new >= 0) {
+            const size_t off = ((size_t)layer * a->kv_heads + h) * a->pages_per_head + first_new;
+            // pageable source: the runtime stages it before returning, the copy itself is in stream order
+            if (cudaMemcpyAsync(a->table_dev + off, a->table_host.data() + off,
+                                (size_t)(last_new - first_new + 1) * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                stream) != cudaSuccess) {
+                set_error("arena: page-table update failed");
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+void arena_destroy(Arena *a) {
+    if (!a) return;
+    cudaDeviceSynchronize();
+    if (a->vmm) {
+        for (size_t i = 0; i < a->chunks.size(); i++) {
+            G.memUnmap(a->va + i * CHUNK_BYTES, CHUNK_BYTES);
+            G.memRelease(a->chunks[i]);
+        }
+        if (a->va) G.memAddressFree(a->va, a->va_size);
+    } else if (a->va) {
+        cudaFree(reinterpret_cast<void *>(a->va));
+    }
+    if (a->table_dev) cudaFree(a->table_dev);
+    delete a;
+}
+
+// ---------------------------------------------------------------------------------------
+// buffers, coherence of shared buffers, scratch
+// ---------------------------------------------------------------------------------------
+
+// Device address of [off, off+bytes) of a ref.  For shared buffers the device mirror of
+// that range is brought up to date (once per command buffer) and, when `write`, marked
+// for copy-back at qw_cmd_wait.
+void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write) {
+    qw_buf b = r.buf;
+    if (!b) return nullptr;
+    if (b->kind == BUF_ARENA) { cmd_fail(c, "an arena can only be a cache operand"); return nullptr; }
+    if (r.off + bytes > b->len) { cmd_fail(c, "operand [%zu, %zu) exceeds its buffer (%zu bytes)", r.off, r.off + bytes, b->len); return nullptr; }
+    if (b->kind == BUF_SHARED && bytes) {
+        const size_t lo = r.off, hi = r.off + bytes;
+        Touch *t = nullptr;
+        for (auto &x : c->touched) if (x.b == b) { t = &x; break; }
+        if (!t) {
+            c->touched.push_back(Touch{b, lo, hi, 0, 0});
+            t = &c->touched.back();
+            cuda_ok(c, cudaMemcpyAsync((char *)b->dev + lo, (char *)b->host + lo, hi - lo, cudaMemcpyHostToDevice, c->stream), "upload");
+        } else {
+            if (lo < t->lo) {
+                cuda_ok(c, cudaMemcpyAsync((char *)b->dev + lo, (char *)b->host + lo, t->lo - lo, cudaMemcpyHostToDevice, c->stream), "upload");
+                t->lo = lo;
+            }
+            if (hi > t->hi) {
+                cuda_ok(c, cudaMemcpyAsync((char *)b->dev + t->hi, (char *)b->host + t->hi, hi - t->hi, cudaMemcpyHostToDevice, c->stream), "upload");
+                t->hi = hi;
+            }
+        }
+        if (write) {
+            if (t->whi == 0) { t->wlo = lo; t->whi = hi; }
+            else { t->wlo = std::min(t->wlo, lo); t->whi = std::max(t->whi, hi); }
+        }
+    }
+    return (char *)b->dev + r.off;
+}
+
+void *cmd_scratch(qw_cmd c, size_t bytes) {
+    bytes = (bytes + 1023) & ~(size_t)1023;
+    if (!c->scratch.empty() && c->scratch.back().n >= bytes) return c->scratch.back().p;
+    // a block from the pool, else a new allocation (never inside a steady-state step:
+    // blocks return to the pool when their command buffer is freed)
+    size_t best = (size_t)-1;
+    for (size_t i = 0; i < G.scratch_pool.size(); i++)
+        if (G.scratch_pool[i].n >= bytes && (best == (size_t)-1 || G.scratch_pool[i].n < G.scratch_pool[best].n)) best = i;
+    Scratch s;
+    if (best != (size_t)-1) {
+        s = G.scratch_pool[best];
+        G.scratch_pool.erase(G.scratch_pool.begin() + (long)best);
+    } else {
+        s.n = std::max(bytes, (size_t)8 << 20);
+        if (cudaMalloc(&s.p, s.n) != cudaSuccess) { cmd_fail(c, "cannot allocate %zu bytes of scratch", s.n); return nullptr; }
+    }
+    c->scratch.push_back(s);
+    return s.p;
+}
+
+bool shape_ok(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos) {
+    return rows > 0 && kv_heads > 0 && q_heads > 0 && q_heads % kv_heads == 0 && head_dim == QW_HEAD_DIM &&
+           base_pos >= 0 && (int64_t)base_pos + rows <= max_ctx;
+}
+
+// One layer's cache operand -> KvLayer + tensor map.  n_tokens: positions that must be
+// addressable (pages are mapped up to there when `append`).
+bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int32_t head_dim, int32_t n_tokens,
+                   bool append, bool will_write, KvLayer *out, CUtensorMap *map) {
+    qw_buf b = ref.buf;
+    if (!b) { cmd_fail(c, "cache operand is null"); return false; }
+    const size_t layer_bytes = (size_t)kv_heads * max_ctx * head_dim * 2;
+    if (b->kind == BUF_ARENA) {
+        Arena *a = b->arena;
+        if (a->kv_heads != kv_heads || a->max_ctx != max_ctx || a->head_dim != head_dim) {
+            cmd_fail(c, "arena was created for [%d heads, %d ctx, %d dim], op says [%d, %d, %d]", a->kv_heads, a->max_ctx,
+                     a->head_dim, kv_heads, max_ctx, head_dim);
+            return false;
+        }
+        if (ref.off % layer_bytes) { cmd_fail(c, "arena offset %zu is not a layer boundary", ref.off); return false; }
+        const int layer = (int)(ref.off / layer_bytes);
+        if (layer >= a->n_layers) { cmd_fail(c, "arena layer %d out of range", layer); return false; }
+        if (append && !arena_ensure(a, layer, n_tokens, c->stream)) { cmd_fail(c, "%s", G.last_error); return false; }
+        out->base = reinterpret_cast<__nv_bfloat16 *>(a->va);
+        out->table = a->table_dev + (size_t)layer * a->kv_heads * a->pages_per_head;
+        out->pt_stride = a->pages_per_head;
+        out->max_ctx = max_ctx;
+        if (map) *map = a->map;
+        return true;
+    }
+    void *d = dev_range(c, ref, layer_bytes, will_write);
+    if (!d) return false;
+    if ((uintptr_t)d & 127) { cmd_fail(c, "cache operand is not 128-byte aligned"); return false; }
+    out->base = reinterpret_cast<__nv_bfloat16 *>(d);
+    out->table = nullptr;
+    out->pt_stride = 0;
+    out->max_ctx = max_ctx;
+    if (map) {
+        const uint64_t rows = (uint64_t)kv_heads * max_ctx;
+        auto key = std::make_pair((uintptr_t)d, rows);
+        auto it = G.map_cache.find(key);
+        if (it == G.map_cache.end()) {
+            CUtensorMap m;
+            if (!encode_rows_map(&m, d, rows, 32)) { cmd_fail(c, "%s", G.last_error); return false; }
+            it = G.map_cache.emplace(key, m).first;
+        }
+        *map = it->second;
+    }
+    return true;
+}
+
+// Fills the schedule fields of a launch's sequences and sizes its grid.
+void plan_split(AttnParams &p) {
+    int cum = 0;
+    int row_slot = 0;
+    for (int i = 0; i < p.n_seq; i++) {
+        AttnSeq &s = p.seq[i];
+        s.tile0 = s.key_lo / 32;
+        s.n_tiles = std::max(1, (s.key_hi + 31) / 32 - s.tile0);
+        s.cum_tiles = cum;
+        s.row_slot0 = row_slot;
+        cum += s.n_tiles * p.kv_heads;
+        row_slot += s.rows;
+    }
+    p.total_tiles = cum;
+    p.n_cta = std::min(sm_count(), cum);
+}
+
+// Launches the split-KV kernel (and the merge where any group was cut) for the sequences
+// already described in p.seq; `scr` holds attn_split_scratch_bytes(p, max_rows).
+bool launch_split_merge(qw_cmd c, AttnParams &p, int max_rows, float *scr) {
+    const int mt16 = ((max_rows * p.gqa + 15) / 16 <= 1 ? 1 : ((max_rows * p.gqa + 15) / 16 <= 2 ? 2 : 4)) * 16;
+    size_t rows_total = 0;
+    for (int i = 0; i < p.n_seq; i++) rows_total += p.seq[i].rows;
+    const size_t n_part_rows = (size_t)attn_split_slots(p) * mt16 + rows_total * p.q_heads;
+    p.pacc = scr;
+    p.pstat = scr + n_part_rows * 256;
+    p.status = G.status_dev;
+    KTime kt = {nullptr, nullptr, "qw_attn_split"};
+    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    if (timed) cudaEventRecord(kt.t0, c->stream);
+    launch_attn_split(c->stream, p, max_rows);
+    if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
+    bool need_merge = p.mode == 1;
+    const int64_t T = p.total_tiles, C = p.n_cta;
+    for (int i = 0; i < p.n_seq && !need_merge; i++)
+        for (int h = 0; h < p.kv_heads && !need_merge; h++) {
+            // a group is written directly only when one CTA's share covers it whole
+            const int64_t g0 = (int64_t)p.seq[i].cum_tiles + (int64_t)h * p.seq[i].n_tiles, g1 = g0 + p.seq[i].n_tiles - 1;
+            int64_t c0 = (g0 * C) / T, c1 = (g1 * C) / T;
+            while (c0 + 1 < C && ((c0 + 1) * T) / C <= g0) c0++;
+            while (c1 + 1 < C && ((c1 + 1) * T) / C <= g1) c1++;
+            if (c0 != c1) need_merge = true;
+        }
+    if (need_merge) launch_attn_merge(c->stream, p, max_rows);
+    return cuda_ok(c, cudaGetLastError(), "attention launch");
+}
+
+// Split-KV attention of up to QW_MAX_SEQ sequences already described in p.seq (q, out,
+// gate, caches, rows, base_pos, key range).  max_rows * gqa <= 64.
+bool run_split(qw_cmd c, AttnParams &p, int max_rows) {
+    plan_split(p);
+    float *scr = (float *)cmd_scratch(c, attn_split_scratch_bytes(p, max_rows));
+    if (!scr) return false;
+    return launch_split_merge(c, p, max_rows, scr);
+}
+
+bool live(qw_cmd c) { return G.up && c && !c->failed; }
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// lifecycle
+// ---------------------------------------------------------------------------------------
+extern "C" bool qw_gpu_init(char *err, size_t errcap) {
+    if (G.up) return true;
+    auto fail = [&](const char *fmt, const char *arg) {
+        if (err && errcap) snprintf(err, errcap, fmt, arg);
+        set_error(fmt, arg);
+        return false;
+    };
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) return fail("no CUDA device: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
+    if (cudaGetDevice(&G.device) != cudaSuccess) return fail("%s", "cudaGetDevice failed");
+    if (cudaGetDeviceProperties(&G.prop, G.device) != cudaSuccess) return fail("%s", "cudaGetDeviceProperties failed");
+    if (G.prop.major != 10) return fail("device %s is not compute capability 10.x (this backend is sm_100a only)", G.prop.name);
+    snprintf(G.name, sizeof G.name, "%s", G.prop.name);
+    if (!entry("cuTensorMapEncodeTiled", &G.encodeTiled)) return fail("%s", "driver lacks cuTensorMapEncodeTiled");
+    const bool vmm = entry("cuMemAddressReserve", &G.memAddressReserve) && entry("cuMemAddressFree", &G.memAddressFree) &&
+                     entry("cuMemCreate", &G.memCreate) && entry("cuMemRelease", &G.memRelease) &&
+                     entry("cuMemMap", &G.memMap) && entry("cuMemUnmap", &G.memUnmap) &&
+                     entry("cuMemSetAccess", &G.memSetAccess) && entry("cuMemGetAllocationGranularity", &G.memGetGranularity);
+    if (!vmm) G.memAddressReserve = nullptr;
+    if (cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void **)&G.status_dev, G.status_host, 0) != cudaSuccess)
+        return fail("%s", "cannot allocate the status word");
+    memset(G.status_host, 0, 64);
+    G.up = true;
+    G.has_error = false;
+    return true;
+}
+
+extern "C" void qw_gpu_shutdown(void) {
+    if (!G.up) return;
+    cudaDeviceSynchronize();
+    for (auto &s : G.scratch_pool) cudaFree(s.p);
+    G.scratch_pool.clear();
+    G.map_cache.clear();
+    if (G.status_host) cudaFreeHost(G.status_host);
+    G.status_host = G.status_dev = nullptr;
+    G.up = false;
+}
+
+extern "C" const char *qw_gpu_name(void) { return G.up ? G.name : "(no device)"; }
+extern "C" uint64_t qw_gpu_working_set_limit(void) { return G.up ? (uint64_t)G.prop.totalGlobalMem : 0; }
+extern "C" uint64_t qw_gpu_max_buffer_length(void) { return G.up ? (uint64_t)G.prop.totalGlobalMem : 0; }
+extern "C" const char *qw_gpu_last_error(void) { return G.has_error ? G.last_error : nullptr; }
+extern "C" int32_t qw_gpu_sm_count(void) { return G.up ? sm_count() : 0; }
+extern "C" uint64_t qw_gpu_launch_count(void) { return (uint64_t)qw::g_launches; }
+extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }
+extern "C" bool qw_prof_kernel_read(const char *kernel, double *ms_total, int64_t *launches, bool reset) {
+    auto it = G.kernel_ms.find(kernel ? kernel : "");
+    if (it == G.kernel_ms.end()) { if (ms_total) *ms_total = 0; if (launches) *launches = 0; return false; }
+    if (ms_total) *ms_total = it->second.first;
+    if (launches) *launches = it->second.second;
+    if (reset) G.kernel_ms.erase(it);
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------
+// buffers
+// ---------------------------------------------------------------------------------------
+extern "C" qw_buf qw_buf_alloc(size_t len) {
+    if (!G.up) { set_error("qw_buf_alloc before qw_gpu_init"); return nullptr; }
+    qw_buf b = new qw_buf_s{BUF_SHARED, len, nullptr, nullptr, true, true, false, nullptr};
+    const size_t n = std::max<size_t>(len, 16);
+    if (cudaHostAlloc(&b->host, n, cudaHostAllocDefault) != cudaSuccess || cudaMalloc(&b->dev, n) != cudaSuccess) {
+        set_error("cannot allocate a %zu-byte shared buffer", len);
+        if (b->host) cudaFreeHost(b->host);
+        delete b;
+        cudaGetLastError();
+        return nullptr;
+    }
+    memset(b->host, 0, n);
+    cudaMemset(b->dev, 0, n);
+    return b;
+}
+
+extern "C" qw_buf qw_buf_wrap(void *ptr, size_t len) {
+    if (!G.up || !ptr) return nullptr;
+    qw_buf b = new qw_buf_s{BUF_SHARED, len, ptr, nullptr, false, true, false, nullptr};
+    if (cudaMalloc(&b->dev, std::max<size_t>(len, 16)) != cudaSuccess) { set_error("cannot mirror a %zu-byte wrapped buffer", len); delete b; cudaGetLastError(); return nullptr; }
+    if (cudaHostRegister(ptr, len, cudaHostRegisterDefault) == cudaSuccess) b->registered = true;
+    else cudaGetLastError();   // pageable memory still works, copies are just staged
+    return b;
+}
+
+extern "C" qw_buf qw_buf_alloc_device(size_t len) {
+    if (!G.up) { set_error("qw_buf_alloc_device before qw_gpu_init"); return nullptr; }
+    qw_buf b = new qw_buf_s{BUF_DEVICE, len, nullptr, nullptr, false, true, false, nullptr};
+    if (cudaMalloc(&b->dev, std::max<size_t>(len, 16)) != cudaSuccess) { set_error("cannot allocate %zu bytes of device memory", len); delete b; cudaGetLastError(); return nullptr; }
+    cudaMemset(b->dev, 0, std::max<size_t>(len, 16));
+    return b;
+}
+
+extern "C" qw_buf qw_buf_wrap_device(void *device_ptr, size_t len) {
+    if (!G.up || !device_ptr) return nullptr;
+    return new qw_buf_s{BUF_DEVICE, len, nullptr, device_ptr, false, false, false, nullptr};
+}
+
+extern "C" void qw_buf_free(qw_buf b) {
+    if (!b) return;
+    if (b->kind == BUF_ARENA) { arena_destroy(b->arena); delete b; return; }
+    cudaDeviceSynchronize();
+    G.map_cache.clear();
+    if (b->registered) cudaHostUnregister(b->host);
+    if (b->own_host && b->host) cudaFreeHost(b->host);
+    if (b->own_dev && b->dev) cudaFree(b->dev);
+    delete b;
+}
+
+extern "C" void *qw_buf_contents(qw_buf b) { return b && b->kind == BUF_SHARED ? b->host : nullptr; }
+extern "C" size_t qw_buf_length(qw_buf b) { return b ? b->len : 0; }
+extern "C" void *qw_buf_device_ptr(qw_buf b) { return b ? b->dev : nullptr; }
+
+extern "C" bool qw_buf_upload(qw_buf b, size_t off, const void *src, size_t len) {
+    if (!b || b->kind == BUF_ARENA || off + len > b->len) { set_error("qw_buf_upload: bad range"); return false; }
+    if (b->kind == BUF_SHARED) memcpy((char *)b->host + off, src, len);
+    if (cudaMemcpy((char *)b->dev + off, src, len, cudaMemcpyHostToDevice) != cudaSuccess) { set_error("qw_buf_upload: copy failed"); return false; }
+    return true;
+}
+extern "C" bool qw_buf_download(qw_buf b, size_t off, void *dst, size_t len) {
+    if (!b || b->kind == BUF_ARENA || off + len > b->len) { set_error("qw_buf_download: bad range"); return false; }
+    if (cudaMemcpy(dst, (char *)b->dev + off, len, cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("qw_buf_download: copy failed"); return false; }
+    return true;
+}
+
+// ---------------------------------------------------------------------------------------
+// arena API
+// ---------------------------------------------------------------------------------------
+extern "C" qw_buf qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                                       uint32_t shuffle_seed) {
+    if (!G.up) { set_error("qw_kv_arena_alloc before qw_gpu_init"); return nullptr; }
+    if (n_layers <= 0 || kv_heads <= 0 || max_ctx <= 0 || head_dim != QW_HEAD_DIM) { set_error("arena: unsupported shape"); return nullptr; }
+    Arena *a = new Arena();
+    a->n_layers = n_layers; a->kv_heads = kv_heads; a->max_ctx = max_ctx; a->head_dim = head_dim;
+    a->pages_per_head = (max_ctx + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
+    a->max_pages = (int64_t)n_layers * kv_heads * a->pages_per_head;
+    a->mapped_pages = 0; a->in_use = 0; a->shuffle = shuffle_seed; a->table_dev = nullptr; a->va = 0;
+    const size_t n_chunks = ((size_t)a->max_pages * PAGE_BYTES + CHUNK_BYTES - 1) / CHUNK_BYTES;
+    a->va_size = n_chunks * CHUNK_BYTES;
+    a->vmm = false;
+    if (G.memAddressReserve) {
+        CUmemAllocationProp prop = {};
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = G.device;
+        size_t gran = 0;
+        if (G.memGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) == CUDA_SUCCESS && gran && CHUNK_BYTES % gran == 0 &&
+            G.memAddressReserve(&a->va, a->va_size, CHUNK_BYTES, 0, 0) == CUDA_SUCCESS)
+            a->vmm = true;
+    }
+    if (!a->vmm) {
+        // no virtual-memory management on this platform: the pool is allocated whole
+        void *p = nullptr;
+        if (cudaMalloc(&p, a->va_size) != cudaSuccess) { set_error("arena: cannot allocate %zu bytes", a->va_size); delete a; cudaGetLastError(); return nullptr; }
+        cudaMemset(p, 0, a->va_size);
+        a->va = (CUdeviceptr)p;
+    }
+    a->table_host.assign((size_t)a->max_pages, -1);
+    if (cudaMalloc(&a->table_dev, (size_t)a->max_pages * sizeof(int32_t)) != cudaSuccess) { set_error("arena: cannot allocate the page table"); arena_destroy(a); cudaGetLastError(); return nullptr; }
+    cudaMemset(a->table_dev, 0xff, (size_t)a->max_pages * sizeof(int32_t));
+    // the tensor map spans the whole reserved range; rows of unmapped pages are never addressed
+    if (!encode_rows_map(&a->map, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 32)) { arena_destroy(a); return nullptr; }
+    qw_buf b = new qw_buf_s{BUF_ARENA, (size_t)n_layers * kv_heads * max_ctx * head_dim * 2, nullptr,
+                            reinterpret_cast<void *>(a->va), false, false, false, a};
+    return b;
+}
+extern "C" qw_buf qw_kv_arena_alloc(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
+    return qw_kv_arena_alloc_ex(n_layers, kv_heads, max_ctx, head_dim, 0);
+}
+
+static bool kv_rw(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, void *host, bool store,
+                  int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
+    if (!cache || n < 0 || pos0 < 0 || head_dim != QW_HEAD_DIM || (int64_t)pos0 + n > max_ctx || head < 0 || head >= kv_heads) {
+        set_error("qw_kv_read/store: bad arguments");
+        return false;
+    }
+    const size_t row = (size_t)head_dim * 2;
+    if (cache->kind == BUF_ARENA) {
+        Arena *a = cache->arena;
+        if (a->kv_heads != kv_heads || a->max_ctx != max_ctx || layer < 0 || layer >= a->n_layers) { set_error("qw_kv_read/store: shape differs from the arena's"); return false; }
+        if (store && !arena_ensure(a, layer, pos0 + n, 0)) return false;
+        const int32_t *tab = a->table_host.data() + ((size_t)layer * a->kv_heads + head) * a->pages_per_head;
+        int t = pos0;
+        char *hp = (char *)host;
+        while (t < pos0 + n) {
+            const int pg = t / QW_PAGE_TOKENS, in = t % QW_PAGE_TOKENS;
+            const int cnt = std::min(QW_PAGE_TOKENS - in, pos0 + n - t);
+            if (tab[pg] < 0) {
+                if (store) { set_error("qw_kv_store: page not mapped"); return false; }
+                memset(hp, 0, (size_t)cnt * row);   // never written: reads as zeros
+            } else {
+                char *dp = (char *)a->va + ((size_t)tab[pg] * QW_PAGE_TOKENS + in) * row;
+                if (cudaMemcpy(store ? (void *)dp : (void *)hp, store ? (void *)hp : (void *)dp, (size_t)cnt * row,
+                               store ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost) != cudaSuccess) {
+                    set_error("qw_kv_read/store: copy failed");
+                    return false;
+                }
+            }
+            t += cnt;
+            hp += (size_t)cnt * row;
+        }
+        return true;
+    }
+    const size_t off = (((size_t)layer * kv_heads + head) * max_ctx + pos0) * row;
+    if (off + (size_t)n * row > cache->len) { set_error("qw_kv_read/store: range exceeds the buffer"); return false; }
+    if (store) return qw_buf_upload(cache, off, host, (size_t)n * row);
+    return qw_buf_download(cache, off, host, (size_t)n * row);
+}
+extern "C" bool qw_kv_read(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, void *dst,
+                           int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
+    return kv_rw(cache, layer, head, pos0, n, dst, false, kv_heads, max_ctx, head_dim);
+}
+extern "C" bool qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, const void *src,
+                            int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
+    return kv_rw(cache, layer, head, pos0, n, const_cast<void *>(src), true, kv_heads, max_ctx, head_dim);
+}
+
+extern "C" void qw_kv_arena_trim(qw_buf cache, int32_t n_tokens) {
+    if (!cache || cache->kind != BUF_ARENA) return;
+    Arena *a = cache->arena;
+    cudaDeviceSynchronize();
+    const int keep = (std::max(n_tokens, 0) + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
+    for (size_t lh = 0; lh < (size_t)a->n_layers * a->kv_heads; lh++) {
+        int32_t *row = a->table_host.data() + lh * a->pages_per_head;
+        bool any = false;
+        for (int pg = keep; pg < a->pages_per_head; pg++)
+            if (row[pg] >= 0) { a->free_pages.push_back(row[pg]); row[pg] = -1; a->in_use--; any = true; }
+        if (any && keep < a->pages_per_head)
+            cudaMemcpy(a->table_dev + lh * a->pages_per_head + keep, row + keep, (size_t)(a->pages_per_head - keep) * sizeof(int32_t),
+                       cudaMemcpyHostToDevice);
+    }
+}
+extern "C" int64_t qw_kv_arena_pages_in_use(qw_buf cache) { return cache && cache->kind == BUF_ARENA ? cache->arena->in_use : -1; }
+extern "C" int64_t qw_kv_arena_bytes_committed(qw_buf cache) {
+    if (!cache || cache->kind != BUF_ARENA) return -1;
+    Arena *a = cache->arena;
+    return a->vmm ? (int64_t)(a->chunks.size() * CHUNK_BYTES) : (int64_t)a->va_size;
+}
+
+// ---------------------------------------------------------------------------------------
+// command buffers
+// ---------------------------------------------------------------------------------------
+static qw_cmd cmd_new(cudaStream_t s, bool own) {
+    qw_cmd c = new qw_cmd_s();
+    c->stream = s; c->own_stream = own; c->failed = false; c->err[0] = 0; c->parallel = 0;
+    return c;
+}
+extern "C" qw_cmd qw_cmd_begin(void) {
+    if (!G.up) return nullptr;
+    cudaStream_t s;
+    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { set_error("cannot create a stream"); return nullptr; }
+    qw_cmd c = cmd_new(s, true);
+    if (qw_prof_enabled()) qw_cmd_mark(c, nullptr);
+    return c;
+}
+extern "C" qw_cmd qw_cmd_begin_on_stream(void *cuda_stream) {
+    if (!G.up) return nullptr;
+    return cmd_new(reinterpret_cast<cudaStream_t>(cuda_stream), false);
+}
+extern "C" void qw_cmd_commit(qw_cmd c) { if (c) cudaStreamQuery(c->stream); }
+extern "C" void qw_cmd_flush(qw_cmd c) { if (c) cudaStreamQuery(c->stream); }
+extern "C" void qw_cmd_parallel(qw_cmd c, bool on) { if (c) c->parallel += on ? 1 : (c->parallel > 0 ? -1 : 0); }
+
+extern "C" void qw_cmd_wait(qw_cmd c) {
+    if (!c) return;
+    for (auto &t : c->touched)
+        if (t.whi > t.wlo)
+            cuda_ok(c, cudaMemcpyAsync((char *)t.b->host + t.wlo, (char *)t.b->dev + t.wlo, t.whi - t.wlo, cudaMemcpyDeviceToHost, c->stream), "download");
+    c->touched.clear();
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) cmd_fail(c, "GPU fault: %s", cudaGetErrorString(e));
+    if (G.status_host && G.status_host[0] != 0) {
+        cmd_fail(c, "%s", status_text(G.status_host[0]));
+        G.status_host[0] = 0;
+    }
+    if (c->marks.size() > 1) {
+        for (size_t i = 1; i < c->marks.size(); i++) {
+            float ms = 0;
+            if (c->marks[i].label && cudaEventElapsedTime(&ms, c->marks[i - 1].ev, c->marks[i].ev) == cudaSuccess) {
+                auto &slot = G.prof_ms[c->marks[i].label];
+                slot.first += ms; slot.second++;
+            }
+        }
+    }
+    for (auto &m : c->marks) cudaEventDestroy(m.ev);
+    c->marks.clear();
+    for (auto &k : c->ktimes) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, k.t0, k.t1) == cudaSuccess) {
+            auto &slot = G.kernel_ms[k.kernel];
+            slot.first += ms; slot.second++;
+        }
+        cudaEventDestroy(k.t0); cudaEventDestroy(k.t1);
+    }
+    c->ktimes.clear();
+}
+
+extern "C" void qw_cmd_free(qw_cmd c) {
+    if (!c) return;
+    if (!c->touched.empty() || !c->scratch.empty()) cudaStreamSynchronize(c->stream);
+    for (auto &s : c->scratch) G.scratch_pool.push_back(s);
+    for (auto &m : c->marks) cudaEventDestroy(m.ev);
+    for (auto &k : c->ktimes) { cudaEventDestroy(k.t0); cudaEventDestroy(k.t1); }
+    if (c->own_stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+extern "C" const char *qw_cmd_error(qw_cmd c) { return c && c->failed ? c->err : nullptr; }
+
+extern "C" bool qw_prof_enabled(void) {
+    if (G.prof < 0) { const char *v = getenv("QWASAR_PROFILE"); G.prof = (v && *v && strcmp(v, "0")) ? 1 : 0; }
+    return G.prof == 1;
+}
+extern "C" void qw_cmd_mark(qw_cmd c, const char *label) {
+    if (!c || !qw_prof_enabled()) return;
+    Mark m; m.label = label;
+    if (cudaEventCreate(&m.ev) != cudaSuccess) return;
+    cudaEventRecord(m.ev, c->stream);
+    c->marks.push_back(m);
+}
+extern "C" void qw_prof_report(void) {
+    double total = 0;
+    for (auto &kv : G.prof_ms) total += kv.second.first;
+    for (auto &kv : G.prof_ms)
+        fprintf(stderr, "  %-28s %9.3f ms  %6ld marks  %5.1f%%\n", kv.first.c_str(), kv.second.first, kv.second.second,
+                total > 0 ? 100.0 * kv.second.first / total : 0.0);
+}
+
+extern "C" void qw_op_copy(qw_cmd c, qw_ref dst, qw_ref src, size_t n) {
+    if (!live(c) || !n) return;
+    // a shared source is read straight from its host side; a shared destination is written on
+    // its device side and copied back at wait like any op output
+    void *d = dev_range(c, dst, n, true);
+    const void *s = nullptr;
+    if (src.buf && src.buf->kind == BUF_SHARED) {
+        if (src.off + n > src.buf->len) { cmd_fail(c, "copy source out of range"); return; }
+        s = (char *)src.buf->host + src.off;
+    } else {
+        s = dev_range(c, src, n, false);
+    }
+    if (!d || !s) return;
+    cuda_ok(c, cudaMemcpyAsync(d, s, n, cudaMemcpyDefault, c->stream), "copy");
+}
+
+// ---------------------------------------------------------------------------------------
+// pre/post ops (reference signatures)
+// ---------------------------------------------------------------------------------------
+extern "C" void qw_op_split_heads2(qw_cmd c, qw_ref a, qw_ref b, qw_ref src, int32_t rows, int32_t heads, int32_t dim) {
+    if (!live(c) || rows <= 0 || heads <= 0 || dim <= 0) return;
+    const size_t n = (size_t)rows * heads * dim * 4;
+    float *pa = (float *)dev_range(c, a, n, true), *pb = (float *)dev_range(c, b, n, true);
+    const float *ps = (const float *)dev_range(c, src, 2 * n, false);
+    if (!pa || !pb || !ps) return;
+    launch_split_heads2(c->stream, pa, pb, ps, rows, heads, dim);
+}
+
+extern "C" void qw_op_rms_norm(qw_cmd c, qw_ref y, qw_ref x, qw_ref weight, int32_t dim, int32_t rows, float eps, float out_scale) {
+    if (!live(c) || rows <= 0 || dim <= 0) return;
+    const size_t n = (size_t)rows * dim * 4;
+    const float *px = (const float *)dev_range(c, x, n, false);
+    float *py = (float *)dev_range(c, y, n, true);
+    const uint16_t *pw = weight.buf ? (const uint16_t *)dev_range(c, weight, (size_t)dim * 2, false) : nullptr;
+    if (!px || !py || (weight.buf && !pw)) return;
+    launch_rms_norm(c->stream, py, px, pw, dim, rows, eps, out_scale);
+}
+
+extern "C" void qw_op_rope_partial(qw_cmd c, qw_ref x, qw_ref pos, qw_ref axis, qw_ref inv_freq, int32_t rows, int32_t heads,
+                                   int32_t head_dim, int32_t rotary_dim) {
+    if (!live(c) || rows <= 0 || heads <= 0 || rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)) return;
+    float *px = (float *)dev_range(c, x, (size_t)rows * heads * head_dim * 4, true);
+    const int32_t *pp = (const int32_t *)dev_range(c, pos, (size_t)3 * rows * 4, false);
+    const uint8_t *pa = (const uint8_t *)dev_range(c, axis, (size_t)rotary_dim / 2, false);
+    const float *pf = (const float *)dev_range(c, inv_freq, (size_t)rotary_dim / 2 * 4, false);
+    if (!px || !pp || !pa || !pf) return;
+    launch_rope_partial(c->stream, px, pp, pa, pf, rows, heads, head_dim, rotary_dim);
+}
+
+extern "C" void qw_rope_tables(uint8_t *axis, float *inv_freq, int32_t rotary_dim, float theta, const int32_t mrope_section[3]) {
+    // host arithmetic of qwasar_cpu.c:284-302: time axis by default, axes 1 and 2 on every
+    // third frequency from their own offset, below three times their section
+    const int32_t half = rotary_dim / 2;
+    for (int32_t j = 0; j < half; j++) {
+        uint8_t a = 0;
+        if (j % 3 == 1 && j < std::min(mrope_section[1] * 3, half)) a = 1;
+        if (j % 3 == 2 && j < std::min(mrope_section[2] * 3, half)) a = 2;
+        axis[j] = a;
+        inv_freq[j] = 1.0f / powf(theta, (float)(2 * j) / (float)rotary_dim);
+    }
+}
+
+extern "C" void qw_op_mul_sigmoid(qw_cmd c, qw_ref y, qw_ref gate, int32_t n) {
+    if (!live(c) || n <= 0) return;
+    float *py = (float *)dev_range(c, y, (size_t)n * 4, true);
+    const float *pg = (const float *)dev_range(c, gate, (size_t)n * 4, false);
+    if (!py || !pg) return;
+    launch_mul_sigmoid(c->stream, py, pg, n);
+}
+
+extern "C" void qw_op_kv_write(qw_cmd c, qw_ref kcache, qw_ref vcache, qw_ref k, qw_ref v, int32_t rows, int32_t kv_heads,
+                               int32_t head_dim, int32_t max_ctx, int32_t base_pos) {
+    if (!live(c) || rows <= 0) return;
+    if (head_dim != QW_HEAD_DIM) { fprintf(stderr, "qwasar: kv_write head_dim %d unsupported (kernel is built for 256)\n", head_dim); return; }
+    if (kv_heads <= 0 || base_pos < 0 || (int64_t)base_pos + rows > max_ctx) { cmd_fail(c, "kv_write: positions [%d, %d) outside the cache", base_pos, base_pos + rows); return; }
+    KvLayer kc, vc;
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &kc, nullptr)) return;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &vc, nullptr)) return;
+    const size_t n = (size_t)rows * kv_heads * head_dim * 4;
+    const float *pk = (const float *)dev_range(c, k, n, false), *pv = (const float *)dev_range(c, v, n, false);
+    if (!pk || !pv) return;
+    launch_kv_write(c->stream, kc, vc, pk, pv, rows, kv_heads, base_pos);
+}
+
+// ---------------------------------------------------------------------------------------
+// attention (reference signatures)
+// ---------------------------------------------------------------------------------------
+namespace {
+
+struct AttnArgs {
+    qw_ref out, q, gate, kcache, vcache;
+    int32_t rows, base_pos;
+};
+
+// Rows of one call cut into chunks of at most 64 / gqa rows, each chunk a "sequence" of a
+// split-KV launch; launches carry up to QW_MAX_SEQ chunks.
+bool attn_rows_split(qw_cmd c, const AttnArgs *seqs, int n_seq, int32_t q_heads, int32_t kv_heads, int32_t max_ctx,
+                     float scale, int q_dtype, int out_dtype, int gate_dtype, int gate_stride) {
+    const int gqa = q_heads / kv_heads;
+    if (gqa > 64) return false;
+    const int chunk_rows = std::max(1, 64 / gqa);
+    const size_t q_el = q_dtype == DT_BF16 ? 2 : 4, o_el = out_dtype == DT_BF16 ? 2 : 4, g_el = gate_dtype == DT_BF16 ? 2 : 4;
+    AttnParams p;
+    memset(&p, 0, sizeof p);
+    p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = q_dtype; p.out_dtype = out_dtype;
+    p.gate_dtype = gate_dtype; p.gate_stride = gate_stride; p.scale = scale; p.mode = 0;
+    int n = 0, max_rows = 0;
+    for (int s = 0; s < n_seq; s++) {
+        const AttnArgs &a = seqs[s];
+        KvLayer kc, vc;
+        CUtensorMap km, vm;
+        if (!resolve_cache(c, a.kcache, kv_heads, max_ctx, QW_HEAD_DIM, a.base_pos + a.rows, false, false, &kc, &km)) return false;
+        if (!resolve_cache(c, a.vcache, kv_heads, max_ctx, QW_HEAD_DIM, a.base_pos + a.rows, false, false, &vc, &vm)) return false;
+        const size_t q_bytes = (size_t)a.rows * q_heads * 256 * q_el, o_bytes = (size_t)a.rows * q_heads * 256 * o_el;
+        const char *qp = (const char *)dev_range(c, a.q, q_bytes, false);
+        char *op = (char *)dev_range(c, a.out, o_bytes, true);
+        const char *gp = a.gate.buf ? (const char *)dev_range(c, a.gate, ((size_t)a.rows * q_heads - 1) * gate_stride * g_el + 256 * g_el, false) : nullptr;
+        if (!qp || !op || (a.gate.buf && !gp)) return false;
+        for (int r0 = 0; r0 < a.rows; r0 += chunk_rows) {
+            AttnSeq &sq = p.seq[n];
+            const int rr = std::min(chunk_rows, a.rows - r0);
+            sq.q = qp + (size_t)r0 * q_heads * 256 * q_el;
+            sq.out = op + (size_t)r0 * q_heads * 256 * o_el;
+            sq.gate = gp ? gp + (size_t)r0 * q_heads * gate_stride * g_el : nullptr;
+            sq.kc = kc; sq.vc = vc;
+            sq.rows = rr; sq.base_pos = a.base_pos + r0;
+            sq.key_lo = 0; sq.key_hi = a.base_pos + r0 + rr;
+            p.kmap[n] = km; p.vmap[n] = vm;
+            max_rows = std::max(max_rows, rr);
+            if (++n == QW_MAX_SEQ) {
+                p.n_seq = n;
+                if (!run_split(c, p, max_rows)) return false;
+                n = 0; max_rows = 0;
+            }
+        }
+    }
+    if (n) {
+        p.n_seq = n;
+        if (!run_split(c, p, max_rows)) return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" void qw_op_attn_decode(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads,
+                                  int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale) {
+    if (!live(c)) return;
+    if (head_dim != QW_HEAD_DIM) { fprintf(stderr, "qwasar: attention head_dim %d unsupported (kernel is built for 256)\n", head_dim); return; }
+    if (!shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) { cmd_fail(c, "attn_decode: bad shape"); return; }
+    AttnSeq sq;
+    memset(&sq, 0, sizeof sq);
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, base_pos + rows, false, false, &sq.kc, nullptr)) return;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, base_pos + rows, false, false, &sq.vc, nullptr)) return;
+    const size_t n = (size_t)rows * q_heads * head_dim * 4;
+    sq.q = dev_range(c, q, n, false);
+    void *po = dev_range(c, out, n, true);
+    if (!sq.q || !po) return;
+    sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = 0; sq.key_hi = base_pos + rows;
+    const int splits = attn_per_query_splits(rows, q_heads, base_pos + rows);
+    float *scr = (float *)cmd_scratch(c, attn_per_query_scratch_bytes(rows, q_heads, splits));
+    if (!scr) return;
+    float *pstat = scr + (size_t)splits * rows * q_heads * 256;
+    launch_attn_per_query(c->stream, sq, q_heads, kv_heads, scale, scr, pstat, splits);
+    launch_merge_parts(c->stream, po, DT_F32, scr, pstat, nullptr, DT_F32, 256, rows * q_heads, splits, nullptr, nullptr);
+    cuda_ok(c, cudaGetLastError(), "attn_decode launch");
+}
+
+extern "C" bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows,
+                                         int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                         int32_t base_pos, float scale) {
+    if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
+    if (rows * (q_heads / kv_heads) > 64) return false;
+    AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
+    return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
+}
+extern "C" bool qw_op_attn_decode_split(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows,
+                                        int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                        int32_t base_pos, float scale) {
+    return qw_op_attn_decode_tensor(c, out, q, kcache, vcache, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale);
+}
+
+extern "C" bool qw_op_attn_prefill_as(qw_cmd c, bool half_form, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
+                                      int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                      int32_t base_pos, float scale) {
+    (void)half_form;
+    if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
+    if (q_heads / kv_heads > 64) return false;
+    AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
+    return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
+}
+extern "C" bool qw_op_attn_prefill(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads,
+                                   int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale) {
+    return qw_op_attn_prefill_as(c, true, out, q, kcache, vcache, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale);
+}
+
+extern "C" void qw_op_attn(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads,
+                           int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale) {
+    if (!live(c)) return;
+    // one shape rule, no environment switches: many rows -> the tiled kernel, few -> split-KV
+    if (rows >= 16 && qw_op_attn_prefill(c, out, q, kcache, vcache, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale)) return;
+    if (rows < 16 && qw_op_attn_decode_tensor(c, out, q, kcache, vcache, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale)) return;
+    if (c->failed) return;
+    qw_op_attn_decode(c, out, q, kcache, vcache, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale);
+}
+
+// ---------------------------------------------------------------------------------------
+// additive: fused node, batch, partials
+// ---------------------------------------------------------------------------------------
+namespace {
+
+bool fused_check(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t rotary_dim) {
+    return rows > 0 && q_heads > 0 && kv_heads > 0 && q_heads % kv_heads == 0 && head_dim == QW_HEAD_DIM && rotary_dim == 64;
+}
+
+struct FusedSeq { qw_ref out, qg, k, v, pos, kcache, vcache; int32_t base_pos; };
+
+// pre-op for up to QW_MAX_SEQ sequences; q_out[i] receives each sequence's bf16 query
+bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_out, qw_ref q_norm_w, qw_ref k_norm_w,
+               qw_ref axis, qw_ref inv_freq, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t max_ctx,
+               float eps, int io, bool append) {
+    PreopParams p;
+    memset(&p, 0, sizeof p);
+    const size_t el = io == DT_BF16 ? 2 : 4;
+    p.n_seq = n_seq; p.q_heads = q_heads; p.kv_heads = append ? kv_heads : 0; p.rotary_dim = 64; p.io_dtype = io; p.eps = eps;
+    p.q_norm_w = q_norm_w.buf ? (const uint16_t *)dev_range(c, q_norm_w, 512, false) : nullptr;
+    p.k_norm_w = k_norm_w.buf ? (const uint16_t *)dev_range(c, k_norm_w, 512, false) : nullptr;
+    p.axis = (const uint8_t *)dev_range(c, axis, 32, false);
+    p.inv_freq = (const float *)dev_range(c, inv_freq, 128, false);
+    if (!p.axis || !p.inv_freq || (q_norm_w.buf && !p.q_norm_w) || (k_norm_w.buf && !p.k_norm_w)) return false;
+    for (int i = 0; i < n_seq; i++) {
+        PreopSeq &ps = p.seq[i];
+        ps.qg = dev_range(c, s[i].qg, (size_t)rows * q_heads * 512 * el, false);
+        ps.pos = (const int32_t *)dev_range(c, s[i].pos, (size_t)3 * rows * 4, false);
+        if (!ps.qg || !ps.pos) return false;
+        if (append) {
+            ps.k = dev_range(c, s[i].k, (size_t)rows * kv_heads * 256 * el, false);
+            ps.v = dev_range(c, s[i].v, (size_t)rows * kv_heads * 256 * el, false);
+            if (!ps.k || !ps.v) return false;
+            if (!resolve_cache(c, s[i].kcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.kc, nullptr)) return false;
+            if (!resolve_cache(c, s[i].vcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.vc, nullptr)) return false;
+        }
+        ps.q_out = q_out[i];
+        ps.rows = rows; ps.base_pos = s[i].base_pos;
+    }
+    launch_preop(c->stream, p, rows);
+    return cuda_ok(c, cudaGetLastError(), "pre-op launch");
+}
+
+bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_ref k_norm_w, qw_ref axis, qw_ref inv_freq,
+                 int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t max_ctx, float eps, float scale, int io) {
+    const size_t el = io == DT_BF16 ? 2 : 4;
+    for (int s0 = 0; s0 < n_seq; s0 += QW_MAX_SEQ) {
+        const int ns = std::min(QW_MAX_SEQ, n_seq - s0);
+        for (int i = 0; i < ns; i++)
+            if ((int64_t)seqs[s0 + i].base_pos + rows > max_ctx || seqs[s0 + i].base_pos < 0) { cmd_fail(c, "fused attention: positions outside the cache"); return false; }
+        // scratch: the bf16 queries of this group of sequences, then the attention partials (sized generously)
+        const size_t q_bytes = (size_t)rows * q_heads * 256 * 2;
+        const size_t q_total = ((size_t)ns * q_bytes + 1023) & ~(size_t)1023;
+        const int gqa = q_heads / kv_heads;
+        const int chunk_rows = std::max(1, 64 / gqa);
+        const size_t part_rows = (size_t)(sm_count() + QW_MAX_SEQ * kv_heads) * 64 + (size_t)QW_MAX_SEQ * chunk_rows * q_heads;
+        char *scr = (char *)cmd_scratch(c, q_total + part_rows * 258 * 4);
+        if (!scr) return false;
+        __nv_bfloat16 *qo[QW_MAX_SEQ];
+        for (int i = 0; i < ns; i++) qo[i] = reinterpret_cast<__nv_bfloat16 *>(scr + (size_t)i * q_bytes);
+        if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
+
+        AttnParams p;
+        memset(&p, 0, sizeof p);
+        p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = DT_BF16; p.out_dtype = io;
+        p.gate_dtype = io; p.gate_stride = 512; p.scale = scale; p.mode = 0;
+        int n = 0, max_rows = 0;
+        auto flush = [&]() -> bool {
+            if (!n) return true;
+            p.n_seq = n;
+            plan_split(p);
+            const bool ok = launch_split_merge(c, p, max_rows, reinterpret_cast<float *>(scr + q_total));
+            n = 0; max_rows = 0;
+            return ok;
+        };
+        for (int i = 0; i < ns; i++) {
+            const FusedSeq &fs = seqs[s0 + i];
+            KvLayer kc, vc;
+            CUtensorMap km, vm;
+            if (!resolve_cache(c, fs.kcache, kv_heads, max_ctx, QW_HEAD_DIM, fs.base_pos + rows, false, false, &kc, &km)) return false;
+            if (!resolve_cache(c, fs.vcache, kv_heads, max_ctx, QW_HEAD_DIM, fs.base_pos + rows, false, false, &vc, &vm)) return false;
+            char *op = (char *)dev_range(c, fs.out, (size_t)rows * q_heads * 256 * el, true);
+            const char *gp = (const char *)dev_range(c, fs.qg, (size_t)rows * q_heads * 512 * el, false);
+            if (!op || !gp) return false;
+            for (int r0 = 0; r0 < rows; r0 += chunk_rows) {
+                AttnSeq &sq = p.seq[n];
+                const int rr = std::min(chunk_rows, rows - r0);
+                sq.q = qo[i] + (size_t)r0 * q_heads * 256;
+                sq.out = op + (size_t)r0 * q_heads * 256 * el;
+                sq.gate = gp + ((size_t)r0 * q_heads * 512 + 256) * el;    // the gate half of each [q|gate] head
+                sq.kc = kc; sq.vc = vc;
+                sq.rows = rr; sq.base_pos = fs.base_pos + r0;
+                sq.key_lo = 0; sq.key_hi = fs.base_pos + r0 + rr;
+                p.kmap[n] = km; p.vmap[n] = vm;
+                max_rows = std::max(max_rows, rr);
+                if (++n == QW_MAX_SEQ && !flush()) return false;
+            }
+        }
+        if (!flush()) return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+extern "C" bool qw_op_attn_layer_fused(qw_cmd c, qw_ref out, qw_ref qg, qw_ref k, qw_ref v, qw_ref q_norm_w, qw_ref k_norm_w,
+                                       qw_ref pos, qw_ref axis, qw_ref inv_freq, qw_ref kcache, qw_ref vcache, int32_t rows,
+                                       int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t rotary_dim,
+                                       int32_t max_ctx, int32_t base_pos, float eps, float scale, qw_dtype io) {
+    if (!live(c) || !fused_check(rows, q_heads, kv_heads, head_dim, rotary_dim) || q_heads / kv_heads > 64) return false;
+    FusedSeq s = {out, qg, k, v, pos, kcache, vcache, base_pos};
+    return fused_batch(c, &s, 1, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, scale, (int)io);
+}
+
+extern "C" bool qw_op_attn_layer_fused_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *qg, const qw_ref *k,
+                                             const qw_ref *v, qw_ref q_norm_w, qw_ref k_norm_w, const qw_ref *pos, qw_ref axis,
+                                             qw_ref inv_freq, const qw_ref *kcache, const qw_ref *vcache,
+                                             const int32_t *base_pos, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                                             int32_t head_dim, int32_t rotary_dim, int32_t max_ctx, float eps, float scale,
+                                             qw_dtype io) {
+    if (!live(c) || n_seq <= 0 || !fused_check(rows, q_heads, kv_heads, head_dim, rotary_dim) || q_heads / kv_heads > 64) return false;
+    std::vector<FusedSeq> s((size_t)n_seq);
+    for (int i = 0; i < n_seq; i++) s[(size_t)i] = FusedSeq{out[i], qg[i], k[i], v[i], pos[i], kcache[i], vcache[i], base_pos[i]};
+    return fused_batch(c, s.data(), n_seq, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, scale, (int)io);
+}
+
+extern "C" bool qw_op_attn_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *q, const qw_ref *kcache,
+                                 const qw_ref *vcache, const int32_t *base_pos, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                                 int32_t head_dim, int32_t max_ctx, float scale, qw_dtype io) {
+    if (!live(c) || n_seq <= 0) return false;
+    std::vector<AttnArgs> a((size_t)n_seq);
+    for (int i = 0; i < n_seq; i++) {
+        if (!shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos[i])) return false;
+        a[(size_t)i] = AttnArgs{out[i], q[i], qw_ref{nullptr, 0}, kcache[i], vcache[i], rows, base_pos[i]};
+    }
+    if (q_heads / kv_heads > 64) return false;
+    return attn_rows_split(c, a.data(), n_seq, q_heads, kv_heads, max_ctx, scale, (int)io, (int)io, DT_F32, 256);
+}
+
+extern "C" bool qw_op_attn_preop(qw_cmd c, qw_ref q_out, qw_ref qg, qw_ref k, qw_ref v, qw_ref q_norm_w, qw_ref k_norm_w,
+                                 qw_ref pos, qw_ref axis, qw_ref inv_freq, qw_ref kcache, qw_ref vcache, int32_t rows,
+                                 int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t rotary_dim, int32_t max_ctx,
+                                 int32_t base_pos, float eps, qw_dtype io, bool append) {
+    if (!live(c) || !fused_check(rows, q_heads, kv_heads, head_dim, rotary_dim)) return false;
+    if (append && (base_pos < 0 || (int64_t)base_pos + rows > max_ctx)) return false;
+    __nv_bfloat16 *qo = (__nv_bfloat16 *)dev_range(c, q_out, (size_t)rows * q_heads * 256 * 2, true);
+    if (!qo) return false;
+    FusedSeq s = {qw_ref{nullptr, 0}, qg, k, v, pos, kcache, vcache, base_pos};
+    return run_preop(c, &s, 1, &qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, (int)io, append);
+}
+
+extern "C" bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows,
+                                   int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos,
+                                   int32_t key_lo, int32_t key_hi, float scale, qw_dtype q_dtype) {
+    if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
+    const int gqa = q_heads / kv_heads;
+    if (rows * gqa > 64 || key_lo < 0 || (key_lo & 63)) return false;
+    key_hi = std::min(key_hi, base_pos + rows);
+    const size_t n_rh = (size_t)rows * q_heads;
+    float *pa = (float *)dev_range(c, pacc, n_rh * 256 * 4, true), *ps = (float *)dev_range(c, pstat, n_rh * 2 * 4, true);
+    if (!pa || !ps) return false;
+    if (key_hi <= key_lo) {
+        // nothing of this range is visible: an empty partial (sum 0 drops out of the merge)
+        cuda_ok(c, cudaMemsetAsync(pa, 0, n_rh * 256 * 4, c->stream), "memset");
+        cuda_ok(c, cudaMemsetAsync(ps, 0, n_rh * 2 * 4, c->stream), "memset");
+        return !c->failed;
+    }
+    AttnParams p;
+    memset(&p, 0, sizeof p);
+    p.n_seq = 1; p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = (int)q_dtype; p.out_dtype = DT_F32;
+    p.gate_dtype = DT_F32; p.gate_stride = 256; p.scale = scale; p.mode = 1;
+    AttnSeq &sq = p.seq[0];
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.kc, &p.kmap[0])) return false;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.vc, &p.vmap[0])) return false;
+    sq.q = dev_range(c, q, n_rh * 256 * (q_dtype == QW_BF16 ? 2 : 4), false);
+    if (!sq.q) return false;
+    sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = key_lo; sq.key_hi = key_hi;
+    if (!run_split(c, p, rows)) return false;
+    // the combined partials follow the slots in the scratch block: hand them to the caller
+    const int mt16 = ((rows * gqa + 15) / 16 <= 1 ? 1 : ((rows * gqa + 15) / 16 <= 2 ? 2 : 4)) * 16;
+    const size_t slot_rows = (size_t)attn_split_slots(p) * mt16;
+    cuda_ok(c, cudaMemcpyAsync(pa, p.pacc + slot_rows * 256, n_rh * 256 * 4, cudaMemcpyDeviceToDevice, c->stream), "copy");
+    cuda_ok(c, cudaMemcpyAsync(ps, p.pstat + slot_rows * 2, n_rh * 2 * 4, cudaMemcpyDeviceToDevice, c->stream), "copy");
+    return !c->failed;
+}
+
+extern "C" void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate, int32_t rows, int32_t q_heads,
+                                 int32_t head_dim, int32_t parts, int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype) {
+    if (!live(c) || rows <= 0 || q_heads <= 0 || parts <= 0 || head_dim != QW_HEAD_DIM) return;
+    const size_t n_rh = (size_t)rows * q_heads;
+    const float *pa = (const float *)dev_range(c, pacc, (size_t)parts * n_rh * 256 * 4, false);
+    const float *ps = (const float *)dev_range(c, pstat, (size_t)parts * n_rh * 2 * 4, false);
+    void *po = dev_range(c, out, n_rh * 256 * (out_dtype == QW_BF16 ? 2 : 4), true);
+    const size_t g_el = gate_dtype == QW_BF16 ? 2 : 4;
+    const void *pg = gate.buf ? dev_range(c, gate, ((n_rh - 1) * gate_stride + 256) * g_el, false) : nullptr;
+    if (!pa || !ps || !po || (gate.buf && !pg)) return;
+    launch_merge_parts(c->stream, po, (int)out_dtype, pa, ps, pg, (int)gate_dtype, gate_stride, (int)n_rh, parts, nullptr, nullptr);
+    cuda_ok(c, cudaGetLastError(), "merge launch");
+}

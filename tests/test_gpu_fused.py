@@ -26,18 +26,21 @@ pytestmark = pytest.mark.gpu
 GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "attn_golden.npz"))
 
 
-def bf16_ulp_distance(a_bits, b_bits):
-    """Distance in bf16 codes between same-signed finite values."""
-    def key(x):
-        x = x.astype(np.int32)
-        return np.where(x & 0x8000, 0x8000 - (x & 0x7FFF), 0x8000 + (x & 0x7FFF))
-    return np.abs(key(a_bits) - key(b_bits))
-
-
-def check_k_rows(got, want):
-    d = bf16_ulp_distance(got, want)
-    assert d.max() <= 1, f"appended K differs by {d.max()} bf16 ulps"
-    assert (d != 0).mean() <= 0.005, f"{(d != 0).mean():.4%} of appended K elements differ"
+def check_k_rows(got_bits, want_bits):
+    """Appended K: each element within one bf16 ulp of the oracle's, the ulp taken at
+    max(|want|, 1e-4 * the row's largest magnitude).  The floor only matters where RoPE's
+    x0*c - x1*s cancelled to (almost) nothing: there the fp32 rounding of the two products
+    (1e-7 of the operands) is several ulps of a result a million times smaller than its
+    operands -- that measures the cancellation, not the kernel."""
+    got = synth.bf16_bits_to_f32(got_bits).astype(np.float64)
+    want = synth.bf16_bits_to_f32(want_bits).astype(np.float64)
+    row_max = np.max(np.abs(want), axis=-1, keepdims=True)
+    mag = np.maximum(np.abs(want), 1e-4 * np.maximum(row_max, 1e-30))
+    ulp = 2.0 ** (np.floor(np.log2(mag)) - 7)
+    excess = np.abs(got - want) / ulp
+    assert excess.max() <= 1.0, f"appended K differs by {excess.max():.2f} bf16 ulps"
+    differ = (got_bits != want_bits).mean()
+    assert differ <= 0.005, f"{differ:.4%} of appended K elements differ"
 
 
 def fused_once(be, oracle, *, rows, qh, kvh, base, ctx, io, paged, seed, w_q=None, w_k=None, layer=0, layers=1,

@@ -369,6 +369,10 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
     barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
     be = qwasar_b200.Backend()
+    for kv in filter(None, args.tune.split(",")):
+        k, v = kv.split("=")
+        if not be.tune(k, int(v)):
+            raise SystemExit(f"unknown knob {kv}")
     peaks = measured_peaks()
     wl = synth.WORKLOADS[args.workload]
     if args.seq_shards > 1:
@@ -577,6 +581,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="attention layers per step (default: the model's)")
     ap.add_argument("--seq-shards", type=int, default=1)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--tune", default="", help="diagnostic knobs, e.g. split_kg=4 (see qw_gpu_tune)")
     args = ap.parse_args()
     if args.gpus > 1 and "RANK" not in os.environ:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",

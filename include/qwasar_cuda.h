@@ -156,6 +156,11 @@ int32_t     qw_gpu_sm_count(void);
 
 /* Kernels this library has launched since qw_gpu_init (every __global__ launch counts one). */
 uint64_t    qw_gpu_launch_count(void);
+/* Diagnostic knobs (the counterpart of the reference's QWASAR_ATTN / QWASAR_FA overrides,
+ * qwasar_metal.m:1513-1516): "split_kg" = 4 | 6, consumer warps per 16-row tile of the
+ * split-KV kernel; "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
+ * split-KV kernel over row chunks.  Returns false for an unknown knob or value. */
+bool        qw_gpu_tune(const char *knob, int32_t value);
 /* Per-kernel device timing for roofline figures: while on, every launch of an attention
  * kernel ("qw_attn_split", "qw_attn_prefill") is bracketed by a pair of CUDA events on its
  * stream; qw_cmd_wait folds the elapsed times into per-kernel totals that

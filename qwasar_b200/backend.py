@@ -63,6 +63,7 @@ SIGNATURES = {
     "qw_gpu_last_error": (C.c_char_p, []),
     "qw_gpu_sm_count": (_i32, []),
     "qw_gpu_launch_count": (C.c_uint64, []),
+    "qw_gpu_tune": (_b, [C.c_char_p, _i32]),
     "qw_prof_kernels": (None, [_b]),
     "qw_prof_kernel_read": (_b, [C.c_char_p, _vp, _vp, _b]),
     "qw_buf_alloc_device": (_vp, [_sz]),
@@ -139,6 +140,9 @@ class Backend:
 
     def launch_count(self):
         return int(self.lib.qw_gpu_launch_count())
+
+    def tune(self, knob, value):
+        return bool(self.lib.qw_gpu_tune(knob.encode(), value))
 
     def prof_kernels(self, on):
         self.lib.qw_prof_kernels(bool(on))

@@ -53,6 +53,16 @@ __device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking probe (try_wait may suspend the thread for a hardware time slice; this never does).
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~2^22 polls (seconds), records `code`, raises the
 // CTA-wide abort flag so that every later wait returns at once, and returns false.
 // Control flow never depends on the outcome, so all warps still meet at the same

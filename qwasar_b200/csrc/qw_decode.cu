@@ -35,12 +35,14 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float NEG_BIG = -1.0e30f;
 
-template <int MT>
+template <int MT, int KG_>
 struct SplitCfg {
-    static constexpr int KG = (MT == 4) ? 2 : 4;
+    static constexpr int KG = KG_;
     static constexpr int NW = MT * KG;                    // consumer warps
     static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 4);
-    static constexpr int THREADS = (NW + 1) * 32;
+    static constexpr int THREADS = (NW + 1) * 32;         // + the TMA producer warp
+    static_assert(THREADS <= 256, "warps are allocated in fours: 9 warps would be budgeted as 12");
+    static constexpr int MAXREG = 255;
     static constexpr int Q_BYTES = MT * 16 * 512;
     static constexpr int RED_BYTES = MT * 16 * 256 * 4;
     static constexpr int OFF_Q = NST * STAGE_BYTES;
@@ -80,10 +82,17 @@ __device__ __forceinline__ float load_gate(const void *g, size_t i, int dtype) {
                             : reinterpret_cast<const float *>(g)[i];
 }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// 2^x for x <= 0 (and -inf -> 0): the hardware approximation, 2 ulp
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
-template <int MT>
-__global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel(const __grid_constant__ AttnParams p) {
-    using Cfg = SplitCfg<MT>;
+// One CTA per SM with at most 8 warps, so every thread may use 255 registers.
+template <int MT, int KG_>
+__global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(const __grid_constant__ AttnParams p) {
+    using Cfg = SplitCfg<MT, KG_>;
     constexpr int KG = Cfg::KG, NW = Cfg::NW, NST = Cfg::NST;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -110,34 +119,50 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
     if (lo >= hi) return;
 
     if (warp == NW) {
-        // ---------------- producer ----------------
-        if (lane == 0) {
-            Cursor c = locate(p, lo);
-            for (int T = lo; T < hi; T++) {
-                const int i = T - lo, slot = i % NST;
-                const AttnSeq &sq = p.seq[c.s];
-                const int t_abs = (sq.tile0 + c.t) * TILE_KEYS;
+        // ---------------- producer warp (lane 0 issues the TMA loads) ----------------
+        Cursor pc = locate(p, lo);
+        // page ids of 32 consecutive tiles, one per lane, fetched together: one global-memory
+        // latency per 32 tiles instead of one per tile in front of every issue
+        int win_k = 0, win_v = 0;
+        for (int T = lo; T < hi; T++) {
+            const int i = T - lo, slot = i % NST;
+            if ((i & 31) == 0) {
+                const int T2 = T + lane;
+                if (T2 < hi) {
+                    const Cursor c2 = locate(p, T2);
+                    const AttnSeq &s2 = p.seq[c2.s];
+                    if (s2.kc.table) {
+                        const int pg = ((s2.tile0 + c2.t) * TILE_KEYS) >> 6;
+                        win_k = __ldg(s2.kc.table + (size_t)c2.h * s2.kc.pt_stride + pg);
+                        win_v = __ldg(s2.vc.table + (size_t)c2.h * s2.vc.pt_stride + pg);
+                    }
+                }
+            }
+            const int kp = __shfl_sync(0xffffffffu, win_k, i & 31);
+            const int vp = __shfl_sync(0xffffffffu, win_v, i & 31);
+            if (i >= NST) mbar_wait(&empty[slot], ((i / NST) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+            if (lane == 0) {
+                const AttnSeq &sq = p.seq[pc.s];
+                const int t_abs = (sq.tile0 + pc.t) * TILE_KEYS;
                 int64_t kr, vr;
                 if (sq.kc.table) {
-                    const int kp = __ldg(sq.kc.table + (size_t)c.h * sq.kc.pt_stride + (t_abs >> 6));
-                    const int vp = __ldg(sq.vc.table + (size_t)c.h * sq.vc.pt_stride + (t_abs >> 6));
                     if (kp < 0 || vp < 0) report(p.status, QW_ST_BAD_PAGE);
                     kr = (int64_t)max(kp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
                     vr = (int64_t)max(vp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
                 } else {
-                    kr = (int64_t)c.h * sq.kc.max_ctx + t_abs;
-                    vr = (int64_t)c.h * sq.vc.max_ctx + t_abs;
+                    kr = (int64_t)pc.h * sq.kc.max_ctx + t_abs;
+                    vr = (int64_t)pc.h * sq.vc.max_ctx + t_abs;
                 }
-                if (i >= NST) mbar_wait(&empty[slot], ((i / NST) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
                 uint8_t *st = smem + slot * STAGE_BYTES;
                 mbar_expect_tx(&full[slot], STAGE_BYTES);
 #pragma unroll
-                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.kmap[c.s], b * 64, (int32_t)kr, &full[slot]);
+                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.kmap[pc.s], b * 64, (int32_t)kr, &full[slot]);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
-                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.vmap[c.s], b * 64, (int32_t)vr, &full[slot]);
-                advance(p, c);
+                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.vmap[pc.s], b * 64, (int32_t)vr, &full[slot]);
             }
+            advance(p, pc);
+            __syncwarp();
         }
         // falls through to the end: consumers wait for every stage that was issued.
     } else {
@@ -206,24 +231,33 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
                     if (blk_t0 >= sq.key_hi) continue;
 
                     // ---- S = Q K^T for 16 keys ----
+                    // fragments of k-step ks+1 are requested before the tensor ops of step ks
+                    // are issued, so shared-memory latency hides behind them; two accumulator
+                    // sets halve the dependent chain
                     float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
                     float s2[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
                     {
                         const int mi = lane >> 3;
                         const uint32_t q_row = mt * 16 + (mi & 1) * 8 + (lane & 7);
                         const uint32_t k_row = j * 16 + (mi >> 1) * 8 + (lane & 7);
+                        uint32_t qa[2][4], kb[2][4];
+                        auto fetch = [&](int ks, uint32_t(&a)[4], uint32_t(&b)[4]) {
+                            const uint32_t qc = ks * 2 + (mi >> 1), kc = ks * 2 + (mi & 1);
+                            ldsm_x4(a[0], a[1], a[2], a[3], q_base + (qc >> 3) * (MT * 16 * 128) + swz128(q_row, (qc & 7) * 8));
+                            ldsm_x4(b[0], b[1], b[2], b[3], k_base + (kc >> 3) * BOX_BYTES + swz128(k_row, (kc & 7) * 8));
+                        };
+                        fetch(0, qa[0], kb[0]);
 #pragma unroll
                         for (int ks = 0; ks < 16; ks++) {
-                            const uint32_t qc = ks * 2 + (mi >> 1), kc = ks * 2 + (mi & 1);
-                            uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                            ldsm_x4(a0, a1, a2, a3, q_base + (qc >> 3) * (MT * 16 * 128) + swz128(q_row, (qc & 7) * 8));
-                            ldsm_x4(b0, b1, b2, b3, k_base + (kc >> 3) * BOX_BYTES + swz128(k_row, (kc & 7) * 8));
+                            if (ks + 1 < 16) fetch(ks + 1, qa[(ks + 1) & 1], kb[(ks + 1) & 1]);
+                            const uint32_t(&a)[4] = qa[ks & 1];
+                            const uint32_t(&b)[4] = kb[ks & 1];
                             if (ks & 1) {
-                                mma_bf16(s2[0], a0, a1, a2, a3, b0, b1);
-                                mma_bf16(s2[1], a0, a1, a2, a3, b2, b3);
+                                mma_bf16(s2[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                                mma_bf16(s2[1], a[0], a[1], a[2], a[3], b[2], b[3]);
                             } else {
-                                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
-                                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+                                mma_bf16(s[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                                mma_bf16(s[1], a[0], a[1], a[2], a[3], b[2], b[3]);
                             }
                         }
                     }
@@ -251,7 +285,7 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
                     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
                     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
                     if (__any_sync(0xffffffffu, (mn0 > m0) || (mn1 > m1))) {
-                        const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+                        const float al0 = ex2(m0 - mn0), al1 = ex2(m1 - mn1);
                         l0 *= al0; l1 *= al1;
 #pragma unroll
                         for (int n = 0; n < 32; n++) { o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1; }
@@ -259,10 +293,10 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
                     }
                     uint32_t pa[4];
                     {
-                        const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0);
-                        const float p02 = exp2f(s[0][2] - m1), p03 = exp2f(s[0][3] - m1);
-                        const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0);
-                        const float p12 = exp2f(s[1][2] - m1), p13 = exp2f(s[1][3] - m1);
+                        const float p00 = ex2(s[0][0] - m0), p01 = ex2(s[0][1] - m0);
+                        const float p02 = ex2(s[0][2] - m1), p03 = ex2(s[0][3] - m1);
+                        const float p10 = ex2(s[1][0] - m0), p11 = ex2(s[1][1] - m0);
+                        const float p12 = ex2(s[1][2] - m1), p13 = ex2(s[1][3] - m1);
                         l0 += (p00 + p01) + (p10 + p11);
                         l1 += (p02 + p03) + (p12 + p13);
                         pa[0] = pack_bf16(p00, p01); pa[1] = pack_bf16(p02, p03);
@@ -275,16 +309,19 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
                         const uint32_t v_row = j * 16 + (mi & 1) * 8 + (lane & 7);
                         const bool ragged = blk_t0 + 16 > sq.key_hi;   // keys past the end may hold anything
                         const int k_a = blk_t0 + tig * 2;              // key of a b-register's low half (b0); +8 for b1
+                        const uint32_t keep_a = (k_a < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 1 < sq.key_hi ? 0xffff0000u : 0u);
+                        const uint32_t keep_b = (k_a + 8 < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 9 < sq.key_hi ? 0xffff0000u : 0u);
+                        uint32_t vb[2][4];
+                        auto fetch_v = [&](int np, uint32_t(&b)[4]) {
+                            const uint32_t vc = np * 2 + (mi >> 1);
+                            ldsm_x4_t(b[0], b[1], b[2], b[3], v_base + (vc >> 3) * BOX_BYTES + swz128(v_row, (vc & 7) * 8));
+                        };
+                        fetch_v(0, vb[0]);
 #pragma unroll
                         for (int np = 0; np < 16; np++) {
-                            const uint32_t vc = np * 2 + (mi >> 1);
-                            uint32_t b0, b1, b2, b3;
-                            ldsm_x4_t(b0, b1, b2, b3, v_base + (vc >> 3) * BOX_BYTES + swz128(v_row, (vc & 7) * 8));
-                            if (ragged) {
-                                const uint32_t keep_a = (k_a < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 1 < sq.key_hi ? 0xffff0000u : 0u);
-                                const uint32_t keep_b = (k_a + 8 < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 9 < sq.key_hi ? 0xffff0000u : 0u);
-                                b0 &= keep_a; b2 &= keep_a; b1 &= keep_b; b3 &= keep_b;
-                            }
+                            if (np + 1 < 16) fetch_v(np + 1, vb[(np + 1) & 1]);
+                            uint32_t b0 = vb[np & 1][0], b1 = vb[np & 1][1], b2 = vb[np & 1][2], b3 = vb[np & 1][3];
+                            if (ragged) { b0 &= keep_a; b2 &= keep_a; b1 &= keep_b; b3 &= keep_b; }
                             mma_bf16(o[np * 2], pa[0], pa[1], pa[2], pa[3], b0, b1);
                             mma_bf16(o[np * 2 + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
                         }
@@ -312,7 +349,7 @@ __global__ void __launch_bounds__(SplitCfg<MT>::THREADS, 1) qw_attn_split_kernel
                 M1 = fmaxf(M1, sm_m[(mt * KG + g2) * 16 + gid + 8]);
             }
             {
-                const float f0 = exp2f(m0 - M0), f1 = exp2f(m1 - M1);
+                const float f0 = ex2(m0 - M0), f1 = ex2(m1 - M1);
                 float *r0 = red + (size_t)(mt * 16 + gid) * 256 + tig * 2;
                 float *r1 = r0 + 8 * 256;
 #pragma unroll
@@ -540,15 +577,15 @@ __global__ void __launch_bounds__(256) attn_per_query_kernel(AttnSeq sq, int q_h
     if (threadIdx.x == 0) { pstat[pi * 2] = M; pstat[pi * 2 + 1] = L; }
 }
 
-template <int MT>
+template <int MT, int KG>
 void launch_split_t(cudaStream_t s, const AttnParams &p) {
-    using Cfg = SplitCfg<MT>;
+    using Cfg = SplitCfg<MT, KG>;
     static bool configured = false;
     if (!configured) {
-        cudaFuncSetAttribute(qw_attn_split_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+        cudaFuncSetAttribute(qw_attn_split_kernel<MT, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
         configured = true;
     }
-    qw_attn_split_kernel<MT><<<p.n_cta, Cfg::THREADS, Cfg::SMEM, s>>>(p);
+    qw_attn_split_kernel<MT, KG><<<p.n_cta, Cfg::THREADS, Cfg::SMEM, s>>>(p);
     g_launches++;
 }
 
@@ -560,6 +597,8 @@ int row_tiles(int max_rows, int gqa) {
 }  // namespace
 
 unsigned long long g_launches = 0;
+int g_tune_split_kg = 6;
+int g_tune_prefill_tc = 1;
 
 int sm_count() {
     static int n = 0;
@@ -582,9 +621,12 @@ size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows) {
 
 void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
     switch (row_tiles(max_rows, p.gqa)) {
-        case 1: launch_split_t<1>(s, p); break;
-        case 2: launch_split_t<2>(s, p); break;
-        default: launch_split_t<4>(s, p); break;
+        case 1:
+            if (g_tune_split_kg == 4) launch_split_t<1, 4>(s, p);
+            else launch_split_t<1, 6>(s, p);
+            break;
+        case 2: launch_split_t<2, 3>(s, p); break;
+        default: launch_split_t<4, 1>(s, p); break;
     }
 }
 

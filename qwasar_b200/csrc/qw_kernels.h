@@ -89,6 +89,21 @@ size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows);
 void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows);
 void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
 
+// Causal prefill on tcgen05 tensor cores: one CTA per (128-row tile, query head).
+struct PrefillParams {
+    CUtensorMap qmap;        // bf16 [rows, q_heads*256], box 64 x 128
+    CUtensorMap kmap, vmap;  // cache row maps, box 64 x 64
+    KvLayer kc, vc;
+    void *out;               // [rows, q_heads, 256] f32 or bf16
+    const void *gate;        // nullptr or element (r, h, d) at gate[(r*q_heads + h)*gate_stride + d]
+    int32_t out_dtype, gate_dtype, gate_stride;
+    int32_t rows, base_pos, q_heads, kv_heads, gqa, n_q_tiles;
+    int32_t oob_row;         // a row index past both cache maps: TMA fills zeros there
+    float scale;
+    int *status;
+};
+void launch_attn_prefill(cudaStream_t s, const PrefillParams &p);
+
 // Per-query fp32 kernel (CUDA cores, no rounding of q or of the weights).
 void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale,
                            float *pacc, float *pstat, int splits);
@@ -105,5 +120,9 @@ int sm_count();
 
 // Launch accounting: every launcher adds the kernels it launched.
 extern unsigned long long g_launches;
+// Key groups (consumer warps per 16-row tile) of the split-KV kernel at one row tile: 4 or 6.
+extern int g_tune_split_kg;
+// 1: many-row attention runs on the tcgen05 kernel; 0: on the split-KV kernel over row chunks.
+extern int g_tune_prefill_tc;
 
 }  // namespace qw

@@ -99,7 +99,7 @@ struct Globals {
     PFN_memSetAccess memSetAccess = nullptr;
     PFN_memGetGranularity memGetGranularity = nullptr;
     std::vector<Scratch> scratch_pool;
-    std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows) -> map
+    std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows * 128 + box rows) -> map
     char last_error[256] = "";
     bool has_error = false;
     int prof = -1;
@@ -172,7 +172,8 @@ struct Arena {
     std::vector<int32_t> free_pages;
     int64_t in_use;
     uint32_t shuffle;
-    CUtensorMap map;
+    CUtensorMap map;                      // 32-row boxes (split-KV kernel)
+    CUtensorMap map64;                    // 64-row boxes (prefill kernel)
 };
 
 bool encode_rows_map(CUtensorMap *m, void *base, uint64_t rows, uint32_t box_rows) {
@@ -339,7 +340,8 @@ bool shape_ok(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
 // One layer's cache operand -> KvLayer + tensor map.  n_tokens: positions that must be
 // addressable (pages are mapped up to there when `append`).
 bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int32_t head_dim, int32_t n_tokens,
-                   bool append, bool will_write, KvLayer *out, CUtensorMap *map) {
+                   bool append, bool will_write, KvLayer *out, CUtensorMap *map, uint32_t box_rows = 32,
+                   int64_t *map_rows = nullptr) {
     qw_buf b = ref.buf;
     if (!b) { cmd_fail(c, "cache operand is null"); return false; }
     const size_t layer_bytes = (size_t)kv_heads * max_ctx * head_dim * 2;
@@ -358,7 +360,8 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
         out->table = a->table_dev + (size_t)layer * a->kv_heads * a->pages_per_head;
         out->pt_stride = a->pages_per_head;
         out->max_ctx = max_ctx;
-        if (map) *map = a->map;
+        if (map) *map = box_rows == 64 ? a->map64 : a->map;
+        if (map_rows) *map_rows = (int64_t)(a->va_size / 512);
         return true;
     }
     void *d = dev_range(c, ref, layer_bytes, will_write);
@@ -370,14 +373,15 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
     out->max_ctx = max_ctx;
     if (map) {
         const uint64_t rows = (uint64_t)kv_heads * max_ctx;
-        auto key = std::make_pair((uintptr_t)d, rows);
+        auto key = std::make_pair((uintptr_t)d, rows * 128 + box_rows);
         auto it = G.map_cache.find(key);
         if (it == G.map_cache.end()) {
             CUtensorMap m;
-            if (!encode_rows_map(&m, d, rows, 32)) { cmd_fail(c, "%s", G.last_error); return false; }
+            if (!encode_rows_map(&m, d, rows, box_rows)) { cmd_fail(c, "%s", G.last_error); return false; }
             it = G.map_cache.emplace(key, m).first;
         }
         *map = it->second;
+        if (map_rows) *map_rows = (int64_t)rows;
     }
     return true;
 }
@@ -438,6 +442,39 @@ bool run_split(qw_cmd c, AttnParams &p, int max_rows) {
     return launch_split_merge(c, p, max_rows, scr);
 }
 
+// The tcgen05 prefill kernel over one sequence: q_bf16 is [rows, q_heads, 256] in device memory.
+bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype, const void *gate, int gate_dtype,
+                 int gate_stride, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                 int32_t max_ctx, int32_t base_pos, float scale) {
+    PrefillParams p;
+    memset(&p, 0, sizeof p);
+    int64_t k_rows = 0, v_rows = 0;
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, QW_HEAD_DIM, base_pos + rows, false, false, &p.kc, &p.kmap, 64, &k_rows)) return false;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, QW_HEAD_DIM, base_pos + rows, false, false, &p.vc, &p.vmap, 64, &v_rows)) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)q_heads * QW_HEAD_DIM, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)q_heads * QW_HEAD_DIM * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    if (G.encodeTiled(&p.qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(q_bf16), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        cmd_fail(c, "cuTensorMapEncodeTiled failed for the query tile");
+        return false;
+    }
+    p.out = out; p.out_dtype = out_dtype; p.gate = gate; p.gate_dtype = gate_dtype; p.gate_stride = gate_stride;
+    p.rows = rows; p.base_pos = base_pos; p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = q_heads / kv_heads;
+    p.n_q_tiles = (rows + 127) / 128;
+    p.oob_row = (int32_t)std::min<int64_t>(std::max(k_rows, v_rows), 0x7fffffff);
+    p.scale = scale;
+    p.status = G.status_dev;
+    KTime kt = {nullptr, nullptr, "qw_attn_prefill"};
+    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    if (timed) cudaEventRecord(kt.t0, c->stream);
+    launch_attn_prefill(c->stream, p);
+    if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
+    return cuda_ok(c, cudaGetLastError(), "prefill launch");
+}
+
 bool live(qw_cmd c) { return G.up && c && !c->failed; }
 
 }  // namespace
@@ -491,6 +528,11 @@ extern "C" uint64_t qw_gpu_max_buffer_length(void) { return G.up ? (uint64_t)G.p
 extern "C" const char *qw_gpu_last_error(void) { return G.has_error ? G.last_error : nullptr; }
 extern "C" int32_t qw_gpu_sm_count(void) { return G.up ? sm_count() : 0; }
 extern "C" uint64_t qw_gpu_launch_count(void) { return (uint64_t)qw::g_launches; }
+extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
+    if (knob && !strcmp(knob, "split_kg") && (value == 4 || value == 6)) { qw::g_tune_split_kg = value; return true; }
+    if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
+    return false;
+}
 extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }
 extern "C" bool qw_prof_kernel_read(const char *kernel, double *ms_total, int64_t *launches, bool reset) {
     auto it = G.kernel_ms.find(kernel ? kernel : "");
@@ -605,7 +647,8 @@ extern "C" qw_buf qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32
     if (cudaMalloc(&a->table_dev, (size_t)a->max_pages * sizeof(int32_t)) != cudaSuccess) { set_error("arena: cannot allocate the page table"); arena_destroy(a); cudaGetLastError(); return nullptr; }
     cudaMemset(a->table_dev, 0xff, (size_t)a->max_pages * sizeof(int32_t));
     // the tensor map spans the whole reserved range; rows of unmapped pages are never addressed
-    if (!encode_rows_map(&a->map, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 32)) { arena_destroy(a); return nullptr; }
+    if (!encode_rows_map(&a->map, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 32) ||
+        !encode_rows_map(&a->map64, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 64)) { arena_destroy(a); return nullptr; }
     qw_buf b = new qw_buf_s{BUF_ARENA, (size_t)n_layers * kv_heads * max_ctx * head_dim * 2, nullptr,
                             reinterpret_cast<void *>(a->va), false, false, false, a};
     return b;
@@ -958,9 +1001,18 @@ extern "C" bool qw_op_attn_prefill_as(qw_cmd c, bool half_form, qw_ref out, qw_r
                                       int32_t base_pos, float scale) {
     (void)half_form;
     if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
-    if (q_heads / kv_heads > 64) return false;
-    AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
-    return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
+    if (!g_tune_prefill_tc) {
+        if (q_heads / kv_heads > 64) return false;
+        AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
+        return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
+    }
+    const size_t n = (size_t)rows * q_heads * 256;
+    const float *qp = (const float *)dev_range(c, q, n * 4, false);
+    void *op = dev_range(c, out, n * 4, true);
+    __nv_bfloat16 *qb = (__nv_bfloat16 *)cmd_scratch(c, n * 2);
+    if (!qp || !op || !qb) return false;
+    launch_f32_to_bf16(c->stream, qb, qp, (int64_t)n);
+    return run_prefill(c, qb, op, DT_F32, nullptr, DT_F32, 256, kcache, vcache, rows, q_heads, kv_heads, max_ctx, base_pos, scale);
 }
 extern "C" bool qw_op_attn_prefill(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads,
                                    int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale) {
@@ -1038,6 +1090,19 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
         __nv_bfloat16 *qo[QW_MAX_SEQ];
         for (int i = 0; i < ns; i++) qo[i] = reinterpret_cast<__nv_bfloat16 *>(scr + (size_t)i * q_bytes);
         if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
+
+        if (rows * gqa > 64 && g_tune_prefill_tc) {
+            // many rows: the tcgen05 kernel, one launch per sequence
+            for (int i = 0; i < ns; i++) {
+                const FusedSeq &fs = seqs[s0 + i];
+                char *op = (char *)dev_range(c, fs.out, (size_t)rows * q_heads * 256 * el, true);
+                const char *gp = (const char *)dev_range(c, fs.qg, (size_t)rows * q_heads * 512 * el, false);
+                if (!op || !gp) return false;
+                if (!run_prefill(c, qo[i], op, io, gp + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
+                                 max_ctx, fs.base_pos, scale)) return false;
+            }
+            continue;
+        }
 
         AttnParams p;
         memset(&p, 0, sizeof p);

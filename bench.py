@@ -186,7 +186,7 @@ class DecodeBench:
     """Per-GPU state of the decode / verify workloads: caches in paged arenas, one step's
     activations, pre-built argument lists for the per-layer batched fused call."""
 
-    def __init__(self, be, torch, wl, n_seq, q_heads, kv_heads, layers, device, host_io):
+    def __init__(self, be, torch, wl, n_seq, q_heads, kv_heads, layers, device, host_io, cache="arena"):
         from qwasar_b200.backend import QwRef, BF16
         import ctypes as C
         self.be, self.torch, self.wl = be, torch, wl
@@ -197,9 +197,13 @@ class DecodeBench:
         g = torch.Generator(device=device); g.manual_seed(wl["seed"])
         # caches: one K and one V arena per sequence, `layers` layers each, filled through the
         # library's own append kernel from N(0,1) device data
-        self.karena = [be.kv_arena_alloc(layers, kv_heads, ctx) for _ in range(n_seq)]
-        self.varena = [be.kv_arena_alloc(layers, kv_heads, ctx) for _ in range(n_seq)]
         layer_bytes = kv_heads * ctx * 512
+        if cache == "arena":
+            self.karena = [be.kv_arena_alloc(layers, kv_heads, ctx) for _ in range(n_seq)]
+            self.varena = [be.kv_arena_alloc(layers, kv_heads, ctx) for _ in range(n_seq)]
+        else:   # the reference's head-major layout in plain device buffers
+            self.karena = [be.buf_alloc_device(layers * layer_bytes) for _ in range(n_seq)]
+            self.varena = [be.buf_alloc_device(layers * layer_bytes) for _ in range(n_seq)]
         chunk = 4096
         kf = torch.empty((chunk, kv_heads, 256), dtype=torch.float32, device=device)
         vf = torch.empty_like(kf)
@@ -388,7 +392,7 @@ def run_ours(args):
     qh_l, kvh_l = wl["q_heads"] // hs, wl["kv_heads"] // hs
     layers = args.layers or wl["layers"]
 
-    bench = DecodeBench(be, torch, wl, n_seq_local, qh_l, kvh_l, layers, device, host_io=False)
+    bench = DecodeBench(be, torch, wl, n_seq_local, qh_l, kvh_l, layers, device, host_io=False, cache=args.cache)
     sampler = ClockSampler(local)
     launches0 = be.launch_count()
     be.prof_kernels(True); be.prof_kernel_read("qw_attn_split", True)
@@ -454,7 +458,7 @@ def run_ours(args):
             "config": {"workload": args.workload, "q_heads": wl["q_heads"], "kv_heads": wl["kv_heads"], "head_dim": 256,
                        "context": wl["base_pos"], "rows": wl["rows"], "layers_per_step": layers,
                        "global_batch": batch * world, "kv_head_shards": hs, "replicas": replicas,
-                       "kv_cache": "paged bf16 arena", "l2": "inputs larger than L2 (>=1 GB of K/V per layer)"},
+                       "kv_cache": "paged bf16 arena" if args.cache == "arena" else "head-major bf16 buffers", "l2": "inputs larger than L2 (>=1 GB of K/V per layer)"},
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": round(achieved / peaks["hbm"], 4), "frac_of_nominal_8TBs": round(achieved / 8000.0, 4),
                          "kernel": "qw_attn_split_kernel", "launches_timed": k_n,
@@ -581,6 +585,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="attention layers per step (default: the model's)")
     ap.add_argument("--seq-shards", type=int, default=1)
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--cache", default="arena", choices=["arena", "linear"], help="paged arena or the reference's plain layout")
     ap.add_argument("--tune", default="", help="diagnostic knobs, e.g. split_kg=4 (see qw_gpu_tune)")
     args = ap.parse_args()
     if args.gpus > 1 and "RANK" not in os.environ:

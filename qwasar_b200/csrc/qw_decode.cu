@@ -34,23 +34,25 @@ constexpr int BOX_BYTES = TILE_KEYS * 128;                // 32 keys x 64 dims b
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 constexpr float NEG_BIG = -1.0e30f;
+constexpr int RED_LD = 264;        // floats per row of the reduction buffer: 8 of padding spread the rows over the banks
 
 template <int MT, int KG_>
 struct SplitCfg {
     static constexpr int KG = KG_;
     static constexpr int NW = MT * KG;                    // consumer warps
-    static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 4);
+    static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 3);
     static constexpr int THREADS = (NW + 1) * 32;         // + the TMA producer warp
     static_assert(THREADS <= 256, "warps are allocated in fours: 9 warps would be budgeted as 12");
     static constexpr int MAXREG = 255;
     static constexpr int Q_BYTES = MT * 16 * 512;
-    static constexpr int RED_BYTES = MT * 16 * 256 * 4;
+    static constexpr int RED_BYTES = MT * 16 * RED_LD * 4;
     static constexpr int OFF_Q = NST * STAGE_BYTES;
     static constexpr int OFF_RED = OFF_Q + Q_BYTES;
     static constexpr int OFF_M = OFF_RED + RED_BYTES;     // [MT][KG][16] floats
     static constexpr int OFF_L = OFF_M + MT * KG * 16 * 4;  // [MT][16] floats
     static constexpr int OFF_BAR = OFF_L + MT * 16 * 4;   // full[NST], empty[NST], abort
     static constexpr int SMEM = OFF_BAR + (2 * NST + 1) * 8 + 1024;  // + alignment slack
+    static_assert(SMEM <= 232448, "exceeds the 227 KB a CTA may use");
 };
 
 struct Cursor {      // position on the flattened tile line
@@ -338,9 +340,6 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 sm_m[(mt * KG + kg) * 16 + gid] = m0;
                 sm_m[(mt * KG + kg) * 16 + gid + 8] = m1;
             }
-            if (threadIdx.x < MT * 16) sm_l[threadIdx.x] = 0.0f;
-            for (int idx = warp * 32 + lane; idx < MT * 16 * 64; idx += NW * 32)
-                reinterpret_cast<float4 *>(red)[idx] = make_float4(0.f, 0.f, 0.f, 0.f);
             asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
             float M0 = NEG_BIG, M1 = NEG_BIG;
 #pragma unroll
@@ -349,28 +348,53 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 M1 = fmaxf(M1, sm_m[(mt * KG + g2) * 16 + gid + 8]);
             }
             {
+                // the KG warps of a row tile add their accumulators into `red` one after the
+                // other (plain loads and stores, valid rows only): KG short rounds instead of
+                // thousands of conflicting shared-memory atomics
                 const float f0 = ex2(m0 - M0), f1 = ex2(m1 - M1);
-                float *r0 = red + (size_t)(mt * 16 + gid) * 256 + tig * 2;
-                float *r1 = r0 + 8 * 256;
+                const bool v0 = mt * 16 + gid < valid_rows, v1 = mt * 16 + gid + 8 < valid_rows;
+                float2 *r0 = reinterpret_cast<float2 *>(red + (size_t)(mt * 16 + gid) * RED_LD + tig * 2);
+                float2 *r1 = r0 + 8 * (RED_LD / 2);
+#pragma unroll 1
+                for (int round = 0; round < KG; round++) {
+                    if (kg == round) {
+                        if (round == 0) {
+                            if (v0) {
 #pragma unroll
-                for (int n = 0; n < 32; n++) {
-                    atomicAdd(r0 + n * 8, o[n][0] * f0);
-                    atomicAdd(r0 + n * 8 + 1, o[n][1] * f0);
-                    atomicAdd(r1 + n * 8, o[n][2] * f1);
-                    atomicAdd(r1 + n * 8 + 1, o[n][3] * f1);
-                }
-                if (tig == 0) {
-                    atomicAdd(&sm_l[mt * 16 + gid], l0 * f0);
-                    atomicAdd(&sm_l[mt * 16 + gid + 8], l1 * f1);
+                                for (int n = 0; n < 32; n++) r0[n * 4] = make_float2(o[n][0] * f0, o[n][1] * f0);
+                            }
+                            if (v1) {
+#pragma unroll
+                                for (int n = 0; n < 32; n++) r1[n * 4] = make_float2(o[n][2] * f1, o[n][3] * f1);
+                            }
+                            if (tig == 0) { sm_l[mt * 16 + gid] = l0 * f0; sm_l[mt * 16 + gid + 8] = l1 * f1; }
+                        } else {
+                            if (v0) {
+#pragma unroll
+                                for (int n = 0; n < 32; n++) {
+                                    float2 t = r0[n * 4];
+                                    r0[n * 4] = make_float2(fmaf(o[n][0], f0, t.x), fmaf(o[n][1], f0, t.y));
+                                }
+                            }
+                            if (v1) {
+#pragma unroll
+                                for (int n = 0; n < 32; n++) {
+                                    float2 t = r1[n * 4];
+                                    r1[n * 4] = make_float2(fmaf(o[n][2], f1, t.x), fmaf(o[n][3], f1, t.y));
+                                }
+                            }
+                            if (tig == 0) { sm_l[mt * 16 + gid] += l0 * f0; sm_l[mt * 16 + gid + 8] += l1 * f1; }
+                        }
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
                 }
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
 
             const bool whole = (seg_t0 == 0) && (seg_n == sq.n_tiles) && (p.mode == 0);
             const int slot_id = blockIdx.x + c.s * p.kv_heads + c.h;   // partial slot of (cta, group)
             for (int idx = warp * 32 + lane; idx < valid_rows * 64; idx += NW * 32) {
                 const int row = idx >> 6, d4 = (idx & 63) * 4;
-                float4 acc = *reinterpret_cast<const float4 *>(red + (size_t)row * 256 + d4);
+                float4 acc = *reinterpret_cast<const float4 *>(red + (size_t)row * RED_LD + d4);
                 float Mrow = NEG_BIG;
 #pragma unroll
                 for (int g2 = 0; g2 < KG; g2++) Mrow = fmaxf(Mrow, sm_m[((row >> 4) * KG + g2) * 16 + (row & 15)]);

@@ -2,20 +2,22 @@
 // tensor memory, operands staged by TMA (sm_100a).
 //
 // One CTA per (128-row query tile, query head).  K and V are read from the cache (the rows
-// of this chunk were appended just before), 128 keys per step:
+// of this chunk were appended just before), 64 keys -- one arena page -- per step, each
+// double-buffered in shared memory:
 //
 //   warp 5   TMA: Q tile once (4 SWIZZLE_128B boxes of 128 rows x 64 dims), then K tiles
-//   warp 6   TMA: V tiles                       (8 boxes of 64 keys x 64 dims each)
-//   warp 4   one thread issues tcgen05.mma:  S_b = Q K_j^T   (SS, M128 N128 K16 x 16)
-//                                            O  += P_j V_j   (TS, M128 N256 K16 x 8, P in TMEM)
+//   warp 6   TMA: V tiles                       (4 boxes of 64 keys x 64 dims each)
+//   warp 4   one thread issues tcgen05.mma:  S_b = Q K_j^T   (SS, M128 N64  K16 x 16)
+//                                            O  += P_j V_j   (TS, M128 N256 K16 x 4, P in TMEM)
 //   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Reads S (fp32) from TMEM,
 //            online max / sum in the exp2 domain, writes P (bf16) back over S, rescales O in
 //            TMEM only when a row's max grew by more than 2^8 (the stale max is exact
 //            arithmetic, just a different common factor), and at the end normalises, applies
 //            the sigmoid output gate and stores the row.
 //
-// TMEM columns (512): O [0,256) fp32 | S0 [256,384) | S1 [384,512); P_b aliases the first 64
-// columns of S_b.  S is double-buffered so that Q K_{j+1}^T runs under the softmax of tile j.
+// TMEM columns (512 allocated): O [0,256) fp32 | S0 [256,320) | S1 [320,384); P_b aliases the
+// first 32 columns of S_b.  S is double-buffered so that Q K_{j+1}^T runs under the softmax of
+// tile j, and K/V double-buffered so that the loads of tile j+1 run under the products of tile j.
 // Every wait on an mbarrier is bounded (qw_common.cuh): a stuck pipeline ends the kernel with
 // a status code instead of hanging the GPU, and TMEM is always released.
 //
@@ -26,17 +28,20 @@ namespace qw {
 
 namespace {
 
-constexpr int BM = 128, BN = 128;
-constexpr int TILE_BYTES = 128 * 512;                 // 128 rows x 256 dims bf16
-constexpr int BOX16K = 128 * 128;                     // one 64-dim box of 128 rows
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 2 * TILE_BYTES, OFF_BAR = 3 * TILE_BYTES;
+constexpr int BM = 128, BN = 64;
+constexpr int Q_BYTES = BM * 512;                     // 128 rows x 256 dims bf16
+constexpr int QBOX = BM * 128;                        // one 64-dim box of the Q tile
+constexpr int KV_BYTES = BN * 512;                    // 64 keys x 256 dims bf16
+constexpr int KVBOX = BN * 128;                       // one 64-dim box of a K or V tile
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = Q_BYTES + 2 * KV_BYTES, OFF_BAR = Q_BYTES + 4 * KV_BYTES;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 7 * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
-enum Bar { Q_FULL = 0, K_FULL, V_FULL, K_FREE, V_FREE, S_READY0, S_READY1, P_READY0, P_READY1, PV_DONE, N_BARS };
+enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_FREE0, K_FREE1, V_FREE0, V_FREE1,
+           S_READY0, S_READY1, P_READY0, P_READY1, PV_DONE, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -144,88 +149,70 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     const uint32_t tmem = *tmem_slot;
     const uint32_t t_o = tmem, t_s0 = tmem + 256;
 
-    if (warp == 5) {
-        // ---------------- Q once, then K tiles ----------------
+    if (warp == 5 || warp == 6) {
+        // ---------------- warp 5: Q once, then K tiles; warp 6: V tiles ----------------
         if (lane == 0) {
-            mbar_expect_tx(&bars[Q_FULL], TILE_BYTES);
+            const bool is_k = warp == 5;
+            const KvLayer &L = is_k ? p.kc : p.vc;
+            const CUtensorMap *map = is_k ? &p.kmap : &p.vmap;
+            const int FULL = is_k ? K_FULL0 : V_FULL0, FREE = is_k ? K_FREE0 : V_FREE0;
+            uint8_t *base = smem + (is_k ? OFF_K : OFF_V);
+            if (is_k) {
+                mbar_expect_tx(&bars[Q_FULL], Q_BYTES);
 #pragma unroll
-            for (int b = 0; b < 4; b++) tma_load_2d(smem + OFF_Q + b * BOX16K, &p.qmap, head * 256 + b * 64, q0, &bars[Q_FULL]);
-            for (int j = 0; j < n_t; j++) {
-                if (j > 0) mbar_wait(&bars[K_FREE], (j - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
-                mbar_expect_tx(&bars[K_FULL], TILE_BYTES);
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int t = j * BN + half * 64;
-                    int64_t row;
-                    if (p.kc.table) {
-                        const int pg = (t >> 6) < p.kc.pt_stride ? __ldg(p.kc.table + (size_t)kvh * p.kc.pt_stride + (t >> 6)) : -1;
-                        row = pg >= 0 ? (int64_t)pg * QW_PAGE_TOKENS : (int64_t)p.oob_row;   // unmapped: zero fill
-                    } else {
-                        row = t < p.kc.max_ctx ? (int64_t)kvh * p.kc.max_ctx + t : (int64_t)p.oob_row;
-                    }
-#pragma unroll
-                    for (int b = 0; b < 4; b++)
-                        tma_load_2d(smem + OFF_K + b * BOX16K + half * 8192, &p.kmap, b * 64, (int32_t)row, &bars[K_FULL]);
-                }
+                for (int b = 0; b < 4; b++) tma_load_2d(smem + OFF_Q + b * QBOX, &p.qmap, head * 256 + b * 64, q0, &bars[Q_FULL]);
             }
-        }
-    } else if (warp == 6) {
-        // ---------------- V tiles ----------------
-        if (lane == 0) {
             for (int j = 0; j < n_t; j++) {
-                if (j > 0) mbar_wait(&bars[V_FREE], (j - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
-                mbar_expect_tx(&bars[V_FULL], TILE_BYTES);
-#pragma unroll
-                for (int half = 0; half < 2; half++) {
-                    const int t = j * BN + half * 64;
-                    int64_t row;
-                    if (p.vc.table) {
-                        const int pg = (t >> 6) < p.vc.pt_stride ? __ldg(p.vc.table + (size_t)kvh * p.vc.pt_stride + (t >> 6)) : -1;
-                        row = pg >= 0 ? (int64_t)pg * QW_PAGE_TOKENS : (int64_t)p.oob_row;
-                    } else {
-                        row = t < p.vc.max_ctx ? (int64_t)kvh * p.vc.max_ctx + t : (int64_t)p.oob_row;
-                    }
-#pragma unroll
-                    for (int b = 0; b < 4; b++)
-                        tma_load_2d(smem + OFF_V + b * BOX16K + half * 8192, &p.vmap, b * 64, (int32_t)row, &bars[V_FULL]);
+                const int st = j & 1;
+                const int t = j * BN;
+                int64_t row;
+                if (L.table) {
+                    const int pg = j < L.pt_stride ? __ldg(L.table + (size_t)kvh * L.pt_stride + j) : -1;
+                    row = pg >= 0 ? (int64_t)pg * QW_PAGE_TOKENS : (int64_t)p.oob_row;   // unmapped: zero fill
+                } else {
+                    row = t < L.max_ctx ? (int64_t)kvh * L.max_ctx + t : (int64_t)p.oob_row;
                 }
+                if (j >= 2) mbar_wait(&bars[FREE + st], ((j >> 1) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                mbar_expect_tx(&bars[FULL + st], KV_BYTES);
+#pragma unroll
+                for (int b = 0; b < 4; b++)
+                    tma_load_2d(base + st * KV_BYTES + b * KVBOX, map, b * 64, (int32_t)row, &bars[FULL + st]);
             }
         }
     } else if (warp == 4) {
         // ---------------- tensor-core issue ----------------
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc(128, 128, 0);
+            constexpr uint32_t idesc_qk = instr_desc(128, BN, 0);
             constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
             const uint32_t q_a = smem_u32(smem + OFF_Q), k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V);
             auto issue_qk = [&](int j) {
-                const uint32_t t_s = t_s0 + (j & 1) * 128;
+                const int st = j & 1;
+                mbar_wait(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                tc_fence_after();
+                const uint32_t t_s = t_s0 + st * BN;
 #pragma unroll
                 for (int ks = 0; ks < 16; ks++) {
-                    const uint32_t off = (ks >> 2) * BOX16K + (ks & 3) * 32;       // 16 dims = 32 bytes inside the swizzle atom
-                    mma_ss(t_s, smem_desc(q_a + off, 16, 1024), smem_desc(k_a + off, 16, 1024), idesc_qk, ks > 0);
+                    // 16 dims = 32 bytes inside the swizzle atom; 64 dims per box
+                    mma_ss(t_s, smem_desc(q_a + (ks >> 2) * QBOX + (ks & 3) * 32, 16, 1024),
+                           smem_desc(k_a + st * KV_BYTES + (ks >> 2) * KVBOX + (ks & 3) * 32, 16, 1024), idesc_qk, ks > 0);
                 }
-                tc_commit(&bars[S_READY0 + (j & 1)]);
-                tc_commit(&bars[K_FREE]);
+                tc_commit(&bars[S_READY0 + st]);
+                tc_commit(&bars[K_FREE0 + st]);
             };
             mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-            mbar_wait(&bars[K_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-            tc_fence_after();
             issue_qk(0);
             for (int j = 0; j < n_t; j++) {
-                if (j + 1 < n_t) {
-                    mbar_wait(&bars[K_FULL], (j + 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-                    tc_fence_after();
-                    issue_qk(j + 1);
-                }
-                mbar_wait(&bars[P_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-                mbar_wait(&bars[V_FULL], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                const int st = j & 1;
+                if (j + 1 < n_t) issue_qk(j + 1);
+                mbar_wait(&bars[P_READY0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                mbar_wait(&bars[V_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
-                const uint32_t t_p = t_s0 + (j & 1) * 128;     // P aliases the head of S
+                const uint32_t t_p = t_s0 + st * BN;           // P aliases the head of S
 #pragma unroll
-                for (int ks = 0; ks < 8; ks++)                 // 16 keys per step: 8 TMEM columns of bf16 pairs
-                    mma_ts(t_o, t_p + ks * 8, smem_desc(v_a + ks * 2048, BOX16K, 1024), idesc_pv, (j > 0) || (ks > 0));
+                for (int ks = 0; ks < BN / 16; ks++)           // 16 keys per step: 8 TMEM columns of bf16 pairs
+                    mma_ts(t_o, t_p + ks * 8, smem_desc(v_a + st * KV_BYTES + ks * 2048, KVBOX, 1024), idesc_pv, (j > 0) || (ks > 0));
                 tc_commit(&bars[PV_DONE]);
-                tc_commit(&bars[V_FREE]);
+                tc_commit(&bars[V_FREE0 + st]);
             }
         }
     } else {
@@ -239,23 +226,25 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         float m = NEG_BIG, l = 0.0f;
         uint32_t v[32];
         for (int j = 0; j < n_t; j++) {
-            const uint32_t t_s = t_s0 + (j & 1) * 128 + lane_base;
+            const uint32_t t_s = t_s0 + (j & 1) * BN + lane_base;
             mbar_wait(&bars[S_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             tc_fence_after();
             const bool need_mask = j * BN + BN - 1 > p.base_pos + q0;
-            // pass 1: the row's max over this tile
-            float mx = NEG_BIG;
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                tmem_ld32(t_s + c * 32, v);
-                tmem_wait_ld();
+            // the row's 64 scores, read once
+            uint32_t sa[32], sb[32];
+            tmem_ld32(t_s, sa);
+            tmem_ld32(t_s + 32, sb);
+            tmem_wait_ld();
+            if (need_mask) {
 #pragma unroll
                 for (int e = 0; e < 32; e++) {
-                    float x = __uint_as_float(v[e]);
-                    if (need_mask && j * BN + c * 32 + e > limit) x = NEG_BIG;
-                    mx = fmaxf(mx, x);
+                    if (j * BN + e > limit) sa[e] = __float_as_uint(NEG_BIG);
+                    if (j * BN + 32 + e > limit) sb[e] = __float_as_uint(NEG_BIG);
                 }
             }
+            float mx = NEG_BIG;
+#pragma unroll
+            for (int e = 0; e < 32; e++) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[e]), __uint_as_float(sb[e])));
             const float mx2 = fmaxf(mx * sc2, NEG_BIG);
             if (j == 0) {
                 m = mx2;
@@ -279,25 +268,23 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     if (grow) m = mx2;
                 }
             }
-            // pass 2: weights, their sum, and P (bf16) written over the head of S
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
-                tmem_ld32(t_s + c * 32, v);
-                tmem_wait_ld();
-                uint32_t pk[16];
+            // weights, their sum, and P (bf16) written over the head of S; masked scores are
+            // NEG_BIG, whose weight underflows to exactly 0
+            uint32_t pk[32];
+            float l0 = 0.0f, l1 = 0.0f;
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float x0 = ex2(fmaf(__uint_as_float(v[e]), sc2, -m));
-                    float x1 = ex2(fmaf(__uint_as_float(v[e + 1]), sc2, -m));
-                    if (need_mask) {
-                        if (j * BN + c * 32 + e > limit) x0 = 0.0f;
-                        if (j * BN + c * 32 + e + 1 > limit) x1 = 0.0f;
-                    }
-                    l += x0 + x1;
-                    pk[e >> 1] = pack_bf16(x0, x1);
-                }
-                tmem_st16(t_s + c * 16, pk);
+            for (int e = 0; e < 32; e += 2) {
+                const float x0 = ex2(fmaf(__uint_as_float(sa[e]), sc2, -m));
+                const float x1 = ex2(fmaf(__uint_as_float(sa[e + 1]), sc2, -m));
+                const float y0 = ex2(fmaf(__uint_as_float(sb[e]), sc2, -m));
+                const float y1 = ex2(fmaf(__uint_as_float(sb[e + 1]), sc2, -m));
+                l0 += x0 + x1;
+                l1 += y0 + y1;
+                pk[e >> 1] = pack_bf16(x0, x1);
+                pk[16 + (e >> 1)] = pack_bf16(y0, y1);
             }
+            l += l0 + l1;
+            tmem_st32(t_s, pk);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars[P_READY0 + (j & 1)]);

@@ -99,6 +99,7 @@ struct Globals {
     PFN_memSetAccess memSetAccess = nullptr;
     PFN_memGetGranularity memGetGranularity = nullptr;
     std::vector<Scratch> scratch_pool;
+    std::vector<cudaStream_t> stream_pool;    // streams of freed command buffers, reused
     std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows * 128 + box rows) -> map
     char last_error[256] = "";
     bool has_error = false;
@@ -188,7 +189,7 @@ bool encode_rows_map(CUtensorMap *m, void *base, uint64_t rows, uint32_t box_row
     return true;
 }
 
-bool arena_grow(Arena *a) {
+bool arena_grow(Arena *a, cudaStream_t stream) {
     if (a->mapped_pages >= a->max_pages) return false;
     const int64_t first = a->mapped_pages;
     const int64_t n = std::min<int64_t>(PAGES_PER_CHUNK, a->max_pages - first);
@@ -209,7 +210,8 @@ bool arena_grow(Arena *a) {
             G.memUnmap(at, CHUNK_BYTES); G.memRelease(h); set_error("arena: cuMemSetAccess failed"); return false;
         }
         a->chunks.push_back(h);
-        cudaMemset(reinterpret_cast<void *>(at), 0, CHUNK_BYTES);
+        // zeroed in the order of the stream whose kernels will write the new pages
+        cudaMemsetAsync(reinterpret_cast<void *>(at), 0, CHUNK_BYTES, stream);
     }
     // hand the new pages to the free list, permuted when asked to
     std::vector<int32_t> ids((size_t)n);
@@ -237,7 +239,7 @@ bool arena_ensure(Arena *a, int layer, int n_tokens, cudaStream_t stream) {
         int first_new = -1, last_new = -1;
         for (int pg = 0; pg < need; pg++) {
             if (row[pg] >= 0) continue;
-            if (a->free_pages.empty() && !arena_grow(a)) return false;
+            if (a->free_pages.empty() && !arena_grow(a, stream)) return false;
             row[pg] = a->free_pages.back();
             a->free_pages.pop_back();
             a->in_use++;
@@ -287,7 +289,10 @@ void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write) {
     if (b->kind == BUF_ARENA) { cmd_fail(c, "an arena can only be a cache operand"); return nullptr; }
     if (r.off + bytes > b->len) { cmd_fail(c, "operand [%zu, %zu) exceeds its buffer (%zu bytes)", r.off, r.off + bytes, b->len); return nullptr; }
     if (b->kind == BUF_SHARED && bytes) {
-        const size_t lo = r.off, hi = r.off + bytes;
+        // small buffers are mirrored whole on first touch: one copy instead of one per operand
+        const bool whole = b->len <= ((size_t)4 << 20);
+        const size_t lo = whole ? 0 : r.off, hi = whole ? b->len : r.off + bytes;
+        const size_t w_lo = r.off, w_hi = r.off + bytes;
         Touch *t = nullptr;
         for (auto &x : c->touched) if (x.b == b) { t = &x; break; }
         if (!t) {
@@ -305,8 +310,8 @@ void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write) {
             }
         }
         if (write) {
-            if (t->whi == 0) { t->wlo = lo; t->whi = hi; }
-            else { t->wlo = std::min(t->wlo, lo); t->whi = std::max(t->whi, hi); }
+            if (t->whi == 0) { t->wlo = w_lo; t->whi = w_hi; }
+            else { t->wlo = std::min(t->wlo, w_lo); t->whi = std::max(t->whi, w_hi); }
         }
     }
     return (char *)b->dev + r.off;
@@ -516,6 +521,8 @@ extern "C" void qw_gpu_shutdown(void) {
     cudaDeviceSynchronize();
     for (auto &s : G.scratch_pool) cudaFree(s.p);
     G.scratch_pool.clear();
+    for (auto &st : G.stream_pool) cudaStreamDestroy(st);
+    G.stream_pool.clear();
     G.map_cache.clear();
     if (G.status_host) cudaFreeHost(G.status_host);
     G.status_host = G.status_dev = nullptr;
@@ -559,6 +566,7 @@ extern "C" qw_buf qw_buf_alloc(size_t len) {
     }
     memset(b->host, 0, n);
     cudaMemset(b->dev, 0, n);
+    cudaStreamSynchronize(0);   // the fill must not trail kernels launched on other streams
     return b;
 }
 
@@ -576,6 +584,7 @@ extern "C" qw_buf qw_buf_alloc_device(size_t len) {
     qw_buf b = new qw_buf_s{BUF_DEVICE, len, nullptr, nullptr, false, true, false, nullptr};
     if (cudaMalloc(&b->dev, std::max<size_t>(len, 16)) != cudaSuccess) { set_error("cannot allocate %zu bytes of device memory", len); delete b; cudaGetLastError(); return nullptr; }
     cudaMemset(b->dev, 0, std::max<size_t>(len, 16));
+    cudaStreamSynchronize(0);
     return b;
 }
 
@@ -641,11 +650,13 @@ extern "C" qw_buf qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32
         void *p = nullptr;
         if (cudaMalloc(&p, a->va_size) != cudaSuccess) { set_error("arena: cannot allocate %zu bytes", a->va_size); delete a; cudaGetLastError(); return nullptr; }
         cudaMemset(p, 0, a->va_size);
+        cudaStreamSynchronize(0);
         a->va = (CUdeviceptr)p;
     }
     a->table_host.assign((size_t)a->max_pages, -1);
     if (cudaMalloc(&a->table_dev, (size_t)a->max_pages * sizeof(int32_t)) != cudaSuccess) { set_error("arena: cannot allocate the page table"); arena_destroy(a); cudaGetLastError(); return nullptr; }
     cudaMemset(a->table_dev, 0xff, (size_t)a->max_pages * sizeof(int32_t));
+    cudaStreamSynchronize(0);   // the fill must not trail kernels launched on other streams
     // the tensor map spans the whole reserved range; rows of unmapped pages are never addressed
     if (!encode_rows_map(&a->map, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 32) ||
         !encode_rows_map(&a->map64, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 64)) { arena_destroy(a); return nullptr; }
@@ -737,7 +748,13 @@ static qw_cmd cmd_new(cudaStream_t s, bool own) {
 extern "C" qw_cmd qw_cmd_begin(void) {
     if (!G.up) return nullptr;
     cudaStream_t s;
-    if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) { set_error("cannot create a stream"); return nullptr; }
+    if (!G.stream_pool.empty()) {
+        s = G.stream_pool.back();
+        G.stream_pool.pop_back();
+    } else if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) {
+        set_error("cannot create a stream");
+        return nullptr;
+    }
     qw_cmd c = cmd_new(s, true);
     if (qw_prof_enabled()) qw_cmd_mark(c, nullptr);
     return c;
@@ -790,7 +807,12 @@ extern "C" void qw_cmd_free(qw_cmd c) {
     for (auto &s : c->scratch) G.scratch_pool.push_back(s);
     for (auto &m : c->marks) cudaEventDestroy(m.ev);
     for (auto &k : c->ktimes) { cudaEventDestroy(k.t0); cudaEventDestroy(k.t1); }
-    if (c->own_stream) cudaStreamDestroy(c->stream);
+    if (c->own_stream) {
+        // everything on the stream has been waited for (or is synchronised here) before reuse
+        if (cudaStreamQuery(c->stream) != cudaSuccess) cudaStreamSynchronize(c->stream);
+        if (c->failed || G.stream_pool.size() >= 16) cudaStreamDestroy(c->stream);
+        else G.stream_pool.push_back(c->stream);
+    }
     delete c;
 }
 extern "C" const char *qw_cmd_error(qw_cmd c) { return c && c->failed ? c->err : nullptr; }

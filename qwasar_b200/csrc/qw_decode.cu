@@ -43,6 +43,9 @@ struct SplitCfg {
     static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 3);
     static constexpr int THREADS = (NW + 1) * 32;         // + the TMA producer warp
     static_assert(THREADS <= 256, "warps are allocated in fours: 9 warps would be budgeted as 12");
+    // a warp must take part in every phase of each stage it ever waits on (a parity wait is only
+    // valid one phase behind): the block -> warp pattern has to repeat with the ring
+    static_assert((2 * NST) % KG == 0, "key groups must divide the blocks of one trip round the ring");
     static constexpr int MAXREG = 255;
     static constexpr int Q_BYTES = MT * 16 * 512;
     static constexpr int RED_BYTES = MT * 16 * RED_LD * 4;
@@ -649,7 +652,7 @@ void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
             if (g_tune_split_kg == 4) launch_split_t<1, 4>(s, p);
             else launch_split_t<1, 6>(s, p);
             break;
-        case 2: launch_split_t<2, 3>(s, p); break;
+        case 2: launch_split_t<2, 2>(s, p); break;
         default: launch_split_t<4, 1>(s, p); break;
     }
 }

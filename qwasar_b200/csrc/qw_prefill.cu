@@ -286,6 +286,11 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             l += l0 + l1;
             tmem_st32(t_s, pk);
             tmem_wait_st();
+            // Observe every phase of PV_DONE: a parity wait is only meaningful for a waiter at most
+            // one phase behind, and the epilogue (or a later rescale) waits on this barrier again.
+            // P V_{j-1} was issued long before this point, and P V_j cannot be issued until every
+            // row has arrived below, so the barrier cannot run ahead of this wait.
+            if (j > 0) mbar_wait(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             tc_fence_before();
             mbar_arrive(&bars[P_READY0 + (j & 1)]);
         }

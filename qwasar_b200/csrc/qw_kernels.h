@@ -91,7 +91,7 @@ void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
 
 // Causal prefill on tcgen05 tensor cores: one CTA per (128-row tile, query head).
 struct PrefillParams {
-    CUtensorMap qmap;        // bf16 [rows, q_heads*256], box 64 x 128
+    const __nv_bfloat16 *q;  // [rows, q_heads, 256], 16-byte aligned
     CUtensorMap kmap, vmap;  // cache row maps, box 64 x 64
     KvLayer kc, vc;
     void *out;               // [rows, q_heads, 256] f32 or bf16

@@ -5,19 +5,23 @@
 // of this chunk were appended just before), 64 keys -- one arena page -- per step, each
 // double-buffered in shared memory:
 //
-//   warp 5   TMA: Q tile once (4 SWIZZLE_128B boxes of 128 rows x 64 dims), then K tiles
-//   warp 6   TMA: V tiles                       (4 boxes of 64 keys x 64 dims each)
-//   warp 4   one thread issues tcgen05.mma:  S_b = Q K_j^T   (SS, M128 N64  K16 x 16)
-//                                            O  += P_j V_j   (TS, M128 N256 K16 x 4, P in TMEM)
+//   warp 5   TMA: K tiles   (4 SWIZZLE_128B boxes of 64 keys x 64 dims each, 3 stages)
+//   warp 6   TMA: V tiles   (likewise)
+//   warp 4   one thread issues tcgen05.mma:  S_b = Q K_j^T   (TS, M128 N64  K16 x 16, Q in TMEM)
+//                                            O  += P_j V_j   (TS, M128 N256 K16 x 4,  P in TMEM)
 //   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Reads S (fp32) from TMEM,
 //            online max / sum in the exp2 domain, writes P (bf16) back over S, rescales O in
 //            TMEM only when a row's max grew by more than 2^8 (the stale max is exact
 //            arithmetic, just a different common factor), and at the end normalises, applies
 //            the sigmoid output gate and stores the row.
 //
-// TMEM columns (512 allocated): O [0,256) fp32 | S0 [256,320) | S1 [320,384); P_b aliases the
-// first 32 columns of S_b.  S is double-buffered so that Q K_{j+1}^T runs under the softmax of
-// tile j, and K/V double-buffered so that the loads of tile j+1 run under the products of tile j.
+// TMEM columns (512): O [0,256) fp32 | Q [256,384) bf16 pairs | S0 [384,448) | S1 [448,512);
+// P_b aliases the first 32 columns of S_b.  The query tile lives in tensor memory, not shared
+// memory: as the A operand of every Q K^T it would otherwise be re-read from shared memory for
+// each key tile (64 KB per 64 keys, as much as K and V together), and shared-memory bandwidth,
+// not the tensor pipe, would bound the kernel.  Each softmax thread loads its own row of Q
+// once and stores it to its TMEM lane.  S is double-buffered so that Q K_{j+1}^T runs under
+// the softmax of tile j; K and V have three stages each so that loads run well ahead.
 // Every wait on an mbarrier is bounded (qw_common.cuh): a stuck pipeline ends the kernel with
 // a status code instead of hanging the GPU, and TMEM is always released.
 //
@@ -29,19 +33,19 @@ namespace qw {
 namespace {
 
 constexpr int BM = 128, BN = 64;
-constexpr int Q_BYTES = BM * 512;                     // 128 rows x 256 dims bf16
-constexpr int QBOX = BM * 128;                        // one 64-dim box of the Q tile
+constexpr int NKV = 3;                                // shared-memory stages of K and of V
 constexpr int KV_BYTES = BN * 512;                    // 64 keys x 256 dims bf16
 constexpr int KVBOX = BN * 128;                       // one 64-dim box of a K or V tile
-constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = Q_BYTES + 2 * KV_BYTES, OFF_BAR = Q_BYTES + 4 * KV_BYTES;
+constexpr int OFF_K = 0, OFF_V = NKV * KV_BYTES, OFF_BAR = 2 * NKV * KV_BYTES;
+constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;    // TMEM columns
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 constexpr int THREADS = 7 * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
-enum Bar { Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_FREE0, K_FREE1, V_FREE0, V_FREE1,
-           S_READY0, S_READY1, P_READY0, P_READY1, PV_DONE, N_BARS };
+enum Bar { Q_READY = 0, K_FULL0, K_FULL1, K_FULL2, V_FULL0, V_FULL1, V_FULL2, K_FREE0, K_FREE1, K_FREE2,
+           V_FREE0, V_FREE1, V_FREE2, S_READY0, S_READY1, P_READY0, P_READY1, PV_DONE, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -138,7 +142,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     const int n_t = (k_end + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY0 || i == P_READY1) ? 128 : 1);
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY0 || i == P_READY1 || i == Q_READY) ? 128 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -147,23 +151,18 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_o = tmem, t_s0 = tmem + 256;
+    const uint32_t t_o = tmem + COL_O, t_q = tmem + COL_Q, t_s0 = tmem + COL_S;
 
     if (warp == 5 || warp == 6) {
-        // ---------------- warp 5: Q once, then K tiles; warp 6: V tiles ----------------
+        // ---------------- warp 5: K tiles; warp 6: V tiles ----------------
         if (lane == 0) {
             const bool is_k = warp == 5;
             const KvLayer &L = is_k ? p.kc : p.vc;
             const CUtensorMap *map = is_k ? &p.kmap : &p.vmap;
             const int FULL = is_k ? K_FULL0 : V_FULL0, FREE = is_k ? K_FREE0 : V_FREE0;
             uint8_t *base = smem + (is_k ? OFF_K : OFF_V);
-            if (is_k) {
-                mbar_expect_tx(&bars[Q_FULL], Q_BYTES);
-#pragma unroll
-                for (int b = 0; b < 4; b++) tma_load_2d(smem + OFF_Q + b * QBOX, &p.qmap, head * 256 + b * 64, q0, &bars[Q_FULL]);
-            }
             for (int j = 0; j < n_t; j++) {
-                const int st = j & 1;
+                const int st = j % NKV;
                 const int t = j * BN;
                 int64_t row;
                 if (L.table) {
@@ -172,7 +171,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 } else {
                     row = t < L.max_ctx ? (int64_t)kvh * L.max_ctx + t : (int64_t)p.oob_row;
                 }
-                if (j >= 2) mbar_wait(&bars[FREE + st], ((j >> 1) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                if (j >= NKV) mbar_wait(&bars[FREE + st], ((j / NKV) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
                 mbar_expect_tx(&bars[FULL + st], KV_BYTES);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
@@ -184,30 +183,30 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(128, BN, 0);
             constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
-            const uint32_t q_a = smem_u32(smem + OFF_Q), k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V);
+            const uint32_t k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V);
             auto issue_qk = [&](int j) {
-                const int st = j & 1;
-                mbar_wait(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                const int st = j % NKV;
+                mbar_wait(&bars[K_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
-                const uint32_t t_s = t_s0 + st * BN;
+                const uint32_t t_s = t_s0 + (j & 1) * BN;
 #pragma unroll
                 for (int ks = 0; ks < 16; ks++) {
-                    // 16 dims = 32 bytes inside the swizzle atom; 64 dims per box
-                    mma_ss(t_s, smem_desc(q_a + (ks >> 2) * QBOX + (ks & 3) * 32, 16, 1024),
-                           smem_desc(k_a + st * KV_BYTES + (ks >> 2) * KVBOX + (ks & 3) * 32, 16, 1024), idesc_qk, ks > 0);
+                    // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes inside the swizzle atom, 64 dims per box
+                    mma_ts(t_s, t_q + ks * 8, smem_desc(k_a + st * KV_BYTES + (ks >> 2) * KVBOX + (ks & 3) * 32, 16, 1024),
+                           idesc_qk, ks > 0);
                 }
-                tc_commit(&bars[S_READY0 + st]);
+                tc_commit(&bars[S_READY0 + (j & 1)]);
                 tc_commit(&bars[K_FREE0 + st]);
             };
-            mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             issue_qk(0);
             for (int j = 0; j < n_t; j++) {
-                const int st = j & 1;
+                const int st = j % NKV;
                 if (j + 1 < n_t) issue_qk(j + 1);
-                mbar_wait(&bars[P_READY0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-                mbar_wait(&bars[V_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                mbar_wait(&bars[P_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                mbar_wait(&bars[V_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
-                const uint32_t t_p = t_s0 + st * BN;           // P aliases the head of S
+                const uint32_t t_p = t_s0 + (j & 1) * BN;      // P aliases the head of S
 #pragma unroll
                 for (int ks = 0; ks < BN / 16; ks++)           // 16 keys per step: 8 TMEM columns of bf16 pairs
                     mma_ts(t_o, t_p + ks * 8, smem_desc(v_a + st * KV_BYTES + ks * 2048, KVBOX, 1024), idesc_pv, (j > 0) || (ks > 0));
@@ -225,6 +224,22 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         const float sc2 = p.scale * LOG2E;
         float m = NEG_BIG, l = 0.0f;
         uint32_t v[32];
+        {
+            // this row of Q (256 bf16 = 128 columns of pairs) into the row's TMEM lane
+            const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((size_t)row_g * p.q_heads + head) * 256);
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const uint4 x = valid ? __ldg(src + c * 8 + e) : make_uint4(0, 0, 0, 0);
+                    v[e * 4] = x.x; v[e * 4 + 1] = x.y; v[e * 4 + 2] = x.z; v[e * 4 + 3] = x.w;
+                }
+                tmem_st32(t_q + lane_base + c * 32, v);
+            }
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[Q_READY]);
+        }
         for (int j = 0; j < n_t; j++) {
             const uint32_t t_s = t_s0 + (j & 1) * BN + lane_base;
             mbar_wait(&bars[S_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);

@@ -456,16 +456,7 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
     int64_t k_rows = 0, v_rows = 0;
     if (!resolve_cache(c, kcache, kv_heads, max_ctx, QW_HEAD_DIM, base_pos + rows, false, false, &p.kc, &p.kmap, 64, &k_rows)) return false;
     if (!resolve_cache(c, vcache, kv_heads, max_ctx, QW_HEAD_DIM, base_pos + rows, false, false, &p.vc, &p.vmap, 64, &v_rows)) return false;
-    cuuint64_t dims[2] = {(cuuint64_t)q_heads * QW_HEAD_DIM, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)q_heads * QW_HEAD_DIM * 2};
-    cuuint32_t box[2] = {64, 128};
-    cuuint32_t estr[2] = {1, 1};
-    if (G.encodeTiled(&p.qmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16 *>(q_bf16), dims, strides, box, estr,
-                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-        cmd_fail(c, "cuTensorMapEncodeTiled failed for the query tile");
-        return false;
-    }
+    p.q = q_bf16;
     p.out = out; p.out_dtype = out_dtype; p.gate = gate; p.gate_dtype = gate_dtype; p.gate_stride = gate_stride;
     p.rows = rows; p.base_pos = base_pos; p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = q_heads / kv_heads;
     p.n_q_tiles = (rows + 127) / 128;

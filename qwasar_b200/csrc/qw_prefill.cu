@@ -66,19 +66,21 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+// D[tmem] (+)= A[tmem] * B[smem].  The descriptor arrives as its two 32-bit halves (only the low
+// one, which holds the start address, changes between steps) and ACC is a compile-time flag, so
+// that one issue costs a handful of instructions: a single thread feeds the whole tensor pipe.
+template <bool ACC>
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint32_t bdesc_lo, uint32_t bdesc_hi, uint32_t idesc) {
+    if (ACC)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\tsetp.eq.u32 p, 0, 0;\n\tmov.b64 bd, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
+            ::"r"(d), "r"(a_tmem), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\tsetp.ne.u32 p, 0, 0;\n\tmov.b64 bd, {%2, %3};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
+            ::"r"(d), "r"(a_tmem), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
     asm volatile(
@@ -108,10 +110,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, SWIZZLE_128B (layout type 2), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+// Shared-memory matrix descriptor, SWIZZLE_128B (layout type 2), descriptor version 1, as halves:
+// low = start address >> 4 (14 bits) | leading byte offset >> 4 at bit 16; high = stride byte
+// offset >> 4 | version 1 at bit 14 | layout type 2 at bit 29.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr >> 4) & 0x3FFF) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t desc_hi(uint32_t sbo_bytes) {
+    return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
 }
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 A and B.
 __device__ __forceinline__ constexpr uint32_t instr_desc(int m, int n, int b_mn_major) {
@@ -184,17 +190,19 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             constexpr uint32_t idesc_qk = instr_desc(128, BN, 0);
             constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
             const uint32_t k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V);
+            constexpr uint32_t hi = desc_hi(1024);
             auto issue_qk = [&](int j) {
                 const int st = j % NKV;
                 mbar_wait(&bars[K_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
                 const uint32_t t_s = t_s0 + (j & 1) * BN;
+                const uint32_t k_lo = desc_lo(k_a + st * KV_BYTES, 16);
+                // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes (2 units) inside the swizzle atom,
+                // 64 dims per box (KVBOX / 16 units)
+                mma_ts<false>(t_s, t_q, k_lo, hi, idesc_qk);
 #pragma unroll
-                for (int ks = 0; ks < 16; ks++) {
-                    // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes inside the swizzle atom, 64 dims per box
-                    mma_ts(t_s, t_q + ks * 8, smem_desc(k_a + st * KV_BYTES + (ks >> 2) * KVBOX + (ks & 3) * 32, 16, 1024),
-                           idesc_qk, ks > 0);
-                }
+                for (int ks = 1; ks < 16; ks++)
+                    mma_ts<true>(t_s, t_q + ks * 8, k_lo + (ks >> 2) * (KVBOX >> 4) + (ks & 3) * 2, hi, idesc_qk);
                 tc_commit(&bars[S_READY0 + (j & 1)]);
                 tc_commit(&bars[K_FREE0 + st]);
             };
@@ -207,9 +215,12 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 mbar_wait(&bars[V_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
                 const uint32_t t_p = t_s0 + (j & 1) * BN;      // P aliases the head of S
+                const uint32_t v_lo = desc_lo(v_a + st * KV_BYTES, KVBOX);
+                // 16 keys per step: 8 TMEM columns of bf16 pairs, 2048 bytes (128 units) of V
+                if (j > 0) mma_ts<true>(t_o, t_p, v_lo, hi, idesc_pv);
+                else mma_ts<false>(t_o, t_p, v_lo, hi, idesc_pv);
 #pragma unroll
-                for (int ks = 0; ks < BN / 16; ks++)           // 16 keys per step: 8 TMEM columns of bf16 pairs
-                    mma_ts(t_o, t_p + ks * 8, smem_desc(v_a + st * KV_BYTES + ks * 2048, KVBOX, 1024), idesc_pv, (j > 0) || (ks > 0));
+                for (int ks = 1; ks < BN / 16; ks++) mma_ts<true>(t_o, t_p + ks * 8, v_lo + ks * 128, hi, idesc_pv);
                 tc_commit(&bars[PV_DONE]);
                 tc_commit(&bars[V_FREE0 + st]);
             }

@@ -276,6 +276,44 @@ bool qw_op_attn_preop(qw_cmd c, qw_ref q_out, qw_ref qg, qw_ref k, qw_ref v,
                       int32_t head_dim, int32_t rotary_dim, int32_t max_ctx, int32_t base_pos,
                       float eps, qw_dtype io, bool append);
 
+/* ---- decode attention without any allocation --------------------------------
+ * No counterpart in the reference, whose buffers all come from its own
+ * allocator (qw_buf_alloc / qw_cmd_scratch).
+ *
+ * For callers that cannot let this library allocate: an embedder that gave all
+ * device memory to its own pool at start-up, or a serving loop in a phase where
+ * cudaMalloc is forbidden because it stalls every stream of the device.  The
+ * ordinary attention ops draw their partial-softmax scratch from a pool that
+ * grows by cudaMalloc on first use; this entry point instead keeps its scratch
+ * in a fixed array inside the library image (qw_attn_decode_noalloc_scratch_bytes()
+ * = 4 MiB, resident on every GPU that loads the library until the process ends)
+ * and calls no cudaMalloc, cudaFree or other allocating routine.  It does not
+ * need qw_gpu_init either.
+ *
+ * Split-KV attention of `rows` query rows (the new token, or a few speculative
+ * ones) of one sequence against a head-major cache, same arithmetic and result
+ * as qw_op_attn_decode_tensor, optionally with the sigmoid output gate.  All
+ * pointers are device pointers the caller owns:
+ *   out, q   [rows, q_heads, 256]   gate: the same shape, or NULL   (f32 or bf16 per `io`)
+ *   kcache, vcache   bf16 [kv_heads, max_ctx, 256], 128-byte aligned
+ *   cuda_stream      a cudaStream_t (NULL = the default stream)
+ * Limits: head_dim 256; rows * (q_heads / kv_heads) <= 16; the scratch this
+ * shape needs, (SMs + kv_heads) * 16 + rows * q_heads partial rows of 1032
+ * bytes, must fit the array -- otherwise false is returned with the reason in
+ * err, and nothing is launched.
+ *
+ * The first call on each device (made with that device current) resolves the
+ * array's device address and sets a kernel attribute; make that call before
+ * any stream capture begins.  All calls on a device share the one array: two
+ * calls whose kernels overlap on the GPU (different streams, no dependency)
+ * race on it -- order them on one stream or with events.  Nothing in the array
+ * needs clearing between calls; stale contents are never read. */
+bool   qw_attn_decode_noalloc(void *out, const void *q, const void *gate, const void *kcache, const void *vcache,
+                              int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                              int32_t max_ctx, int32_t base_pos, float scale, qw_dtype io, void *cuda_stream,
+                              char *err, size_t errcap);
+size_t qw_attn_decode_noalloc_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -607,10 +607,12 @@ __global__ void __launch_bounds__(256) attn_per_query_kernel(AttnSeq sq, int q_h
 template <int MT, int KG>
 void launch_split_t(cudaStream_t s, const AttnParams &p) {
     using Cfg = SplitCfg<MT, KG>;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};      // the attribute is per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaFuncSetAttribute(qw_attn_split_kernel<MT, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
-        configured = true;
+        configured[dev] = true;
     }
     qw_attn_split_kernel<MT, KG><<<p.n_cta, Cfg::THREADS, Cfg::SMEM, s>>>(p);
     g_launches++;

@@ -383,10 +383,8 @@ def run_ours(args):
         return run_seq_split(args, be, torch, dist, wl, world, rank, device, peaks, barrier)
 
     # weak scaling: heads sharded over hs GPUs, batch grown by hs so per-GPU bytes stay fixed
-    hs = min(world, wl["kv_heads"])
-    while wl["kv_heads"] % hs or world % hs:
-        hs -= 1
-    replicas = world // hs
+    from qwasar_b200 import sharding
+    hs, _, replicas = sharding.plan(world, wl["kv_heads"], 1)
     batch = args.batch or max(wl["batch"])
     n_seq_local = batch * hs
     qh_l, kvh_l = wl["q_heads"] // hs, wl["kv_heads"] // hs
@@ -478,69 +476,69 @@ def run_ours(args):
 
 
 def run_seq_split(args, be, torch, dist, wl, world, rank, device, peaks, barrier):
-    """Long-context decode split by position over `seq_shards` GPUs: every rank holds the keys
-    of its own range (pages of the arena mapped only there), computes its partial with
-    qw_op_attn_partial, the partials are all-gathered over NCCL, every rank merges + gates."""
-    from qwasar_b200.backend import QwRef, BF16, F32
+    """Long-context decode split by position over `seq_shards` GPUs (and by KV heads over the rest):
+    every rank holds the keys of its own position range -- its arena maps only those pages --
+    computes its partial with qw_op_attn_partial, the ranks of a sequence group all-gather one packed
+    record (acc | max, sum) per rank over NCCL, and every rank merges + gates."""
+    from qwasar_b200.backend import QwRef, BF16
+    from qwasar_b200 import sharding
     ss = args.seq_shards
-    if world % ss:
-        raise SystemExit("--seq-shards must divide the number of GPUs")
-    qh, kvh, rows, base = wl["q_heads"], wl["kv_heads"], wl["rows"], wl["base_pos"]
+    hs, _, replicas = sharding.plan(world, wl["kv_heads"], ss)
+    rep, hshard, srank = sharding.rank_coords(rank, world, wl["kv_heads"], ss)
+    (q0, q1), (k0, k1) = sharding.head_slice(hshard, hs, wl["q_heads"], wl["kv_heads"])
+    qh, kvh, rows, base = q1 - q0, k1 - k0, wl["rows"], wl["base_pos"]
     layers = args.layers or wl["layers"]
-    batch = args.batch or 1
     ctx = base + rows + 56
     n_keys = base + rows
-    span = ((n_keys + ss - 1) // ss + 63) // 64 * 64
-    srank = rank % ss
-    lo, hi = srank * span, min(n_keys, (srank + 1) * span)
-    group = dist.new_group(list(range(rank - srank, rank - srank + ss))) if world > ss else None
-    g = torch.Generator(device=device); g.manual_seed(wl["seed"] + srank)
+    lo, hi = sharding.seq_range(srank, ss, n_keys)
+    group = None
+    if world > 1:
+        for g0 in range(0, world, ss):                      # every rank creates every group
+            g = dist.new_group(list(range(g0, g0 + ss)))
+            if g0 <= rank < g0 + ss:
+                group = g
     stream = torch.cuda.Stream()
+    gen = torch.Generator(device=device); gen.manual_seed(wl["seed"] + rank)
     layer_bytes = kvh * ctx * 512
-    # each rank's cache: a plain device buffer per (sequence), only its own range filled
-    caches = []
-    for s in range(batch):
-        kc = torch.zeros((layers, kvh, ctx, 256), dtype=torch.bfloat16, device=device)
-        vc = torch.zeros_like(kc)
-        kc[:, :, lo:hi].normal_(generator=g); vc[:, :, lo:hi].normal_(generator=g)
-        caches.append((kc, vc, be.buf_wrap_device(kc.data_ptr(), kc.numel() * 2), be.buf_wrap_device(vc.data_ptr(), vc.numel() * 2)))
+    ka, va = be.kv_arena_alloc(layers, kvh, ctx), be.kv_arena_alloc(layers, kvh, ctx)
+    chunk = 4096
+    kf = torch.empty((chunk, kvh, 256), dtype=torch.float32, device=device); vf = torch.empty_like(kf)
+    kfb = be.buf_wrap_device(kf.data_ptr(), kf.numel() * 4); vfb = be.buf_wrap_device(vf.data_ptr(), vf.numel() * 4)
+    c = be.cmd_begin(torch.cuda.current_stream().cuda_stream)
+    for l in range(layers):
+        for t0 in range(lo, hi, chunk):
+            n = min(chunk, hi - t0)
+            kf.normal_(generator=gen); vf.normal_(generator=gen)
+            be.op_kv_write(c, QwRef(ka, l * layer_bytes), QwRef(va, l * layer_bytes), QwRef(kfb, 0), QwRef(vfb, 0),
+                           n, kvh, 256, ctx, t0)
+    be.cmd_wait(c); be.cmd_free(c)
+    be.buf_free(kfb); be.buf_free(vfb)
+    committed = be.kv_arena_bytes_committed(ka) + be.kv_arena_bytes_committed(va)
     n_rh = rows * qh
-    q = torch.randn((batch, rows, qh, 256), generator=g, device=device).to(torch.bfloat16)
-    gate = torch.randn((batch, rows, qh, 256), generator=g, device=device).to(torch.bfloat16)
-    out = torch.empty((batch, rows, qh, 256), dtype=torch.bfloat16, device=device)
-    part = torch.empty((batch, n_rh, 258), dtype=torch.float32, device=device)        # acc | stat per row-head
-    gathered = torch.empty((ss, batch, n_rh, 258), dtype=torch.float32, device=device)
-    pa = torch.empty((ss, batch, n_rh, 256), dtype=torch.float32, device=device)
-    ps = torch.empty((ss, batch, n_rh, 2), dtype=torch.float32, device=device)
+    q = torch.randn((rows, qh, 256), generator=gen, device=device).to(torch.bfloat16)
+    gate = torch.randn((rows, qh, 256), generator=gen, device=device).to(torch.bfloat16)
+    out = torch.empty((rows, qh, 256), dtype=torch.bfloat16, device=device)
+    rec = n_rh * 258                                          # floats per rank: acc block, then stat block
+    local = torch.zeros(rec, dtype=torch.float32, device=device)
+    gathered = torch.zeros((ss, rec), dtype=torch.float32, device=device)
     W = lambda t: be.buf_wrap_device(t.data_ptr(), t.numel() * t.element_size())
-    qb, gb, ob, pab, psb = W(q), W(gate), W(out), W(pa), W(ps)
-    lp = torch.empty((batch, n_rh, 256), dtype=torch.float32, device=device)
-    lst = torch.empty((batch, n_rh, 2), dtype=torch.float32, device=device)
-    lpb, lsb = W(lp), W(lst)
+    qb, gb, ob, lb, gbuf = W(q), W(gate), W(out), W(local), W(gathered)
 
-    def step(c, with_collective=True):
+    def step(c, with_collective):
         for l in range(layers):
-            for s in range(batch):
-                ok = be.op_attn_partial(c, QwRef(lpb, s * n_rh * 1024), QwRef(lsb, s * n_rh * 8), QwRef(qb, s * n_rh * 512),
-                                        QwRef(caches[s][2], l * layer_bytes), QwRef(caches[s][3], l * layer_bytes),
-                                        rows, qh, kvh, 256, ctx, base, lo, hi, synth.SCALE, BF16)
-                if not ok:
-                    raise RuntimeError("partial declined: " + str(be.cmd_error(c)))
-            with torch.cuda.stream(stream):
-                if with_collective and ss > 1:
-                    part[:, :, :256].copy_(lp); part[:, :, 256:].copy_(lst)
-                    dist.all_gather_into_tensor(gathered, part, group=group)
-                    pa.copy_(gathered[..., :256]); ps.copy_(gathered[..., 256:])
-                else:
-                    pa[0].copy_(lp); ps[0].copy_(lst)
-            for s in range(batch):
-                # [parts, n_rh] view of sequence s: stride between parts is batch * n_rh
-                be.op_attn_merge(c, QwRef(ob, s * n_rh * 512), QwRef(pab, s * n_rh * 1024), QwRef(psb, s * n_rh * 8),
-                                 QwRef(gb, s * n_rh * 512), rows, qh, 256, ss if (with_collective and batch == 1) else 1,
-                                 256, BF16, BF16)
+            ok = be.op_attn_partial(c, QwRef(lb, 0), QwRef(lb, n_rh * 256 * 4), QwRef(qb, 0), QwRef(ka, l * layer_bytes),
+                                    QwRef(va, l * layer_bytes), rows, qh, kvh, 256, ctx, base, lo, hi, synth.SCALE, BF16)
+            if not ok:
+                raise RuntimeError("partial declined: " + str(be.cmd_error(c)))
+            if with_collective and ss > 1:
+                with torch.cuda.stream(stream):
+                    dist.all_gather_into_tensor(gathered, local, group=group)
+                be.op_attn_merge(c, QwRef(ob, 0), QwRef(gbuf, 0), QwRef(gbuf, n_rh * 256 * 4), QwRef(gb, 0), rows, qh, 256,
+                                 ss, 256, BF16, BF16, rec)
+            else:
+                be.op_attn_merge(c, QwRef(ob, 0), QwRef(lb, 0), QwRef(lb, n_rh * 256 * 4), QwRef(gb, 0), rows, qh, 256,
+                                 1, 256, BF16, BF16, rec)
 
-    if batch != 1:
-        raise SystemExit("--seq-shards currently measures batch 1 (the merge reads parts contiguously per sequence)")
     res = {}
     for name, coll in (("with_collective", True), ("kernels_only", False)):
         c = be.cmd_begin(stream.cuda_stream)
@@ -555,19 +553,23 @@ def run_seq_split(args, be, torch, dist, wl, world, rank, device, peaks, barrier
         be.cmd_wait(c); torch.cuda.synchronize(); barrier()
         be.cmd_free(c)
         t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX) if world > 1 else None
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res[name] = float(t.item())
-    total_bytes = layers * batch * synth.decode_kv_bytes(n_keys, kvh) * (world // ss)
+    total_bytes = layers * synth.decode_kv_bytes(n_keys, wl["kv_heads"]) * replicas
     if rank == 0:
         ms = res["with_collective"]
         value = total_bytes / 1e9 / (ms * 1e-3)
-        line = {"metric": "attn decode KV-read GB/s @262K ctx, sequence split", "value": round(value, 1), "unit": UNIT,
+        line = {"metric": "attn decode KV-read GB/s, sequence split", "value": round(value, 1), "unit": UNIT,
                 "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": round(ms, 4),
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": {"workload": args.workload, "seq_shards": ss, "layers_per_step": layers, "batch": batch,
-                           "context": base, "collective": "nccl all_gather of (m, l, acc) per layer"},
+                "config": {"workload": args.workload, "seq_shards": ss, "kv_head_shards": hs, "replicas": replicas,
+                           "layers_per_step": layers, "batch": 1, "context": base,
+                           "collective": "one NCCL all_gather of the packed (acc, max, sum) record per layer",
+                           "arena_bytes_committed_rank0": committed},
                 "kernels_only_ms_per_step": round(res["kernels_only"], 4),
-                "per_gpu_frac_of_hbm": round(total_bytes / world / 1e9 / (res["kernels_only"] * 1e-3) / peaks["hbm"], 4),
+                "us_per_layer": round(ms * 1e3 / layers, 2), "kernels_only_us_per_layer": round(res["kernels_only"] * 1e3 / layers, 2),
+                "per_gpu_frac_of_hbm_kernels_only": round(total_bytes / world / 1e9 / (res["kernels_only"] * 1e-3) / peaks["hbm"], 4),
                 "peak_source": peaks["which"]}
         print(json.dumps(line), flush=True)
     if world > 1:

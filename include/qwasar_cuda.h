@@ -258,14 +258,17 @@ bool qw_op_attn_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *
  * laid out [parts, rows*q_heads, ...] (what an all-gather of the ranks'
  * partials produces), by log-sum-exp exactly as qw_attn_merge_gated does
  * (metal/attn.metal:273-331), applying sigmoid(gate) when gate is not a null
- * ref; gate element (r, h, d) is read at gate[(r*q_heads + h)*gate_stride + d]. */
+ * ref; gate element (r, h, d) is read at gate[(r*q_heads + h)*gate_stride + d].
+ * part_stride: floats between consecutive parts in both pacc and pstat, for partials that
+ * were gathered as one packed record per rank (acc block then stat block); 0 = the dense
+ * layouts above. */
 bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q, qw_ref kcache, qw_ref vcache,
                         int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                         int32_t max_ctx, int32_t base_pos, int32_t key_lo, int32_t key_hi,
                         float scale, qw_dtype q_dtype);
 void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate,
                       int32_t rows, int32_t q_heads, int32_t head_dim, int32_t parts,
-                      int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype);
+                      int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype, int64_t part_stride);
 
 /* The pre-op half of the fused node alone (split, norm, RoPE, append; q_out
  * receives the normed + roped query as bf16 [rows, q_heads, head_dim]), for

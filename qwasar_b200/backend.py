@@ -85,7 +85,7 @@ SIGNATURES = {
                                           _vp, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _f32, C.c_int]),
     "qw_op_attn_batch": (_b, [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _f32, C.c_int]),
     "qw_op_attn_partial": (_b, [_vp] + [QwRef] * 5 + [_i32] * 8 + [_f32, C.c_int]),
-    "qw_op_attn_merge": (None, [_vp] + [QwRef] * 4 + [_i32] * 5 + [C.c_int, C.c_int]),
+    "qw_op_attn_merge": (None, [_vp] + [QwRef] * 4 + [_i32] * 5 + [C.c_int, C.c_int, C.c_int64]),
     "qw_op_attn_preop": (_b, [_vp] + [QwRef] * 11 + [_i32] * 7 + [_f32, C.c_int, _b]),
     "qw_attn_decode_noalloc": (_b, [_vp] * 5 + [_i32] * 6 + [_f32, C.c_int, _vp, C.c_char_p, _sz]),
     "qw_attn_decode_noalloc_scratch_bytes": (_sz, []),

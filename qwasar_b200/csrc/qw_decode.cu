@@ -505,21 +505,22 @@ __global__ void __launch_bounds__(64) qw_attn_merge_kernel(const __grid_constant
 __global__ void __launch_bounds__(64) merge_parts_kernel(void *out, int out_dtype, const float *__restrict__ pacc,
                                                          const float *__restrict__ pstat, const void *gate,
                                                          int gate_dtype, int gate_stride, int n_rh, int parts,
-                                                         float *pacc_out, float *pstat_out) {
+                                                         float *pacc_out, float *pstat_out, size_t acc_stride,
+                                                         size_t stat_stride) {
     const int rh = blockIdx.x;
     const int d4 = threadIdx.x * 4;
     float m = -3.0e38f;
     for (int q = 0; q < parts; q++) {
-        const size_t pi = (size_t)q * n_rh + rh;
-        if (pstat[pi * 2 + 1] > 0.0f) m = fmaxf(m, pstat[pi * 2]);
+        const float *st = pstat + (size_t)q * stat_stride + (size_t)rh * 2;
+        if (st[1] > 0.0f) m = fmaxf(m, st[0]);
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.0f;
     for (int q = 0; q < parts; q++) {
-        const size_t pi = (size_t)q * n_rh + rh;
-        const float l = pstat[pi * 2 + 1];
-        const float w = l > 0.0f ? __expf(pstat[pi * 2] - m) : 0.0f;
-        const float4 a = *reinterpret_cast<const float4 *>(pacc + pi * 256 + d4);
+        const float *st = pstat + (size_t)q * stat_stride + (size_t)rh * 2;
+        const float l = st[1];
+        const float w = l > 0.0f ? __expf(st[0] - m) : 0.0f;
+        const float4 a = *reinterpret_cast<const float4 *>(pacc + (size_t)q * acc_stride + (size_t)rh * 256 + d4);
         den += l * w;
         acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
     }
@@ -671,10 +672,12 @@ void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows) {
 
 void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,
                         const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
-                        float *pacc_out, float *pstat_out) {
+                        float *pacc_out, float *pstat_out, size_t acc_stride, size_t stat_stride) {
     if (n_rows_heads <= 0) return;
+    if (!acc_stride) acc_stride = (size_t)n_rows_heads * 256;
+    if (!stat_stride) stat_stride = (size_t)n_rows_heads * 2;
     merge_parts_kernel<<<n_rows_heads, 64, 0, s>>>(out, out_dtype, pacc, pstat, gate, gate_dtype, gate_stride,
-                                                   n_rows_heads, parts, pacc_out, pstat_out);
+                                                   n_rows_heads, parts, pacc_out, pstat_out, acc_stride, stat_stride);
     g_launches++;
 }
 

@@ -114,7 +114,7 @@ int attn_per_query_splits(int rows, int q_heads, int n_keys);
 // pstat [parts, rows*q_heads, 2] -> out (gated when gate != nullptr).
 void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,
                         const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
-                        float *pacc_out, float *pstat_out);
+                        float *pacc_out, float *pstat_out, size_t acc_stride = 0, size_t stat_stride = 0);
 
 int sm_count();
 

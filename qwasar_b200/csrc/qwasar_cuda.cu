@@ -229,15 +229,17 @@ bool arena_grow(Arena *a, cudaStream_t stream) {
     return true;
 }
 
-// Makes sure the pages that hold tokens [0, n_tokens) of `layer` exist, and pushes new
-// page-table entries to the device in stream order.
-bool arena_ensure(Arena *a, int layer, int n_tokens, cudaStream_t stream) {
+// Makes sure the pages that hold tokens [first_token, n_tokens) of `layer` exist, and pushes new
+// page-table entries to the device in stream order.  Pages below first_token are left alone: a
+// rank that owns only a range of positions maps only that range.
+bool arena_ensure(Arena *a, int layer, int first_token, int n_tokens, cudaStream_t stream) {
     const int need = (n_tokens + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
+    const int first_page = std::max(first_token, 0) / QW_PAGE_TOKENS;
     if (need > a->pages_per_head) { set_error("arena: %d tokens exceed max_ctx %d", n_tokens, a->max_ctx); return false; }
     for (int h = 0; h < a->kv_heads; h++) {
         int32_t *row = a->table_host.data() + ((size_t)layer * a->kv_heads + h) * a->pages_per_head;
         int first_new = -1, last_new = -1;
-        for (int pg = 0; pg < need; pg++) {
+        for (int pg = first_page; pg < need; pg++) {
             if (row[pg] >= 0) continue;
             if (a->free_pages.empty() && !arena_grow(a, stream)) return false;
             row[pg] = a->free_pages.back();
@@ -346,7 +348,7 @@ bool shape_ok(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
 // addressable (pages are mapped up to there when `append`).
 bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int32_t head_dim, int32_t n_tokens,
                    bool append, bool will_write, KvLayer *out, CUtensorMap *map, uint32_t box_rows = 32,
-                   int64_t *map_rows = nullptr) {
+                   int64_t *map_rows = nullptr, int32_t first_token = 0) {
     qw_buf b = ref.buf;
     if (!b) { cmd_fail(c, "cache operand is null"); return false; }
     const size_t layer_bytes = (size_t)kv_heads * max_ctx * head_dim * 2;
@@ -360,7 +362,7 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
         if (ref.off % layer_bytes) { cmd_fail(c, "arena offset %zu is not a layer boundary", ref.off); return false; }
         const int layer = (int)(ref.off / layer_bytes);
         if (layer >= a->n_layers) { cmd_fail(c, "arena layer %d out of range", layer); return false; }
-        if (append && !arena_ensure(a, layer, n_tokens, c->stream)) { cmd_fail(c, "%s", G.last_error); return false; }
+        if (append && !arena_ensure(a, layer, first_token, n_tokens, c->stream)) { cmd_fail(c, "%s", G.last_error); return false; }
         out->base = reinterpret_cast<__nv_bfloat16 *>(a->va);
         out->table = a->table_dev + (size_t)layer * a->kv_heads * a->pages_per_head;
         out->pt_stride = a->pages_per_head;
@@ -669,7 +671,7 @@ static bool kv_rw(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32
     if (cache->kind == BUF_ARENA) {
         Arena *a = cache->arena;
         if (a->kv_heads != kv_heads || a->max_ctx != max_ctx || layer < 0 || layer >= a->n_layers) { set_error("qw_kv_read/store: shape differs from the arena's"); return false; }
-        if (store && !arena_ensure(a, layer, pos0 + n, 0)) return false;
+        if (store && !arena_ensure(a, layer, pos0, pos0 + n, 0)) return false;
         const int32_t *tab = a->table_host.data() + ((size_t)layer * a->kv_heads + head) * a->pages_per_head;
         int t = pos0;
         char *hp = (char *)host;
@@ -903,8 +905,8 @@ extern "C" void qw_op_kv_write(qw_cmd c, qw_ref kcache, qw_ref vcache, qw_ref k,
     if (head_dim != QW_HEAD_DIM) { fprintf(stderr, "qwasar: kv_write head_dim %d unsupported (kernel is built for 256)\n", head_dim); return; }
     if (kv_heads <= 0 || base_pos < 0 || (int64_t)base_pos + rows > max_ctx) { cmd_fail(c, "kv_write: positions [%d, %d) outside the cache", base_pos, base_pos + rows); return; }
     KvLayer kc, vc;
-    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &kc, nullptr)) return;
-    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &vc, nullptr)) return;
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &kc, nullptr, 32, nullptr, base_pos)) return;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, base_pos + rows, true, true, &vc, nullptr, 32, nullptr, base_pos)) return;
     const size_t n = (size_t)rows * kv_heads * head_dim * 4;
     const float *pk = (const float *)dev_range(c, k, n, false), *pv = (const float *)dev_range(c, v, n, false);
     if (!pk || !pv) return;
@@ -1075,8 +1077,8 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
             ps.k = dev_range(c, s[i].k, (size_t)rows * kv_heads * 256 * el, false);
             ps.v = dev_range(c, s[i].v, (size_t)rows * kv_heads * 256 * el, false);
             if (!ps.k || !ps.v) return false;
-            if (!resolve_cache(c, s[i].kcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.kc, nullptr)) return false;
-            if (!resolve_cache(c, s[i].vcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.vc, nullptr)) return false;
+            if (!resolve_cache(c, s[i].kcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.kc, nullptr, 32, nullptr, s[i].base_pos)) return false;
+            if (!resolve_cache(c, s[i].vcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.vc, nullptr, 32, nullptr, s[i].base_pos)) return false;
         }
         ps.q_out = q_out[i];
         ps.rows = rows; ps.base_pos = s[i].base_pos;
@@ -1242,15 +1244,18 @@ extern "C" bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q
 }
 
 extern "C" void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate, int32_t rows, int32_t q_heads,
-                                 int32_t head_dim, int32_t parts, int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype) {
-    if (!live(c) || rows <= 0 || q_heads <= 0 || parts <= 0 || head_dim != QW_HEAD_DIM) return;
+                                 int32_t head_dim, int32_t parts, int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype,
+                                 int64_t part_stride) {
+    if (!live(c) || rows <= 0 || q_heads <= 0 || parts <= 0 || head_dim != QW_HEAD_DIM || part_stride < 0) return;
     const size_t n_rh = (size_t)rows * q_heads;
-    const float *pa = (const float *)dev_range(c, pacc, (size_t)parts * n_rh * 256 * 4, false);
-    const float *ps = (const float *)dev_range(c, pstat, (size_t)parts * n_rh * 2 * 4, false);
+    const size_t a_stride = part_stride ? (size_t)part_stride : n_rh * 256, s_stride = part_stride ? (size_t)part_stride : n_rh * 2;
+    const float *pa = (const float *)dev_range(c, pacc, ((size_t)(parts - 1) * a_stride + n_rh * 256) * 4, false);
+    const float *ps = (const float *)dev_range(c, pstat, ((size_t)(parts - 1) * s_stride + n_rh * 2) * 4, false);
     void *po = dev_range(c, out, n_rh * 256 * (out_dtype == QW_BF16 ? 2 : 4), true);
     const size_t g_el = gate_dtype == QW_BF16 ? 2 : 4;
     const void *pg = gate.buf ? dev_range(c, gate, ((n_rh - 1) * gate_stride + 256) * g_el, false) : nullptr;
     if (!pa || !ps || !po || (gate.buf && !pg)) return;
-    launch_merge_parts(c->stream, po, (int)out_dtype, pa, ps, pg, (int)gate_dtype, gate_stride, (int)n_rh, parts, nullptr, nullptr);
+    launch_merge_parts(c->stream, po, (int)out_dtype, pa, ps, pg, (int)gate_dtype, gate_stride, (int)n_rh, parts, nullptr, nullptr,
+                       a_stride, s_stride);
     cuda_ok(c, cudaGetLastError(), "merge launch");
 }

@@ -35,7 +35,7 @@ def test_partials_merge_to_whole(be, oracle, rows, qh, kvh, base, cuts):
             assert be.op_attn_partial(c, QwRef(pa, i * n_rh * 256 * 4), QwRef(ps, i * n_rh * 2 * 4), QwRef(qb, 0),
                                       QwRef(kcb, 0), QwRef(vcb, 0), rows, qh, kvh, 256, ctx, base, cuts[i],
                                       cuts[i + 1], 0.0625, F32)
-        be.op_attn_merge(c, QwRef(ob, 0), QwRef(pa, 0), QwRef(ps, 0), QwRef(gb, 0), rows, qh, 256, parts, 256, F32, F32)
+        be.op_attn_merge(c, QwRef(ob, 0), QwRef(pa, 0), QwRef(ps, 0), QwRef(gb, 0), rows, qh, 256, parts, 256, F32, F32, 0)
         be.cmd_wait(c); be.cmd_free(c)
         got = np.array(ov); stats = np.array(psv)
     want = oracle.mul_sigmoid(oracle.attn_decode(q, kc, vc, rows, qh, kvh, 256, ctx, base, 0.0625), gate)

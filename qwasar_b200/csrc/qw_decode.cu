@@ -476,8 +476,7 @@ __global__ void __launch_bounds__(64) qw_attn_merge_kernel(const __grid_constant
     if (p.mode == 1) {
         // leave one combined partial per (row, head) for the exchange between GPUs
         const size_t ci = (size_t)sq.row_slot0 * p.q_heads + rh;
-        float *ca = p.pacc + (size_t)attn_split_slots(p) * (MT * 16) * 256;      // combined area follows the slots
-        float *cs = p.pstat + (size_t)attn_split_slots(p) * (MT * 16) * 2;
+        float *ca = p.comb_acc, *cs = p.comb_stat;
         *reinterpret_cast<float4 *>(ca + ci * 256 + d4) = acc;
         if (threadIdx.x == 0) { cs[ci * 2] = den > 0.0f ? m : -3.0e38f; cs[ci * 2 + 1] = den; }
         return;

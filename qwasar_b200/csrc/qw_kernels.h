@@ -80,6 +80,7 @@ struct AttnParams {
     int32_t mode;            // 0: write normalised (gated) output; 1: always leave partials (m, l, acc)
     float scale;
     float *pacc, *pstat;     // partial scratch: [slot, MT*16, 256] and [slot, MT*16, 2]
+    float *comb_acc, *comb_stat;   // mode 1: where the one combined partial per (row, head) goes
     int *status;
 };
 // rows_per_seq * gqa <= 64.  The number of partial slots a launch may write: a (CTA, group)

@@ -2,26 +2,24 @@
 // tensor memory, operands staged by TMA (sm_100a).
 //
 // One CTA per (128-row query tile, query head).  K and V are read from the cache (the rows
-// of this chunk were appended just before), 64 keys -- one arena page -- per step, each
-// double-buffered in shared memory:
+// of this chunk were appended just before), 128 keys per step:
 //
-//   warp 5   TMA: K tiles   (4 SWIZZLE_128B boxes of 64 keys x 64 dims each, 3 stages)
-//   warp 6   TMA: V tiles   (likewise)
-//   warp 4   one thread issues tcgen05.mma:  S_b = Q K_j^T   (TS, M128 N64  K16 x 16, Q in TMEM)
-//                                            O  += P_j V_j   (TS, M128 N256 K16 x 4,  P in TMEM)
-//   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Reads S (fp32) from TMEM,
-//            online max / sum in the exp2 domain, writes P (bf16) back over S, rescales O in
-//            TMEM only when a row's max grew by more than 2^8 (the stale max is exact
-//            arithmetic, just a different common factor), and at the end normalises, applies
-//            the sigmoid output gate and stores the row.
+//   warp 5   TMA: K tiles   (two stages of 128 keys x 256 dims; 8 SWIZZLE_128B boxes of one page half each)
+//   warp 6   TMA: V pages   (two stages of 64 keys x 256 dims: the two halves of a step)
+//   warp 4   one thread issues tcgen05.mma:  S  = Q K_j^T   (TS, M128 N128 K16 x 16, Q in TMEM)
+//                                            O += P_j V_j   (SS, M128 N256 K16 x 8,  P in shared memory)
+//   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Reads its 128 scores from TMEM
+//            into registers and hands S back at once (so Q K_{j+1}^T runs under this step's
+//            exponentials), online max / sum in the exp2 domain, writes P (bf16) into shared
+//            memory in the tensor core's swizzled K-major layout, rescales O in TMEM only when a
+//            row's max grew by more than 2^8, and at the end normalises, applies the sigmoid
+//            output gate and stores the row.
 //
-// TMEM columns (512): O [0,256) fp32 | Q [256,384) bf16 pairs | S0 [384,448) | S1 [448,512);
-// P_b aliases the first 32 columns of S_b.  The query tile lives in tensor memory, not shared
-// memory: as the A operand of every Q K^T it would otherwise be re-read from shared memory for
-// each key tile (64 KB per 64 keys, as much as K and V together), and shared-memory bandwidth,
-// not the tensor pipe, would bound the kernel.  Each softmax thread loads its own row of Q
-// once and stores it to its TMEM lane.  S is double-buffered so that Q K_{j+1}^T runs under
-// the softmax of tile j; K and V have three stages each so that loads run well ahead.
+// TMEM columns (512): O [0,256) fp32 | Q [256,384) bf16 pairs | S [384,512) fp32.  The query tile
+// lives in tensor memory: as a shared-memory A operand it would be re-read for every key tile
+// (as many bytes as K), and each softmax thread can store its own row there once.  Steps are 128
+// keys wide because one thread issues every tcgen05.mma at roughly one per 65 clocks: a 64-key
+// Q K^T step (32 clocks of tensor work) would be issue-bound.
 // Every wait on an mbarrier is bounded (qw_common.cuh): a stuck pipeline ends the kernel with
 // a status code instead of hanging the GPU, and TMEM is always released.
 //
@@ -32,20 +30,24 @@ namespace qw {
 
 namespace {
 
-constexpr int BM = 128, BN = 64;
-constexpr int NKV = 3;                                // shared-memory stages of K and of V
-constexpr int KV_BYTES = BN * 512;                    // 64 keys x 256 dims bf16
-constexpr int KVBOX = BN * 128;                       // one 64-dim box of a K or V tile
-constexpr int OFF_K = 0, OFF_V = NKV * KV_BYTES, OFF_BAR = 2 * NKV * KV_BYTES;
+constexpr int BM = 128, BN = 128;                     // query rows per CTA, keys per step
+constexpr int K_BYTES = BN * 512;                     // 128 keys x 256 dims bf16
+constexpr int KBOX = BN * 128;                        // one 64-dim box of a K tile (128 rows)
+constexpr int V_BYTES = 64 * 512;                     // a V stage is one 64-key page
+constexpr int VBOX = 64 * 128;
+constexpr int P_BYTES = BM * BN * 2;                  // bf16 weights of one step, as an A operand
+constexpr int PBOX = BM * 128;                        // 64 keys of every row
+constexpr int OFF_K = 0, OFF_V = 2 * K_BYTES, OFF_P = OFF_V + 2 * V_BYTES, OFF_BAR = OFF_P + P_BYTES;
 constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;    // TMEM columns
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
 constexpr int THREADS = 7 * 32;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
-enum Bar { Q_READY = 0, K_FULL0, K_FULL1, K_FULL2, V_FULL0, V_FULL1, V_FULL2, K_FREE0, K_FREE1, K_FREE2,
-           V_FREE0, V_FREE1, V_FREE2, S_READY0, S_READY1, P_READY0, P_READY1, PV_DONE, N_BARS };
+enum Bar { Q_READY = 0, K_FULL0, K_FULL1, K_FREE0, K_FREE1, V_FULL0, V_FULL1, V_FREE0, V_FREE1,
+           S_READY, S_FREE, P_READY, PV_DONE, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -81,6 +83,21 @@ __device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, uint32_t bde
             "{\n\t.reg .pred p;\n\t.reg .b64 bd;\n\tsetp.ne.u32 p, 0, 0;\n\tmov.b64 bd, {%2, %3};\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], bd, %4, p;\n\t}"
             ::"r"(d), "r"(a_tmem), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+template <bool ACC>
+__device__ __forceinline__ void mma_ss(uint32_t d, uint32_t adesc_lo, uint32_t adesc_hi, uint32_t bdesc_lo, uint32_t bdesc_hi,
+                                       uint32_t idesc) {
+    if (ACC)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\tsetp.eq.u32 p, 0, 0;\n\tmov.b64 ad, {%1, %2};\n\tmov.b64 bd, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, p;\n\t}"
+            ::"r"(d), "r"(adesc_lo), "r"(adesc_hi), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc) : "memory");
+    else
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\tsetp.ne.u32 p, 0, 0;\n\tmov.b64 ad, {%1, %2};\n\tmov.b64 bd, {%3, %4};\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], ad, bd, %5, p;\n\t}"
+            ::"r"(d), "r"(adesc_lo), "r"(adesc_hi), "r"(bdesc_lo), "r"(bdesc_hi), "r"(idesc) : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t addr, uint32_t (&r)[32]) {
     asm volatile(
@@ -148,7 +165,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     const int n_t = (k_end + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY0 || i == P_READY1 || i == Q_READY) ? 128 : 1);
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY || i == S_FREE || i == Q_READY) ? 128 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -157,31 +174,44 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_o = tmem + COL_O, t_q = tmem + COL_Q, t_s0 = tmem + COL_S;
+    const uint32_t t_o = tmem + COL_O, t_q = tmem + COL_Q, t_s = tmem + COL_S;
 
-    if (warp == 5 || warp == 6) {
-        // ---------------- warp 5: K tiles; warp 6: V tiles ----------------
+    // first row of the tensor map that holds page `pg` of this kv head (or a row past the map: zero fill)
+    auto page_row = [&](const KvLayer &L, int pg) -> int32_t {
+        if (L.table) {
+            const int id = pg < L.pt_stride ? __ldg(L.table + (size_t)kvh * L.pt_stride + pg) : -1;
+            return id >= 0 ? id * QW_PAGE_TOKENS : p.oob_row;
+        }
+        return pg * QW_PAGE_TOKENS < L.max_ctx ? kvh * L.max_ctx + pg * QW_PAGE_TOKENS : p.oob_row;
+    };
+
+    if (warp == 5) {
+        // ---------------- K tiles: two pages each, rows 0-63 and 64-127 of every 64-dim box ----------------
         if (lane == 0) {
-            const bool is_k = warp == 5;
-            const KvLayer &L = is_k ? p.kc : p.vc;
-            const CUtensorMap *map = is_k ? &p.kmap : &p.vmap;
-            const int FULL = is_k ? K_FULL0 : V_FULL0, FREE = is_k ? K_FREE0 : V_FREE0;
-            uint8_t *base = smem + (is_k ? OFF_K : OFF_V);
             for (int j = 0; j < n_t; j++) {
-                const int st = j % NKV;
-                const int t = j * BN;
-                int64_t row;
-                if (L.table) {
-                    const int pg = j < L.pt_stride ? __ldg(L.table + (size_t)kvh * L.pt_stride + j) : -1;
-                    row = pg >= 0 ? (int64_t)pg * QW_PAGE_TOKENS : (int64_t)p.oob_row;   // unmapped: zero fill
-                } else {
-                    row = t < L.max_ctx ? (int64_t)kvh * L.max_ctx + t : (int64_t)p.oob_row;
+                const int st = j & 1;
+                const int32_t r0 = page_row(p.kc, 2 * j), r1 = page_row(p.kc, 2 * j + 1);
+                if (j >= 2) mbar_wait(&bars[K_FREE0 + st], ((j >> 1) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                mbar_expect_tx(&bars[K_FULL0 + st], K_BYTES);
+                uint8_t *dst = smem + OFF_K + st * K_BYTES;
+#pragma unroll
+                for (int b = 0; b < 4; b++) {
+                    tma_load_2d(dst + b * KBOX, &p.kmap, b * 64, r0, &bars[K_FULL0 + st]);
+                    tma_load_2d(dst + b * KBOX + 8192, &p.kmap, b * 64, r1, &bars[K_FULL0 + st]);
                 }
-                if (j >= NKV) mbar_wait(&bars[FREE + st], ((j / NKV) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
-                mbar_expect_tx(&bars[FULL + st], KV_BYTES);
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------- V pages ----------------
+        if (lane == 0) {
+            for (int pg = 0; pg < 2 * n_t; pg++) {
+                const int st = pg & 1;
+                const int32_t r = page_row(p.vc, pg);
+                if (pg >= 2) mbar_wait(&bars[V_FREE0 + st], ((pg >> 1) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                mbar_expect_tx(&bars[V_FULL0 + st], V_BYTES);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
-                    tma_load_2d(base + st * KV_BYTES + b * KVBOX, map, b * 64, (int32_t)row, &bars[FULL + st]);
+                    tma_load_2d(smem + OFF_V + st * V_BYTES + b * VBOX, &p.vmap, b * 64, r, &bars[V_FULL0 + st]);
             }
         }
     } else if (warp == 4) {
@@ -189,40 +219,47 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(128, BN, 0);
             constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
-            const uint32_t k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V);
             constexpr uint32_t hi = desc_hi(1024);
+            const uint32_t k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V), p_a = smem_u32(smem + OFF_P);
+            const uint32_t p_lo = desc_lo(p_a, 16);
             auto issue_qk = [&](int j) {
-                const int st = j % NKV;
-                mbar_wait(&bars[K_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                const int st = j & 1;
+                mbar_wait(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
-                const uint32_t t_s = t_s0 + (j & 1) * BN;
-                const uint32_t k_lo = desc_lo(k_a + st * KV_BYTES, 16);
+                const uint32_t k_lo = desc_lo(k_a + st * K_BYTES, 16);
                 // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes (2 units) inside the swizzle atom,
-                // 64 dims per box (KVBOX / 16 units)
+                // 64 dims per box (KBOX / 16 units)
                 mma_ts<false>(t_s, t_q, k_lo, hi, idesc_qk);
 #pragma unroll
                 for (int ks = 1; ks < 16; ks++)
-                    mma_ts<true>(t_s, t_q + ks * 8, k_lo + (ks >> 2) * (KVBOX >> 4) + (ks & 3) * 2, hi, idesc_qk);
-                tc_commit(&bars[S_READY0 + (j & 1)]);
+                    mma_ts<true>(t_s, t_q + ks * 8, k_lo + (ks >> 2) * (KBOX >> 4) + (ks & 3) * 2, hi, idesc_qk);
+                tc_commit(&bars[S_READY]);
                 tc_commit(&bars[K_FREE0 + st]);
             };
             mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             issue_qk(0);
             for (int j = 0; j < n_t; j++) {
-                const int st = j % NKV;
-                if (j + 1 < n_t) issue_qk(j + 1);
-                mbar_wait(&bars[P_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-                mbar_wait(&bars[V_FULL0 + st], (j / NKV) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-                tc_fence_after();
-                const uint32_t t_p = t_s0 + (j & 1) * BN;      // P aliases the head of S
-                const uint32_t v_lo = desc_lo(v_a + st * KV_BYTES, KVBOX);
-                // 16 keys per step: 8 TMEM columns of bf16 pairs, 2048 bytes (128 units) of V
-                if (j > 0) mma_ts<true>(t_o, t_p, v_lo, hi, idesc_pv);
-                else mma_ts<false>(t_o, t_p, v_lo, hi, idesc_pv);
+                if (j + 1 < n_t) {
+                    // S is handed back as soon as the softmax threads hold it in registers
+                    mbar_wait(&bars[S_FREE], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                    issue_qk(j + 1);
+                }
+                mbar_wait(&bars[P_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
 #pragma unroll
-                for (int ks = 1; ks < BN / 16; ks++) mma_ts<true>(t_o, t_p + ks * 8, v_lo + ks * 128, hi, idesc_pv);
+                for (int h = 0; h < 2; h++) {                  // the two 64-key pages of the step
+                    mbar_wait(&bars[V_FULL0 + h], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                    tc_fence_after();
+                    const uint32_t v_lo = desc_lo(v_a + h * V_BYTES, VBOX);
+#pragma unroll
+                    for (int ks = 0; ks < 4; ks++) {
+                        // A: 16 keys of P = 32 bytes inside the swizzle atom, 64 keys per box; B: 16 keys of V = 2048 bytes
+                        const uint32_t a_lo = p_lo + h * (PBOX >> 4) + ks * 2;
+                        if (j > 0 || h > 0 || ks > 0) mma_ss<true>(t_o, a_lo, hi, v_lo + ks * 128, hi, idesc_pv);
+                        else mma_ss<false>(t_o, a_lo, hi, v_lo + ks * 128, hi, idesc_pv);
+                    }
+                    tc_commit(&bars[V_FREE0 + h]);
+                }
                 tc_commit(&bars[PV_DONE]);
-                tc_commit(&bars[V_FREE0 + st]);
             }
         }
     } else {
@@ -251,74 +288,81 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             tc_fence_before();
             mbar_arrive(&bars[Q_READY]);
         }
+        // P row in shared memory: box = 64 keys, 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
+        uint8_t *p_row = smem + OFF_P + row_l * 128;
+        const uint32_t sw = row_l & 7;
         for (int j = 0; j < n_t; j++) {
-            const uint32_t t_s = t_s0 + (j & 1) * BN + lane_base;
-            mbar_wait(&bars[S_READY0 + (j & 1)], (j >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+            mbar_wait(&bars[S_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             tc_fence_after();
             const bool need_mask = j * BN + BN - 1 > p.base_pos + q0;
-            // the row's 64 scores, read once
-            uint32_t sa[32], sb[32];
-            tmem_ld32(t_s, sa);
-            tmem_ld32(t_s + 32, sb);
+            // the row's 128 scores, read once; S goes back to the tensor core at once
+            uint32_t s0[32], s1[32], s2[32], s3[32];
+            tmem_ld32(t_s + lane_base, s0);
+            tmem_ld32(t_s + lane_base + 32, s1);
+            tmem_ld32(t_s + lane_base + 64, s2);
+            tmem_ld32(t_s + lane_base + 96, s3);
             tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&bars[S_FREE]);
             if (need_mask) {
 #pragma unroll
                 for (int e = 0; e < 32; e++) {
-                    if (j * BN + e > limit) sa[e] = __float_as_uint(NEG_BIG);
-                    if (j * BN + 32 + e > limit) sb[e] = __float_as_uint(NEG_BIG);
+                    if (j * BN + e > limit) s0[e] = __float_as_uint(NEG_BIG);
+                    if (j * BN + 32 + e > limit) s1[e] = __float_as_uint(NEG_BIG);
+                    if (j * BN + 64 + e > limit) s2[e] = __float_as_uint(NEG_BIG);
+                    if (j * BN + 96 + e > limit) s3[e] = __float_as_uint(NEG_BIG);
                 }
             }
-            float mx = NEG_BIG;
+            float mxa = NEG_BIG, mxb = NEG_BIG;
 #pragma unroll
-            for (int e = 0; e < 32; e++) mx = fmaxf(mx, fmaxf(__uint_as_float(sa[e]), __uint_as_float(sb[e])));
-            const float mx2 = fmaxf(mx * sc2, NEG_BIG);
-            if (j == 0) {
-                m = mx2;
-            } else {
-                const bool grow = mx2 - m > RESCALE_AT;
-                if (__any_sync(0xffffffffu, grow)) {
-                    // O must hold every product issued so far before it is rescaled
-                    mbar_wait(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-                    tc_fence_after();
-                    const float alpha = grow ? ex2(m - mx2) : 1.0f;
+            for (int e = 0; e < 32; e++) {
+                mxa = fmaxf(mxa, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
+                mxb = fmaxf(mxb, fmaxf(__uint_as_float(s2[e]), __uint_as_float(s3[e])));
+            }
+            const float mx2 = fmaxf(fmaxf(mxa, mxb) * sc2, NEG_BIG);
+            const bool grow = j > 0 && mx2 - m > RESCALE_AT;
+            const float alpha = grow ? ex2(m - mx2) : 1.0f;
+            if (j == 0 || grow) m = mx2;
+            // weights (masked scores are NEG_BIG: their weight underflows to exactly 0), packed in place
+            float la = 0.0f, lb = 0.0f;
+            auto weights = [&](uint32_t(&s)[32], float &acc) {
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    const float x0 = ex2(fmaf(__uint_as_float(s[e]), sc2, -m));
+                    const float x1 = ex2(fmaf(__uint_as_float(s[e + 1]), sc2, -m));
+                    acc += x0 + x1;
+                    s[e >> 1] = pack_bf16(x0, x1);      // slot e/2 <= e: already consumed
+                }
+            };
+            weights(s0, la); weights(s1, lb); weights(s2, la); weights(s3, lb);
+            l = l * alpha + (la + lb);
+            // P_{j-1} must have been consumed (and O complete) before P is overwritten or O rescaled
+            if (j > 0) {
+                mbar_wait(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                tc_fence_after();
+            }
+            if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                    for (int c = 0; c < 8; c++) {
-                        tmem_ld32(t_o + lane_base + c * 32, v);
-                        tmem_wait_ld();
+                for (int c = 0; c < 8; c++) {
+                    tmem_ld32(t_o + lane_base + c * 32, v);
+                    tmem_wait_ld();
 #pragma unroll
-                        for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                        tmem_st32(t_o + lane_base + c * 32, v);
-                    }
-                    tmem_wait_st();
-                    l *= alpha;
-                    if (grow) m = mx2;
+                    for (int e = 0; e < 32; e++) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                    tmem_st32(t_o + lane_base + c * 32, v);
                 }
+                tmem_wait_st();
             }
-            // weights, their sum, and P (bf16) written over the head of S; masked scores are
-            // NEG_BIG, whose weight underflows to exactly 0
-            uint32_t pk[32];
-            float l0 = 0.0f, l1 = 0.0f;
+            // 16 packed pairs per 32 scores = 4 chunks of 16 bytes; keys 0-63 in box 0, 64-127 in box 1
+            auto store_p = [&](const uint32_t(&s)[32], int box, int chunk0) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-                const float x0 = ex2(fmaf(__uint_as_float(sa[e]), sc2, -m));
-                const float x1 = ex2(fmaf(__uint_as_float(sa[e + 1]), sc2, -m));
-                const float y0 = ex2(fmaf(__uint_as_float(sb[e]), sc2, -m));
-                const float y1 = ex2(fmaf(__uint_as_float(sb[e + 1]), sc2, -m));
-                l0 += x0 + x1;
-                l1 += y0 + y1;
-                pk[e >> 1] = pack_bf16(x0, x1);
-                pk[16 + (e >> 1)] = pack_bf16(y0, y1);
-            }
-            l += l0 + l1;
-            tmem_st32(t_s, pk);
-            tmem_wait_st();
-            // Observe every phase of PV_DONE: a parity wait is only meaningful for a waiter at most
-            // one phase behind, and the epilogue (or a later rescale) waits on this barrier again.
-            // P V_{j-1} was issued long before this point, and P V_j cannot be issued until every
-            // row has arrived below, so the barrier cannot run ahead of this wait.
-            if (j > 0) mbar_wait(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4 *>(p_row + box * PBOX + (((chunk0 + c) ^ sw) << 4)) =
+                        make_uint4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+            };
+            store_p(s0, 0, 0); store_p(s1, 0, 4); store_p(s2, 1, 0); store_p(s3, 1, 4);
+            fence_proxy_async();          // generic-proxy writes -> visible to the tensor core's reads
             tc_fence_before();
-            mbar_arrive(&bars[P_READY0 + (j & 1)]);
+            mbar_arrive(&bars[P_READY]);
         }
         // epilogue
         mbar_wait(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);

@@ -1234,13 +1234,9 @@ extern "C" bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q
     sq.q = dev_range(c, q, n_rh * 256 * (q_dtype == QW_BF16 ? 2 : 4), false);
     if (!sq.q) return false;
     sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = key_lo; sq.key_hi = key_hi;
-    if (!run_split(c, p, rows)) return false;
-    // the combined partials follow the slots in the scratch block: hand them to the caller
-    const int mt16 = ((rows * gqa + 15) / 16 <= 1 ? 1 : ((rows * gqa + 15) / 16 <= 2 ? 2 : 4)) * 16;
-    const size_t slot_rows = (size_t)attn_split_slots(p) * mt16;
-    cuda_ok(c, cudaMemcpyAsync(pa, p.pacc + slot_rows * 256, n_rh * 256 * 4, cudaMemcpyDeviceToDevice, c->stream), "copy");
-    cuda_ok(c, cudaMemcpyAsync(ps, p.pstat + slot_rows * 2, n_rh * 2 * 4, cudaMemcpyDeviceToDevice, c->stream), "copy");
-    return !c->failed;
+    p.comb_acc = pa;          // the merge leaves the one combined partial per (row, head) here
+    p.comb_stat = ps;
+    return run_split(c, p, rows);
 }
 
 extern "C" void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate, int32_t rows, int32_t q_heads,

@@ -185,9 +185,21 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         return pg * QW_PAGE_TOKENS < L.max_ctx ? kvh * L.max_ctx + pg * QW_PAGE_TOKENS : p.oob_row;
     };
 
+    if ((warp == 5 || warp == 6) && lane > 0 && p.gate) {
+        // idle lanes: pull this tile's gate rows into L2 while the main loop runs (the epilogue reads them)
+        const size_t el = p.gate_dtype == DT_BF16 ? 2 : 4;
+        const int n_valid = min(BM, p.rows - q0);
+        const int lines = (int)(256 * el / 128);                     // 128-byte lines per row
+        for (int i = (warp - 5) * 31 + lane - 1; i < n_valid * lines; i += 62) {
+            const int r = i / lines, ln = i - r * lines;
+            const char *a = reinterpret_cast<const char *>(p.gate) + (((size_t)(q0 + r) * p.q_heads + head) * p.gate_stride) * el + ln * 128;
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+        }
+    }
     if (warp == 5) {
         // ---------------- K tiles: two pages each, rows 0-63 and 64-127 of every 64-dim box ----------------
         if (lane == 0) {
+            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the Q staging borrowed this region
             for (int j = 0; j < n_t; j++) {
                 const int st = j & 1;
                 const int32_t r0 = page_row(p.kc, 2 * j), r1 = page_row(p.kc, 2 * j + 1);
@@ -273,20 +285,31 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         float m = NEG_BIG, l = 0.0f;
         uint32_t v[32];
         {
-            // this row of Q (256 bf16 = 128 columns of pairs) into the row's TMEM lane
-            const uint4 *src = reinterpret_cast<const uint4 *>(p.q + ((size_t)row_g * p.q_heads + head) * 256);
+            // The Q tile: coalesced 16-byte loads by all 128 threads into shared memory (rows padded
+            // to 528 bytes so that 32 lanes reading 32 different rows spread over the banks), then
+            // every thread moves its own row (256 bf16 = 128 columns of pairs) into its TMEM lane.
+            uint8_t *stage = smem + OFF_K;
+            const uint4 *qsrc = reinterpret_cast<const uint4 *>(p.q);
+#pragma unroll 16
+            for (int k = 0; k < 32; k++) {
+                const int idx = row_l + 128 * k, r = idx >> 5, ch = idx & 31;
+                uint4 x = make_uint4(0, 0, 0, 0);
+                if (q0 + r < p.rows) x = __ldg(qsrc + ((size_t)(q0 + r) * p.q_heads + head) * 32 + ch);
+                *reinterpret_cast<uint4 *>(stage + r * 528 + ch * 16) = x;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
-                    const uint4 x = valid ? __ldg(src + c * 8 + e) : make_uint4(0, 0, 0, 0);
+                    const uint4 x = *reinterpret_cast<const uint4 *>(stage + row_l * 528 + (c * 8 + e) * 16);
                     v[e * 4] = x.x; v[e * 4 + 1] = x.y; v[e * 4 + 2] = x.z; v[e * 4 + 3] = x.w;
                 }
                 tmem_st32(t_q + lane_base + c * 32, v);
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[Q_READY]);
+            mbar_arrive(&bars[Q_READY]);      // also releases the K region to the TMA producer
         }
         // P row in shared memory: box = 64 keys, 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
         uint8_t *p_row = smem + OFF_P + row_l * 128;
@@ -364,35 +387,71 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             tc_fence_before();
             mbar_arrive(&bars[P_READY]);
         }
-        // epilogue
+        // epilogue: every thread drops its normalised O row into shared memory (the K/V stages are
+        // idle now; rows padded to 1040 bytes), then the 128 threads walk the rows together so
+        // that the gate is read and the output written in whole coalesced rows.  The gate loads
+        // of 16 rows are in flight together, and the first 16 are issued before the wait for the
+        // last product: under the K/V stream of the other SMs a global load takes microseconds,
+        // and the epilogue must not pay that latency once per row.
+        const int n_valid = min(BM, p.rows - q0);
+        const int d2 = row_l * 2;                                       // this thread's two dims of every row
+        constexpr int NB = 16;                                          // rows per batch
+        float g0[NB], g1[NB];
+        auto load_gates = [&](int r0) {
+            if (!p.gate) return;
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const int r = min(r0 + i, n_valid - 1);
+                const size_t gi = ((size_t)(q0 + r) * p.q_heads + head) * p.gate_stride + d2;
+                if (p.gate_dtype == DT_BF16) {
+                    const __nv_bfloat162 g = __ldg(reinterpret_cast<const __nv_bfloat162 *>(reinterpret_cast<const __nv_bfloat16 *>(p.gate) + gi));
+                    g0[i] = __low2float(g); g1[i] = __high2float(g);
+                } else {
+                    const float2 g = __ldg(reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(p.gate) + gi));
+                    g0[i] = g.x; g1[i] = g.y;
+                }
+            }
+        };
+        auto store_rows = [&](int r0) {
+#pragma unroll
+            for (int i = 0; i < NB; i++) {
+                const int r = r0 + i;
+                if (r < n_valid) {
+                    float2 o = *reinterpret_cast<const float2 *>(smem + OFF_K + (size_t)r * 1040 + d2 * 4);
+                    if (p.gate) {
+                        o.x = __fdividef(o.x, 1.0f + __expf(-g0[i]));
+                        o.y = __fdividef(o.y, 1.0f + __expf(-g1[i]));
+                    }
+                    const size_t rh = (size_t)(q0 + r) * p.q_heads + head;
+                    if (p.out_dtype == DT_BF16)
+                        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + rh * 256 + d2) = pack_bf16(o.x, o.y);
+                    else
+                        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.out) + rh * 256 + d2) = o;
+                }
+            }
+        };
+        load_gates(0);
         mbar_wait(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
         tc_fence_after();
-        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-        const size_t rh = (size_t)row_g * p.q_heads + head;
+        {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            float *orow = reinterpret_cast<float *>(smem + OFF_K + (size_t)row_l * 1040);
 #pragma unroll 1
-        for (int c = 0; c < 8; c++) {
-            tmem_ld32(t_o + lane_base + c * 32, v);
-            tmem_wait_ld();
-            if (valid) {
-                float o[32];
+            for (int c = 0; c < 8; c++) {
+                tmem_ld32(t_o + lane_base + c * 32, v);
+                tmem_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; e++) o[e] = __uint_as_float(v[e]) * inv;
-                if (p.gate) {
-                    const size_t gi = rh * p.gate_stride + c * 32;
-#pragma unroll
-                    for (int e = 0; e < 32; e++) o[e] *= 1.0f / (1.0f + __expf(-load_gate(p.gate, gi + e, p.gate_dtype)));
-                }
-                if (p.out_dtype == DT_BF16) {
-                    uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + rh * 256 + c * 32);
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; q4++)
-                        dst[q4] = make_uint4(pack_bf16(o[q4 * 8], o[q4 * 8 + 1]), pack_bf16(o[q4 * 8 + 2], o[q4 * 8 + 3]),
-                                             pack_bf16(o[q4 * 8 + 4], o[q4 * 8 + 5]), pack_bf16(o[q4 * 8 + 6], o[q4 * 8 + 7]));
-                } else {
-                    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + rh * 256 + c * 32);
-#pragma unroll
-                    for (int q4 = 0; q4 < 8; q4++) dst[q4] = make_float4(o[q4 * 4], o[q4 * 4 + 1], o[q4 * 4 + 2], o[q4 * 4 + 3]);
-                }
+                for (int e = 0; e < 32; e += 4)
+                    *reinterpret_cast<float4 *>(orow + c * 32 + e) =
+                        make_float4(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv,
+                                    __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            store_rows(0);
+#pragma unroll 1
+            for (int r0 = NB; r0 < n_valid; r0 += NB) {
+                load_gates(r0);
+                store_rows(r0);
             }
         }
     }

@@ -104,6 +104,9 @@ struct PrefillParams {
     int *status;
 };
 void launch_attn_prefill(cudaStream_t s, const PrefillParams &p);
+// The same attention with the two query heads 2u, 2u+1 of a row tile as one CTA pair (even grouping only).
+bool attn_prefill_pair_ok(const PrefillParams &p);
+void launch_attn_prefill_pair(cudaStream_t s, const PrefillParams &p);
 
 // Per-query fp32 kernel (CUDA cores, no rounding of q or of the weights).
 void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale,
@@ -125,5 +128,7 @@ extern unsigned long long g_launches;
 extern int g_tune_split_kg;
 // 1: many-row attention runs on the tcgen05 kernel; 0: on the split-KV kernel over row chunks.
 extern int g_tune_prefill_tc;
+// 1: the tcgen05 prefill runs as CTA pairs (cta_group::2) where the grouping is even; 0: one CTA per head.
+extern int g_tune_prefill_pair;
 
 }  // namespace qw

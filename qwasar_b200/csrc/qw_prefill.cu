@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     const int n_t = (k_end + BN - 1) / BN;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY || i == S_FREE || i == Q_READY) ? 128 : 1);
+        // the softmax side signals once per warp (lane 0, after the warp has converged)
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY || i == S_FREE || i == Q_READY) ? 4 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -309,7 +310,8 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[Q_READY]);      // also releases the K region to the TMA producer
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[Q_READY]);      // also releases the K region to the TMA producer
         }
         // P row in shared memory: box = 64 keys, 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
         uint8_t *p_row = smem + OFF_P + row_l * 128;
@@ -326,7 +328,8 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             tmem_ld32(t_s + lane_base + 96, s3);
             tmem_wait_ld();
             tc_fence_before();
-            mbar_arrive(&bars[S_FREE]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[S_FREE]);
             if (need_mask) {
 #pragma unroll
                 for (int e = 0; e < 32; e++) {
@@ -385,7 +388,8 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             store_p(s0, 0, 0); store_p(s1, 0, 4); store_p(s2, 1, 0); store_p(s3, 1, 4);
             fence_proxy_async();          // generic-proxy writes -> visible to the tensor core's reads
             tc_fence_before();
-            mbar_arrive(&bars[P_READY]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[P_READY]);
         }
         // epilogue: every thread drops its normalised O row into shared memory (the K/V stages are
         // idle now; rows padded to 1040 bytes), then the 128 threads walk the rows together so
@@ -396,8 +400,8 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         const int n_valid = min(BM, p.rows - q0);
         const int d2 = row_l * 2;                                       // this thread's two dims of every row
         constexpr int NB = 16;                                          // rows per batch
-        float g0[NB], g1[NB];
-        auto load_gates = [&](int r0) {
+        float ga0[NB], ga1[NB], gb0[NB], gb1[NB];     // two batches of gates: one in flight, one in use
+        auto load_gates = [&](int r0, float(&g0)[NB], float(&g1)[NB]) {
             if (!p.gate) return;
 #pragma unroll
             for (int i = 0; i < NB; i++) {
@@ -412,7 +416,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 }
             }
         };
-        auto store_rows = [&](int r0) {
+        auto store_rows = [&](int r0, const float(&g0)[NB], const float(&g1)[NB]) {
 #pragma unroll
             for (int i = 0; i < NB; i++) {
                 const int r = r0 + i;
@@ -430,7 +434,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 }
             }
         };
-        load_gates(0);
+        load_gates(0, ga0, ga1);
         mbar_wait(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
         tc_fence_after();
         {
@@ -447,11 +451,13 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                                     __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            store_rows(0);
+            // the next batch's loads are issued before the current batch is consumed
 #pragma unroll 1
-            for (int r0 = NB; r0 < n_valid; r0 += NB) {
-                load_gates(r0);
-                store_rows(r0);
+            for (int r0 = 0; r0 < n_valid; r0 += 2 * NB) {
+                if (r0 + NB < n_valid) load_gates(r0 + NB, gb0, gb1);
+                store_rows(r0, ga0, ga1);
+                if (r0 + 2 * NB < n_valid) load_gates(r0 + 2 * NB, ga0, ga1);
+                if (r0 + NB < n_valid) store_rows(r0 + NB, gb0, gb1);
             }
         }
     }

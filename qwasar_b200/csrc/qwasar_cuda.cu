@@ -468,7 +468,8 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
     KTime kt = {nullptr, nullptr, "qw_attn_prefill"};
     const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
-    launch_attn_prefill(c->stream, p);
+    if (g_tune_prefill_pair && attn_prefill_pair_ok(p)) launch_attn_prefill_pair(c->stream, p);
+    else launch_attn_prefill(c->stream, p);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
     return cuda_ok(c, cudaGetLastError(), "prefill launch");
 }
@@ -531,6 +532,7 @@ extern "C" uint64_t qw_gpu_launch_count(void) { return (uint64_t)qw::g_launches;
 extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "split_kg") && (value == 4 || value == 6)) { qw::g_tune_split_kg = value; return true; }
     if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
+    if (knob && !strcmp(knob, "prefill_pair") && (value == 0 || value == 1)) { qw::g_tune_prefill_pair = value; return true; }
     return false;
 }
 extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }

@@ -94,6 +94,10 @@ void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
 struct PrefillParams {
     const __nv_bfloat16 *q;  // [rows, q_heads, 256], 16-byte aligned
     CUtensorMap kmap, vmap;  // cache row maps, box 64 x 64
+    // Tile maps of the single-CTA kernel, all SWIZZLE_128B with 128-byte x 128-row boxes: q as
+    // [rows][q_heads*256] bf16; out the same shape in out_dtype; gate as [rows][q_heads*gate_stride]
+    // in gate_dtype (== out_dtype).  Bases 16-byte aligned, row pitches multiples of 16 bytes.
+    CUtensorMap qmap, omap, gmap;
     KvLayer kc, vc;
     void *out;               // [rows, q_heads, 256] f32 or bf16
     const void *gate;        // nullptr or element (r, h, d) at gate[(r*q_heads + h)*gate_stride + d]
@@ -104,6 +108,8 @@ struct PrefillParams {
     int *status;
 };
 void launch_attn_prefill(cudaStream_t s, const PrefillParams &p);
+// Whether out / gate can be described by the tile maps above (alignment, equal dtypes).
+bool attn_prefill_io_ok(const void *out, int out_dtype, const void *gate, int gate_dtype, int gate_stride);
 // The same attention with the two query heads 2u, 2u+1 of a row tile as one CTA pair (even grouping only).
 bool attn_prefill_pair_ok(const PrefillParams &p);
 void launch_attn_prefill_pair(cudaStream_t s, const PrefillParams &p);

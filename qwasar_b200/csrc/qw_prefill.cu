@@ -38,6 +38,17 @@ constexpr int VBOX = 64 * 128;
 constexpr int P_BYTES = BM * BN * 2;                  // bf16 weights of one step, as an A operand
 constexpr int PBOX = BM * 128;                        // 64 keys of every row
 constexpr int OFF_K = 0, OFF_V = 2 * K_BYTES, OFF_P = OFF_V + 2 * V_BYTES, OFF_BAR = OFF_P + P_BYTES;
+// Tiles that borrow the idle operand regions, all as SWIZZLE_128B boxes of 128 rows x 128 bytes
+// (16 KB) moved by TMA.  In such a box a thread that owns one row touches 16-byte chunk c at
+// c ^ (row & 7): eight neighbouring rows hit eight different bank groups, so the row-per-thread
+// accesses below are conflict-free, and the transposition between "thread = row" and coalesced
+// global rows is left to the copy engine.
+//   Q tile (bf16, 4 boxes) in the V stages while the first K tile is already on its way;
+//   gate tile (4 boxes bf16 / 8 boxes f32) in the K stages, loaded under the last step;
+//   output tile written over the gate tile in place (same dtype), stored box by box.
+constexpr int IO_BOX = BM * 128;
+constexpr int OFF_STAGE_Q = OFF_V, OFF_STAGE_IO = OFF_K;
+static_assert(4 * IO_BOX <= 2 * V_BYTES && 8 * IO_BOX <= 2 * K_BYTES, "staging overruns the operand regions");
 constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;    // TMEM columns
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
@@ -46,7 +57,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
-enum Bar { Q_READY = 0, K_FULL0, K_FULL1, K_FREE0, K_FREE1, V_FULL0, V_FULL1, V_FREE0, V_FREE1,
+enum Bar { Q_READY = 0, Q_FULL, G_FULL, K_FULL0, K_FULL1, K_FREE0, K_FREE1, V_FULL0, V_FULL1, V_FREE0, V_FREE1,
            S_READY, S_FREE, P_READY, PV_DONE, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -142,11 +153,6 @@ __device__ __forceinline__ constexpr uint32_t instr_desc(int m, int n, int b_mn_
            ((uint32_t)(m >> 4) << 24);
 }
 
-__device__ __forceinline__ float load_gate(const void *g, size_t i, int dtype) {
-    return dtype == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(g)[i])
-                            : reinterpret_cast<const float *>(g)[i];
-}
-
 __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __grid_constant__ PrefillParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -186,21 +192,9 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         return pg * QW_PAGE_TOKENS < L.max_ctx ? kvh * L.max_ctx + pg * QW_PAGE_TOKENS : p.oob_row;
     };
 
-    if ((warp == 5 || warp == 6) && lane > 0 && p.gate) {
-        // idle lanes: pull this tile's gate rows into L2 while the main loop runs (the epilogue reads them)
-        const size_t el = p.gate_dtype == DT_BF16 ? 2 : 4;
-        const int n_valid = min(BM, p.rows - q0);
-        const int lines = (int)(256 * el / 128);                     // 128-byte lines per row
-        for (int i = (warp - 5) * 31 + lane - 1; i < n_valid * lines; i += 62) {
-            const int r = i / lines, ln = i - r * lines;
-            const char *a = reinterpret_cast<const char *>(p.gate) + (((size_t)(q0 + r) * p.q_heads + head) * p.gate_stride) * el + ln * 128;
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
-        }
-    }
     if (warp == 5) {
         // ---------------- K tiles: two pages each, rows 0-63 and 64-127 of every 64-dim box ----------------
         if (lane == 0) {
-            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the Q staging borrowed this region
             for (int j = 0; j < n_t; j++) {
                 const int st = j & 1;
                 const int32_t r0 = page_row(p.kc, 2 * j), r1 = page_row(p.kc, 2 * j + 1);
@@ -213,10 +207,24 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     tma_load_2d(dst + b * KBOX + 8192, &p.kmap, b * 64, r1, &bars[K_FULL0 + st]);
                 }
             }
+            if (p.gate) {
+                // the gate tile, into the K stages: both are idle once the last Q K^T has completed
+                // (completions are in order), which is a whole step before the epilogue starts
+                mbar_wait(&bars[K_FREE0 + ((n_t - 1) & 1)], ((n_t - 1) >> 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                const int n_box = p.gate_dtype == DT_BF16 ? 4 : 8, w = p.gate_dtype == DT_BF16 ? 64 : 32;
+                mbar_expect_tx(&bars[G_FULL], n_box * IO_BOX);
+                for (int b = 0; b < n_box; b++)
+                    tma_load_2d(smem + OFF_STAGE_IO + b * IO_BOX, &p.gmap, head * p.gate_stride + b * w, q0, &bars[G_FULL]);
+            }
         }
     } else if (warp == 6) {
         // ---------------- V pages ----------------
         if (lane == 0) {
+            mbar_expect_tx(&bars[Q_FULL], 4 * IO_BOX);
+#pragma unroll
+            for (int b = 0; b < 4; b++)
+                tma_load_2d(smem + OFF_STAGE_Q + b * IO_BOX, &p.qmap, head * 256 + b * 64, q0, &bars[Q_FULL]);
+            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the Q tile borrowed this region
             for (int pg = 0; pg < 2 * n_t; pg++) {
                 const int st = pg & 1;
                 const int32_t r = page_row(p.vc, pg);
@@ -285,25 +293,17 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         const float sc2 = p.scale * LOG2E;
         float m = NEG_BIG, l = 0.0f;
         uint32_t v[32];
+        const uint32_t sw = row_l & 7;
         {
-            // The Q tile: coalesced 16-byte loads by all 128 threads into shared memory (rows padded
-            // to 528 bytes so that 32 lanes reading 32 different rows spread over the banks), then
-            // every thread moves its own row (256 bf16 = 128 columns of pairs) into its TMEM lane.
-            uint8_t *stage = smem + OFF_K;
-            const uint4 *qsrc = reinterpret_cast<const uint4 *>(p.q);
-#pragma unroll 16
-            for (int k = 0; k < 32; k++) {
-                const int idx = row_l + 128 * k, r = idx >> 5, ch = idx & 31;
-                uint4 x = make_uint4(0, 0, 0, 0);
-                if (q0 + r < p.rows) x = __ldg(qsrc + ((size_t)(q0 + r) * p.q_heads + head) * 32 + ch);
-                *reinterpret_cast<uint4 *>(stage + r * 528 + ch * 16) = x;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // The Q tile arrives by TMA; every thread moves its own row (256 bf16 = 128 columns of
+            // pairs) into its TMEM lane.  Rows past the end of the chunk read as zeros.
+            const uint8_t *q_row = smem + OFF_STAGE_Q + row_l * 128;
+            mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
-                    const uint4 x = *reinterpret_cast<const uint4 *>(stage + row_l * 528 + (c * 8 + e) * 16);
+                    const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
                     v[e * 4] = x.x; v[e * 4 + 1] = x.y; v[e * 4 + 2] = x.z; v[e * 4 + 3] = x.w;
                 }
                 tmem_st32(t_q + lane_base + c * 32, v);
@@ -311,11 +311,10 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             tmem_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars[Q_READY]);      // also releases the K region to the TMA producer
+            if (lane == 0) mbar_arrive(&bars[Q_READY]);      // also releases the V stages to the TMA producer
         }
         // P row in shared memory: box = 64 keys, 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
         uint8_t *p_row = smem + OFF_P + row_l * 128;
-        const uint32_t sw = row_l & 7;
         for (int j = 0; j < n_t; j++) {
             mbar_wait(&bars[S_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             tc_fence_after();
@@ -391,75 +390,76 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[P_READY]);
         }
-        // epilogue: every thread drops its normalised O row into shared memory (the K/V stages are
-        // idle now; rows padded to 1040 bytes), then the 128 threads walk the rows together so
-        // that the gate is read and the output written in whole coalesced rows.  The gate loads
-        // of 16 rows are in flight together, and the first 16 are issued before the wait for the
-        // last product: under the K/V stream of the other SMs a global load takes microseconds,
-        // and the epilogue must not pay that latency once per row.
-        const int n_valid = min(BM, p.rows - q0);
-        const int d2 = row_l * 2;                                       // this thread's two dims of every row
-        constexpr int NB = 16;                                          // rows per batch
-        float ga0[NB], ga1[NB], gb0[NB], gb1[NB];     // two batches of gates: one in flight, one in use
-        auto load_gates = [&](int r0, float(&g0)[NB], float(&g1)[NB]) {
-            if (!p.gate) return;
-#pragma unroll
-            for (int i = 0; i < NB; i++) {
-                const int r = min(r0 + i, n_valid - 1);
-                const size_t gi = ((size_t)(q0 + r) * p.q_heads + head) * p.gate_stride + d2;
-                if (p.gate_dtype == DT_BF16) {
-                    const __nv_bfloat162 g = __ldg(reinterpret_cast<const __nv_bfloat162 *>(reinterpret_cast<const __nv_bfloat16 *>(p.gate) + gi));
-                    g0[i] = __low2float(g); g1[i] = __high2float(g);
-                } else {
-                    const float2 g = __ldg(reinterpret_cast<const float2 *>(reinterpret_cast<const float *>(p.gate) + gi));
-                    g0[i] = g.x; g1[i] = g.y;
-                }
-            }
-        };
-        auto store_rows = [&](int r0, const float(&g0)[NB], const float(&g1)[NB]) {
-#pragma unroll
-            for (int i = 0; i < NB; i++) {
-                const int r = r0 + i;
-                if (r < n_valid) {
-                    float2 o = *reinterpret_cast<const float2 *>(smem + OFF_K + (size_t)r * 1040 + d2 * 4);
-                    if (p.gate) {
-                        o.x = __fdividef(o.x, 1.0f + __expf(-g0[i]));
-                        o.y = __fdividef(o.y, 1.0f + __expf(-g1[i]));
-                    }
-                    const size_t rh = (size_t)(q0 + r) * p.q_heads + head;
-                    if (p.out_dtype == DT_BF16)
-                        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + rh * 256 + d2) = pack_bf16(o.x, o.y);
-                    else
-                        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.out) + rh * 256 + d2) = o;
-                }
-            }
-        };
-        load_gates(0, ga0, ga1);
+        // epilogue: thread = row.  Each 128-byte slice of the row (64 bf16 or 32 f32 outputs) is
+        // normalised, multiplied by the sigmoid of the gate slice found at the same place of the
+        // gate tile, written back over it, and the box is handed to the copy engine as soon as
+        // the four warps are through with it.  Rows past the end of the chunk are not written.
         mbar_wait(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
         tc_fence_after();
-        {
-            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            float *orow = reinterpret_cast<float *>(smem + OFF_K + (size_t)row_l * 1040);
+        if (p.gate) mbar_wait(&bars[G_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+        const bool gated = p.gate != nullptr;
+        uint8_t *io_row = smem + OFF_STAGE_IO + row_l * 128;
+        auto sig = [&](float o, float g) { return __fdividef(o * inv, 1.0f + __expf(-g)); };
+        auto publish = [&](int box, int x) {
+            fence_proxy_async();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 0) {
+                tma_store_2d(&p.omap, x, q0, smem + OFF_STAGE_IO + box * IO_BOX);
+                tma_store_commit();
+            }
+        };
+        if (p.out_dtype == DT_BF16) {
 #pragma unroll 1
-            for (int c = 0; c < 8; c++) {
+            for (int c = 0; c < 8; c++) {                      // 32 outputs = 64 bytes = half a box row
                 tmem_ld32(t_o + lane_base + c * 32, v);
                 tmem_wait_ld();
+                uint8_t *bx = io_row + (c >> 1) * IO_BOX;
 #pragma unroll
-                for (int e = 0; e < 32; e += 4)
-                    *reinterpret_cast<float4 *>(orow + c * 32 + e) =
-                        make_float4(__uint_as_float(v[e]) * inv, __uint_as_float(v[e + 1]) * inv,
-                                    __uint_as_float(v[e + 2]) * inv, __uint_as_float(v[e + 3]) * inv);
+                for (int k = 0; k < 4; k++) {
+                    uint4 *slot = reinterpret_cast<uint4 *>(bx + ((((c & 1) * 4 + k) ^ sw) << 4));
+                    float o[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) o[e] = __uint_as_float(v[k * 8 + e]);
+                    if (gated) {
+                        const uint4 g = *slot;
+                        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            o[2 * e] = sig(o[2 * e], __uint_as_float(gw[e] << 16));
+                            o[2 * e + 1] = sig(o[2 * e + 1], __uint_as_float(gw[e] & 0xffff0000u));
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; e++) o[e] *= inv;
+                    }
+                    *slot = make_uint4(pack_bf16(o[0], o[1]), pack_bf16(o[2], o[3]), pack_bf16(o[4], o[5]), pack_bf16(o[6], o[7]));
+                }
+                if (c & 1) publish(c >> 1, head * 256 + (c >> 1) * 64);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            // the next batch's loads are issued before the current batch is consumed
+        } else {
 #pragma unroll 1
-            for (int r0 = 0; r0 < n_valid; r0 += 2 * NB) {
-                if (r0 + NB < n_valid) load_gates(r0 + NB, gb0, gb1);
-                store_rows(r0, ga0, ga1);
-                if (r0 + 2 * NB < n_valid) load_gates(r0 + 2 * NB, ga0, ga1);
-                if (r0 + NB < n_valid) store_rows(r0 + NB, gb0, gb1);
+            for (int c = 0; c < 8; c++) {                      // 32 outputs = 128 bytes = one box row
+                tmem_ld32(t_o + lane_base + c * 32, v);
+                tmem_wait_ld();
+                uint8_t *bx = io_row + c * IO_BOX;
+#pragma unroll
+                for (int k = 0; k < 8; k++) {
+                    float4 *slot = reinterpret_cast<float4 *>(bx + ((k ^ sw) << 4));
+                    float4 o = make_float4(__uint_as_float(v[k * 4]), __uint_as_float(v[k * 4 + 1]),
+                                           __uint_as_float(v[k * 4 + 2]), __uint_as_float(v[k * 4 + 3]));
+                    if (gated) {
+                        const float4 g = *slot;
+                        o = make_float4(sig(o.x, g.x), sig(o.y, g.y), sig(o.z, g.z), sig(o.w, g.w));
+                    } else {
+                        o = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
+                    }
+                    *slot = o;
+                }
+                publish(c, head * 256 + c * 32);
             }
         }
+        if (threadIdx.x == 0) tma_store_wait_read();          // shared memory must outlive the copies
     }
     tc_fence_before();
     __syncthreads();
@@ -470,6 +470,13 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
 }
 
 }  // namespace
+
+bool attn_prefill_io_ok(const void *out, int out_dtype, const void *gate, int gate_dtype, int gate_stride) {
+    const size_t el = out_dtype == DT_BF16 ? 2 : 4;
+    if (reinterpret_cast<uintptr_t>(out) & 15) return false;
+    if (!gate) return true;
+    return gate_dtype == out_dtype && !(reinterpret_cast<uintptr_t>(gate) & 15) && gate_stride >= 256 && (gate_stride * el) % 16 == 0;
+}
 
 void launch_attn_prefill(cudaStream_t s, const PrefillParams &p) {
     static bool configured = false;

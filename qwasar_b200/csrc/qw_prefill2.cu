@@ -31,6 +31,7 @@ constexpr int VBOX = BN * 128;                        // one 64-dim box of it (1
 constexpr int P_BYTES = BM * BN * 2;
 constexpr int PBOX = BM * 128;
 constexpr int OFF_K = 0, OFF_V = NKV * K_BYTES, OFF_P = OFF_V + NKV * V_BYTES, OFF_BAR = OFF_P + P_BYTES;
+constexpr int OFF_STAGE_O = OFF_K;                    // the normalised O tile (fp32, 1040-byte rows) over the idle K/V stages
 constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;
 constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
@@ -408,21 +409,30 @@ qw_attn_prefill_pair_kernel(const __grid_constant__ PrefillParams p) {
                 }
             }
         };
+        // The rows of a batch are read from shared memory first, all together: a shared-memory
+        // load cannot be moved above the global store of the row before it (the compiler sees
+        // two generic pointers), so a load-compute-store loop runs one row at a time.
         auto store_rows = [&](int r0, const float(&g0)[NB], const float(&g1)[NB]) {
+            float2 o[NB];
+#pragma unroll
+            for (int i = 0; i < NB; i++)
+                o[i] = *reinterpret_cast<const float2 *>(smem + OFF_STAGE_O + (size_t)min(r0 + i, n_valid - 1) * 1040 + d2 * 4);
+            if (p.gate) {
+#pragma unroll
+                for (int i = 0; i < NB; i++) {
+                    o[i].x = __fdividef(o[i].x, 1.0f + __expf(-g0[i]));
+                    o[i].y = __fdividef(o[i].y, 1.0f + __expf(-g1[i]));
+                }
+            }
 #pragma unroll
             for (int i = 0; i < NB; i++) {
                 const int r = r0 + i;
                 if (r < n_valid) {
-                    float2 o = *reinterpret_cast<const float2 *>(smem + OFF_K + (size_t)r * 1040 + d2 * 4);
-                    if (p.gate) {
-                        o.x = __fdividef(o.x, 1.0f + __expf(-g0[i]));
-                        o.y = __fdividef(o.y, 1.0f + __expf(-g1[i]));
-                    }
                     const size_t rh = (size_t)(q0 + r) * p.q_heads + head;
                     if (p.out_dtype == DT_BF16)
-                        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + rh * 256 + d2) = pack_bf16(o.x, o.y);
+                        *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(p.out) + rh * 256 + d2) = pack_bf16(o[i].x, o[i].y);
                     else
-                        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.out) + rh * 256 + d2) = o;
+                        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(p.out) + rh * 256 + d2) = o[i];
                 }
             }
         };
@@ -431,7 +441,7 @@ qw_attn_prefill_pair_kernel(const __grid_constant__ PrefillParams p) {
         tc_fence_after();
         {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            float *orow = reinterpret_cast<float *>(smem + OFF_K + (size_t)row_l * 1040);
+            float *orow = reinterpret_cast<float *>(smem + OFF_STAGE_O + (size_t)row_l * 1040);
 #pragma unroll 1
             for (int c = 0; c < 8; c++) {
                 tmem_ld32(t_o + lane_base + c * 32, v);

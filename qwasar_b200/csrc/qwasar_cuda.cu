@@ -189,6 +189,20 @@ bool encode_rows_map(CUtensorMap *m, void *base, uint64_t rows, uint32_t box_row
     return true;
 }
 
+// A [rows][row_elems] tensor of bf16 or f32 with a row pitch of pitch_elems, as 128-byte x 128-row boxes.
+bool encode_tile_map(CUtensorMap *m, const void *base, int dtype, uint64_t row_elems, uint64_t pitch_elems, uint64_t rows) {
+    const uint32_t el = dtype == DT_BF16 ? 2 : 4;
+    cuuint64_t dims[2] = {row_elems, rows};
+    cuuint64_t strides[1] = {pitch_elems * el};
+    cuuint32_t box[2] = {128 / el, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = G.encodeTiled(m, dtype == DT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                               const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return false; }
+    return true;
+}
+
 bool arena_grow(Arena *a, cudaStream_t stream) {
     if (a->mapped_pages >= a->max_pages) return false;
     const int64_t first = a->mapped_pages;
@@ -465,6 +479,10 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
     p.oob_row = (int32_t)std::min<int64_t>(std::max(k_rows, v_rows), 0x7fffffff);
     p.scale = scale;
     p.status = G.status_dev;
+    const uint64_t row = (uint64_t)q_heads * 256;
+    if (!encode_tile_map(&p.qmap, q_bf16, DT_BF16, row, row, rows) || !encode_tile_map(&p.omap, out, out_dtype, row, row, rows) ||
+        (gate && !encode_tile_map(&p.gmap, gate, gate_dtype, (uint64_t)(q_heads - 1) * gate_stride + 256, (uint64_t)q_heads * gate_stride, rows)))
+        return cmd_fail(c, "%s", "prefill: tensor map encoding failed"), false;
     KTime kt = {nullptr, nullptr, "qw_attn_prefill"};
     const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
@@ -1018,14 +1036,14 @@ extern "C" bool qw_op_attn_prefill_as(qw_cmd c, bool half_form, qw_ref out, qw_r
                                       int32_t base_pos, float scale) {
     (void)half_form;
     if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
-    if (!g_tune_prefill_tc) {
+    const size_t n = (size_t)rows * q_heads * 256;
+    void *op = dev_range(c, out, n * 4, true);
+    if (!g_tune_prefill_tc || !attn_prefill_io_ok(op, DT_F32, nullptr, DT_F32, 256)) {
         if (q_heads / kv_heads > 64) return false;
         AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
         return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
     }
-    const size_t n = (size_t)rows * q_heads * 256;
     const float *qp = (const float *)dev_range(c, q, n * 4, false);
-    void *op = dev_range(c, out, n * 4, true);
     __nv_bfloat16 *qb = (__nv_bfloat16 *)cmd_scratch(c, n * 2);
     if (!qp || !op || !qb) return false;
     launch_f32_to_bf16(c->stream, qb, qp, (int64_t)n);
@@ -1109,16 +1127,26 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
         if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
 
         if (rows * gqa > 64 && g_tune_prefill_tc) {
-            // many rows: the tcgen05 kernel, one launch per sequence
+            // many rows: the tcgen05 kernel, one launch per sequence (operands that its tile maps
+            // cannot describe, e.g. an output that is not 16-byte aligned, take the chunked path below)
+            char *op[QW_MAX_SEQ];
+            const char *gp[QW_MAX_SEQ];
+            bool tiles_ok = true;
             for (int i = 0; i < ns; i++) {
                 const FusedSeq &fs = seqs[s0 + i];
-                char *op = (char *)dev_range(c, fs.out, (size_t)rows * q_heads * 256 * el, true);
-                const char *gp = (const char *)dev_range(c, fs.qg, (size_t)rows * q_heads * 512 * el, false);
-                if (!op || !gp) return false;
-                if (!run_prefill(c, qo[i], op, io, gp + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
-                                 max_ctx, fs.base_pos, scale)) return false;
+                op[i] = (char *)dev_range(c, fs.out, (size_t)rows * q_heads * 256 * el, true);
+                gp[i] = (const char *)dev_range(c, fs.qg, (size_t)rows * q_heads * 512 * el, false);
+                if (!op[i] || !gp[i]) return false;
+                tiles_ok = tiles_ok && attn_prefill_io_ok(op[i], io, gp[i] + 256 * el, io, 512);
             }
-            continue;
+            if (tiles_ok) {
+                for (int i = 0; i < ns; i++) {
+                    const FusedSeq &fs = seqs[s0 + i];
+                    if (!run_prefill(c, qo[i], op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
+                                     max_ctx, fs.base_pos, scale)) return false;
+                }
+                continue;
+            }
         }
 
         AttnParams p;

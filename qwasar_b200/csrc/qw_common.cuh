@@ -16,6 +16,7 @@ enum : int {
     QW_ST_SLOT_TIMEOUT = 2,      // a wait on an "empty" barrier ran out
     QW_ST_MMA_TIMEOUT = 3,       // a wait on a tcgen05 commit barrier ran out
     QW_ST_BAD_PAGE = 4,          // a page-table entry was unmapped where a key was needed
+    QW_ST_BAD_SMEM = 5,          // the dynamic shared-memory window was not 1024-byte aligned
 };
 
 namespace qw {
@@ -78,6 +79,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     *abort_flag = 1;
     report(status, code);
     return false;
+}
+
+// The same bounded wait for hand-offs on a critical path: polls with test_wait first (try_wait
+// may park the thread, and waking it costs more than the hand-off it waits for), then falls
+// back to the parking wait.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
+                                              int *status, int code) {
+    if (*abort_flag) return false;
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < 4096; ++spin)
+        if (mbar_test(bar, parity)) return true;
+    return mbar_wait(bar, parity, abort_flag, status, code);
 }
 
 // ---- TMA (tiled, no multicast anywhere in this library) -------------------------

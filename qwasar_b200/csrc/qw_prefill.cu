@@ -4,16 +4,20 @@
 // One CTA per (128-row query tile, query head).  K and V are read from the cache (the rows
 // of this chunk were appended just before), 128 keys per step:
 //
-//   warp 5   TMA: K tiles   (two stages of 128 keys x 256 dims; 8 SWIZZLE_128B boxes of one page half each)
-//   warp 6   TMA: V pages   (two stages of 64 keys x 256 dims: the two halves of a step)
-//   warp 4   one thread issues tcgen05.mma:  S  = Q K_j^T   (TS, M128 N128 K16 x 16, Q in TMEM)
-//                                            O += P_j V_j   (SS, M128 N256 K16 x 8,  P in shared memory)
-//   warps 0-3  softmax: thread i owns query row i = TMEM lane i.  Reads its 128 scores from TMEM
-//            into registers and hands S back at once (so Q K_{j+1}^T runs under this step's
-//            exponentials), online max / sum in the exp2 domain, writes P (bf16) into shared
-//            memory in the tensor core's swizzled K-major layout, rescales O in TMEM only when a
-//            row's max grew by more than 2^8, and at the end normalises, applies the sigmoid
-//            output gate and stores the row.
+//   warp 9   TMA: K tiles   (two stages of 128 keys x 256 dims; 8 SWIZZLE_128B boxes of one page half each)
+//   warp 10  TMA: V pages   (two stages of 64 keys x 256 dims: the two halves of a step)
+//   warp 8   one thread issues tcgen05.mma:  S  = Q K_j^T   (TS, M128 N128 K16 x 16, Q in TMEM)
+//   warp 11  one thread issues tcgen05.mma:  O += P_j V_j   (SS, M128 N256 K16 x 8,  P in shared memory)
+//   warps 0-7  softmax: two threads per query row (= TMEM lane), 64 keys of every step each.  A
+//            thread reads its scores from TMEM into registers and hands S back at once (so
+//            Q K_{j+1}^T runs under this step's exponentials), online max / sum in the exp2
+//            domain (the two halves swap their maxima through shared memory), writes P (bf16)
+//            into shared memory in the tensor core's swizzled K-major layout, rescales its half
+//            of O in TMEM only when the row's max grew by more than 2^8, and at the end
+//            normalises, applies the sigmoid output gate and stores its 128 dims of the row.
+//            The exponentials are bounded by the special-function unit (16 per clock per SM,
+//            half of a step's tensor time), so the step's critical chain -- read S, max,
+//            exponentials, write P -- is split over two warps per scheduler.
 //
 // TMEM columns (512): O [0,256) fp32 | Q [256,384) bf16 pairs | S [384,512) fp32.  The query tile
 // lives in tensor memory: as a shared-memory A operand it would be re-read for every key tile
@@ -50,9 +54,11 @@ constexpr int IO_BOX = BM * 128;
 constexpr int OFF_STAGE_Q = OFF_V, OFF_STAGE_IO = OFF_K;
 static_assert(4 * IO_BOX <= 2 * V_BYTES && 8 * IO_BOX <= 2 * K_BYTES, "staging overruns the operand regions");
 constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;    // TMEM columns
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
+constexpr int OFF_XCH = OFF_BAR + 256;                // row maxima / sums passed between the two softmax halves
+constexpr int SMEM_BYTES = OFF_XCH + 2 * 2 * BM * 4;  // the dynamic window is declared 1024-byte aligned
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
-constexpr int THREADS = 7 * 32;
+constexpr int THREADS = 12 * 32;                      // 8 softmax warps, Q K^T issue, K loads, V loads, P V issue
+constexpr int W_MMA = 8, W_K = 9, W_V = 10, W_PV = 11;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
@@ -154,8 +160,11 @@ __device__ __forceinline__ constexpr uint32_t instr_desc(int m, int n, int b_mn_
 }
 
 __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __grid_constant__ PrefillParams p) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if (smem_u32(smem) & 1023u) {                      // swizzled boxes need 1024-byte alignment
+        if (threadIdx.x == 0) report(p.status, QW_ST_BAD_SMEM);
+        return;
+    }
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + OFF_BAR);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + N_BARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -172,11 +181,11 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
 
     if (threadIdx.x == 0) {
         // the softmax side signals once per warp (lane 0, after the warp has converged)
-        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY || i == S_FREE || i == Q_READY) ? 4 : 1);
+        for (int i = 0; i < N_BARS; i++) mbar_init(&bars[i], (i == P_READY || i == S_FREE || i == Q_READY) ? 8 : 1);
         *abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 4) tmem_alloc(tmem_slot, 512);
+    if (warp == W_MMA) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -192,7 +201,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         return pg * QW_PAGE_TOKENS < L.max_ctx ? kvh * L.max_ctx + pg * QW_PAGE_TOKENS : p.oob_row;
     };
 
-    if (warp == 5) {
+    if (warp == W_K) {
         // ---------------- K tiles: two pages each, rows 0-63 and 64-127 of every 64-dim box ----------------
         if (lane == 0) {
             for (int j = 0; j < n_t; j++) {
@@ -217,7 +226,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     tma_load_2d(smem + OFF_STAGE_IO + b * IO_BOX, &p.gmap, head * p.gate_stride + b * w, q0, &bars[G_FULL]);
             }
         }
-    } else if (warp == 6) {
+    } else if (warp == W_V) {
         // ---------------- V pages ----------------
         if (lane == 0) {
             mbar_expect_tx(&bars[Q_FULL], 4 * IO_BOX);
@@ -235,17 +244,21 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     tma_load_2d(smem + OFF_V + st * V_BYTES + b * VBOX, &p.vmap, b * 64, r, &bars[V_FULL0 + st]);
             }
         }
-    } else if (warp == 4) {
-        // ---------------- tensor-core issue ----------------
+    } else if (warp == W_MMA) {
+        // ---------------- tensor-core issue, S = Q K^T ----------------
+        // The two products are issued by two threads (this one and warp W_PV): a thread that has
+        // just queued tensor work is slow to get through its next barrier, and with one issuer
+        // those pauses (five per step) left the tensor pipe idle for almost half of the step.
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc(128, BN, 0);
-            constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
             constexpr uint32_t hi = desc_hi(1024);
-            const uint32_t k_a = smem_u32(smem + OFF_K), v_a = smem_u32(smem + OFF_V), p_a = smem_u32(smem + OFF_P);
-            const uint32_t p_lo = desc_lo(p_a, 16);
-            auto issue_qk = [&](int j) {
+            const uint32_t k_a = smem_u32(smem + OFF_K);
+            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+            for (int j = 0; j < n_t; j++) {
                 const int st = j & 1;
-                mbar_wait(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                // S is handed back as soon as the softmax threads hold step j-1 in registers
+                if (j > 0) mbar_wait_hot(&bars[S_FREE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                mbar_wait_hot(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 tc_fence_after();
                 const uint32_t k_lo = desc_lo(k_a + st * K_BYTES, 16);
                 // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes (2 units) inside the swizzle atom,
@@ -256,19 +269,20 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     mma_ts<true>(t_s, t_q + ks * 8, k_lo + (ks >> 2) * (KBOX >> 4) + (ks & 3) * 2, hi, idesc_qk);
                 tc_commit(&bars[S_READY]);
                 tc_commit(&bars[K_FREE0 + st]);
-            };
-            mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-            issue_qk(0);
+            }
+        }
+    } else if (warp == W_PV) {
+        // ---------------- tensor-core issue, O += P V ----------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = instr_desc(128, 256, 1);
+            constexpr uint32_t hi = desc_hi(1024);
+            const uint32_t v_a = smem_u32(smem + OFF_V), p_a = smem_u32(smem + OFF_P);
+            const uint32_t p_lo = desc_lo(p_a, 16);
             for (int j = 0; j < n_t; j++) {
-                if (j + 1 < n_t) {
-                    // S is handed back as soon as the softmax threads hold it in registers
-                    mbar_wait(&bars[S_FREE], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
-                    issue_qk(j + 1);
-                }
-                mbar_wait(&bars[P_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                mbar_wait_hot(&bars[P_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
 #pragma unroll
                 for (int h = 0; h < 2; h++) {                  // the two 64-key pages of the step
-                    mbar_wait(&bars[V_FULL0 + h], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                    mbar_wait_hot(&bars[V_FULL0 + h], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                     tc_fence_after();
                     const uint32_t v_lo = desc_lo(v_a + h * V_BYTES, VBOX);
 #pragma unroll
@@ -284,23 +298,30 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             }
         }
     } else {
-        // ---------------- softmax + epilogue: thread = query row = TMEM lane ----------------
-        const int row_l = warp * 32 + lane;
+        // ---------------- softmax + epilogue ----------------
+        // Two threads per query row (= TMEM lane): warps 0-3 take keys 0-63 of every step and
+        // output dims 0-127, warps 4-7 keys 64-127 and dims 128-255 (a warp reaches the 32 lanes
+        // of its index modulo 4).  The halves exchange their row maxima through shared memory, so
+        // both follow the same running max and rescale decisions; each keeps the sum of its keys.
+        const int wg = warp >> 2;
+        const int row_l = (warp & 3) * 32 + lane;
         const int row_g = q0 + row_l;
         const bool valid = row_g < p.rows;
         const int limit = valid ? p.base_pos + row_g : 0x7fffffff;         // last key this row may read
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
         const float sc2 = p.scale * LOG2E;
+        float *xch = reinterpret_cast<float *>(smem + OFF_XCH);             // [2][2][BM]
         float m = NEG_BIG, l = 0.0f;
         uint32_t v[32];
         const uint32_t sw = row_l & 7;
         {
-            // The Q tile arrives by TMA; every thread moves its own row (256 bf16 = 128 columns of
-            // pairs) into its TMEM lane.  Rows past the end of the chunk read as zeros.
+            // The Q tile arrives by TMA; the two threads of a row move half of it each (two boxes
+            // = 128 bf16 = 64 columns of pairs) into the row's TMEM lane.  Rows past the end of
+            // the chunk read as zeros.
             const uint8_t *q_row = smem + OFF_STAGE_Q + row_l * 128;
             mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-#pragma unroll 1
-            for (int c = 0; c < 4; c++) {
+#pragma unroll
+            for (int c = 2 * wg; c < 2 * wg + 2; c++) {
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
@@ -313,38 +334,39 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[Q_READY]);      // also releases the V stages to the TMA producer
         }
-        // P row in shared memory: box = 64 keys, 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
-        uint8_t *p_row = smem + OFF_P + row_l * 128;
+        // P row in shared memory: box = 64 keys (one per half), 128 bytes per row, 16-byte chunk c at c ^ (row & 7)
+        uint8_t *p_row = smem + OFF_P + wg * PBOX + row_l * 128;
         for (int j = 0; j < n_t; j++) {
-            mbar_wait(&bars[S_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+            mbar_wait_hot(&bars[S_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             tc_fence_after();
-            const bool need_mask = j * BN + BN - 1 > p.base_pos + q0;
-            // the row's 128 scores, read once; S goes back to the tensor core at once
-            uint32_t s0[32], s1[32], s2[32], s3[32];
-            tmem_ld32(t_s + lane_base, s0);
-            tmem_ld32(t_s + lane_base + 32, s1);
-            tmem_ld32(t_s + lane_base + 64, s2);
-            tmem_ld32(t_s + lane_base + 96, s3);
+            const int key0 = j * BN + wg * 64;
+            // the row's 64 scores of this half, read once; S goes back to the tensor core at once
+            uint32_t s0[32], s1[32];
+            tmem_ld32(t_s + lane_base + wg * 64, s0);
+            tmem_ld32(t_s + lane_base + wg * 64 + 32, s1);
             tmem_wait_ld();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[S_FREE]);
-            if (need_mask) {
+            if (key0 + 63 > p.base_pos + q0) {
 #pragma unroll
                 for (int e = 0; e < 32; e++) {
-                    if (j * BN + e > limit) s0[e] = __float_as_uint(NEG_BIG);
-                    if (j * BN + 32 + e > limit) s1[e] = __float_as_uint(NEG_BIG);
-                    if (j * BN + 64 + e > limit) s2[e] = __float_as_uint(NEG_BIG);
-                    if (j * BN + 96 + e > limit) s3[e] = __float_as_uint(NEG_BIG);
+                    if (key0 + e > limit) s0[e] = __float_as_uint(NEG_BIG);
+                    if (key0 + 32 + e > limit) s1[e] = __float_as_uint(NEG_BIG);
                 }
             }
             float mxa = NEG_BIG, mxb = NEG_BIG;
 #pragma unroll
-            for (int e = 0; e < 32; e++) {
+            for (int e = 0; e < 32; e += 2) {
                 mxa = fmaxf(mxa, fmaxf(__uint_as_float(s0[e]), __uint_as_float(s1[e])));
-                mxb = fmaxf(mxb, fmaxf(__uint_as_float(s2[e]), __uint_as_float(s3[e])));
+                mxb = fmaxf(mxb, fmaxf(__uint_as_float(s0[e + 1]), __uint_as_float(s1[e + 1])));
             }
-            const float mx2 = fmaxf(fmaxf(mxa, mxb) * sc2, NEG_BIG);
+            // the other half's maximum (slots alternate between steps: a slot is rewritten only
+            // after the barrier of the step in between, which every reader has then passed)
+            float *slot = xch + (j & 1) * 2 * BM;
+            slot[wg * BM + row_l] = fmaxf(mxa, mxb);
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float mx2 = fmaxf(fmaxf(fmaxf(mxa, mxb), slot[(wg ^ 1) * BM + row_l]) * sc2, NEG_BIG);
             const bool grow = j > 0 && mx2 - m > RESCALE_AT;
             const float alpha = grow ? ex2(m - mx2) : 1.0f;
             if (j == 0 || grow) m = mx2;
@@ -359,16 +381,16 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     s[e >> 1] = pack_bf16(x0, x1);      // slot e/2 <= e: already consumed
                 }
             };
-            weights(s0, la); weights(s1, lb); weights(s2, la); weights(s3, lb);
+            weights(s0, la); weights(s1, lb);
             l = l * alpha + (la + lb);
             // P_{j-1} must have been consumed (and O complete) before P is overwritten or O rescaled
             if (j > 0) {
-                mbar_wait(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                mbar_wait_hot(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
                 tc_fence_after();
             }
-            if (__any_sync(0xffffffffu, grow)) {
+            if (__any_sync(0xffffffffu, grow)) {               // both halves of a row see the same flag
 #pragma unroll 1
-                for (int c = 0; c < 8; c++) {
+                for (int c = 4 * wg; c < 4 * wg + 4; c++) {
                     tmem_ld32(t_o + lane_base + c * 32, v);
                     tmem_wait_ld();
 #pragma unroll
@@ -377,41 +399,48 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 }
                 tmem_wait_st();
             }
-            // 16 packed pairs per 32 scores = 4 chunks of 16 bytes; keys 0-63 in box 0, 64-127 in box 1
-            auto store_p = [&](const uint32_t(&s)[32], int box, int chunk0) {
+            // 16 packed pairs per 32 scores = 4 chunks of 16 bytes
 #pragma unroll
-                for (int c = 0; c < 4; c++)
-                    *reinterpret_cast<uint4 *>(p_row + box * PBOX + (((chunk0 + c) ^ sw) << 4)) =
-                        make_uint4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
-            };
-            store_p(s0, 0, 0); store_p(s1, 0, 4); store_p(s2, 1, 0); store_p(s3, 1, 4);
+            for (int c = 0; c < 4; c++) {
+                *reinterpret_cast<uint4 *>(p_row + ((c ^ sw) << 4)) = make_uint4(s0[c * 4], s0[c * 4 + 1], s0[c * 4 + 2], s0[c * 4 + 3]);
+                *reinterpret_cast<uint4 *>(p_row + (((4 + c) ^ sw) << 4)) = make_uint4(s1[c * 4], s1[c * 4 + 1], s1[c * 4 + 2], s1[c * 4 + 3]);
+            }
             fence_proxy_async();          // generic-proxy writes -> visible to the tensor core's reads
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars[P_READY]);
         }
-        // epilogue: thread = row.  Each 128-byte slice of the row (64 bf16 or 32 f32 outputs) is
-        // normalised, multiplied by the sigmoid of the gate slice found at the same place of the
-        // gate tile, written back over it, and the box is handed to the copy engine as soon as
-        // the four warps are through with it.  Rows past the end of the chunk are not written.
-        mbar_wait(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+        // the row's sum: both halves
+        {
+            float *slot = xch + (n_t & 1) * 2 * BM;
+            slot[wg * BM + row_l] = l;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            l += slot[(wg ^ 1) * BM + row_l];
+        }
+        // epilogue: each 128-byte slice of the row (64 bf16 or 32 f32 outputs) is normalised,
+        // multiplied by the sigmoid of the gate slice found at the same place of the gate tile,
+        // written back over it, and the box is handed to the copy engine as soon as the four
+        // warps of the half are through with it.  Rows past the end of the chunk are not written.
+        mbar_wait_hot(&bars[PV_DONE], (n_t - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
         tc_fence_after();
         if (p.gate) mbar_wait(&bars[G_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
         const float inv = l > 0.0f ? 1.0f / l : 0.0f;
         const bool gated = p.gate != nullptr;
+        const bool elected = (warp & 3) == 0 && lane == 0;
         uint8_t *io_row = smem + OFF_STAGE_IO + row_l * 128;
         auto sig = [&](float o, float g) { return __fdividef(o * inv, 1.0f + __expf(-g)); };
         auto publish = [&](int box, int x) {
             fence_proxy_async();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (threadIdx.x == 0) {
+            if (wg == 0) asm volatile("bar.sync 2, 128;" ::: "memory");
+            else asm volatile("bar.sync 3, 128;" ::: "memory");
+            if (elected) {
                 tma_store_2d(&p.omap, x, q0, smem + OFF_STAGE_IO + box * IO_BOX);
                 tma_store_commit();
             }
         };
         if (p.out_dtype == DT_BF16) {
 #pragma unroll 1
-            for (int c = 0; c < 8; c++) {                      // 32 outputs = 64 bytes = half a box row
+            for (int c = 4 * wg; c < 4 * wg + 4; c++) {        // 32 outputs = 64 bytes = half a box row
                 tmem_ld32(t_o + lane_base + c * 32, v);
                 tmem_wait_ld();
                 uint8_t *bx = io_row + (c >> 1) * IO_BOX;
@@ -439,7 +468,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             }
         } else {
 #pragma unroll 1
-            for (int c = 0; c < 8; c++) {                      // 32 outputs = 128 bytes = one box row
+            for (int c = 4 * wg; c < 4 * wg + 4; c++) {        // 32 outputs = 128 bytes = one box row
                 tmem_ld32(t_o + lane_base + c * 32, v);
                 tmem_wait_ld();
                 uint8_t *bx = io_row + c * IO_BOX;
@@ -459,11 +488,11 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 publish(c, head * 256 + c * 32);
             }
         }
-        if (threadIdx.x == 0) tma_store_wait_read();          // shared memory must outlive the copies
+        if (elected) tma_store_wait_read();                   // shared memory must outlive the copies
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == W_MMA) {
         tc_fence_after();
         tmem_dealloc(tmem, 512);
     }

@@ -148,6 +148,7 @@ const char *status_text(int code) {
         case QW_ST_SLOT_TIMEOUT: return "kernel gave up waiting for a free pipeline stage";
         case QW_ST_MMA_TIMEOUT: return "kernel gave up waiting for a tensor-core commit";
         case QW_ST_BAD_PAGE: return "attention reached a cache position whose page was never mapped";
+        case QW_ST_BAD_SMEM: return "the prefill kernel's shared-memory window was not 1024-byte aligned";
         default: return "unknown kernel status";
     }
 }

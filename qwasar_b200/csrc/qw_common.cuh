@@ -82,11 +82,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
 }
 
 // The same bounded wait for hand-offs on a critical path: polls with test_wait first (try_wait
-// may park the thread, and waking it costs more than the hand-off it waits for), then falls
-// back to the parking wait.
+// may park the thread, and waking it costs more than the hand-off it waits for) and looks at
+// the abort flag only on the slow path -- under load every shared-memory round trip of the
+// waiting thread costs a hundred clocks or more.
 __device__ __forceinline__ bool mbar_wait_hot(uint64_t *bar, uint32_t parity, volatile int *abort_flag,
                                               int *status, int code) {
-    if (*abort_flag) return false;
 #pragma unroll 1
     for (uint32_t spin = 0; spin < 4096; ++spin)
         if (mbar_test(bar, parity)) return true;

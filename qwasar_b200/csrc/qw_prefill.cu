@@ -59,12 +59,16 @@ constexpr int SMEM_BYTES = OFF_XCH + 2 * 2 * BM * 4;  // the dynamic window is d
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
 constexpr int THREADS = 12 * 32;                      // 8 softmax warps, Q K^T issue, K loads, V loads, P V issue
 constexpr int W_MMA = 8, W_K = 9, W_V = 10, W_PV = 11;
+#ifndef QW_QK_AFTER_PV
+#define QW_QK_AFTER_PV 1
+#endif
+constexpr bool QK_AFTER_PV = QW_QK_AFTER_PV;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
 enum Bar { Q_READY = 0, Q_FULL, G_FULL, K_FULL0, K_FULL1, K_FREE0, K_FREE1, V_FULL0, V_FULL1, V_FREE0, V_FREE1,
-           S_READY, S_FREE, P_READY, PV_DONE, N_BARS };
+           S_READY, S_FREE, P_READY, PV_DONE, PV_ISSUED, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -257,8 +261,14 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             for (int j = 0; j < n_t; j++) {
                 const int st = j & 1;
                 // S is handed back as soon as the softmax threads hold step j-1 in registers
-                if (j > 0) mbar_wait_hot(&bars[S_FREE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                // The waits that are normally over long before come first: even a satisfied wait
+                // costs a few hundred clocks here.
                 mbar_wait_hot(&bars[K_FULL0 + st], (j >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                if (j > 0) mbar_wait_hot(&bars[S_FREE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                // P V of step j-2 goes into the tensor queue first: queued side by side the two
+                // products share the pipe, and the softmax threads wait for the end of P V before
+                // they may write the next P -- which they then do under this product.
+                if (QK_AFTER_PV && j > 1) mbar_wait_hot(&bars[PV_ISSUED], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
                 tc_fence_after();
                 const uint32_t k_lo = desc_lo(k_a + st * K_BYTES, 16);
                 // A: 16 dims of Q = 8 TMEM columns; B: 16 dims = 32 bytes (2 units) inside the swizzle atom,
@@ -279,11 +289,17 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             const uint32_t v_a = smem_u32(smem + OFF_V), p_a = smem_u32(smem + OFF_P);
             const uint32_t p_lo = desc_lo(p_a, 16);
             for (int j = 0; j < n_t; j++) {
+                // the first V page (normally there already), then the weights; the second page
+                // was requested only when the step before ended and lands under the first half
+                mbar_wait_hot(&bars[V_FULL0], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 mbar_wait_hot(&bars[P_READY], j & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                tc_fence_after();
 #pragma unroll
                 for (int h = 0; h < 2; h++) {                  // the two 64-key pages of the step
-                    mbar_wait_hot(&bars[V_FULL0 + h], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-                    tc_fence_after();
+                    if (h == 1) {
+                        mbar_wait_hot(&bars[V_FULL1], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                        tc_fence_after();
+                    }
                     const uint32_t v_lo = desc_lo(v_a + h * V_BYTES, VBOX);
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++) {
@@ -295,6 +311,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     tc_commit(&bars[V_FREE0 + h]);
                 }
                 tc_commit(&bars[PV_DONE]);
+                if (QK_AFTER_PV) mbar_arrive(&bars[PV_ISSUED]);
             }
         }
     } else {

@@ -398,8 +398,13 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     s[e >> 1] = pack_bf16(x0, x1);      // slot e/2 <= e: already consumed
                 }
             };
-            weights(s0, la); weights(s1, lb);
-            l = l * alpha + (la + lb);
+            // 16 packed pairs per 32 scores = 4 chunks of 16 bytes
+            auto store_p = [&](const uint32_t(&s)[32], int chunk0) {
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    *reinterpret_cast<uint4 *>(p_row + (((chunk0 + c) ^ sw) << 4)) = make_uint4(s[c * 4], s[c * 4 + 1], s[c * 4 + 2], s[c * 4 + 3]);
+            };
+            weights(s0, la);
             // P_{j-1} must have been consumed (and O complete) before P is overwritten or O rescaled
             if (j > 0) {
                 mbar_wait_hot(&bars[PV_DONE], (j - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
@@ -416,12 +421,10 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 }
                 tmem_wait_st();
             }
-            // 16 packed pairs per 32 scores = 4 chunks of 16 bytes
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                *reinterpret_cast<uint4 *>(p_row + ((c ^ sw) << 4)) = make_uint4(s0[c * 4], s0[c * 4 + 1], s0[c * 4 + 2], s0[c * 4 + 3]);
-                *reinterpret_cast<uint4 *>(p_row + (((4 + c) ^ sw) << 4)) = make_uint4(s1[c * 4], s1[c * 4 + 1], s1[c * 4 + 2], s1[c * 4 + 3]);
-            }
+            store_p(s0, 0);               // drains under the second half's exponentials
+            weights(s1, lb);
+            store_p(s1, 4);
+            l = l * alpha + (la + lb);
             fence_proxy_async();          // generic-proxy writes -> visible to the tensor core's reads
             tc_fence_before();
             __syncwarp();

@@ -52,6 +52,7 @@ struct PreopSeq {
 struct PreopParams {
     PreopSeq seq[QW_MAX_SEQ];
     int32_t n_seq, q_heads, kv_heads, rotary_dim, io_dtype;
+    int32_t vec_io;                        // every qg / k / v pointer is 16-byte aligned: rows move as 16-byte pieces
     const uint16_t *q_norm_w, *k_norm_w;   // bf16 [256] or nullptr
     const uint8_t *axis;
     const float *inv_freq;

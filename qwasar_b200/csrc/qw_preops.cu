@@ -132,10 +132,45 @@ __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float 
     }
 }
 
+// A 256-wide head row between global memory and the lane layout above (lane l holds dims
+// l + 32 i), through a per-warp row buffer in shared memory: global accesses are 16 bytes per
+// lane (one or two instructions per row instead of eight 2- or 4-byte ones), and the strided
+// shared-memory accesses are conflict-free.
+__device__ __forceinline__ void load_row(float (&x)[8], const void *src, size_t first, int dtype, bool vec, uint32_t *buf, int lane) {
+    if (!vec) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = load_io(src, first + lane + 32 * i, dtype);
+    } else if (dtype == DT_BF16) {
+        reinterpret_cast<uint4 *>(buf)[lane] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(src) + first) + lane);
+        __syncwarp();
+        const uint16_t *h = reinterpret_cast<const uint16_t *>(buf);
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = bf16_bits_to_f32(h[lane + 32 * i]);
+    } else {
+        const uint4 *g = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(src) + first);
+        reinterpret_cast<uint4 *>(buf)[lane] = __ldg(g + lane);
+        reinterpret_cast<uint4 *>(buf)[lane + 32] = __ldg(g + lane + 32);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; i++) x[i] = __uint_as_float(buf[lane + 32 * i]);
+    }
+    __syncwarp();
+}
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16 *dst, const float (&x)[8], uint32_t *buf, int lane) {
+    __nv_bfloat16 *h = reinterpret_cast<__nv_bfloat16 *>(buf);
+#pragma unroll
+    for (int i = 0; i < 8; i++) h[lane + 32 * i] = __float2bfloat16_rn(x[i]);
+    __syncwarp();
+    reinterpret_cast<uint4 *>(dst)[lane] = reinterpret_cast<const uint4 *>(buf)[lane];
+    __syncwarp();
+}
+
 // ---- the fused pre-op ---------------------------------------------------------------------
 // grid = (max_rows * ceil(slots / 8), 1, n_seq) with slots = q_heads + 2 * kv_heads; one warp per
 // (sequence, row, slot): slot < q_heads is a query head, then the key heads, then the value heads.
 __global__ void __launch_bounds__(256) preop_kernel(const __grid_constant__ PreopParams p) {
+    __shared__ __align__(16) uint32_t rowbuf[8][256];
+    uint32_t *buf = rowbuf[threadIdx.x >> 5];
     const PreopSeq &s = p.seq[blockIdx.z];
     const int nblk = (p.q_heads + 2 * p.kv_heads + 7) / 8;
     const int r = blockIdx.x / nblk;
@@ -147,34 +182,24 @@ __global__ void __launch_bounds__(256) preop_kernel(const __grid_constant__ Preo
 
     float x[8];
     if (slot < qh) {
-        const size_t src = ((size_t)r * qh + slot) * 512;
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = load_io(s.qg, src + lane + 32 * i, p.io_dtype);
+        load_row(x, s.qg, ((size_t)r * qh + slot) * 512, p.io_dtype, p.vec_io != 0, buf, lane);
         norm8(x, p.q_norm_w, lane, p.eps, 1.0f);
         rope64(x, s.pos, p.axis, p.inv_freq, s.rows, r, lane);
-        __nv_bfloat16 *dst = s.q_out + ((size_t)r * qh + slot) * 256;
-#pragma unroll
-        for (int i = 0; i < 8; i++) dst[lane + 32 * i] = __float2bfloat16_rn(x[i]);
+        store_row_bf16(s.q_out + ((size_t)r * qh + slot) * 256, x, buf, lane);
     } else if (slot < qh + kvh) {
         const int h = slot - qh;
-        const size_t src = ((size_t)r * kvh + h) * 256;
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = load_io(s.k, src + lane + 32 * i, p.io_dtype);
+        load_row(x, s.k, ((size_t)r * kvh + h) * 256, p.io_dtype, p.vec_io != 0, buf, lane);
         norm8(x, p.k_norm_w, lane, p.eps, 1.0f);
         rope64(x, s.pos, p.axis, p.inv_freq, s.rows, r, lane);
         const int64_t row = kv_row(s.kc, h, s.base_pos + r);
         if (row < 0) return;
-        __nv_bfloat16 *dst = s.kc.base + row * 256;
-#pragma unroll
-        for (int i = 0; i < 8; i++) dst[lane + 32 * i] = __float2bfloat16_rn(x[i]);
+        store_row_bf16(s.kc.base + row * 256, x, buf, lane);
     } else {
         const int h = slot - qh - kvh;
-        const size_t src = ((size_t)r * kvh + h) * 256;
         const int64_t row = kv_row(s.vc, h, s.base_pos + r);
         if (row < 0) return;
-        __nv_bfloat16 *dst = s.vc.base + row * 256;
-#pragma unroll
-        for (int i = 0; i < 8; i++) dst[lane + 32 * i] = __float2bfloat16_rn(load_io(s.v, src + lane + 32 * i, p.io_dtype));
+        load_row(x, s.v, ((size_t)r * kvh + h) * 256, p.io_dtype, p.vec_io != 0, buf, lane);
+        store_row_bf16(s.vc.base + row * 256, x, buf, lane);
     }
 }
 

@@ -1104,6 +1104,9 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
         ps.q_out = q_out[i];
         ps.rows = rows; ps.base_pos = s[i].base_pos;
     }
+    p.vec_io = 1;
+    for (int i = 0; i < n_seq; i++)
+        if ((reinterpret_cast<uintptr_t>(p.seq[i].qg) | reinterpret_cast<uintptr_t>(p.seq[i].k) | reinterpret_cast<uintptr_t>(p.seq[i].v)) & 15) p.vec_io = 0;
     launch_preop(c->stream, p, rows);
     return cuda_ok(c, cudaGetLastError(), "pre-op launch");
 }

@@ -159,12 +159,12 @@ uint64_t    qw_gpu_launch_count(void);
 /* Diagnostic knobs (the counterpart of the reference's QWASAR_ATTN / QWASAR_FA overrides,
  * qwasar_metal.m:1513-1516): "split_kg" = 4 | 6, consumer warps per 16-row tile of the
  * split-KV kernel; "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
- * split-KV kernel over row chunks; "prefill_pair" = 0 | 1, the tcgen05 prefill as one CTA per
- * 128-row tile (default) or as a CTA pair per 256-row tile (cta_group::2 MMAs, K and V halves
- * shared across the pair).  Returns false for an unknown knob or value. */
+ * split-KV kernel over row chunks; "prefill_fuse_q" = 1 | 0, with bf16 rows the tcgen05 prefill norms and
+ * rotates its own query tiles (default) or the pre-op kernel does.  Returns false for an unknown
+ * knob or value. */
 bool        qw_gpu_tune(const char *knob, int32_t value);
 /* Per-kernel device timing for roofline figures: while on, every launch of an attention
- * kernel ("qw_attn_split", "qw_attn_prefill") is bracketed by a pair of CUDA events on its
+ * kernel ("qw_attn_split", "qw_attn_prefill", "qw_attn_preop") is bracketed by a pair of CUDA events on its
  * stream; qw_cmd_wait folds the elapsed times into per-kernel totals that
  * qw_prof_kernel_read returns (false for an unknown name). */
 void        qw_prof_kernels(bool on);

@@ -628,7 +628,7 @@ int row_tiles(int max_rows, int gqa) {
 unsigned long long g_launches = 0;
 int g_tune_split_kg = 6;
 int g_tune_prefill_tc = 1;
-int g_tune_prefill_pair = 0;
+int g_tune_prefill_fuse_q = 1;
 
 int sm_count() {
     static int n = 0;

@@ -46,6 +46,7 @@ struct PreopSeq {
     const void *k, *v;       // [rows, kv_heads, 256]  (io dtype)
     const int32_t *pos;      // [3, rows]
     __nv_bfloat16 *q_out;    // [rows, q_heads, 256]
+    float *cs_out;           // nullptr, or [rows, 64]: cos then sin of the 32 rotation angles of every row
     KvLayer kc, vc;
     int32_t rows, base_pos;
 };
@@ -53,6 +54,7 @@ struct PreopParams {
     PreopSeq seq[QW_MAX_SEQ];
     int32_t n_seq, q_heads, kv_heads, rotary_dim, io_dtype;
     int32_t vec_io;                        // every qg / k / v pointer is 16-byte aligned: rows move as 16-byte pieces
+    int32_t skip_q;                        // leave the query heads alone (the prefill kernel norms and rotates its own tiles)
     const uint16_t *q_norm_w, *k_norm_w;   // bf16 [256] or nullptr
     const uint8_t *axis;
     const float *inv_freq;
@@ -99,6 +101,13 @@ struct PrefillParams {
     // [rows][q_heads*256] bf16; out the same shape in out_dtype; gate as [rows][q_heads*gate_stride]
     // in gate_dtype (== out_dtype).  Bases 16-byte aligned, row pitches multiples of 16 bytes.
     CUtensorMap qmap, omap, gmap;
+    // fuse_q: qmap covers the raw [q|gate] rows ([rows][q_heads*512] bf16) and the kernel applies the
+    // per-head RMS norm (weights q_norm_w, bf16 [256] or nullptr) and the partial RoPE itself, with the
+    // angles' cos / sin read from csmap ([rows][64] f32, written by the pre-op's key warps).
+    CUtensorMap csmap;
+    const uint16_t *q_norm_w;
+    float eps;
+    int32_t fuse_q;
     KvLayer kc, vc;
     void *out;               // [rows, q_heads, 256] f32 or bf16
     const void *gate;        // nullptr or element (r, h, d) at gate[(r*q_heads + h)*gate_stride + d]
@@ -111,9 +120,6 @@ struct PrefillParams {
 void launch_attn_prefill(cudaStream_t s, const PrefillParams &p);
 // Whether out / gate can be described by the tile maps above (alignment, equal dtypes).
 bool attn_prefill_io_ok(const void *out, int out_dtype, const void *gate, int gate_dtype, int gate_stride);
-// The same attention with the two query heads 2u, 2u+1 of a row tile as one CTA pair (even grouping only).
-bool attn_prefill_pair_ok(const PrefillParams &p);
-void launch_attn_prefill_pair(cudaStream_t s, const PrefillParams &p);
 
 // Per-query fp32 kernel (CUDA cores, no rounding of q or of the weights).
 void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale,
@@ -135,7 +141,7 @@ extern unsigned long long g_launches;
 extern int g_tune_split_kg;
 // 1: many-row attention runs on the tcgen05 kernel; 0: on the split-KV kernel over row chunks.
 extern int g_tune_prefill_tc;
-// 1: the tcgen05 prefill runs as CTA pairs (cta_group::2) where the grouping is even; 0: one CTA per head.
-extern int g_tune_prefill_pair;
+// 1: with bf16 rows the tcgen05 prefill norms and rotates its own query tiles; 0: the pre-op does.
+extern int g_tune_prefill_fuse_q;
 
 }  // namespace qw

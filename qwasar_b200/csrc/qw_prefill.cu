@@ -55,7 +55,8 @@ constexpr int OFF_STAGE_Q = OFF_V, OFF_STAGE_IO = OFF_K;
 static_assert(4 * IO_BOX <= 2 * V_BYTES && 8 * IO_BOX <= 2 * K_BYTES, "staging overruns the operand regions");
 constexpr int COL_O = 0, COL_Q = 256, COL_S = 384;    // TMEM columns
 constexpr int OFF_XCH = OFF_BAR + 256;                // row maxima / sums passed between the two softmax halves
-constexpr int SMEM_BYTES = OFF_XCH + 2 * 2 * BM * 4;  // the dynamic window is declared 1024-byte aligned
+constexpr int OFF_WQ = OFF_XCH + 2 * 2 * BM * 4;      // the query norm weights (bf16 [256]) when the kernel norms its own tiles
+constexpr int SMEM_BYTES = OFF_WQ + 512;              // the dynamic window is declared 1024-byte aligned
 static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB a CTA may use");
 constexpr int THREADS = 12 * 32;                      // 8 softmax warps, Q K^T issue, K loads, V loads, P V issue
 constexpr int W_MMA = 8, W_K = 9, W_V = 10, W_PV = 11;
@@ -190,6 +191,9 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
         mbar_fence_init();
     }
     if (warp == W_MMA) tmem_alloc(tmem_slot, 512);
+    if (warp == W_K && p.fuse_q)                       // weights: 32 lanes x 8 bf16 (1.0 where there are none)
+        reinterpret_cast<uint4 *>(smem + OFF_WQ)[lane] =
+            p.q_norm_w ? __ldg(reinterpret_cast<const uint4 *>(p.q_norm_w) + lane) : make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -233,10 +237,16 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     } else if (warp == W_V) {
         // ---------------- V pages ----------------
         if (lane == 0) {
-            mbar_expect_tx(&bars[Q_FULL], 4 * IO_BOX);
+            // the Q tile (raw q rows of the [q|gate] input when the kernel norms and rotates them
+            // itself, then together with the rows' cos / sin, parked in the P region)
+            mbar_expect_tx(&bars[Q_FULL], (p.fuse_q ? 6 : 4) * IO_BOX);
 #pragma unroll
             for (int b = 0; b < 4; b++)
-                tma_load_2d(smem + OFF_STAGE_Q + b * IO_BOX, &p.qmap, head * 256 + b * 64, q0, &bars[Q_FULL]);
+                tma_load_2d(smem + OFF_STAGE_Q + b * IO_BOX, &p.qmap, head * (p.fuse_q ? 512 : 256) + b * 64, q0, &bars[Q_FULL]);
+            if (p.fuse_q) {
+                tma_load_2d(smem + OFF_P, &p.csmap, 0, q0, &bars[Q_FULL]);
+                tma_load_2d(smem + OFF_P + IO_BOX, &p.csmap, 32, q0, &bars[Q_FULL]);
+            }
             mbar_wait(&bars[Q_READY], 0, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the Q tile borrowed this region
             for (int pg = 0; pg < 2 * n_t; pg++) {
                 const int st = pg & 1;
@@ -337,14 +347,78 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             // the chunk read as zeros.
             const uint8_t *q_row = smem + OFF_STAGE_Q + row_l * 128;
             mbar_wait(&bars[Q_FULL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+            if (!p.fuse_q) {
 #pragma unroll
-            for (int c = 2 * wg; c < 2 * wg + 2; c++) {
+                for (int c = 2 * wg; c < 2 * wg + 2; c++) {
 #pragma unroll
-                for (int e = 0; e < 8; e++) {
-                    const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
-                    v[e * 4] = x.x; v[e * 4 + 1] = x.y; v[e * 4 + 2] = x.z; v[e * 4 + 3] = x.w;
+                    for (int e = 0; e < 8; e++) {
+                        const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
+                        v[e * 4] = x.x; v[e * 4 + 1] = x.y; v[e * 4 + 2] = x.z; v[e * 4 + 3] = x.w;
+                    }
+                    tmem_st32(t_q + lane_base + c * 32, v);
                 }
-                tmem_st32(t_q + lane_base + c * 32, v);
+            } else {
+                // Per-head RMS norm and partial RoPE of the raw rows, operation for operation as the
+                // pre-op does them (qwasar_cpu.c:68-82, 304-319) except for the order of the sum of
+                // squares: each of the row's two threads sums its 128 dims, the halves are added.
+                float ss = 0.0f;
+#pragma unroll
+                for (int c = 2 * wg; c < 2 * wg + 2; c++) {
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
+                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float lo = __uint_as_float(xw[i] << 16), hi = __uint_as_float(xw[i] & 0xffff0000u);
+                            ss = __fadd_rn(ss, __fmul_rn(lo, lo));
+                            ss = __fadd_rn(ss, __fmul_rn(hi, hi));
+                        }
+                    }
+                }
+                // (through the odd steps' exchange slots: step 0 writes the even ones right away)
+                xch[2 * BM + wg * BM + row_l] = ss;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                ss = __fadd_rn(xch[2 * BM + row_l], xch[3 * BM + row_l]);
+                const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
+                const uint4 *wq = reinterpret_cast<const uint4 *>(smem + OFF_WQ);
+                const uint8_t *cs_row = smem + OFF_P + row_l * 128;
+#pragma unroll
+                for (int c = 2 * wg; c < 2 * wg + 2; c++) {
+                    float t[64];                                   // box c: dims 64c .. 64c+63, normed
+#pragma unroll
+                    for (int e = 0; e < 8; e++) {
+                        const uint4 x = *reinterpret_cast<const uint4 *>(q_row + c * IO_BOX + ((e ^ sw) << 4));
+                        const uint32_t xw[4] = {x.x, x.y, x.z, x.w};
+                        const uint4 w4 = wq[c * 8 + e];
+                        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            float lo = __fmul_rn(__uint_as_float(xw[i] << 16), inv), hi = __fmul_rn(__uint_as_float(xw[i] & 0xffff0000u), inv);
+                            if (p.q_norm_w) { lo = __fmul_rn(lo, __uint_as_float(ww[i] << 16)); hi = __fmul_rn(hi, __uint_as_float(ww[i] & 0xffff0000u)); }
+                            t[e * 8 + 2 * i] = lo; t[e * 8 + 2 * i + 1] = hi;
+                        }
+                    }
+                    if (c == 0) {
+                        // pairs (d, d + 32), d < 32; cos in the first box of the row's table, sin in the second
+#pragma unroll
+                        for (int k = 0; k < 8; k++) {
+                            const float4 cs = *reinterpret_cast<const float4 *>(cs_row + ((k ^ sw) << 4));
+                            const float4 sn = *reinterpret_cast<const float4 *>(cs_row + IO_BOX + ((k ^ sw) << 4));
+                            const float c4[4] = {cs.x, cs.y, cs.z, cs.w}, s4[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const int d = k * 4 + i;
+                                const float lo = t[d], hi = t[d + 32];
+                                t[d] = __fsub_rn(__fmul_rn(lo, c4[i]), __fmul_rn(hi, s4[i]));
+                                t[d + 32] = __fadd_rn(__fmul_rn(hi, c4[i]), __fmul_rn(lo, s4[i]));
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < 32; e++) v[e] = pack_bf16(t[2 * e], t[2 * e + 1]);
+                    tmem_st32(t_q + lane_base + c * 32, v);
+                }
             }
             tmem_wait_st();
             tc_fence_before();

@@ -2,8 +2,7 @@
 // partial RoPE, KV append, sigmoid gate -- as separate kernels behind the
 // reference's op signatures, and as one fused kernel for the node.
 //
-// All of it is HBM-bound element work: one warp owns one 256-wide head row, loads
-// and stores are 128 B per warp instruction, and nothing is read twice.
+// All of it is element work on 256-wide head rows, one warp per row, nothing read twice.
 //
 // Arithmetic follows the reference's scalar twins operation for operation
 // (qwasar_cpu.c:68-82, 304-319, 344-355) with contraction switched off through
@@ -18,33 +17,6 @@ namespace {
 __device__ __forceinline__ float load_io(const void *p, size_t i, int dtype) {
     return dtype == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i])
                             : reinterpret_cast<const float *>(p)[i];
-}
-
-// Lane l of a warp holds dims l, l+32, ..., l+224 of a head row, so that the RoPE
-// pair (j, j + 32) for j < 32 sits in one lane (x[0], x[1]).
-__device__ __forceinline__ void norm8(float (&x)[8], const uint16_t *w, int lane, float eps, float out_scale) {
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
-    ss = warp_sum(ss);
-    const float inv = __fmul_rn(__fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), eps))), out_scale);
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        float t = __fmul_rn(x[i], inv);
-        if (w) t = __fmul_rn(t, bf16_bits_to_f32(w[lane + 32 * i]));
-        x[i] = t;
-    }
-}
-
-// Rotates (x[0], x[1]) = dims (lane, lane + 32); rotary_dim == 64 here.
-__device__ __forceinline__ void rope64(float (&x)[8], const int32_t *pos, const uint8_t *axis,
-                                       const float *inv_freq, int rows, int r, int lane) {
-    const float ang = __fmul_rn((float)pos[(size_t)axis[lane] * rows + r], inv_freq[lane]);
-    float sn, cs;
-    sincosf(ang, &sn, &cs);
-    const float lo = x[0], hi = x[1];
-    x[0] = __fsub_rn(__fmul_rn(lo, cs), __fmul_rn(hi, sn));
-    x[1] = __fadd_rn(__fmul_rn(hi, cs), __fmul_rn(lo, sn));
 }
 
 // ---- unfused ops, reference signatures ------------------------------------------------
@@ -132,74 +104,126 @@ __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float 
     }
 }
 
-// A 256-wide head row between global memory and the lane layout above (lane l holds dims
-// l + 32 i), through a per-warp row buffer in shared memory: global accesses are 16 bytes per
-// lane (one or two instructions per row instead of eight 2- or 4-byte ones), and the strided
-// shared-memory accesses are conflict-free.
-__device__ __forceinline__ void load_row(float (&x)[8], const void *src, size_t first, int dtype, bool vec, uint32_t *buf, int lane) {
-    if (!vec) {
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = load_io(src, first + lane + 32 * i, dtype);
-    } else if (dtype == DT_BF16) {
-        reinterpret_cast<uint4 *>(buf)[lane] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(src) + first) + lane);
-        __syncwarp();
-        const uint16_t *h = reinterpret_cast<const uint16_t *>(buf);
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = bf16_bits_to_f32(h[lane + 32 * i]);
-    } else {
-        const uint4 *g = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(src) + first);
-        reinterpret_cast<uint4 *>(buf)[lane] = __ldg(g + lane);
-        reinterpret_cast<uint4 *>(buf)[lane + 32] = __ldg(g + lane + 32);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 8; i++) x[i] = __uint_as_float(buf[lane + 32 * i]);
-    }
-    __syncwarp();
-}
-__device__ __forceinline__ void store_row_bf16(__nv_bfloat16 *dst, const float (&x)[8], uint32_t *buf, int lane) {
-    __nv_bfloat16 *h = reinterpret_cast<__nv_bfloat16 *>(buf);
-#pragma unroll
-    for (int i = 0; i < 8; i++) h[lane + 32 * i] = __float2bfloat16_rn(x[i]);
-    __syncwarp();
-    reinterpret_cast<uint4 *>(dst)[lane] = reinterpret_cast<const uint4 *>(buf)[lane];
-    __syncwarp();
-}
-
 // ---- the fused pre-op ---------------------------------------------------------------------
-// grid = (max_rows * ceil(slots / 8), 1, n_seq) with slots = q_heads + 2 * kv_heads; one warp per
-// (sequence, row, slot): slot < q_heads is a query head, then the key heads, then the value heads.
-__global__ void __launch_bounds__(256) preop_kernel(const __grid_constant__ PreopParams p) {
-    __shared__ __align__(16) uint32_t rowbuf[8][256];
-    uint32_t *buf = rowbuf[threadIdx.x >> 5];
+// grid = (ceil(max_rows / PRE_ROWS) * ceil(slots / 8), 1, n_seq) with slots = q_heads + 2 * kv_heads
+// (the query heads are left out when the prefill kernel norms its own tiles).  A block covers
+// PRE_ROWS consecutive tokens and eight slots, one warp per slot: slot < q_heads is a query head,
+// then the key heads, then the value heads.
+//
+// Lane l holds the eight consecutive dims 8l .. 8l+7 of a head row: one 16-byte load and one
+// 16-byte store per bf16 row and lane, no staging.  The RoPE pair (d, d + 32), d < 32, then sits
+// in lanes l and l ^ 4 (l < 8) at the same register.  The 32 angles of a token are the same for
+// all its heads: the block's first PRE_ROWS warps compute cos / sin once, into shared memory.
+// The kernel issues few bytes per instruction, so the instruction count per row is what it pays for.
+constexpr int PRE_ROWS = 4;
+__global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
+    __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
     const PreopSeq &s = p.seq[blockIdx.z];
-    const int nblk = (p.q_heads + 2 * p.kv_heads + 7) / 8;
-    const int r = blockIdx.x / nblk;
-    if (r >= s.rows) return;
-    const int slot = (blockIdx.x % nblk) * 8 + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
     const int qh = p.q_heads, kvh = p.kv_heads;
-    if (slot >= qh + 2 * kvh) return;
+    const int qs = p.skip_q ? 0 : qh;                    // query slots this launch handles
+    const int nblk = (qs + 2 * kvh + 7) / 8;
+    const int r0 = (blockIdx.x / nblk) * PRE_ROWS;
+    if (r0 >= s.rows) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot0 = (blockIdx.x % nblk) * 8, slot = slot0 + warp;
+    const int n = min(PRE_ROWS, s.rows - r0);
+    const bool active = slot < qs + 2 * kvh;             // (idle warps still help with the angles below)
+    const bool is_q = slot < qs, is_k = !is_q && slot < qs + kvh;
+    const int h = !active ? 0 : is_q ? slot : is_k ? slot - qs : slot - qs - kvh;
+    const void *src = is_q ? s.qg : is_k ? s.k : s.v;
+    const size_t pitch = is_q ? (size_t)qh * 512 : (size_t)kvh * 256, off = is_q ? (size_t)h * 512 : (size_t)h * 256;
+    __nv_bfloat16 *dst = is_q ? s.q_out : is_k ? s.kc.base : s.vc.base;
+    const uint16_t *wn = is_q ? p.q_norm_w : p.k_norm_w;
 
-    float x[8];
-    if (slot < qh) {
-        load_row(x, s.qg, ((size_t)r * qh + slot) * 512, p.io_dtype, p.vec_io != 0, buf, lane);
-        norm8(x, p.q_norm_w, lane, p.eps, 1.0f);
-        rope64(x, s.pos, p.axis, p.inv_freq, s.rows, r, lane);
-        store_row_bf16(s.q_out + ((size_t)r * qh + slot) * 256, x, buf, lane);
-    } else if (slot < qh + kvh) {
-        const int h = slot - qh;
-        load_row(x, s.k, ((size_t)r * kvh + h) * 256, p.io_dtype, p.vec_io != 0, buf, lane);
-        norm8(x, p.k_norm_w, lane, p.eps, 1.0f);
-        rope64(x, s.pos, p.axis, p.inv_freq, s.rows, r, lane);
-        const int64_t row = kv_row(s.kc, h, s.base_pos + r);
-        if (row < 0) return;
-        store_row_bf16(s.kc.base + row * 256, x, buf, lane);
-    } else {
-        const int h = slot - qh - kvh;
-        const int64_t row = kv_row(s.vc, h, s.base_pos + r);
-        if (row < 0) return;
-        load_row(x, s.v, ((size_t)r * kvh + h) * 256, p.io_dtype, p.vec_io != 0, buf, lane);
-        store_row_bf16(s.vc.base + row * 256, x, buf, lane);
+    // all rows of the warp in flight before the first is touched, and before the angles
+    uint4 raw[PRE_ROWS][2];
+    int64_t dst_row[PRE_ROWS];
+#pragma unroll
+    for (int u = 0; u < PRE_ROWS; u++) {
+        if (!active) { dst_row[u] = -1; continue; }
+        const int r = min(r0 + u, s.rows - 1);
+        const size_t first = (size_t)r * pitch + off + lane * 8;
+        raw[u][1] = make_uint4(0, 0, 0, 0);
+        if (!p.vec_io) {
+            // operands that are not 16-byte aligned: element loads
+            float e[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = load_io(src, first + i, p.io_dtype);
+            if (p.io_dtype == DT_BF16) {
+                raw[u][0] = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+            } else {
+                raw[u][0] = make_uint4(__float_as_uint(e[0]), __float_as_uint(e[1]), __float_as_uint(e[2]), __float_as_uint(e[3]));
+                raw[u][1] = make_uint4(__float_as_uint(e[4]), __float_as_uint(e[5]), __float_as_uint(e[6]), __float_as_uint(e[7]));
+            }
+        } else if (p.io_dtype == DT_BF16) {
+            raw[u][0] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(src) + first));
+        } else {
+            const uint4 *g = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(src) + first);
+            raw[u][0] = __ldg(g);
+            raw[u][1] = __ldg(g + 1);
+        }
+        dst_row[u] = is_q ? (int64_t)r * qh + h : kv_row(is_k ? s.kc : s.vc, h, s.base_pos + r);
+    }
+    if (slot0 < qs + kvh) {                              // the block holds a query or key head
+        if (warp < n) {
+            const int r = r0 + warp;
+            const float ang = __fmul_rn((float)s.pos[(size_t)p.axis[lane] * s.rows + r], p.inv_freq[lane]);
+            float sn, cs;
+            sincosf(ang, &sn, &cs);
+            cs_s[warp][lane] = cs; cs_s[warp][32 + lane] = sn;
+            if (s.cs_out && slot0 <= qs && qs < slot0 + 8) {          // the block with key head 0 publishes the table
+                s.cs_out[(size_t)r * 64 + lane] = cs; s.cs_out[(size_t)r * 64 + 32 + lane] = sn;
+            }
+        }
+        __syncthreads();
+    }
+    if (!active) return;
+    float w[8];
+    if (wn && (is_q || is_k)) {
+        const uint4 w4 = __ldg(reinterpret_cast<const uint4 *>(wn) + lane);
+        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(ww[i] << 16); w[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }
+    }
+#pragma unroll
+    for (int u = 0; u < PRE_ROWS; u++) {
+        if (u >= n || dst_row[u] < 0) continue;          // warp-uniform
+        uint4 *out = reinterpret_cast<uint4 *>(dst + dst_row[u] * 256) + lane;
+        if (!is_q && !is_k && p.io_dtype == DT_BF16) { *out = raw[u][0]; continue; }      // V, already bf16: a copy
+        float x[8];
+        if (p.io_dtype == DT_BF16) {
+            const uint32_t xw[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) { x[2 * i] = __uint_as_float(xw[i] << 16); x[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u); }
+        } else {
+            x[0] = __uint_as_float(raw[u][0].x); x[1] = __uint_as_float(raw[u][0].y); x[2] = __uint_as_float(raw[u][0].z); x[3] = __uint_as_float(raw[u][0].w);
+            x[4] = __uint_as_float(raw[u][1].x); x[5] = __uint_as_float(raw[u][1].y); x[6] = __uint_as_float(raw[u][1].z); x[7] = __uint_as_float(raw[u][1].w);
+        }
+        if (is_q || is_k) {
+            // RMS norm (qwasar_cpu.c:68-82), then the weight
+            float ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+            ss = warp_sum(ss);
+            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                x[i] = __fmul_rn(x[i], inv);
+                if (wn) x[i] = __fmul_rn(x[i], w[i]);
+            }
+            // partial RoPE (qwasar_cpu.c:304-319): dims d < 32 in lanes 0-3, their partners d + 32 in lanes 4-7
+            const float *cr = cs_s[u] + 8 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float other = __shfl_xor_sync(0xffffffffu, x[i], 4);
+                if (lane < 8) {
+                    const float c = cr[i], sn = cr[32 + i];
+                    x[i] = lane < 4 ? __fsub_rn(__fmul_rn(x[i], c), __fmul_rn(other, sn))      // lo' = lo c - hi s
+                                    : __fadd_rn(__fmul_rn(x[i], c), __fmul_rn(other, sn));     // hi' = hi c + lo s
+                }
+            }
+        }
+        *out = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
     }
 }
 
@@ -243,8 +267,9 @@ void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, in
     g_launches++;
 }
 void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
-    const int slots = p.q_heads + 2 * p.kv_heads;
-    dim3 grid((unsigned)max_rows * ((slots + 7) / 8), 1, p.n_seq);
+    const int slots = (p.skip_q ? 0 : p.q_heads) + 2 * p.kv_heads;
+    if (slots == 0) return;
+    dim3 grid((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
     preop_kernel<<<grid, 256, 0, s>>>(p);
     g_launches++;
 }

@@ -465,9 +465,13 @@ bool run_split(qw_cmd c, AttnParams &p, int max_rows) {
 }
 
 // The tcgen05 prefill kernel over one sequence: q_bf16 is [rows, q_heads, 256] in device memory.
+// With cs_table != nullptr, q_bf16 is instead the raw [rows, q_heads, 512] bf16 [q|gate] input: the kernel
+// norms (weights q_norm_w or nullptr, eps) and rotates its own query tiles, with the angles' cos / sin from
+// cs_table ([rows, 64] f32, left by the pre-op).
 bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype, const void *gate, int gate_dtype,
                  int gate_stride, qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads, int32_t kv_heads,
-                 int32_t max_ctx, int32_t base_pos, float scale) {
+                 int32_t max_ctx, int32_t base_pos, float scale, const float *cs_table = nullptr,
+                 const uint16_t *q_norm_w = nullptr, float eps = 0.0f) {
     PrefillParams p;
     memset(&p, 0, sizeof p);
     int64_t k_rows = 0, v_rows = 0;
@@ -481,14 +485,16 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
     p.scale = scale;
     p.status = G.status_dev;
     const uint64_t row = (uint64_t)q_heads * 256;
-    if (!encode_tile_map(&p.qmap, q_bf16, DT_BF16, row, row, rows) || !encode_tile_map(&p.omap, out, out_dtype, row, row, rows) ||
+    p.fuse_q = cs_table != nullptr; p.q_norm_w = q_norm_w; p.eps = eps;
+    if (p.fuse_q && !encode_tile_map(&p.csmap, cs_table, DT_F32, 64, 64, rows)) return cmd_fail(c, "%s", "prefill: tensor map encoding failed"), false;
+    if (!encode_tile_map(&p.qmap, q_bf16, DT_BF16, p.fuse_q ? 2 * row - 256 : row, p.fuse_q ? 2 * row : row, rows) ||
+        !encode_tile_map(&p.omap, out, out_dtype, row, row, rows) ||
         (gate && !encode_tile_map(&p.gmap, gate, gate_dtype, (uint64_t)(q_heads - 1) * gate_stride + 256, (uint64_t)q_heads * gate_stride, rows)))
         return cmd_fail(c, "%s", "prefill: tensor map encoding failed"), false;
     KTime kt = {nullptr, nullptr, "qw_attn_prefill"};
     const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
-    if (g_tune_prefill_pair && attn_prefill_pair_ok(p)) launch_attn_prefill_pair(c->stream, p);
-    else launch_attn_prefill(c->stream, p);
+    launch_attn_prefill(c->stream, p);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
     return cuda_ok(c, cudaGetLastError(), "prefill launch");
 }
@@ -551,7 +557,7 @@ extern "C" uint64_t qw_gpu_launch_count(void) { return (uint64_t)qw::g_launches;
 extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "split_kg") && (value == 4 || value == 6)) { qw::g_tune_split_kg = value; return true; }
     if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
-    if (knob && !strcmp(knob, "prefill_pair") && (value == 0 || value == 1)) { qw::g_tune_prefill_pair = value; return true; }
+    if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     return false;
 }
 extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }
@@ -1077,9 +1083,11 @@ bool fused_check(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_d
 struct FusedSeq { qw_ref out, qg, k, v, pos, kcache, vcache; int32_t base_pos; };
 
 // pre-op for up to QW_MAX_SEQ sequences; q_out[i] receives each sequence's bf16 query
+// cs_out != nullptr: the query heads are left alone and the rotation angles' cos / sin of every row
+// go to cs_out[i] ([rows, 64] f32) -- for the prefill kernel that norms and rotates its own tiles.
 bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_out, qw_ref q_norm_w, qw_ref k_norm_w,
                qw_ref axis, qw_ref inv_freq, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t max_ctx,
-               float eps, int io, bool append) {
+               float eps, int io, bool append, float *const *cs_out = nullptr) {
     PreopParams p;
     memset(&p, 0, sizeof p);
     const size_t el = io == DT_BF16 ? 2 : 4;
@@ -1102,12 +1110,18 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
             if (!resolve_cache(c, s[i].vcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.vc, nullptr, 32, nullptr, s[i].base_pos)) return false;
         }
         ps.q_out = q_out[i];
+        ps.cs_out = cs_out ? cs_out[i] : nullptr;
         ps.rows = rows; ps.base_pos = s[i].base_pos;
     }
+    p.skip_q = cs_out != nullptr;
     p.vec_io = 1;
     for (int i = 0; i < n_seq; i++)
         if ((reinterpret_cast<uintptr_t>(p.seq[i].qg) | reinterpret_cast<uintptr_t>(p.seq[i].k) | reinterpret_cast<uintptr_t>(p.seq[i].v)) & 15) p.vec_io = 0;
+    KTime kt = {nullptr, nullptr, "qw_attn_preop"};
+    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    if (timed) cudaEventRecord(kt.t0, c->stream);
     launch_preop(c->stream, p, rows);
+    if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
     return cuda_ok(c, cudaGetLastError(), "pre-op launch");
 }
 
@@ -1128,8 +1142,6 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
         if (!scr) return false;
         __nv_bfloat16 *qo[QW_MAX_SEQ];
         for (int i = 0; i < ns; i++) qo[i] = reinterpret_cast<__nv_bfloat16 *>(scr + (size_t)i * q_bytes);
-        if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
-
         if (rows * gqa > 64 && g_tune_prefill_tc) {
             // many rows: the tcgen05 kernel, one launch per sequence (operands that its tile maps
             // cannot describe, e.g. an output that is not 16-byte aligned, take the chunked path below)
@@ -1143,7 +1155,23 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
                 if (!op[i] || !gp[i]) return false;
                 tiles_ok = tiles_ok && attn_prefill_io_ok(op[i], io, gp[i] + 256 * el, io, 512);
             }
+            if (tiles_ok && io == DT_BF16 && g_tune_prefill_fuse_q) {
+                // bf16 rows: the kernel norms and rotates its own query tiles; the pre-op only appends
+                // K and V and leaves the rows' cos / sin (in the scratch the bf16 queries would have taken)
+                float *cs[QW_MAX_SEQ];
+                for (int i = 0; i < ns; i++) cs[i] = reinterpret_cast<float *>(scr + (size_t)i * q_bytes);
+                const uint16_t *wq = q_norm_w.buf ? (const uint16_t *)dev_range(c, q_norm_w, 512, false) : nullptr;
+                if (q_norm_w.buf && !wq) return false;
+                if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true, cs)) return false;
+                for (int i = 0; i < ns; i++) {
+                    const FusedSeq &fs = seqs[s0 + i];
+                    if (!run_prefill(c, reinterpret_cast<const __nv_bfloat16 *>(gp[i]), op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache,
+                                     rows, q_heads, kv_heads, max_ctx, fs.base_pos, scale, cs[i], wq, eps)) return false;
+                }
+                continue;
+            }
             if (tiles_ok) {
+                if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
                 for (int i = 0; i < ns; i++) {
                     const FusedSeq &fs = seqs[s0 + i];
                     if (!run_prefill(c, qo[i], op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
@@ -1152,6 +1180,7 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
                 continue;
             }
         }
+        if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
 
         AttnParams p;
         memset(&p, 0, sizeof p);

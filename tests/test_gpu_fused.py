@@ -44,9 +44,11 @@ def check_k_rows(got_bits, want_bits):
 
 
 def fused_once(be, oracle, *, rows, qh, kvh, base, ctx, io, paged, seed, w_q=None, w_k=None, layer=0, layers=1,
-               inputs=None):
+               inputs=None, shift=0):
     """Runs one fused step on the device and the oracle's composition on the host.
-    Returns (got_out, want_out, got_k_rows, want_k_rows, got_v_rows, want_v_rows)."""
+    Returns (got_out, want_out, got_k_rows, want_k_rows, got_v_rows, want_v_rows).
+    shift: the activations (qg, k, v, out) start that many elements into their buffers, so
+    that they are not 16-byte aligned."""
     rng = np.random.default_rng(seed)
     if inputs is None:
         qg, k, v = synth.step_inputs(rng, rows, qh, kvh)
@@ -59,8 +61,10 @@ def fused_once(be, oracle, *, rows, qh, kvh, base, ctx, io, paged, seed, w_q=Non
     axis, inv = oracle.rope_tables()
     layer_bytes = kvh * ctx * 512
     with Bufs(be) as B:
-        qgb, _ = B.shared(to_io(qg, io)); kb, _ = B.shared(to_io(k, io)); vb, _ = B.shared(to_io(v, io))
-        ob, ov = B.shared_empty((rows, qh, 256), io_np(io))
+        el = 2 if io == BF16 else 4
+        pad = lambda a: np.concatenate([np.zeros(shift, a.dtype), a.ravel()])
+        qgb, _ = B.shared(pad(to_io(qg, io))); kb, _ = B.shared(pad(to_io(k, io))); vb, _ = B.shared(pad(to_io(v, io)))
+        ob, ov = B.shared_empty((shift + rows * qh * 256,), io_np(io))
         pb, _ = B.shared(pos); ab, _ = B.shared(axis); fb, _ = B.shared(inv)
         wq = QwRef(B.shared(w_q)[0], 0) if w_q is not None else NULL_REF
         wk = QwRef(B.shared(w_k)[0], 0) if w_k is not None else NULL_REF
@@ -73,12 +77,12 @@ def fused_once(be, oracle, *, rows, qh, kvh, base, ctx, io, paged, seed, w_q=Non
             full_k[layer] = kc; full_v[layer] = vc
             kcb = B.device(full_k); vcb = B.device(full_v)
         c = be.cmd_begin()
-        ok = be.op_attn_layer_fused(c, QwRef(ob, 0), QwRef(qgb, 0), QwRef(kb, 0), QwRef(vb, 0), wq, wk, QwRef(pb, 0),
+        ok = be.op_attn_layer_fused(c, QwRef(ob, shift * el), QwRef(qgb, shift * el), QwRef(kb, shift * el), QwRef(vb, shift * el), wq, wk, QwRef(pb, 0),
                                     QwRef(ab, 0), QwRef(fb, 0), QwRef(kcb, layer * layer_bytes),
                                     QwRef(vcb, layer * layer_bytes), rows, qh, kvh, 256, 64, ctx, base, 1e-6, 0.0625, io)
         assert ok, "the fused node declined"
         be.cmd_wait(c); be.cmd_free(c)
-        got = from_io(ov, io)
+        got = from_io(ov[shift:].reshape(rows, qh, 256), io)
         gk = np.stack([be.kv_read(kcb, layer, h, base, rows, kvh, ctx) for h in range(kvh)])
         gv = np.stack([be.kv_read(vcb, layer, h, base, rows, kvh, ctx) for h in range(kvh)])
         if base:   # history untouched
@@ -99,6 +103,39 @@ def test_fused_matches_oracle(be, oracle, io, paged, rows, qh, kvh, base, ctx):
     got, want, gk, wk_, gv, wv = fused_once(be, oracle, rows=rows, qh=qh, kvh=kvh, base=base, ctx=ctx, io=io,
                                             paged=paged, seed=rows * 1000 + base, w_q=w, w_k=w)
     assert np.array_equal(gv, wv), "appended V must be bit-exact"
+    check_k_rows(gk, wk_)
+    assert max_rel_err(got, want) <= 1e-2
+    assert rel_l2(got, want) < 6e-3
+
+
+@pytest.mark.parametrize("fuse_q", [1, 0], ids=["q-in-kernel", "q-in-preop"])
+@pytest.mark.parametrize("rows,base", [(300, 0), (200, 77)])
+def test_fused_prefill_norm_weights_and_knob(be, oracle, fuse_q, rows, base):
+    """Many-row bf16 prefill with non-trivial norm weights, with the query norm + RoPE done by the
+    tcgen05 kernel on its own tiles (default) and by the pre-op kernel."""
+    rng = np.random.default_rng(11)
+    w_q = synth.f32_to_bf16_bits(1.0 + 0.3 * rng.standard_normal(256).astype(np.float32))
+    w_k = synth.f32_to_bf16_bits(1.0 + 0.3 * rng.standard_normal(256).astype(np.float32))
+    assert be.tune("prefill_fuse_q", fuse_q)
+    try:
+        got, want, gk, wk_, gv, wv = fused_once(be, oracle, rows=rows, qh=8, kvh=2, base=base, ctx=rows + base + 20,
+                                                io=BF16, paged=True, seed=rows + fuse_q, w_q=w_q, w_k=w_k)
+    finally:
+        be.tune("prefill_fuse_q", 1)
+    assert np.array_equal(gv, wv)
+    check_k_rows(gk, wk_)
+    assert max_rel_err(got, want) <= 1e-2
+    assert rel_l2(got, want) < 6e-3
+
+
+@pytest.mark.parametrize("io", [F32, BF16], ids=["f32", "bf16"])
+@pytest.mark.parametrize("rows", [1, 5, 150])
+def test_fused_unaligned_activations(be, oracle, io, rows):
+    """Activations one element into their buffers (not 16-byte aligned): the element-load paths."""
+    w = synth.f32_to_bf16_bits(1.0 + 0.1 * np.random.default_rng(3).standard_normal(256).astype(np.float32))
+    got, want, gk, wk_, gv, wv = fused_once(be, oracle, rows=rows, qh=8, kvh=2, base=40, ctx=rows + 64, io=io,
+                                            paged=True, seed=rows + 7, w_q=w, w_k=w, shift=1)
+    assert np.array_equal(gv, wv)
     check_k_rows(gk, wk_)
     assert max_rel_err(got, want) <= 1e-2
     assert rel_l2(got, want) < 6e-3

@@ -13,7 +13,14 @@
  *
  * Cache element type: bfloat16 (the reference stores IEEE half,
  * qwasar_gpu.h:395-400).  Activations are fp32 in the reference signatures;
- * the additive entry points take a qw_dtype. */
+ * the additive entry points take a qw_dtype.
+ *
+ * Alignment: activation and weight operands (q, qg, k, v, out, gate, norm
+ * weights, partials) must start on a 16-byte boundary of device memory, i.e.
+ * qw_ref offsets that are multiples of 16 into buffers from qw_buf_alloc
+ * (256-byte aligned); positions, rope axes and frequencies need only their
+ * element alignment.  An op given an operand that is not declines: bool ops
+ * return false, and qw_cmd_error names the operand. */
 #ifndef QWASAR_CUDA_H
 #define QWASAR_CUDA_H
 

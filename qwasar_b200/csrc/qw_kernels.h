@@ -53,7 +53,6 @@ struct PreopSeq {
 struct PreopParams {
     PreopSeq seq[QW_MAX_SEQ];
     int32_t n_seq, q_heads, kv_heads, rotary_dim, io_dtype;
-    int32_t vec_io;                        // every qg / k / v pointer is 16-byte aligned: rows move as 16-byte pieces
     int32_t skip_q;                        // leave the query heads alone (the prefill kernel norms and rotates its own tiles)
     const uint16_t *q_norm_w, *k_norm_w;   // bf16 [256] or nullptr
     const uint8_t *axis;
@@ -134,6 +133,7 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
                         float *pacc_out, float *pstat_out, size_t acc_stride = 0, size_t stat_stride = 0);
 
 int sm_count();
+
 
 // Launch accounting: every launcher adds the kernels it launched.
 extern unsigned long long g_launches;

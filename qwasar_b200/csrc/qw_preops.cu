@@ -14,11 +14,6 @@ namespace qw {
 
 namespace {
 
-__device__ __forceinline__ float load_io(const void *p, size_t i, int dtype) {
-    return dtype == DT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p)[i])
-                            : reinterpret_cast<const float *>(p)[i];
-}
-
 // ---- unfused ops, reference signatures ------------------------------------------------
 
 __global__ void split_heads2_kernel(float *__restrict__ a, float *__restrict__ b, const float *__restrict__ src,
@@ -144,18 +139,7 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
         const int r = min(r0 + u, s.rows - 1);
         const size_t first = (size_t)r * pitch + off + lane * 8;
         raw[u][1] = make_uint4(0, 0, 0, 0);
-        if (!p.vec_io) {
-            // operands that are not 16-byte aligned: element loads
-            float e[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) e[i] = load_io(src, first + i, p.io_dtype);
-            if (p.io_dtype == DT_BF16) {
-                raw[u][0] = make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
-            } else {
-                raw[u][0] = make_uint4(__float_as_uint(e[0]), __float_as_uint(e[1]), __float_as_uint(e[2]), __float_as_uint(e[3]));
-                raw[u][1] = make_uint4(__float_as_uint(e[4]), __float_as_uint(e[5]), __float_as_uint(e[6]), __float_as_uint(e[7]));
-            }
-        } else if (p.io_dtype == DT_BF16) {
+        if (p.io_dtype == DT_BF16) {
             raw[u][0] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(src) + first));
         } else {
             const uint4 *g = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(src) + first);

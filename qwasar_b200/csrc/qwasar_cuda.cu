@@ -299,12 +299,18 @@ void arena_destroy(Arena *a) {
 
 // Device address of [off, off+bytes) of a ref.  For shared buffers the device mirror of
 // that range is brought up to date (once per command buffer) and, when `write`, marked
-// for copy-back at qw_cmd_wait.
-void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write) {
+// for copy-back at qw_cmd_wait.  Activations and weights move as 16-byte pieces: an operand
+// that does not start on a 16-byte boundary is refused here (an error string, not a fault);
+// the small tables (positions, axes, frequencies) pass their own element size.
+void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write, size_t align = 16) {
     qw_buf b = r.buf;
     if (!b) return nullptr;
     if (b->kind == BUF_ARENA) { cmd_fail(c, "an arena can only be a cache operand"); return nullptr; }
     if (r.off + bytes > b->len) { cmd_fail(c, "operand [%zu, %zu) exceeds its buffer (%zu bytes)", r.off, r.off + bytes, b->len); return nullptr; }
+    if ((reinterpret_cast<uintptr_t>(b->dev) + r.off) & (align - 1)) {
+        cmd_fail(c, "operand at byte offset %zu of its buffer is not %zu-byte aligned", r.off, align);
+        return nullptr;
+    }
     if (b->kind == BUF_SHARED && bytes) {
         // small buffers are mirrored whole on first touch: one copy instead of one per operand
         const bool whole = b->len <= ((size_t)4 << 20);
@@ -898,9 +904,9 @@ extern "C" void qw_op_rope_partial(qw_cmd c, qw_ref x, qw_ref pos, qw_ref axis, 
                                    int32_t head_dim, int32_t rotary_dim) {
     if (!live(c) || rows <= 0 || heads <= 0 || rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)) return;
     float *px = (float *)dev_range(c, x, (size_t)rows * heads * head_dim * 4, true);
-    const int32_t *pp = (const int32_t *)dev_range(c, pos, (size_t)3 * rows * 4, false);
-    const uint8_t *pa = (const uint8_t *)dev_range(c, axis, (size_t)rotary_dim / 2, false);
-    const float *pf = (const float *)dev_range(c, inv_freq, (size_t)rotary_dim / 2 * 4, false);
+    const int32_t *pp = (const int32_t *)dev_range(c, pos, (size_t)3 * rows * 4, false, 4);
+    const uint8_t *pa = (const uint8_t *)dev_range(c, axis, (size_t)rotary_dim / 2, false, 1);
+    const float *pf = (const float *)dev_range(c, inv_freq, (size_t)rotary_dim / 2 * 4, false, 4);
     if (!px || !pp || !pa || !pf) return;
     launch_rope_partial(c->stream, px, pp, pa, pf, rows, heads, head_dim, rotary_dim);
 }
@@ -1094,13 +1100,13 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
     p.n_seq = n_seq; p.q_heads = q_heads; p.kv_heads = append ? kv_heads : 0; p.rotary_dim = 64; p.io_dtype = io; p.eps = eps;
     p.q_norm_w = q_norm_w.buf ? (const uint16_t *)dev_range(c, q_norm_w, 512, false) : nullptr;
     p.k_norm_w = k_norm_w.buf ? (const uint16_t *)dev_range(c, k_norm_w, 512, false) : nullptr;
-    p.axis = (const uint8_t *)dev_range(c, axis, 32, false);
-    p.inv_freq = (const float *)dev_range(c, inv_freq, 128, false);
+    p.axis = (const uint8_t *)dev_range(c, axis, 32, false, 1);
+    p.inv_freq = (const float *)dev_range(c, inv_freq, 128, false, 4);
     if (!p.axis || !p.inv_freq || (q_norm_w.buf && !p.q_norm_w) || (k_norm_w.buf && !p.k_norm_w)) return false;
     for (int i = 0; i < n_seq; i++) {
         PreopSeq &ps = p.seq[i];
         ps.qg = dev_range(c, s[i].qg, (size_t)rows * q_heads * 512 * el, false);
-        ps.pos = (const int32_t *)dev_range(c, s[i].pos, (size_t)3 * rows * 4, false);
+        ps.pos = (const int32_t *)dev_range(c, s[i].pos, (size_t)3 * rows * 4, false, 4);
         if (!ps.qg || !ps.pos) return false;
         if (append) {
             ps.k = dev_range(c, s[i].k, (size_t)rows * kv_heads * 256 * el, false);
@@ -1114,9 +1120,6 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
         ps.rows = rows; ps.base_pos = s[i].base_pos;
     }
     p.skip_q = cs_out != nullptr;
-    p.vec_io = 1;
-    for (int i = 0; i < n_seq; i++)
-        if ((reinterpret_cast<uintptr_t>(p.seq[i].qg) | reinterpret_cast<uintptr_t>(p.seq[i].k) | reinterpret_cast<uintptr_t>(p.seq[i].v)) & 15) p.vec_io = 0;
     KTime kt = {nullptr, nullptr, "qw_attn_preop"};
     const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);

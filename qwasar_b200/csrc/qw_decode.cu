@@ -437,9 +437,17 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
     }
 }
 
-// One block per (group, row i): combine the group's partials.  64 threads x float4.
+// One block per (group, row i): combine the group's partials.  A group cut over many CTAs (one
+// long sequence: up to one partial per SM) must not be walked one partial at a time -- every
+// step of such a walk is a trip to L2 -- so the block reads all (max, sum) pairs at once, one per
+// thread, and its four quarters of 64 threads x float4 each take every fourth partial, four
+// loads in flight, before their sums are added through shared memory.
+constexpr int MERGE_THREADS = 256;
 template <int MT>
-__global__ void __launch_bounds__(64) qw_attn_merge_kernel(const __grid_constant__ AttnParams p, int max_valid_rows) {
+__global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __grid_constant__ AttnParams p, int max_valid_rows) {
+    __shared__ float w_s[MERGE_THREADS];                      // weight of partial q (0 for an empty one)
+    __shared__ float red_s[2][8];
+    __shared__ __align__(16) float acc_s[3][256];
     const int gidx = blockIdx.x / max_valid_rows;            // sequence * kv_heads + head
     const int row = blockIdx.x - gidx * max_valid_rows;
     const int s = gidx / p.kv_heads, h = gidx - s * p.kv_heads;
@@ -452,24 +460,60 @@ __global__ void __launch_bounds__(64) qw_attn_merge_kernel(const __grid_constant
     while (c_first + 1 < C && ((int64_t)(c_first + 1) * Tt) / C <= G0) c_first++;
     int c_last = (int)(((G1 - 1) * C) / Tt);
     while (c_last + 1 < C && ((int64_t)(c_last + 1) * Tt) / C <= G1 - 1) c_last++;
-    const int parts = c_last - c_first + 1;
+    const int parts = c_last - c_first + 1;                   // <= n_cta <= MERGE_THREADS
     if (parts == 1 && p.mode == 0) return;                     // the split kernel wrote the output itself
 
-    const int d4 = threadIdx.x * 4;
-    float m = -3.0e38f;
-    for (int q = 0; q < parts; q++) {
-        const size_t pi = (size_t)(c_first + q + gidx) * (MT * 16) + row;
-        if (p.pstat[pi * 2 + 1] > 0.0f) m = fmaxf(m, p.pstat[pi * 2]);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t pi0 = (size_t)(c_first + gidx) * (MT * 16) + row;      // partial q sits MT*16 rows further per q
+    // max over the non-empty partials, then each partial's weight and the denominator
+    float mq = -3.0e38f, lq = 0.0f;
+    if (tid < parts) {
+        const float2 st = *reinterpret_cast<const float2 *>(p.pstat + (pi0 + (size_t)tid * (MT * 16)) * 2);
+        lq = st.y;
+        if (lq > 0.0f) mq = st.x;
     }
+    float m = warp_max(mq);
+    if (lane == 0) red_s[0][warp] = m;
+    __syncthreads();
+    m = red_s[0][0];
+#pragma unroll
+    for (int i = 1; i < MERGE_THREADS / 32; i++) m = fmaxf(m, red_s[0][i]);
+    const float wq = lq > 0.0f ? __expf(mq - m) : 0.0f;
+    w_s[tid] = wq;
+    float den = warp_sum(lq * wq);
+    if (lane == 0) red_s[1][warp] = den;
+    __syncthreads();
+    den = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MERGE_THREADS / 32; i++) den += red_s[1][i];
+
+    const int quarter = tid >> 6, d4 = (tid & 63) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.0f;
-    for (int q = 0; q < parts; q++) {
-        const size_t pi = (size_t)(c_first + q + gidx) * (MT * 16) + row;
-        const float l = p.pstat[pi * 2 + 1];
-        const float w = l > 0.0f ? __expf(p.pstat[pi * 2] - m) : 0.0f;
-        const float4 a = *reinterpret_cast<const float4 *>(p.pacc + pi * 256 + d4);
-        den += l * w;
+    const float *base = p.pacc + pi0 * 256 + d4;
+    const size_t step = (size_t)(MT * 16) * 256;
+    int q = quarter;
+    for (; q + 12 < parts; q += 16) {
+        float4 a[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) a[u] = *reinterpret_cast<const float4 *>(base + (size_t)(q + 4 * u) * step);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float w = w_s[q + 4 * u];
+            acc.x += a[u].x * w; acc.y += a[u].y * w; acc.z += a[u].z * w; acc.w += a[u].w * w;
+        }
+    }
+    for (; q < parts; q += 4) {
+        const float4 a = *reinterpret_cast<const float4 *>(base + (size_t)q * step);
+        const float w = w_s[q];
         acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+    }
+    if (quarter > 0) *reinterpret_cast<float4 *>(&acc_s[quarter - 1][d4]) = acc;
+    __syncthreads();
+    if (quarter > 0) return;
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const float4 o = *reinterpret_cast<const float4 *>(&acc_s[i][d4]);
+        acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
     }
     const int r = row / p.gqa, g = row - r * p.gqa;
     const size_t rh = (size_t)r * p.q_heads + h * p.gqa + g;
@@ -664,9 +708,9 @@ void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows) {
     const int vr = max_rows * p.gqa;
     const unsigned blocks = (unsigned)(p.n_seq * p.kv_heads * vr);
     switch (row_tiles(max_rows, p.gqa)) {
-        case 1: qw_attn_merge_kernel<1><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
-        case 2: qw_attn_merge_kernel<2><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
-        default: qw_attn_merge_kernel<4><<<blocks, 64, 0, s>>>(p, vr); g_launches++; break;
+        case 1: qw_attn_merge_kernel<1><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
+        case 2: qw_attn_merge_kernel<2><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
+        default: qw_attn_merge_kernel<4><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
     }
 }
 

@@ -112,6 +112,7 @@ extern "C" bool qw_attn_decode_noalloc(void *out, const void *q, const void *gat
     s.tile0 = 0; s.n_tiles = (s.key_hi + 31) / 32; s.cum_tiles = 0; s.row_slot0 = 0;
     p.total_tiles = s.n_tiles * kv_heads;
     p.n_cta = p.total_tiles < g_dev[dev].sms ? p.total_tiles : g_dev[dev].sms;
+    if (p.n_cta > 256) p.n_cta = 256;                       // the merge kernel reads one partial per thread of 256
     const size_t need = attn_split_scratch_bytes(p, rows);
     if (need > QW_NOALLOC_SCRATCH_BYTES) {
         char msg[200];

@@ -428,7 +428,7 @@ void plan_split(AttnParams &p) {
         row_slot += s.rows;
     }
     p.total_tiles = cum;
-    p.n_cta = std::min(sm_count(), cum);
+    p.n_cta = std::min(std::min(sm_count(), 256), cum);      // the merge kernel reads one partial per thread of 256
 }
 
 // Launches the split-KV kernel (and the merge where any group was cut) for the sequences

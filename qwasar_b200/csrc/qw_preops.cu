@@ -110,7 +110,10 @@ __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float 
 // in lanes l and l ^ 4 (l < 8) at the same register.  The 32 angles of a token are the same for
 // all its heads: the block's first PRE_ROWS warps compute cos / sin once, into shared memory.
 // The kernel issues few bytes per instruction, so the instruction count per row is what it pays for.
-constexpr int PRE_ROWS = 4;
+#ifndef QW_PRE_ROWS
+#define QW_PRE_ROWS 4
+#endif
+constexpr int PRE_ROWS = QW_PRE_ROWS;
 __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
     const PreopSeq &s = p.seq[blockIdx.z];

@@ -63,6 +63,7 @@ struct qw_cmd_s {
     char err[256];
     int parallel;
     std::vector<Touch> touched;
+    cudaEvent_t uploaded = nullptr; // last first-touch upload on the copy stream (see dev_range)
     std::vector<Scratch> scratch;   // last one is current; earlier ones may still be in flight
     std::vector<Mark> marks;
     std::vector<KTime> ktimes;
@@ -100,6 +101,7 @@ struct Globals {
     PFN_memGetGranularity memGetGranularity = nullptr;
     std::vector<Scratch> scratch_pool;
     std::vector<cudaStream_t> stream_pool;    // streams of freed command buffers, reused
+    cudaStream_t copy_stream = nullptr;       // first-touch uploads of shared buffers, see dev_range
     std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows * 128 + box rows) -> map
     char last_error[256] = "";
     bool has_error = false;
@@ -321,7 +323,18 @@ void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write, size_t align = 16)
         if (!t) {
             c->touched.push_back(Touch{b, lo, hi, 0, 0});
             t = &c->touched.back();
-            cuda_ok(c, cudaMemcpyAsync((char *)b->dev + lo, (char *)b->host + lo, hi - lo, cudaMemcpyHostToDevice, c->stream), "upload");
+            // The first upload of a buffer in a command buffer goes to the copy stream and the
+            // command's stream waits for it: nothing encoded earlier in this command buffer can
+            // have used the mirror, and the caller may not change a buffer that an uncompleted
+            // command buffer uses, so the copy may run while the ops encoded before it (the
+            // layers before this one) still execute instead of queueing behind them.
+            if (!c->uploaded && cudaEventCreateWithFlags(&c->uploaded, cudaEventDisableTiming) != cudaSuccess) c->uploaded = nullptr;
+            cudaStream_t up = G.copy_stream && c->uploaded ? G.copy_stream : c->stream;
+            cuda_ok(c, cudaMemcpyAsync((char *)b->dev + lo, (char *)b->host + lo, hi - lo, cudaMemcpyHostToDevice, up), "upload");
+            if (up != c->stream) {
+                cuda_ok(c, cudaEventRecord(c->uploaded, up), "upload event");
+                cuda_ok(c, cudaStreamWaitEvent(c->stream, c->uploaded, 0), "upload wait");
+            }
         } else {
             if (lo < t->lo) {
                 cuda_ok(c, cudaMemcpyAsync((char *)b->dev + lo, (char *)b->host + lo, t->lo - lo, cudaMemcpyHostToDevice, c->stream), "upload");
@@ -536,6 +549,7 @@ extern "C" bool qw_gpu_init(char *err, size_t errcap) {
         cudaHostGetDevicePointer((void **)&G.status_dev, G.status_host, 0) != cudaSuccess)
         return fail("%s", "cannot allocate the status word");
     memset(G.status_host, 0, 64);
+    if (cudaStreamCreateWithFlags(&G.copy_stream, cudaStreamNonBlocking) != cudaSuccess) G.copy_stream = nullptr;
     G.up = true;
     G.has_error = false;
     return true;
@@ -548,6 +562,7 @@ extern "C" void qw_gpu_shutdown(void) {
     G.scratch_pool.clear();
     for (auto &st : G.stream_pool) cudaStreamDestroy(st);
     G.stream_pool.clear();
+    if (G.copy_stream) { cudaStreamDestroy(G.copy_stream); G.copy_stream = nullptr; }
     G.map_cache.clear();
     if (G.status_host) cudaFreeHost(G.status_host);
     G.status_host = G.status_dev = nullptr;
@@ -831,6 +846,7 @@ extern "C" void qw_cmd_free(qw_cmd c) {
     if (!c) return;
     if (!c->touched.empty() || !c->scratch.empty()) cudaStreamSynchronize(c->stream);
     for (auto &s : c->scratch) G.scratch_pool.push_back(s);
+    if (c->uploaded) cudaEventDestroy(c->uploaded);
     for (auto &m : c->marks) cudaEventDestroy(m.ev);
     for (auto &k : c->ktimes) { cudaEventDestroy(k.t0); cudaEventDestroy(k.t1); }
     if (c->own_stream) {

@@ -216,6 +216,21 @@ bool    qw_kv_read(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int3
                    int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
 bool    qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, const void *src,
                     int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
+/* The whole KV section of the reference's packed session state in one call
+ * (qw_session_pack / qw_session_unpack, qwasar_graph.c:296-303, 320-373):
+ * for every layer, for every kv head, the K rows of positions [0, n_tokens)
+ * then the V rows, head_dim bf16 each, nothing else.  qw_kv_state_bytes is
+ * that section's size; pack wants cap >= it, unpack wants len == it (the
+ * reference's own length check, qwasar_graph.c:361-362) and maps the pages it
+ * fills.  Blocking; one gather or scatter kernel and one copy per layer.  The
+ * element type is bf16, not the reference's IEEE half: a checkpoint written
+ * by the other build must be refused by the file header, which is the
+ * caller's (qwasar_kvstore.c:52-63 records no dtype yet). */
+size_t  qw_kv_state_bytes(int32_t n_layers, int32_t kv_heads, int32_t head_dim, int32_t n_tokens);
+bool    qw_kv_pack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx,
+                   int32_t head_dim, int32_t n_tokens, void *dst, size_t cap);
+bool    qw_kv_unpack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx,
+                     int32_t head_dim, int32_t n_tokens, const void *src, size_t len);
 /* Returns to the pool every page that lies wholly at or past n_tokens
  * (a rewind, qwasar_graph.c:407-463, needs no undo of KV rows; this only
  * gives memory back). */

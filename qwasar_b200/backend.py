@@ -77,6 +77,9 @@ SIGNATURES = {
     "qw_kv_arena_alloc_ex": (_vp, [_i32, _i32, _i32, _i32, C.c_uint32]),
     "qw_kv_read": (_b, [_vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32]),
     "qw_kv_store": (_b, [_vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32]),
+    "qw_kv_state_bytes": (_sz, [_i32, _i32, _i32, _i32]),
+    "qw_kv_pack": (_b, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz]),
+    "qw_kv_unpack": (_b, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz]),
     "qw_kv_arena_trim": (None, [_vp, _i32]),
     "qw_kv_arena_pages_in_use": (C.c_int64, [_vp]),
     "qw_kv_arena_bytes_committed": (C.c_int64, [_vp]),
@@ -218,6 +221,23 @@ class Backend:
         import numpy as np
         a = np.ascontiguousarray(rows_u16, np.uint16)
         if not self.lib.qw_kv_store(cache, layer, head, pos0, a.shape[0], a.ctypes.data, kv_heads, max_ctx, head_dim):
+            raise RuntimeError(self.last_error())
+
+    def kv_pack(self, kcache, vcache, n_layers, kv_heads, max_ctx, n_tokens, head_dim=256):
+        """The KV section of the reference's packed session state as uint16
+        [n_layers, kv_heads, 2 (K, V), n_tokens, head_dim]."""
+        import numpy as np
+        out = np.empty((n_layers, kv_heads, 2, n_tokens, head_dim), np.uint16)
+        assert out.nbytes == self.lib.qw_kv_state_bytes(n_layers, kv_heads, head_dim, n_tokens) or n_tokens == 0
+        if not self.lib.qw_kv_pack(kcache, vcache, n_layers, kv_heads, max_ctx, head_dim, n_tokens, out.ctypes.data, out.nbytes):
+            raise RuntimeError(self.last_error())
+        return out
+
+    def kv_unpack(self, kcache, vcache, packed_u16, max_ctx):
+        import numpy as np
+        a = np.ascontiguousarray(packed_u16, np.uint16)
+        n_layers, kv_heads, _, n_tokens, head_dim = a.shape
+        if not self.lib.qw_kv_unpack(kcache, vcache, n_layers, kv_heads, max_ctx, head_dim, n_tokens, a.ctypes.data, a.nbytes):
             raise RuntimeError(self.last_error())
 
     # -- command buffers

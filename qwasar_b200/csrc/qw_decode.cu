@@ -78,8 +78,28 @@ __device__ __forceinline__ void advance(const AttnParams &p, Cursor &c) {
         if (++c.h == p.kv_heads) { c.h = 0; c.s++; }
     }
 }
+// First tile of a CTA's share.  The tile line is cut into shares of equal cost, not equal
+// length: a share that begins a group pays that segment's prologue (Q load) and epilogue
+// (cross-warp sum, partial write) on top of its tiles, SEG_COST tile times by measurement
+// (CTAs with a group boundary inside their share finished 2.6 us after the others at
+// 0.79 us per tile).  So every group is given SEG_COST virtual tiles in front of its real
+// ones, the virtual line is cut evenly, and a cut that falls among the virtual tiles moves
+// to the group's first real tile.
+#ifndef QW_SEG_COST
+#define QW_SEG_COST 3
+#endif
+constexpr int SEG_COST = QW_SEG_COST;
 __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
-    return (int)(((int64_t)cta * p.total_tiles) / p.n_cta);
+    if (cta >= p.n_cta) return p.total_tiles;
+    const int64_t v_total = (int64_t)p.total_tiles + (int64_t)SEG_COST * p.n_seq * p.kv_heads;
+    const int64_t v = ((int64_t)cta * v_total) / p.n_cta;
+    int s = 0;
+    while (s + 1 < p.n_seq && (int64_t)p.seq[s + 1].cum_tiles + (int64_t)SEG_COST * (s + 1) * p.kv_heads <= v) s++;
+    const int64_t rel = v - ((int64_t)p.seq[s].cum_tiles + (int64_t)SEG_COST * s * p.kv_heads);
+    const int per = p.seq[s].n_tiles + SEG_COST;
+    const int h = min((int)(rel / per), p.kv_heads - 1);
+    const int o = (int)(rel - (int64_t)h * per);
+    return p.seq[s].cum_tiles + h * p.seq[s].n_tiles + min(max(o - SEG_COST, 0), p.seq[s].n_tiles);
 }
 
 __device__ __forceinline__ float load_gate(const void *g, size_t i, int dtype) {
@@ -455,11 +475,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
     const AttnSeq &sq = p.seq[s];
     if (row >= sq.rows * p.gqa) return;
     const int64_t G0 = (int64_t)sq.cum_tiles + (int64_t)h * sq.n_tiles, G1 = G0 + sq.n_tiles;
-    const int64_t Tt = p.total_tiles, C = p.n_cta;
-    int c_first = (int)((G0 * C) / Tt);
-    while (c_first + 1 < C && ((int64_t)(c_first + 1) * Tt) / C <= G0) c_first++;
-    int c_last = (int)(((G1 - 1) * C) / Tt);
-    while (c_last + 1 < C && ((int64_t)(c_last + 1) * Tt) / C <= G1 - 1) c_last++;
+    // the CTAs whose shares [share_lo(c), share_lo(c + 1)) meet the group's tiles [G0, G1): a guess
+    // from the even cut, then a short walk (the cost-weighted cut moves a boundary by a few CTAs at most)
+    const int C = p.n_cta;
+    int c_first = (int)min((G0 * C) / p.total_tiles, (int64_t)C - 1);
+    while (c_first > 0 && share_lo(p, c_first) > G0) c_first--;
+    while (c_first + 1 < C && share_lo(p, c_first + 1) <= G0) c_first++;
+    int c_last = (int)min(((G1 - 1) * C) / p.total_tiles, (int64_t)C - 1);
+    while (c_last > 0 && share_lo(p, c_last) >= G1) c_last--;
+    while (c_last + 1 < C && share_lo(p, c_last + 1) < G1) c_last++;
     const int parts = c_last - c_first + 1;                   // <= n_cta <= MERGE_THREADS
     if (parts == 1 && p.mode == 0) return;                     // the split kernel wrote the output itself
 

@@ -37,6 +37,8 @@ void launch_rope_partial(cudaStream_t s, float *x, const int32_t *pos, const uin
 void launch_kv_write(cudaStream_t s, KvLayer kc, KvLayer vc, const float *k, const float *v, int rows, int kv_heads,
                      int base_pos);
 void launch_mul_sigmoid(cudaStream_t s, float *y, const float *gate, int64_t n);
+// One layer between the cache and the packed layout [kv_heads][K rows | V rows][n_tokens][256] bf16.
+void launch_kv_pack(cudaStream_t s, KvLayer kc, KvLayer vc, void *packed, int kv_heads, int n_tokens, bool unpack);
 void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, int64_t n);
 
 // One sequence of the fused pre-op: split [q|gate], RMS-norm q and k, partial RoPE,

@@ -99,6 +99,32 @@ __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float 
     }
 }
 
+// ---- one layer's rows between the cache and the packed checkpoint layout ------------------
+// packed: for every kv head, its K rows [n_tokens][256] then its V rows (qwasar_graph.c:296-303,
+// 332-339 for one layer).  One warp per 512-byte row; a position whose page was never mapped packs
+// as zeros.
+__global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, uint4 *__restrict__ packed, int kv_heads,
+                                                      int n_tokens, bool unpack) {
+    const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (w >= (int64_t)kv_heads * 2 * n_tokens) return;
+    const int t = (int)(w % n_tokens);
+    const int hv = (int)(w / n_tokens);                  // head * 2 + (0: K, 1: V)
+    const int h = hv >> 1;
+    const KvLayer &L = (hv & 1) ? vc : kc;
+    int64_t row = -1;
+    if (L.table) {
+        const int32_t id = __ldg(L.table + (size_t)h * L.pt_stride + (t >> 6));
+        if (id >= 0) row = (int64_t)id * QW_PAGE_TOKENS + (t & 63);
+    } else {
+        row = (int64_t)h * L.max_ctx + t;
+    }
+    uint4 *cache_row = row >= 0 ? reinterpret_cast<uint4 *>(L.base + row * 256) + lane : nullptr;
+    uint4 *pk = packed + w * 32 + lane;
+    if (unpack) { if (cache_row) *cache_row = *pk; }
+    else *pk = cache_row ? *cache_row : make_uint4(0, 0, 0, 0);
+}
+
 // ---- the fused pre-op ---------------------------------------------------------------------
 // grid = (ceil(max_rows / PRE_ROWS) * ceil(slots / 8), 1, n_seq) with slots = q_heads + 2 * kv_heads
 // (the query heads are left out when the prefill kernel norms its own tiles).  A block covers
@@ -216,6 +242,12 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
 
 }  // namespace
 
+void launch_kv_pack(cudaStream_t s, KvLayer kc, KvLayer vc, void *packed, int kv_heads, int n_tokens, bool unpack) {
+    const int64_t rows = (int64_t)kv_heads * 2 * n_tokens;
+    if (rows <= 0) return;
+    kv_pack_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(kc, vc, reinterpret_cast<uint4 *>(packed), kv_heads, n_tokens, unpack);
+    g_launches++;
+}
 void launch_split_heads2(cudaStream_t s, float *a, float *b, const float *src, int rows, int heads, int dim) {
     const int64_t n = (int64_t)rows * heads * dim;
     if (n <= 0) return;

@@ -756,6 +756,55 @@ extern "C" bool qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t p
     return kv_rw(cache, layer, head, pos0, n, const_cast<void *>(src), true, kv_heads, max_ctx, head_dim);
 }
 
+// The KV section of the reference's packed session state (qwasar_graph.c:296-303): layer by layer,
+// head by head, the K rows of the first n_tokens positions then the V rows.  One gather (or scatter)
+// kernel and one copy per layer through a staging buffer.
+static bool kv_pack_io(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                       int32_t n_tokens, void *host, size_t len, bool unpack) {
+    if (!G.up || !kcache || !vcache || n_layers <= 0 || kv_heads <= 0 || head_dim != QW_HEAD_DIM || n_tokens < 0 || n_tokens > max_ctx || !host) {
+        set_error("qw_kv_pack/unpack: bad arguments");
+        return false;
+    }
+    const size_t layer_packed = (size_t)kv_heads * 2 * n_tokens * head_dim * 2;
+    if (len != layer_packed * n_layers) { set_error("qw_kv_pack/unpack: %zu bytes given, the state is %zu", len, layer_packed * n_layers); return false; }
+    if (n_tokens == 0) return true;
+    qw_cmd c = qw_cmd_begin();
+    if (!c) return false;
+    void *stage = cmd_scratch(c, layer_packed);
+    const size_t layer_bytes = (size_t)kv_heads * max_ctx * head_dim * 2;
+    bool ok = stage != nullptr;
+    for (int32_t l = 0; ok && l < n_layers; l++) {
+        KvLayer kc, vc;
+        ok = resolve_cache(c, qw_ref{kcache, l * layer_bytes}, kv_heads, max_ctx, head_dim, n_tokens, unpack, unpack, &kc, nullptr) &&
+             resolve_cache(c, qw_ref{vcache, l * layer_bytes}, kv_heads, max_ctx, head_dim, n_tokens, unpack, unpack, &vc, nullptr);
+        if (!ok) break;
+        char *hp = (char *)host + (size_t)l * layer_packed;
+        if (unpack) ok = cuda_ok(c, cudaMemcpyAsync(stage, hp, layer_packed, cudaMemcpyHostToDevice, c->stream), "unpack copy");
+        if (ok) launch_kv_pack(c->stream, kc, vc, stage, kv_heads, n_tokens, unpack);
+        if (ok && !unpack) ok = cuda_ok(c, cudaMemcpyAsync(hp, stage, layer_packed, cudaMemcpyDeviceToHost, c->stream), "pack copy");
+        // the staging buffer is reused by the next layer: the copy of this one must have left it
+        if (ok) ok = cuda_ok(c, cudaStreamSynchronize(c->stream), "pack");
+    }
+    qw_cmd_wait(c);
+    if (c->failed) { set_error("%s", c->err); ok = false; }
+    qw_cmd_free(c);
+    return ok;
+}
+extern "C" size_t qw_kv_state_bytes(int32_t n_layers, int32_t kv_heads, int32_t head_dim, int32_t n_tokens) {
+    if (n_layers <= 0 || kv_heads <= 0 || head_dim <= 0 || n_tokens <= 0) return 0;
+    return (size_t)n_layers * kv_heads * 2 * n_tokens * head_dim * 2;
+}
+extern "C" bool qw_kv_pack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                           int32_t n_tokens, void *dst, size_t cap) {
+    const size_t need = qw_kv_state_bytes(n_layers, kv_heads, head_dim, n_tokens);
+    if (cap < need) { set_error("qw_kv_pack: %zu bytes given, the state is %zu", cap, need); return false; }
+    return kv_pack_io(kcache, vcache, n_layers, kv_heads, max_ctx, head_dim, n_tokens, dst, need, false);
+}
+extern "C" bool qw_kv_unpack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                             int32_t n_tokens, const void *src, size_t len) {
+    return kv_pack_io(kcache, vcache, n_layers, kv_heads, max_ctx, head_dim, n_tokens, const_cast<void *>(src), len, true);
+}
+
 extern "C" void qw_kv_arena_trim(qw_buf cache, int32_t n_tokens) {
     if (!cache || cache->kind != BUF_ARENA) return;
     Arena *a = cache->arena;

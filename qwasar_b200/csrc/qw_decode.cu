@@ -89,7 +89,7 @@ __device__ __forceinline__ void advance(const AttnParams &p, Cursor &c) {
 #define QW_SEG_COST 3
 #endif
 constexpr int SEG_COST = QW_SEG_COST;
-__device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
+__host__ __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
     if (cta >= p.n_cta) return p.total_tiles;
     const int64_t v_total = (int64_t)p.total_tiles + (int64_t)SEG_COST * p.n_seq * p.kv_heads;
     const int64_t v = ((int64_t)cta * v_total) / p.n_cta;
@@ -97,9 +97,25 @@ __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
     while (s + 1 < p.n_seq && (int64_t)p.seq[s + 1].cum_tiles + (int64_t)SEG_COST * (s + 1) * p.kv_heads <= v) s++;
     const int64_t rel = v - ((int64_t)p.seq[s].cum_tiles + (int64_t)SEG_COST * s * p.kv_heads);
     const int per = p.seq[s].n_tiles + SEG_COST;
-    const int h = min((int)(rel / per), p.kv_heads - 1);
-    const int o = (int)(rel - (int64_t)h * per);
-    return p.seq[s].cum_tiles + h * p.seq[s].n_tiles + min(max(o - SEG_COST, 0), p.seq[s].n_tiles);
+    int h = (int)(rel / per);
+    if (h > p.kv_heads - 1) h = p.kv_heads - 1;
+    int o = (int)(rel - (int64_t)h * per) - SEG_COST;
+    if (o < 0) o = 0;
+    if (o > p.seq[s].n_tiles) o = p.seq[s].n_tiles;
+    return p.seq[s].cum_tiles + h * p.seq[s].n_tiles + o;
+}
+// The CTAs whose shares [share_lo(c), share_lo(c + 1)) meet the tiles [G0, G1) of one group: a guess
+// from the even cut, then a short walk (the cost-weighted cut moves a boundary by a few CTAs at most).
+__host__ __device__ __forceinline__ void group_ctas(const AttnParams &p, int64_t G0, int64_t G1, int &c_first, int &c_last) {
+    const int C = p.n_cta;
+    int64_t g = (G0 * C) / p.total_tiles;
+    c_first = (int)(g < C - 1 ? g : C - 1);
+    while (c_first > 0 && share_lo(p, c_first) > G0) c_first--;
+    while (c_first + 1 < C && share_lo(p, c_first + 1) <= G0) c_first++;
+    g = ((G1 - 1) * C) / p.total_tiles;
+    c_last = (int)(g < C - 1 ? g : C - 1);
+    while (c_last > 0 && share_lo(p, c_last) >= G1) c_last--;
+    while (c_last + 1 < C && share_lo(p, c_last + 1) < G1) c_last++;
 }
 
 __device__ __forceinline__ float load_gate(const void *g, size_t i, int dtype) {
@@ -475,15 +491,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
     const AttnSeq &sq = p.seq[s];
     if (row >= sq.rows * p.gqa) return;
     const int64_t G0 = (int64_t)sq.cum_tiles + (int64_t)h * sq.n_tiles, G1 = G0 + sq.n_tiles;
-    // the CTAs whose shares [share_lo(c), share_lo(c + 1)) meet the group's tiles [G0, G1): a guess
-    // from the even cut, then a short walk (the cost-weighted cut moves a boundary by a few CTAs at most)
-    const int C = p.n_cta;
-    int c_first = (int)min((G0 * C) / p.total_tiles, (int64_t)C - 1);
-    while (c_first > 0 && share_lo(p, c_first) > G0) c_first--;
-    while (c_first + 1 < C && share_lo(p, c_first + 1) <= G0) c_first++;
-    int c_last = (int)min(((G1 - 1) * C) / p.total_tiles, (int64_t)C - 1);
-    while (c_last > 0 && share_lo(p, c_last) >= G1) c_last--;
-    while (c_last + 1 < C && share_lo(p, c_last + 1) < G1) c_last++;
+    int c_first, c_last;
+    group_ctas(p, G0, G1, c_first, c_last);
     const int parts = c_last - c_first + 1;                   // <= n_cta <= MERGE_THREADS
     if (parts == 1 && p.mode == 0) return;                     // the split kernel wrote the output itself
 
@@ -726,6 +735,18 @@ void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
         case 2: launch_split_t<2, 2>(s, p); break;
         default: launch_split_t<4, 1>(s, p); break;
     }
+}
+
+// Whether any group of the launch is cut over more than one CTA (its output then comes from the merge).
+bool attn_split_needs_merge(const AttnParams &p) {
+    for (int i = 0; i < p.n_seq; i++)
+        for (int h = 0; h < p.kv_heads; h++) {
+            const int64_t g0 = (int64_t)p.seq[i].cum_tiles + (int64_t)h * p.seq[i].n_tiles;
+            int c0, c1;
+            group_ctas(p, g0, g0 + p.seq[i].n_tiles, c0, c1);
+            if (c0 != c1) return true;
+        }
+    return false;
 }
 
 void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows) {

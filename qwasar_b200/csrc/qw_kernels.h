@@ -93,6 +93,7 @@ __host__ __device__ inline int attn_split_slots(const AttnParams &p) { return p.
 size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows);
 void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows);
 void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
+bool attn_split_needs_merge(const AttnParams &p);
 
 // Causal prefill on tcgen05 tensor cores: one CTA per (128-row tile, query head).
 struct PrefillParams {

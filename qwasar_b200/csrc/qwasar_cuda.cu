@@ -459,18 +459,8 @@ bool launch_split_merge(qw_cmd c, AttnParams &p, int max_rows, float *scr) {
     if (timed) cudaEventRecord(kt.t0, c->stream);
     launch_attn_split(c->stream, p, max_rows);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
-    bool need_merge = p.mode == 1;
-    const int64_t T = p.total_tiles, C = p.n_cta;
-    for (int i = 0; i < p.n_seq && !need_merge; i++)
-        for (int h = 0; h < p.kv_heads && !need_merge; h++) {
-            // a group is written directly only when one CTA's share covers it whole
-            const int64_t g0 = (int64_t)p.seq[i].cum_tiles + (int64_t)h * p.seq[i].n_tiles, g1 = g0 + p.seq[i].n_tiles - 1;
-            int64_t c0 = (g0 * C) / T, c1 = (g1 * C) / T;
-            while (c0 + 1 < C && ((c0 + 1) * T) / C <= g0) c0++;
-            while (c1 + 1 < C && ((c1 + 1) * T) / C <= g1) c1++;
-            if (c0 != c1) need_merge = true;
-        }
-    if (need_merge) launch_attn_merge(c->stream, p, max_rows);
+    // a group is written directly only when one CTA's share covers it whole
+    if (p.mode == 1 || attn_split_needs_merge(p)) launch_attn_merge(c->stream, p, max_rows);
     return cuda_ok(c, cudaGetLastError(), "attention launch");
 }
 

@@ -170,6 +170,14 @@ uint64_t    qw_gpu_launch_count(void);
  * rotates its own query tiles (default) or the pre-op kernel does.  Returns false for an unknown
  * knob or value. */
 bool        qw_gpu_tune(const char *knob, int32_t value);
+/* How the split-KV decode kernel divides a launch of n_seq sequences (n_keys[i] keys each, kv_heads
+ * heads) over at most n_cta_max CTAs: all (sequence, kv head) groups are laid end to end as one line
+ * of 32-key tiles and share_first[c] is the first tile of CTA c's share, share_first[n] the total
+ * (n = the return value = CTAs used, <= 256; share_first holds n_cta_max + 1 entries).  Shares are
+ * equal in cost, a group start counting as three tiles.  *needs_merge (may be NULL) tells whether any
+ * group is cut over several CTAs.  Host arithmetic only -- works without a device; 0 on bad arguments. */
+int32_t     qw_attn_split_plan(int32_t n_seq, int32_t kv_heads, const int32_t *n_keys, int32_t n_cta_max,
+                               int32_t *share_first, int32_t *needs_merge);
 /* Per-kernel device timing for roofline figures: while on, every launch of an attention
  * kernel ("qw_attn_split", "qw_attn_prefill", "qw_attn_preop") is bracketed by a pair of CUDA events on its
  * stream; qw_cmd_wait folds the elapsed times into per-kernel totals that

@@ -64,6 +64,7 @@ SIGNATURES = {
     "qw_gpu_sm_count": (_i32, []),
     "qw_gpu_launch_count": (C.c_uint64, []),
     "qw_gpu_tune": (_b, [C.c_char_p, _i32]),
+    "qw_attn_split_plan": (_i32, [_i32, _i32, _vp, _i32, _vp, _vp]),
     "qw_prof_kernels": (None, [_b]),
     "qw_prof_kernel_read": (_b, [C.c_char_p, _vp, _vp, _b]),
     "qw_buf_alloc_device": (_vp, [_sz]),

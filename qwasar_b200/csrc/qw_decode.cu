@@ -737,6 +737,10 @@ void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
     }
 }
 
+// The cut of the tile line, for the host: first tile of every CTA's share (n_cta + 1 entries).
+void attn_split_shares(const AttnParams &p, int32_t *share_first) {
+    for (int c = 0; c <= p.n_cta; c++) share_first[c] = share_lo(p, c);
+}
 // Whether any group of the launch is cut over more than one CTA (its output then comes from the merge).
 bool attn_split_needs_merge(const AttnParams &p) {
     for (int i = 0; i < p.n_seq; i++)

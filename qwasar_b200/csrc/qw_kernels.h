@@ -94,6 +94,7 @@ size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows);
 void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows);
 void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows);
 bool attn_split_needs_merge(const AttnParams &p);
+void attn_split_shares(const AttnParams &p, int32_t *share_first);
 
 // Causal prefill on tcgen05 tensor cores: one CTA per (128-row tile, query head).
 struct PrefillParams {

@@ -571,6 +571,26 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     return false;
 }
+// How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
+extern "C" int32_t qw_attn_split_plan(int32_t n_seq, int32_t kv_heads, const int32_t *n_keys, int32_t n_cta_max,
+                                      int32_t *share_first, int32_t *needs_merge) {
+    if (n_seq <= 0 || n_seq > QW_MAX_SEQ || kv_heads <= 0 || !n_keys || n_cta_max <= 0 || !share_first) return 0;
+    AttnParams p;
+    memset(&p, 0, sizeof p);
+    p.n_seq = n_seq; p.kv_heads = kv_heads;
+    int cum = 0;
+    for (int i = 0; i < n_seq; i++) {
+        if (n_keys[i] <= 0) return 0;
+        p.seq[i].key_lo = 0; p.seq[i].key_hi = n_keys[i];
+        p.seq[i].tile0 = 0; p.seq[i].n_tiles = (n_keys[i] + 31) / 32; p.seq[i].cum_tiles = cum;
+        cum += p.seq[i].n_tiles * kv_heads;
+    }
+    p.total_tiles = cum;
+    p.n_cta = std::min(std::min(n_cta_max, 256), cum);
+    attn_split_shares(p, share_first);
+    if (needs_merge) *needs_merge = attn_split_needs_merge(p) ? 1 : 0;
+    return p.n_cta;
+}
 extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }
 extern "C" bool qw_prof_kernel_read(const char *kernel, double *ms_total, int64_t *launches, bool reset) {
     auto it = G.kernel_ms.find(kernel ? kernel : "");

@@ -180,7 +180,11 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
     if (slot0 < qs + kvh) {                              // the block holds a query or key head
         if (warp < n) {
             const int r = r0 + warp;
-            const float ang = __fmul_rn((float)s.pos[(size_t)p.axis[lane] * s.rows + r], p.inv_freq[lane]);
+            // the token's position on all three axes and the dim's axis are fetched side by side
+            // (a position looked up through the axis would be a second trip to memory)
+            const int32_t p0 = s.pos[r], p1 = s.pos[(size_t)s.rows + r], p2 = s.pos[(size_t)2 * s.rows + r];
+            const int ax = p.axis[lane];
+            const float ang = __fmul_rn((float)(ax == 0 ? p0 : ax == 1 ? p1 : p2), p.inv_freq[lane]);
             float sn, cs;
             sincosf(ang, &sn, &cs);
             cs_s[warp][lane] = cs; cs_s[warp][32 + lane] = sn;

@@ -498,6 +498,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const size_t pi0 = (size_t)(c_first + gidx) * (MT * 16) + row;      // partial q sits MT*16 rows further per q
+    // the gate of the row is fetched now, by the quarter that will use it: it depends on nothing here
+    const int r = row / p.gqa, g = row - r * p.gqa;
+    const size_t rh = (size_t)r * p.q_heads + h * p.gqa + g;
+    float gate4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sq.gate && p.mode == 0 && tid < 64) {
+        const size_t gi = rh * p.gate_stride + tid * 4;
+#pragma unroll
+        for (int i = 0; i < 4; i++) gate4[i] = load_gate(sq.gate, gi + i, p.gate_dtype);
+    }
     // max over the non-empty partials, then each partial's weight and the denominator
     float mq = -3.0e38f, lq = 0.0f;
     if (tid < parts) {
@@ -548,8 +557,6 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
         const float4 o = *reinterpret_cast<const float4 *>(&acc_s[i][d4]);
         acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
     }
-    const int r = row / p.gqa, g = row - r * p.gqa;
-    const size_t rh = (size_t)r * p.q_heads + h * p.gqa + g;
     if (p.mode == 1) {
         // leave one combined partial per (row, head) for the exchange between GPUs
         const size_t ci = (size_t)sq.row_slot0 * p.q_heads + rh;
@@ -561,11 +568,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
     acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
     if (sq.gate) {
-        const size_t gi = rh * p.gate_stride + d4;
-        acc.x *= sigmoidf(load_gate(sq.gate, gi, p.gate_dtype));
-        acc.y *= sigmoidf(load_gate(sq.gate, gi + 1, p.gate_dtype));
-        acc.z *= sigmoidf(load_gate(sq.gate, gi + 2, p.gate_dtype));
-        acc.w *= sigmoidf(load_gate(sq.gate, gi + 3, p.gate_dtype));
+        acc.x *= sigmoidf(gate4[0]); acc.y *= sigmoidf(gate4[1]); acc.z *= sigmoidf(gate4[2]); acc.w *= sigmoidf(gate4[3]);
     }
     if (p.out_dtype == DT_BF16) {
         uint2 v;

@@ -177,6 +177,8 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
         }
         dst_row[u] = is_q ? (int64_t)r * qh + h : kv_row(is_k ? s.kc : s.vc, h, s.base_pos + r);
     }
+    uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);     // the norm weights ride along with the rows
+    if (active && wn && (is_q || is_k)) w4 = __ldg(reinterpret_cast<const uint4 *>(wn) + lane);
     if (slot0 < qs + kvh) {                              // the block holds a query or key head
         if (warp < n) {
             const int r = r0 + warp;
@@ -197,7 +199,6 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
     if (!active) return;
     float w[8];
     if (wn && (is_q || is_k)) {
-        const uint4 w4 = __ldg(reinterpret_cast<const uint4 *>(wn) + lane);
         const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
         for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(ww[i] << 16); w[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }

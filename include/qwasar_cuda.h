@@ -143,6 +143,19 @@ bool qw_op_attn_decode_split(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_r
 bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache,
                               int32_t rows, int32_t q_heads, int32_t kv_heads,
                               int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale);
+/* qwasar_gpu.h:635-651 -- attention that sees only listed cache positions (what the QSA layers of
+ * Flash-Next run once a selection exists).  list: uint32 [rows, 1 + cap] with cap = block_topk *
+ * ratio + ratio (qw_qsa_list_cap, :637-639): per row a count, then that many positions ascending;
+ * entries past the count are never read.  Row r of query head h attends those positions of kv head
+ * h / (q_heads / kv_heads).  The gated form multiplies by sigmoid(gate), gate f32 [rows, q_heads,
+ * head_dim].  fp32 throughout (CUDA cores).  The selection ops that build the list
+ * (qw_op_qsa_scores / _pool / _select) are not provided. */
+void qw_op_attn_masked(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list,
+                       int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                       int32_t max_ctx, int32_t base_pos, float scale, int32_t block_topk, int32_t ratio);
+void qw_op_attn_masked_gated(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache,
+                             qw_ref list, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                             int32_t max_ctx, int32_t base_pos, float scale, int32_t block_topk, int32_t ratio);
 /* qwasar_gpu.h:439-446.  What the graph calls: rows >= 16 -> the tiled
  * kernel; fewer -> the split-KV kernel; the per-query kernel where those
  * decline. */

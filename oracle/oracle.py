@@ -62,6 +62,8 @@ class Oracle:
         L.orc_attn_decode.argtypes = [_f32p, _f32p, _u16p, _u16p, _i32, _i32, _i32, _i32, _i32,
                                       _i32, _f32, _int, _int]
         L.orc_mul_sigmoid.argtypes = [_f32p, _f32p, _sz]
+        L.orc_attn_masked.argtypes = [C.c_void_p] * 5 + [_i32] * 6 + [_f32, _int]
+        L.orc_attn_masked.restype = None
         L.orc_attn_partial.argtypes = [_f32p, _f32p, _f32p, C.c_void_p, C.c_void_p, _i32, _i32,
                                        _i32, _f32, _int]
         L.orc_attn_merge.argtypes = [_f32p, _f32p, _f32p, _i32, _i32, C.c_void_p]
@@ -120,6 +122,17 @@ class Oracle:
         out = np.empty((rows, q_heads, head_dim), np.float32)
         self.lib.orc_attn_decode(out, q, kc, vc, rows, q_heads, kv_heads, head_dim, max_ctx,
                                  base_pos, scale, fmt, threads or self.max_threads)
+        return out
+
+    def attn_masked(self, q, kc, vc, lists, rows, q_heads, kv_heads, head_dim, max_ctx, scale, fmt=BF16):
+        """lists: uint32 [rows, 1 + cap] (count, then positions ascending)."""
+        q = np.ascontiguousarray(q, np.float32)
+        lists = np.ascontiguousarray(lists, np.uint32)
+        out = np.empty((rows, q_heads, head_dim), np.float32)
+        self.lib.orc_attn_masked(out.ctypes.data_as(C.c_void_p), q.ctypes.data_as(C.c_void_p), kc.ctypes.data_as(C.c_void_p),
+                                 vc.ctypes.data_as(C.c_void_p), lists.ctypes.data_as(C.c_void_p), C.c_int32(lists.shape[1]),
+                                 C.c_int32(rows), C.c_int32(q_heads), C.c_int32(kv_heads), C.c_int32(head_dim),
+                                 C.c_int32(max_ctx), C.c_float(scale), C.c_int(fmt))
         return out
 
     def mul_sigmoid(self, y, gate):

@@ -225,6 +225,40 @@ void orc_attn_decode(float *out, const float *q, const uint16_t *kc,
     }
 }
 
+/* Attention that sees only listed cache positions (the QSA mask as a list):
+ * row r of query head h attends positions list[r][1 .. 1 + list[r][0]) of kv
+ * head h / (q_heads/kv_heads), in list order; list rows are list_stride
+ * uint32 apart (a count, then positions ascending, entries past the count
+ * unspecified) -- qwasar_gpu.h:635-645.  The arithmetic is the reference's
+ * masked softmax (qwasar_flash_cpu.c:447-478: scores of the allowed
+ * positions, max, expf, sum, weighted V), which over a list is
+ * orc_attend_one on the listed rows: the K and V rows are gathered into a
+ * dense run and attended like a cache of that many positions. */
+void orc_attn_masked(float *out, const float *q, const uint16_t *kc, const uint16_t *vc,
+                     const uint32_t *list, int32_t list_stride, int32_t rows, int32_t q_heads,
+                     int32_t kv_heads, int32_t head_dim, int32_t max_ctx, float scale, int fmt) {
+    const int32_t gqa = q_heads / kv_heads;
+    for (int32_t r = 0; r < rows; r++) {
+        const uint32_t *l = list + (size_t)r * list_stride;
+        const int32_t n = (int32_t)l[0];
+        uint16_t *kd = (uint16_t *)malloc((size_t)(n ? n : 1) * head_dim * 2);
+        uint16_t *vd = (uint16_t *)malloc((size_t)(n ? n : 1) * head_dim * 2);
+        float *work = (float *)malloc((size_t)(n ? n : 1) * sizeof(float));
+        for (int32_t kvh = 0; kvh < kv_heads; kvh++) {
+            for (int32_t j = 0; j < n; j++) {
+                memcpy(kd + (size_t)j * head_dim, kc + ((size_t)kvh * max_ctx + l[1 + j]) * head_dim, (size_t)head_dim * 2);
+                memcpy(vd + (size_t)j * head_dim, vc + ((size_t)kvh * max_ctx + l[1 + j]) * head_dim, (size_t)head_dim * 2);
+            }
+            for (int32_t g = 0; g < gqa; g++) {
+                const size_t p = (size_t)r * q_heads + (size_t)kvh * gqa + g;
+                if (n > 0) orc_attend_one(out + p * head_dim, q + p * head_dim, kd, vd, n, head_dim, scale, fmt, work);
+                else memset(out + p * head_dim, 0, (size_t)head_dim * sizeof(float));
+            }
+        }
+        free(kd); free(vd); free(work);
+    }
+}
+
 /* out[i] *= 1 / (1 + exp(-gate[i]))  (metal/act.metal:29-37). */
 void orc_mul_sigmoid(float *y, const float *gate, size_t n) {
     for (size_t i = 0; i < n; i++) y[i] *= 1.0f / (1.0f + expf(-gate[i]));

@@ -630,22 +630,36 @@ __global__ void __launch_bounds__(64) merge_parts_kernel(void *out, int out_dtyp
 // The counterpart of the reference's qw_attn_decode (metal/attn.metal:32-129): no rounding
 // of q or of the softmax weights, so it tracks the CPU twin to float rounding.  One block
 // per (key slice, row, query head); 8 warps stride the slice's keys, a lane owns 8 dims.
+// With a list (the QSA mask as positions, qwasar_gpu.h:635-645: per row a count, then that many
+// positions ascending, list_stride uint32 apart) the "keys" are the list's entries, and only
+// those positions of the cache are read; entries past the count are never touched, a position
+// outside the cache is skipped.
 __global__ void __launch_bounds__(256) attn_per_query_kernel(AttnSeq sq, int q_heads, int kv_heads, float scale,
-                                                             float *pacc, float *pstat, int splits) {
+                                                             float *pacc, float *pstat, int splits,
+                                                             const uint32_t *__restrict__ list, int list_stride) {
     const int split = blockIdx.y, rh = blockIdx.x;
     const int r = rh / q_heads, h = rh - r * q_heads;
     const int kvh = h / (q_heads / kv_heads);
-    const int n = min(sq.key_hi, sq.base_pos + r + 1);
-    const int per = max(1, (n - sq.key_lo + splits - 1) / splits);
-    const int t0 = sq.key_lo + split * per, t1 = min(n, t0 + per);
+    const uint32_t *row_list = list ? list + (size_t)r * list_stride : nullptr;
+    const int lo = list ? 0 : sq.key_lo;
+    const int n = list ? (int)min(row_list[0], (uint32_t)(list_stride - 1)) : min(sq.key_hi, sq.base_pos + r + 1);
+    const int per = max(1, (n - lo + splits - 1) / splits);
+    const int t0 = lo + split * per, t1 = min(n, t0 + per);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const float *qv = reinterpret_cast<const float *>(sq.q) + (size_t)rh * 256 + lane * 8;
     float q[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) q[i] = qv[i] * scale;
     float m = -3.0e38f, l = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int t = t0 + warp; t < t1; t += 8) {
+    for (int j = t0 + warp; j < t1; j += 8) {
+        int t = j;
+        if (row_list) {
+            const uint32_t pos = row_list[1 + j];
+            if (pos >= (uint32_t)sq.kc.max_ctx) continue;        // warp-uniform
+            t = (int)pos;
+        }
         const int64_t kr = kv_row(sq.kc, kvh, t), vr = kv_row(sq.vc, kvh, t);
+        if (kr < 0 || vr < 0) continue;                          // a page that was never mapped
         const uint4 kk = reinterpret_cast<const uint4 *>(sq.kc.base + kr * 256)[lane];
         const uint4 vv = reinterpret_cast<const uint4 *>(sq.vc.base + vr * 256)[lane];
         const uint32_t kw[4] = {kk.x, kk.y, kk.z, kk.w}, vw[4] = {vv.x, vv.y, vv.z, vv.w};
@@ -786,9 +800,9 @@ size_t attn_per_query_scratch_bytes(int rows, int q_heads, int splits) {
     return (size_t)splits * rows * q_heads * 258 * sizeof(float);
 }
 void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, float *pacc,
-                           float *pstat, int splits) {
+                           float *pstat, int splits, const uint32_t *list, int list_stride) {
     dim3 grid(seq.rows * q_heads, splits);
-    attn_per_query_kernel<<<grid, 256, 0, s>>>(seq, q_heads, kv_heads, scale, pacc, pstat, splits);
+    attn_per_query_kernel<<<grid, 256, 0, s>>>(seq, q_heads, kv_heads, scale, pacc, pstat, splits, list, list_stride);
     g_launches++;
 }
 

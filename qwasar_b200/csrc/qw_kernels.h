@@ -125,8 +125,9 @@ void launch_attn_prefill(cudaStream_t s, const PrefillParams &p);
 bool attn_prefill_io_ok(const void *out, int out_dtype, const void *gate, int gate_dtype, int gate_stride);
 
 // Per-query fp32 kernel (CUDA cores, no rounding of q or of the weights).
+// list != nullptr: row r attends only the positions list[r * list_stride + 1 ...] (count at [0]).
 void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale,
-                           float *pacc, float *pstat, int splits);
+                           float *pacc, float *pstat, int splits, const uint32_t *list = nullptr, int list_stride = 0);
 size_t attn_per_query_scratch_bytes(int rows, int q_heads, int splits);
 int attn_per_query_splits(int rows, int q_heads, int n_keys);
 

@@ -1105,6 +1105,46 @@ extern "C" void qw_op_attn_decode(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache,
     cuda_ok(c, cudaGetLastError(), "attn_decode launch");
 }
 
+// Attention over listed positions only (the QSA mask as a list): the fp32 per-query kernel walks
+// each row's list in `splits` slices, the merge combines them (and applies the gate).
+static void attn_masked(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list, int32_t rows,
+                        int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale,
+                        int32_t block_topk, int32_t ratio) {
+    if (!live(c)) return;
+    if (head_dim != QW_HEAD_DIM) { fprintf(stderr, "qwasar: attention head_dim %d unsupported (kernel is built for 256)\n", head_dim); return; }
+    if (!shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos) || block_topk < 0 || ratio <= 0) { cmd_fail(c, "attn_masked: bad shape"); return; }
+    const int32_t cap = block_topk * ratio + ratio;               // qw_qsa_list_cap (qwasar_gpu.h:637-639)
+    AttnSeq sq;
+    memset(&sq, 0, sizeof sq);
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, base_pos + rows, false, false, &sq.kc, nullptr)) return;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, base_pos + rows, false, false, &sq.vc, nullptr)) return;
+    const size_t n = (size_t)rows * q_heads * head_dim * 4;
+    sq.q = dev_range(c, q, n, false);
+    void *po = dev_range(c, out, n, true);
+    const void *pg = gate.buf ? dev_range(c, gate, n, false) : nullptr;
+    const uint32_t *pl = (const uint32_t *)dev_range(c, list, (size_t)rows * (1 + cap) * 4, false, 4);
+    if (!sq.q || !po || !pl || (gate.buf && !pg)) return;
+    sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = 0; sq.key_hi = base_pos + rows;
+    const int splits = attn_per_query_splits(rows, q_heads, cap);
+    float *scr = (float *)cmd_scratch(c, attn_per_query_scratch_bytes(rows, q_heads, splits));
+    if (!scr) return;
+    float *pstat = scr + (size_t)splits * rows * q_heads * 256;
+    launch_attn_per_query(c->stream, sq, q_heads, kv_heads, scale, scr, pstat, splits, pl, 1 + cap);
+    launch_merge_parts(c->stream, po, DT_F32, scr, pstat, pg, DT_F32, 256, rows * q_heads, splits, nullptr, nullptr);
+    cuda_ok(c, cudaGetLastError(), "attn_masked launch");
+}
+extern "C" void qw_op_attn_masked(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list, int32_t rows,
+                                  int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx, int32_t base_pos, float scale,
+                                  int32_t block_topk, int32_t ratio) {
+    attn_masked(c, out, qw_ref{nullptr, 0}, q, kcache, vcache, list, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale, block_topk, ratio);
+}
+extern "C" void qw_op_attn_masked_gated(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list,
+                                        int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                        int32_t base_pos, float scale, int32_t block_topk, int32_t ratio) {
+    if (!gate.buf) { if (c) cmd_fail(c, "attn_masked_gated: no gate"); return; }
+    attn_masked(c, out, gate, q, kcache, vcache, list, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos, scale, block_topk, ratio);
+}
+
 extern "C" bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, int32_t rows,
                                          int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
                                          int32_t base_pos, float scale) {

@@ -1,0 +1,102 @@
+"""qw_op_attn_masked / qw_op_attn_masked_gated (qwasar_gpu.h:635-651) against the oracle, in the
+shape of the reference's own test (tests/test_sparse.c:1036-1122): 24 query / 2 KV heads, 64 rows
+at base 6000, per row about a third of the positions plus the newest four, every 16th row only a
+handful, the list poisoned past its count; as one chunk and a row at a time; plain and gated;
+over a plain cache and over the paged arena.  The kernel is fp32 throughout, so the bound is the
+reference's for its fp32 path: rel-L2 < 1e-4 (tests/test_sparse.c:1115-1119), and it is also
+held to 2e-5 here."""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+from gpu_util import Bufs, QwRef, arena_fill
+from qwasar_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def make_lists(rows, base, cap, seed=5):
+    """The reference test's lists (tests/test_sparse.c:1050-1066), LCG and all."""
+    lists = np.full((rows, 1 + cap), 0xFFFFFFF0, np.uint32)
+    st = seed
+    for r in range(rows):
+        n_keys = base + r + 1
+        want = 3 if r % 16 == 3 else cap - 8 - (r % 5) * 37
+        n, t = 0, 0
+        while t < n_keys - 4 and n < want:
+            st = (st * 1664525 + 1013904223) & 0xFFFFFFFF
+            if (st >> 16) % 3 == 0:
+                lists[r, 1 + n] = t; n += 1
+            t += 1
+        for t in range(n_keys - 4, n_keys):
+            lists[r, 1 + n] = t; n += 1
+        lists[r, 0] = n
+    return lists
+
+
+@pytest.mark.parametrize("paged", [False, True], ids=["linear", "arena"])
+def test_masked_chunk_and_rows_plain_and_gated(be, oracle, paged):
+    rows, qh, kvh, base, topk, ratio = 64, 24, 2, 6000, 576, 4
+    ctx = base + rows + 8
+    cap = topk * ratio + ratio
+    rng = np.random.default_rng(71)
+    q = (3.0 * rng.standard_normal((rows, qh, 256))).astype(np.float32)          # sharper softmax, as the reference's test
+    gate = rng.standard_normal((rows, qh, 256)).astype(np.float32)
+    kc = np.zeros((kvh, ctx, 256), np.uint16); vc = np.zeros_like(kc)
+    kc[:, :base + rows] = synth.cache_bits(rng, kvh, base + rows); vc[:, :base + rows] = synth.cache_bits(rng, kvh, base + rows)
+    kc[:, base + rows:] = synth.f32_to_bf16_bits(np.float32(30.0)); vc[:, base + rows:] = synth.f32_to_bf16_bits(np.float32(-999.0))
+    lists = make_lists(rows, base, cap)
+    want = oracle.attn_masked(q, kc, vc, lists, rows, qh, kvh, 256, ctx, 0.0625)
+    want_gated = oracle.mul_sigmoid(want, gate)
+    with Bufs(be) as B:
+        qb, _ = B.shared(q); gb, _ = B.shared(gate); lb, _ = B.shared(lists)
+        o_chunk, v_chunk = B.shared_empty((rows, qh, 256), np.float32); o_rows, v_rows = B.shared_empty((rows, qh, 256), np.float32)
+        g_chunk, w_chunk = B.shared_empty((rows, qh, 256), np.float32); g_rows, w_rows = B.shared_empty((rows, qh, 256), np.float32)
+        if paged:
+            kb = B.arena(1, kvh, ctx, seed=3); vb = B.arena(1, kvh, ctx, seed=4)
+            arena_fill(be, kb, 0, kc[:, :base + rows], kvh, ctx); arena_fill(be, vb, 0, vc[:, :base + rows], kvh, ctx)
+        else:
+            kb = B.device(kc); vb = B.device(vc)
+        c = be.cmd_begin()
+        be.op_attn_masked(c, QwRef(o_chunk, 0), QwRef(qb, 0), QwRef(kb, 0), QwRef(vb, 0), QwRef(lb, 0), rows, qh, kvh, 256, ctx, base,
+                          0.0625, topk, ratio)
+        be.op_attn_masked_gated(c, QwRef(g_chunk, 0), QwRef(gb, 0), QwRef(qb, 0), QwRef(kb, 0), QwRef(vb, 0), QwRef(lb, 0), rows, qh,
+                                kvh, 256, ctx, base, 0.0625, topk, ratio)
+        row_bytes, list_bytes = qh * 256 * 4, (1 + cap) * 4
+        for r in range(rows):
+            be.op_attn_masked(c, QwRef(o_rows, r * row_bytes), QwRef(qb, r * row_bytes), QwRef(kb, 0), QwRef(vb, 0),
+                              QwRef(lb, r * list_bytes), 1, qh, kvh, 256, ctx, base + r, 0.0625, topk, ratio)
+            be.op_attn_masked_gated(c, QwRef(g_rows, r * row_bytes), QwRef(gb, r * row_bytes), QwRef(qb, r * row_bytes), QwRef(kb, 0),
+                                    QwRef(vb, 0), QwRef(lb, r * list_bytes), 1, qh, kvh, 256, ctx, base + r, 0.0625, topk, ratio)
+        be.cmd_wait(c); be.cmd_free(c)
+        for name, got, ref in (("chunk", v_chunk, want), ("row at a time", v_rows, want), ("gated chunk", w_chunk, want_gated),
+                               ("gated rows", w_rows, want_gated)):
+            e = rel_l2(np.array(got), ref)
+            assert e < 2e-5, f"attn_masked, {name}: rel-L2 {e:.3e}"
+        # the same kernel either way; only the number of list slices per row differs with the row count
+        assert rel_l2(np.array(v_chunk), np.array(v_rows)) < 1e-6
+
+
+def test_masked_edge_lists(be, oracle):
+    """A list of one position, a full list, and a position outside the cache (skipped, no fault)."""
+    rows, qh, kvh, base, topk, ratio = 3, 8, 2, 100, 8, 4
+    ctx, cap = 128, topk * ratio + ratio
+    rng = np.random.default_rng(9)
+    q = rng.standard_normal((rows, qh, 256)).astype(np.float32)
+    kc = synth.cache_bits(rng, kvh, ctx); vc = synth.cache_bits(rng, kvh, ctx)
+    lists = np.full((rows, 1 + cap), 0xFFFFFFF0, np.uint32)
+    lists[0, 0] = 1; lists[0, 1] = 100
+    lists[1, 0] = cap; lists[1, 1:1 + cap] = np.arange(101 - cap + 1, 102)
+    lists[2, 0] = 3; lists[2, 1:4] = [5, 50, 102]
+    want = oracle.attn_masked(q, kc, vc, lists, rows, qh, kvh, 256, ctx, 0.0625)
+    dev_lists = lists.copy()
+    dev_lists[2, 0] = 4; dev_lists[2, 4] = 5000                                   # outside the cache: must be skipped
+    with Bufs(be) as B:
+        qb, _ = B.shared(q); lb, _ = B.shared(dev_lists)
+        ob, ov = B.shared_empty((rows, qh, 256), np.float32)
+        kb = B.device(kc); vb = B.device(vc)
+        c = be.cmd_begin()
+        be.op_attn_masked(c, QwRef(ob, 0), QwRef(qb, 0), QwRef(kb, 0), QwRef(vb, 0), QwRef(lb, 0), rows, qh, kvh, 256, ctx, base,
+                          0.0625, topk, ratio)
+        be.cmd_wait(c); be.cmd_free(c)
+        assert rel_l2(np.array(ov), want) < 2e-5

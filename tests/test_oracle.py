@@ -195,3 +195,24 @@ def test_fast_math_build_is_immaterial(oracle):
     a = oracle.attn_decode(q, kc, vc, rows, qh, kvh, 256, ctx, base, 0.0625)
     b = fast.attn_decode(q, kc, vc, rows, qh, kvh, 256, ctx, base, 0.0625)
     assert rel_l2(b, a) < 1e-5
+
+
+def test_masked_attention_is_the_reference_function_over_the_listed_rows(oracle, refcpu):
+    """orc_attn_masked (attention over a list of visible positions, qwasar_gpu.h:635-645) against the
+    reference's own compiled qw_cpu_attn_decode: over the K/V rows of the list gathered into a dense
+    cache of that many positions the two are the same arithmetic in the same order -- bit for bit."""
+    rng = np.random.default_rng(42)
+    rows, qh, kvh, ctx, cap = 5, 12, 2, 700, 96
+    q = rng.standard_normal((rows, qh, 256)).astype(np.float32)
+    kc = synth.cache_bits(rng, kvh, ctx); vc = synth.cache_bits(rng, kvh, ctx)
+    lists = np.full((rows, 1 + cap), 0xFFFFFFF0, np.uint32)             # poisoned past the count
+    for r in range(rows):
+        n = [1, 3, cap, 17, cap - 1][r]
+        lists[r, 0] = n
+        lists[r, 1:1 + n] = np.sort(rng.choice(ctx, n, replace=False))
+    got = oracle.attn_masked(q, kc, vc, lists, rows, qh, kvh, 256, ctx, 0.0625)
+    for r in range(rows):
+        n = int(lists[r, 0]); pos = lists[r, 1:1 + n].astype(np.int64)
+        want = refcpu.attn_decode(q[r:r + 1], np.ascontiguousarray(kc[:, pos]), np.ascontiguousarray(vc[:, pos]),
+                                  1, qh, kvh, 256, n, n - 1, 0.0625)
+        assert np.array_equal(got[r], want[0])

@@ -148,14 +148,35 @@ bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_
  * ratio + ratio (qw_qsa_list_cap, :637-639): per row a count, then that many positions ascending;
  * entries past the count are never read.  Row r of query head h attends those positions of kv head
  * h / (q_heads / kv_heads).  The gated form multiplies by sigmoid(gate), gate f32 [rows, q_heads,
- * head_dim].  fp32 throughout (CUDA cores).  The selection ops that build the list
- * (qw_op_qsa_scores / _pool / _select) are not provided. */
+ * head_dim].  fp32 throughout (CUDA cores). */
 void qw_op_attn_masked(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list,
                        int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                        int32_t max_ctx, int32_t base_pos, float scale, int32_t block_topk, int32_t ratio);
 void qw_op_attn_masked_gated(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache,
                              qw_ref list, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                              int32_t max_ctx, int32_t base_pos, float scale, int32_t block_topk, int32_t ratio);
+/* qwasar_gpu.h:620-634 -- QSA's indexer.  qn f32 [rows, nq, d] are the normed + rotated index
+ * queries, ikeys f32 [positions, d] a layer's raw index keys, k_norm bf16 [d] (or a null ref),
+ * inv_freq f32 [rotary_dim / 2].  Block b = positions [b * ratio, (b + 1) * ratio): its key is the
+ * mean of its raw keys, RMS-normed, rotated at position b * ratio; score(r, b) = sum over heads of
+ * max(qn[r, h] . key_b, 0) / sqrt(d) for the (base_pos + r + 1) / ratio complete blocks row r sees
+ * (scores f32 [rows, max_blocks]; other entries are left alone).  qw_op_qsa_pool stores the keys of
+ * blocks [b0, b1) into pool f32 [max_blocks, d]; qw_op_qsa_scores_pooled scores from them, with
+ * results identical to qw_op_qsa_scores.  d: a multiple of 32 from 64 to 256; rotary_dim 64. */
+void qw_op_qsa_scores(qw_cmd c, qw_ref scores, qw_ref qn, qw_ref ikeys, qw_ref k_norm,
+                      qw_ref inv_freq, int32_t rows, int32_t nq, int32_t d, int32_t ratio,
+                      int32_t base_pos, int32_t rotary_dim, int32_t max_blocks, float eps);
+void qw_op_qsa_pool(qw_cmd c, qw_ref pool, qw_ref ikeys, qw_ref k_norm, qw_ref inv_freq,
+                    int32_t d, int32_t ratio, int32_t b0, int32_t b1, int32_t rotary_dim, float eps);
+void qw_op_qsa_scores_pooled(qw_cmd c, qw_ref scores, qw_ref qn, qw_ref pool, int32_t rows,
+                             int32_t nq, int32_t d, int32_t ratio, int32_t base_pos, int32_t max_blocks);
+/* qwasar_gpu.h:635-641 -- per row the block_topk best complete blocks (one at a time: the largest
+ * score above -FLT_MAX, the lowest index among equals) plus the incomplete trailing block, as a
+ * byte mask (uint8 [rows, max_ctx]; positions [0, base_pos + r] of row r are written) and as the
+ * list qw_op_attn_masked walks (uint32 [rows, 1 + block_topk * ratio + ratio]: count, then the
+ * visible positions ascending). */
+void qw_op_qsa_select(qw_cmd c, qw_ref mask, qw_ref list, qw_ref scores, int32_t rows, int32_t ratio,
+                      int32_t base_pos, int32_t block_topk, int32_t max_ctx, int32_t max_blocks);
 /* qwasar_gpu.h:439-446.  What the graph calls: rows >= 16 -> the tiled
  * kernel; fewer -> the split-KV kernel; the per-query kernel where those
  * decline. */

@@ -64,6 +64,10 @@ class Oracle:
         L.orc_mul_sigmoid.argtypes = [_f32p, _f32p, _sz]
         L.orc_attn_masked.argtypes = [C.c_void_p] * 5 + [_i32] * 6 + [_f32, _int]
         L.orc_attn_masked.restype = None
+        L.orc_qsa_scores.argtypes = [C.c_void_p] * 6 + [_i32] * 7 + [_f32]
+        L.orc_qsa_scores.restype = None
+        L.orc_qsa_select.argtypes = [C.c_void_p] * 3 + [_i32] * 6
+        L.orc_qsa_select.restype = None
         L.orc_attn_partial.argtypes = [_f32p, _f32p, _f32p, C.c_void_p, C.c_void_p, _i32, _i32,
                                        _i32, _f32, _int]
         L.orc_attn_merge.argtypes = [_f32p, _f32p, _f32p, _i32, _i32, C.c_void_p]
@@ -134,6 +138,24 @@ class Oracle:
                                  C.c_int32(rows), C.c_int32(q_heads), C.c_int32(kv_heads), C.c_int32(head_dim),
                                  C.c_int32(max_ctx), C.c_float(scale), C.c_int(fmt))
         return out
+
+    def qsa_scores(self, qn, ikeys, k_norm_bits, inv_freq, rows, nq, d, ratio, base_pos, rotary_dim, max_blocks, eps):
+        """Returns (scores [rows, max_blocks] with NaN where no block is complete, pool [max_blocks, d])."""
+        qn = np.ascontiguousarray(qn, np.float32); ikeys = np.ascontiguousarray(ikeys, np.float32)
+        w = np.ascontiguousarray(k_norm_bits, np.uint16); f = np.ascontiguousarray(inv_freq, np.float32)
+        scores = np.full((rows, max_blocks), np.nan, np.float32); pool = np.zeros((max_blocks, d), np.float32)
+        self.lib.orc_qsa_scores(scores.ctypes.data, pool.ctypes.data, qn.ctypes.data, ikeys.ctypes.data, w.ctypes.data,
+                                f.ctypes.data, rows, nq, d, ratio, base_pos, rotary_dim, max_blocks, eps)
+        return scores, pool
+
+    def qsa_select(self, scores, rows, ratio, base_pos, block_topk, max_ctx):
+        """Returns (mask uint8 [rows, max_ctx] with 255 where not written, list uint32 [rows, 1 + cap])."""
+        scores = np.ascontiguousarray(scores, np.float32)
+        mask = np.full((rows, max_ctx), 255, np.uint8)
+        lists = np.full((rows, 1 + block_topk * ratio + ratio), 0xFFFFFFF0, np.uint32)
+        self.lib.orc_qsa_select(mask.ctypes.data, lists.ctypes.data, scores.ctypes.data, rows, ratio, base_pos, block_topk,
+                                max_ctx, scores.shape[1])
+        return mask, lists
 
     def mul_sigmoid(self, y, gate):
         y = np.array(y, np.float32, copy=True, order="C")

@@ -259,6 +259,81 @@ void orc_attn_masked(float *out, const float *q, const uint16_t *kc, const uint1
     }
 }
 
+/* QSA block scores (qwasar_flash_cpu.c:372-397; the check of tests/test_sparse.c:392-416): for
+ * row r the first (base_pos + r + 1) / ratio blocks of `ratio` raw index keys each are mean-pooled
+ * (sum in position order, then / ratio), RMS-normed with weight k_norm, rotated at the block's
+ * first position (all three axes equal, so only inv_freq matters), and scored against the row's
+ * nq normed + rotated query heads: sum over heads of max(dot, 0), / sqrt(d).  scores is
+ * [rows, max_blocks]; entries of blocks not yet complete are left alone.  pool (optional,
+ * [max_blocks, d]) receives the block keys. */
+void orc_qsa_scores(float *scores, float *pool, const float *qn, const float *ikeys, const uint16_t *k_norm,
+                    const float *inv_freq, int32_t rows, int32_t nq, int32_t d, int32_t ratio, int32_t base_pos,
+                    int32_t rotary_dim, int32_t max_blocks, float eps) {
+    uint8_t axis[128];
+    memset(axis, 0, sizeof axis);
+    float *pooled = (float *)malloc((size_t)d * sizeof(float));
+    float *kn = (float *)malloc((size_t)d * sizeof(float));
+    const int32_t all = (base_pos + rows) / ratio;
+    float *keys = (float *)malloc((size_t)(all ? all : 1) * d * sizeof(float));
+    for (int32_t b = 0; b < all; b++) {
+        for (int32_t i = 0; i < d; i++) {
+            float acc = 0.0f;
+            for (int32_t t = 0; t < ratio; t++) acc += ikeys[(size_t)(b * ratio + t) * d + i];
+            pooled[i] = acc / (float)ratio;
+        }
+        orc_rms_norm(kn, pooled, k_norm, d, 1, eps, 1.0f);
+        const int32_t bp[3] = { b * ratio, b * ratio, b * ratio };
+        orc_rope_partial(kn, bp, axis, inv_freq, 1, 1, d, rotary_dim);
+        memcpy(keys + (size_t)b * d, kn, (size_t)d * sizeof(float));
+        if (pool) memcpy(pool + (size_t)b * d, kn, (size_t)d * sizeof(float));
+    }
+    for (int32_t r = 0; r < rows; r++) {
+        const int32_t n_blocks = (base_pos + r + 1) / ratio;
+        for (int32_t b = 0; b < n_blocks && b < max_blocks; b++) {
+            float s = 0.0f;
+            for (int32_t h = 0; h < nq; h++) {
+                float dot = 0.0f;
+                for (int32_t i = 0; i < d; i++) dot += qn[((size_t)r * nq + h) * d + i] * keys[(size_t)b * d + i];
+                if (dot > 0.0f) s += dot;
+            }
+            scores[(size_t)r * max_blocks + b] = s / sqrtf((float)d);
+        }
+    }
+    free(pooled); free(kn); free(keys);
+}
+
+/* QSA selection (qwasar_flash_cpu.c:363-406; tests/test_sparse.c:452-470): row r sees positions
+ * [0, base_pos + r]; the incomplete trailing block is always visible, and of the complete blocks
+ * the block_topk best by score, found one at a time -- the largest score above -FLT_MAX, the
+ * lowest index among equals.  mask is [rows, max_ctx] bytes (only positions [0, n_keys) of a row
+ * are written), list [rows, 1 + block_topk * ratio + ratio] uint32: the count, then the visible
+ * positions ascending (qwasar_gpu.h:632-639). */
+void orc_qsa_select(uint8_t *mask, uint32_t *list, const float *scores, int32_t rows, int32_t ratio, int32_t base_pos,
+                    int32_t block_topk, int32_t max_ctx, int32_t max_blocks) {
+    const int32_t stride = 1 + block_topk * ratio + ratio;
+    for (int32_t r = 0; r < rows; r++) {
+        const int32_t n_keys = base_pos + r + 1, n_blocks = n_keys / ratio;
+        uint8_t *m = mask + (size_t)r * max_ctx;
+        for (int32_t t = 0; t < n_keys; t++) m[t] = t >= n_blocks * ratio;
+        float *s = (float *)malloc((size_t)(n_blocks ? n_blocks : 1) * sizeof(float));
+        memcpy(s, scores + (size_t)r * max_blocks, (size_t)n_blocks * sizeof(float));
+        const int32_t take = block_topk < n_blocks ? block_topk : n_blocks;
+        for (int32_t n = 0; n < take; n++) {
+            int32_t best = -1;
+            for (int32_t b = 0; b < n_blocks; b++)
+                if (s[b] > -FLT_MAX && (best < 0 || s[b] > s[best])) best = b;
+            if (best < 0) break;
+            for (int32_t t = 0; t < ratio; t++) m[best * ratio + t] = 1;
+            s[best] = -FLT_MAX;
+        }
+        free(s);
+        uint32_t *l = list + (size_t)r * stride;
+        uint32_t cnt = 0;
+        for (int32_t t = 0; t < n_keys; t++) if (m[t]) l[1 + cnt++] = (uint32_t)t;
+        l[0] = cnt;
+    }
+}
+
 /* out[i] *= 1 / (1 + exp(-gate[i]))  (metal/act.metal:29-37). */
 void orc_mul_sigmoid(float *y, const float *gate, size_t n) {
     for (size_t i = 0; i < n; i++) y[i] *= 1.0f / (1.0f + expf(-gate[i]));

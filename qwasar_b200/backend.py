@@ -62,6 +62,10 @@ SIGNATURES = {
     "qw_op_attn": (None, _ATTN),
     "qw_op_attn_masked": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 6 + [_f32, _i32, _i32]),
     "qw_op_attn_masked_gated": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 6 + [_f32, _i32, _i32]),
+    "qw_op_qsa_scores": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 7 + [_f32]),
+    "qw_op_qsa_pool": (None, [_vp, QwRef, QwRef, QwRef, QwRef] + [_i32] * 5 + [_f32]),
+    "qw_op_qsa_scores_pooled": (None, [_vp, QwRef, QwRef, QwRef] + [_i32] * 6),
+    "qw_op_qsa_select": (None, [_vp, QwRef, QwRef, QwRef] + [_i32] * 6),
     "qw_gpu_last_error": (C.c_char_p, []),
     "qw_gpu_sm_count": (_i32, []),
     "qw_gpu_launch_count": (C.c_uint64, []),

@@ -137,6 +137,14 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
                         const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
                         float *pacc_out, float *pstat_out, size_t acc_stride = 0, size_t stat_stride = 0);
 
+// ---- QSA indexer (qw_qsa.cu) ----------------------------------------------------------------
+void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
+                     int b0, int b1, float eps);
+void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const float *pool, int rows, int nq, int d, int ratio,
+                       int base_pos, int max_blocks);
+void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const float *scores, int rows, int ratio, int base_pos,
+                       int block_topk, int max_ctx, int max_blocks);
+
 int sm_count();
 
 

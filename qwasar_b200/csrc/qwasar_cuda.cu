@@ -1105,6 +1105,72 @@ extern "C" void qw_op_attn_decode(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache,
     cuda_ok(c, cudaGetLastError(), "attn_decode launch");
 }
 
+// ---- QSA indexer: block keys, block scores, selection (qwasar_gpu.h:620-639) ----
+static bool qsa_shape_ok(qw_cmd c, const char *op, int32_t d, int32_t ratio, int32_t rotary_dim) {
+    if (d <= 0 || d > 256 || d % 32 || ratio <= 0 || rotary_dim != 64 || d < 64) {
+        cmd_fail(c, "%s: index head dim %d (a multiple of 32 up to 256), ratio %d, rotary_dim %d (64) not supported", op, d, ratio, rotary_dim);
+        return false;
+    }
+    return true;
+}
+extern "C" void qw_op_qsa_pool(qw_cmd c, qw_ref pool, qw_ref ikeys, qw_ref k_norm, qw_ref inv_freq, int32_t d, int32_t ratio,
+                               int32_t b0, int32_t b1, int32_t rotary_dim, float eps) {
+    if (!live(c) || !qsa_shape_ok(c, "qsa_pool", d, ratio, rotary_dim)) return;
+    if (b0 < 0 || b1 < b0) { cmd_fail(c, "qsa_pool: bad block range"); return; }
+    if (b1 == b0) return;
+    float *pp = (float *)dev_range(c, pool, (size_t)b1 * d * 4, true, 4);
+    const float *pk = (const float *)dev_range(c, ikeys, (size_t)b1 * ratio * d * 4, false, 4);
+    const uint16_t *pw = k_norm.buf ? (const uint16_t *)dev_range(c, k_norm, (size_t)d * 2, false, 2) : nullptr;
+    const float *pf = (const float *)dev_range(c, inv_freq, 32 * 4, false, 4);
+    if (!pp || !pk || !pf || (k_norm.buf && !pw)) return;
+    launch_qsa_pool(c->stream, pp, pk, pw, pf, d, ratio, b0, b1, eps);
+    cuda_ok(c, cudaGetLastError(), "qsa_pool launch");
+}
+extern "C" void qw_op_qsa_scores_pooled(qw_cmd c, qw_ref scores, qw_ref qn, qw_ref pool, int32_t rows, int32_t nq, int32_t d,
+                                        int32_t ratio, int32_t base_pos, int32_t max_blocks) {
+    if (!live(c) || !qsa_shape_ok(c, "qsa_scores_pooled", d, ratio, 64)) return;
+    if (rows <= 0 || nq <= 0 || base_pos < 0 || max_blocks <= 0 || (base_pos + rows) / ratio > max_blocks) { cmd_fail(c, "qsa_scores_pooled: bad shape"); return; }
+    const int32_t all = (base_pos + rows) / ratio;
+    if (all == 0) return;
+    float *ps = (float *)dev_range(c, scores, (size_t)rows * max_blocks * 4, true, 4);
+    const float *pq = (const float *)dev_range(c, qn, (size_t)rows * nq * d * 4, false, 4);
+    const float *pp = (const float *)dev_range(c, pool, (size_t)all * d * 4, false, 4);
+    if (!ps || !pq || !pp) return;
+    launch_qsa_scores(c->stream, ps, pq, pp, rows, nq, d, ratio, base_pos, max_blocks);
+    cuda_ok(c, cudaGetLastError(), "qsa_scores_pooled launch");
+}
+extern "C" void qw_op_qsa_scores(qw_cmd c, qw_ref scores, qw_ref qn, qw_ref ikeys, qw_ref k_norm, qw_ref inv_freq, int32_t rows,
+                                 int32_t nq, int32_t d, int32_t ratio, int32_t base_pos, int32_t rotary_dim, int32_t max_blocks, float eps) {
+    if (!live(c) || !qsa_shape_ok(c, "qsa_scores", d, ratio, rotary_dim)) return;
+    if (rows <= 0 || nq <= 0 || base_pos < 0 || max_blocks <= 0 || (base_pos + rows) / ratio > max_blocks) { cmd_fail(c, "qsa_scores: bad shape"); return; }
+    const int32_t all = (base_pos + rows) / ratio;
+    if (all == 0) return;
+    float *ps = (float *)dev_range(c, scores, (size_t)rows * max_blocks * 4, true, 4);
+    const float *pq = (const float *)dev_range(c, qn, (size_t)rows * nq * d * 4, false, 4);
+    const float *pk = (const float *)dev_range(c, ikeys, (size_t)all * ratio * d * 4, false, 4);
+    const uint16_t *pw = k_norm.buf ? (const uint16_t *)dev_range(c, k_norm, (size_t)d * 2, false, 2) : nullptr;
+    const float *pf = (const float *)dev_range(c, inv_freq, 32 * 4, false, 4);
+    if (!ps || !pq || !pk || !pf || (k_norm.buf && !pw)) return;
+    // the block keys first (the same arithmetic as qw_op_qsa_pool, so both routes give identical scores), then the scores
+    float *keys = (float *)cmd_scratch(c, (size_t)all * d * 4);
+    if (!keys) return;
+    launch_qsa_pool(c->stream, keys, pk, pw, pf, d, ratio, 0, all, eps);
+    launch_qsa_scores(c->stream, ps, pq, keys, rows, nq, d, ratio, base_pos, max_blocks);
+    cuda_ok(c, cudaGetLastError(), "qsa_scores launch");
+}
+extern "C" void qw_op_qsa_select(qw_cmd c, qw_ref mask, qw_ref list, qw_ref scores, int32_t rows, int32_t ratio, int32_t base_pos,
+                                 int32_t block_topk, int32_t max_ctx, int32_t max_blocks) {
+    if (!live(c)) return;
+    if (rows <= 0 || ratio <= 0 || base_pos < 0 || block_topk < 0 || max_blocks <= 0 || (int64_t)base_pos + rows > max_ctx ||
+        (base_pos + rows) / ratio > max_blocks || max_blocks > (1 << 20)) { cmd_fail(c, "qsa_select: bad shape"); return; }
+    uint8_t *pm = (uint8_t *)dev_range(c, mask, (size_t)rows * max_ctx, true, 1);
+    uint32_t *pl = (uint32_t *)dev_range(c, list, (size_t)rows * (1 + block_topk * ratio + ratio) * 4, true, 4);
+    const float *ps = (const float *)dev_range(c, scores, (size_t)rows * max_blocks * 4, false, 4);
+    if (!pm || !pl || !ps) return;
+    launch_qsa_select(c->stream, pm, pl, ps, rows, ratio, base_pos, block_topk, max_ctx, max_blocks);
+    cuda_ok(c, cudaGetLastError(), "qsa_select launch");
+}
+
 // Attention over listed positions only (the QSA mask as a list): the fp32 per-query kernel walks
 // each row's list in `splits` slices, the merge combines them (and applies the gate).
 static void attn_masked(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache, qw_ref list, int32_t rows,

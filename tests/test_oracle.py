@@ -216,3 +216,55 @@ def test_masked_attention_is_the_reference_function_over_the_listed_rows(oracle,
         want = refcpu.attn_decode(q[r:r + 1], np.ascontiguousarray(kc[:, pos]), np.ascontiguousarray(vc[:, pos]),
                                   1, qh, kvh, 256, n, n - 1, 0.0625)
         assert np.array_equal(got[r], want[0])
+
+
+def test_qsa_scores_are_the_reference_functions_composed(oracle, refcpu):
+    """orc_qsa_scores against the composition the reference's own test writes out
+    (tests/test_sparse.c:392-416) from its compiled qw_cpu_rms_norm and qw_cpu_rope_partial:
+    bit for bit, block keys and scores."""
+    rng = np.random.default_rng(51)
+    rows, nq, d, ratio, base, max_ctx, rd = 5, 4, 128, 4, 13, 64, 64
+    max_blocks = max_ctx // ratio
+    qn = rng.standard_normal((rows, nq, d)).astype(np.float32)
+    ik = rng.standard_normal((max_ctx, d)).astype(np.float32)
+    w = synth.f32_to_bf16_bits(1.0 + 0.1 * rng.standard_normal(d).astype(np.float32))
+    axis, inv = refcpu.rope_tables(rd, 1e7)
+    got, pool = oracle.qsa_scores(qn, ik, w, inv, rows, nq, d, ratio, base, rd, max_blocks, 1e-6)
+    for r in range(rows):
+        n_blocks = (base + r + 1) // ratio
+        assert np.all(np.isnan(got[r, n_blocks:]))
+        for b in range(n_blocks):
+            pooled = np.zeros(d, np.float32)
+            for t in range(ratio):
+                pooled = pooled + ik[b * ratio + t]
+            pooled = pooled / np.float32(ratio)
+            kn = refcpu.rms_norm(pooled[None], w, d, 1, 1e-6)
+            kn = refcpu.rope_partial(kn, np.full((3, 1), b * ratio, np.int32), axis, inv, 1, 1, d, rd)[0]
+            assert np.array_equal(kn, pool[b])
+            s = np.float32(0)
+            for h in range(nq):
+                dot = np.float32(0)
+                for i in range(d):
+                    dot = np.float32(dot + qn[r, h, i] * kn[i])
+                if dot > 0:
+                    s = np.float32(s + dot)
+            assert got[r, b] == np.float32(s / np.float32(np.sqrt(np.float32(d))))
+
+
+def test_qsa_select_known_answers(oracle):
+    """Top-k blocks by repeated arg-max (lowest index among equals), the trailing incomplete block
+    always visible, the list = the mask's positions ascending (qwasar_flash_cpu.c:363-406)."""
+    ratio, base, topk, max_ctx = 4, 13, 2, 64
+    scores = np.zeros((3, 16), np.float32)
+    scores[0, :3] = [0.5, 0.9, 0.1]          # 14 keys: 3 blocks + tail {12, 13}
+    scores[1, :3] = [0.7, 0.7, 0.7]          # 15 keys: ties -> blocks 0 and 1
+    scores[2, :4] = [0.1, -3.0e38, 0.3, 0.2]  # 16 keys: 4 blocks, no tail
+    mask, lists = oracle.qsa_select(scores, 3, ratio, base, topk, max_ctx)
+    vis = lambda r: list(np.nonzero(mask[r, :base + r + 1] == 1)[0])
+    assert vis(0) == [0, 1, 2, 3, 4, 5, 6, 7, 12, 13]
+    assert vis(1) == [0, 1, 2, 3, 4, 5, 6, 7, 12, 13, 14]
+    assert vis(2) == [8, 9, 10, 11, 12, 13, 14, 15]
+    for r in range(3):
+        assert np.all(mask[r, base + r + 1:] == 255)                     # positions the row cannot see: not written
+        n = int(lists[r, 0])
+        assert list(lists[r, 1:1 + n]) == vis(r)

@@ -155,6 +155,20 @@ void qw_op_attn_masked(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache, qw_ref vca
 void qw_op_attn_masked_gated(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache,
                              qw_ref list, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                              int32_t max_ctx, int32_t base_pos, float scale, int32_t block_topk, int32_t ratio);
+/* qwasar_gpu.h:84-118 -- the 4-bit affine product that produces qg, k, v and consumes attn_out:
+ * y f32 [rows, n] = x f32 [rows, k] . dequant(w)^T, with w U32 [n, k/8] (MLX affine 4-bit: element
+ * i of a row in word i/8 at bit 4 (i % 8)), scales and biases bf16 [n, k/group], group 32 or 64,
+ * element = scale * nibble + bias.  The three names reach one fp32 kernel (the reference picks
+ * among three by shape).  qw_op_qmv_q4_multi: up to 4 one-token products sharing x, k >= 2048,
+ * else false and nothing encoded (:105-109). */
+void qw_op_qmat_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases,
+                   int32_t k, int32_t n, int32_t rows, int32_t group);
+void qw_op_qmv_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases,
+                  int32_t k, int32_t n, int32_t rows, int32_t group);
+void qw_op_qmm_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases,
+                  int32_t k, int32_t n, int32_t rows, int32_t group);
+typedef struct { qw_ref y, w, scales, biases; int32_t n; } qw_qmv_part;
+bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group, int32_t count, const qw_qmv_part *parts);
 /* qwasar_gpu.h:620-634 -- QSA's indexer.  qn f32 [rows, nq, d] are the normed + rotated index
  * queries, ikeys f32 [positions, d] a layer's raw index keys, k_norm bf16 [d] (or a null ref),
  * inv_freq f32 [rotary_dim / 2].  Block b = positions [b * ratio, (b + 1) * ratio): its key is the

@@ -64,6 +64,8 @@ class Oracle:
         L.orc_mul_sigmoid.argtypes = [_f32p, _f32p, _sz]
         L.orc_attn_masked.argtypes = [C.c_void_p] * 5 + [_i32] * 6 + [_f32, _int]
         L.orc_attn_masked.restype = None
+        L.orc_qmv_q4.argtypes = [C.c_void_p] * 5 + [_i32] * 4
+        L.orc_qmv_q4.restype = None
         L.orc_qsa_scores.argtypes = [C.c_void_p] * 6 + [_i32] * 7 + [_f32]
         L.orc_qsa_scores.restype = None
         L.orc_qsa_select.argtypes = [C.c_void_p] * 3 + [_i32] * 6
@@ -138,6 +140,13 @@ class Oracle:
                                  C.c_int32(rows), C.c_int32(q_heads), C.c_int32(kv_heads), C.c_int32(head_dim),
                                  C.c_int32(max_ctx), C.c_float(scale), C.c_int(fmt))
         return out
+
+    def qmv_q4(self, x, w, scales, biases, k, n, rows, group):
+        x = np.ascontiguousarray(x, np.float32); w = np.ascontiguousarray(w, np.uint32)
+        sc = np.ascontiguousarray(scales, np.uint16); bi = np.ascontiguousarray(biases, np.uint16)
+        y = np.empty((rows, n), np.float32)
+        self.lib.orc_qmv_q4(y.ctypes.data, x.ctypes.data, w.ctypes.data, sc.ctypes.data, bi.ctypes.data, k, n, rows, group)
+        return y
 
     def qsa_scores(self, qn, ikeys, k_norm_bits, inv_freq, rows, nq, d, ratio, base_pos, rotary_dim, max_blocks, eps):
         """Returns (scores [rows, max_blocks] with NaN where no block is complete, pool [max_blocks, d])."""
@@ -258,6 +267,17 @@ class RefCpu:
             self.lib.qwref_attn_decode_mt(out, q, kc, vc, rows, q_heads, kv_heads, head_dim,
                                           max_ctx, base_pos, scale, threads or self.max_threads)
         return out
+
+    def qmv_q4(self, x, w, scales, biases, k, n, rows, group):
+        """The reference's own qw_cpu_qmv_q4 (qwasar_cpu.c:36-63)."""
+        x = np.ascontiguousarray(x, np.float32); w = np.ascontiguousarray(w, np.uint32)
+        sc = np.ascontiguousarray(scales, np.uint16); bi = np.ascontiguousarray(biases, np.uint16)
+        y = np.empty((rows, n), np.float32)
+        fn = self.lib.qw_cpu_qmv_q4
+        fn.argtypes = [C.c_void_p] * 5 + [C.c_int32] * 4
+        fn.restype = None
+        fn(y.ctypes.data, x.ctypes.data, w.ctypes.data, sc.ctypes.data, bi.ctypes.data, k, n, rows, group)
+        return y
 
     def attn_layer(self, qg, k, v, qw, kw, pos, axis, inv_freq, kc, vc, rows, q_heads, kv_heads,
                    head_dim, rotary_dim, max_ctx, base_pos, eps, scale, threads=0):

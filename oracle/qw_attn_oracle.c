@@ -259,6 +259,26 @@ void orc_attn_masked(float *out, const float *q, const uint16_t *kc, const uint1
     }
 }
 
+/* The 4-bit affine product that makes qg, k, v and consumes attn_out (qwasar_gpu.h:84-103;
+ * qwasar_cpu.c:21-63): y[r][o] = sum_i (scale * nibble + bias) * x[r][i], element i of output
+ * row o in word i/8 at bit 4 (i % 8) of w [n, k/8], scale and bias bf16 per group of `group`
+ * elements ([n, k/group]); fp32, terms added in index order. */
+void orc_qmv_q4(float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases,
+                int32_t k, int32_t n, int32_t rows, int32_t group) {
+    const int32_t words = k / 8, groups = k / group;
+    for (int32_t r = 0; r < rows; r++)
+        for (int32_t o = 0; o < n; o++) {
+            float acc = 0.0f;
+            for (int32_t i = 0; i < k; i++) {
+                const uint32_t nib = (w[(size_t)o * words + i / 8] >> (4 * (i % 8))) & 0xF;
+                const float sc = orc_bf16_up(scales[(size_t)o * groups + i / group]);
+                const float bi = orc_bf16_up(biases[(size_t)o * groups + i / group]);
+                acc += (sc * (float)nib + bi) * x[(size_t)r * k + i];
+            }
+            y[(size_t)r * n + o] = acc;
+        }
+}
+
 /* QSA block scores (qwasar_flash_cpu.c:372-397; the check of tests/test_sparse.c:392-416): for
  * row r the first (base_pos + r + 1) / ratio blocks of `ratio` raw index keys each are mean-pooled
  * (sum in position order, then / ratio), RMS-normed with weight k_norm, rotated at the block's

@@ -66,6 +66,10 @@ SIGNATURES = {
     "qw_op_qsa_pool": (None, [_vp, QwRef, QwRef, QwRef, QwRef] + [_i32] * 5 + [_f32]),
     "qw_op_qsa_scores_pooled": (None, [_vp, QwRef, QwRef, QwRef] + [_i32] * 6),
     "qw_op_qsa_select": (None, [_vp, QwRef, QwRef, QwRef] + [_i32] * 6),
+    "qw_op_qmat_q4": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 4),
+    "qw_op_qmv_q4": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 4),
+    "qw_op_qmm_q4": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 4),
+    "qw_op_qmv_q4_multi": (_b, [_vp, QwRef, _i32, _i32, _i32, _vp]),
     "qw_gpu_last_error": (C.c_char_p, []),
     "qw_gpu_sm_count": (_i32, []),
     "qw_gpu_launch_count": (C.c_uint64, []),

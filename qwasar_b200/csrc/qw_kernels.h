@@ -137,6 +137,10 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
                         const void *gate, int gate_dtype, int gate_stride, int n_rows_heads, int parts,
                         float *pacc_out, float *pstat_out, size_t acc_stride = 0, size_t stat_stride = 0);
 
+// ---- 4-bit affine product (qw_qmat.cu): y [rows, n] = x [rows, k] . dequant(w [n, k/8])^T ----
+void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
+                    int n, int rows, int group);
+
 // ---- QSA indexer (qw_qsa.cu) ----------------------------------------------------------------
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
                      int b0, int b1, float eps);

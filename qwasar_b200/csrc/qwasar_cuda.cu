@@ -1105,6 +1105,41 @@ extern "C" void qw_op_attn_decode(qw_cmd c, qw_ref out, qw_ref q, qw_ref kcache,
     cuda_ok(c, cudaGetLastError(), "attn_decode launch");
 }
 
+// ---- the 4-bit affine product (qwasar_gpu.h:84-118): one kernel behind all three names ----
+static bool qmat_q4(qw_cmd c, const char *op, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n,
+                    int32_t rows, int32_t group) {
+    if (k <= 0 || n <= 0 || rows <= 0 || (group != 32 && group != 64) || k % group) {
+        cmd_fail(c, "%s: k %d, n %d, rows %d, group %d (32 or 64, dividing k) not supported", op, k, n, rows, group);
+        return false;
+    }
+    float *py = (float *)dev_range(c, y, (size_t)rows * n * 4, true, 4);
+    const float *px = (const float *)dev_range(c, x, (size_t)rows * k * 4, false, 16);
+    const uint32_t *pw = (const uint32_t *)dev_range(c, w, (size_t)n * (k / 8) * 4, false, 4);
+    const uint16_t *ps = (const uint16_t *)dev_range(c, scales, (size_t)n * (k / group) * 2, false, 2);
+    const uint16_t *pb = (const uint16_t *)dev_range(c, biases, (size_t)n * (k / group) * 2, false, 2);
+    if (!py || !px || !pw || !ps || !pb) return false;
+    launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group);
+    return cuda_ok(c, cudaGetLastError(), "qmat_q4 launch");
+}
+extern "C" void qw_op_qmat_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n, int32_t rows,
+                              int32_t group) {
+    if (live(c)) qmat_q4(c, "qmat_q4", y, x, w, scales, biases, k, n, rows, group);
+}
+extern "C" void qw_op_qmv_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n, int32_t rows,
+                             int32_t group) {
+    if (live(c)) qmat_q4(c, "qmv_q4", y, x, w, scales, biases, k, n, rows, group);
+}
+extern "C" void qw_op_qmm_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n, int32_t rows,
+                             int32_t group) {
+    if (live(c)) qmat_q4(c, "qmm_q4", y, x, w, scales, biases, k, n, rows, group);
+}
+extern "C" bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group, int32_t count, const qw_qmv_part *parts) {
+    if (!live(c) || !parts || count <= 0 || count > 4 || k < 2048) return false;        // the reference's limits (qwasar_gpu.h:105-109)
+    for (int32_t i = 0; i < count; i++)
+        if (!qmat_q4(c, "qmv_q4_multi", parts[i].y, x, parts[i].w, parts[i].scales, parts[i].biases, k, parts[i].n, 1, group)) return false;
+    return true;
+}
+
 // ---- QSA indexer: block keys, block scores, selection (qwasar_gpu.h:620-639) ----
 static bool qsa_shape_ok(qw_cmd c, const char *op, int32_t d, int32_t ratio, int32_t rotary_dim) {
     if (d <= 0 || d > 256 || d % 32 || ratio <= 0 || rotary_dim != 64 || d < 64) {

@@ -63,7 +63,8 @@ static const any_fn all_symbols[] = {
     (any_fn)qw_op_attn, (any_fn)qw_op_attn_decode, (any_fn)qw_op_attn_prefill, (any_fn)qw_op_attn_prefill_as,
     (any_fn)qw_op_attn_decode_split, (any_fn)qw_op_attn_decode_tensor, (any_fn)qw_op_mul_sigmoid,
     (any_fn)qw_op_attn_masked, (any_fn)qw_op_attn_masked_gated, (any_fn)qw_op_qsa_scores, (any_fn)qw_op_qsa_pool,
-    (any_fn)qw_op_qsa_scores_pooled, (any_fn)qw_op_qsa_select,
+    (any_fn)qw_op_qsa_scores_pooled, (any_fn)qw_op_qsa_select, (any_fn)qw_op_qmat_q4, (any_fn)qw_op_qmv_q4,
+    (any_fn)qw_op_qmm_q4, (any_fn)qw_op_qmv_q4_multi,
     (any_fn)qw_gpu_last_error, (any_fn)qw_gpu_sm_count, (any_fn)qw_gpu_launch_count, (any_fn)qw_gpu_tune,
     (any_fn)qw_attn_split_plan, (any_fn)qw_prof_kernels, (any_fn)qw_prof_kernel_read,
     (any_fn)qw_buf_alloc_device, (any_fn)qw_buf_wrap_device, (any_fn)qw_buf_device_ptr, (any_fn)qw_buf_upload,

@@ -1,0 +1,77 @@
+"""The 4-bit affine product (qwasar_gpu.h:84-118) against the oracle, with the reference's own
+error measure and bound for its fp32 kernel (tests/test_qmv.c:31-50, 129): per output,
+|double-precision dot over the dequantised row - got| / sum of the absolute terms < 2e-6."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from gpu_util import Bufs, QwRef
+from qwasar_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def q4_weights(rng, n, k, group):
+    w = rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32)
+    sc = synth.f32_to_bf16_bits((0.02 * rng.standard_normal((n, k // group))).astype(np.float32))
+    bi = synth.f32_to_bf16_bits((0.1 * rng.standard_normal((n, k // group))).astype(np.float32))
+    return w, sc, bi
+
+
+def dequant(w, sc, bi, k, group):
+    nib = ((w[:, :, None] >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).reshape(w.shape[0], k).astype(np.float32)
+    s = np.repeat(synth.bf16_bits_to_f32(sc), group, axis=1); b = np.repeat(synth.bf16_bits_to_f32(bi), group, axis=1)
+    return s * nib + b
+
+
+def worst_rel_err(got, x, deq):
+    terms = deq[None, :, :].astype(np.float64) * x[:, None, :].astype(np.float64)      # [rows, n, k]
+    return float(np.max(np.abs(terms.sum(-1) - got) / np.maximum(np.abs(terms).sum(-1), 1e-300)))
+
+
+@pytest.mark.parametrize("op", ["op_qmat_q4", "op_qmv_q4", "op_qmm_q4"])
+@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32)])
+def test_q4_product(be, oracle, op, k, n, rows, group):
+    rng = np.random.default_rng(k + n + rows)
+    w, sc, bi = q4_weights(rng, n, k, group)
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    with Bufs(be) as B:
+        xb, _ = B.shared(x); wb, _ = B.shared(w); sb, _ = B.shared(sc); bb, _ = B.shared(bi)
+        yb, yv = B.shared_empty((rows, n), np.float32, fill=np.float32(np.nan))
+        c = be.cmd_begin()
+        getattr(be, op)(c, QwRef(yb, 0), QwRef(xb, 0), QwRef(wb, 0), QwRef(sb, 0), QwRef(bb, 0), k, n, rows, group)
+        be.cmd_wait(c); be.cmd_free(c)
+        got = np.array(yv)
+    assert np.all(np.isfinite(got))
+    assert worst_rel_err(got, x, dequant(w, sc, bi, k, group)) < 2e-6
+    if k * n * rows <= 2_000_000:                                # and the oracle itself, to the same measure
+        want = oracle.qmv_q4(x, w, sc, bi, k, n, rows, group)
+        assert worst_rel_err(want, x, dequant(w, sc, bi, k, group)) < 2e-5
+        assert np.allclose(got, want, rtol=0, atol=2e-5 * np.abs(want).max() + 1e-6)
+
+
+def test_q4_multi(be, oracle):
+    """Up to four one-token products sharing x (qwasar_gpu.h:105-109); k < 2048 is declined."""
+    from qwasar_b200.backend import QwRef as Ref
+
+    class Part(C.Structure):
+        _fields_ = [("y", Ref), ("w", Ref), ("scales", Ref), ("biases", Ref), ("n", C.c_int32)]
+    rng = np.random.default_rng(4)
+    k, group, ns = 2048, 64, [48, 7, 130]
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    with Bufs(be) as B:
+        xb, _ = B.shared(x)
+        parts, outs, wts = (Part * len(ns))(), [], []
+        for i, n in enumerate(ns):
+            w, sc, bi = q4_weights(rng, n, k, group)
+            wb, _ = B.shared(w); sb, _ = B.shared(sc); bb, _ = B.shared(bi)
+            yb, yv = B.shared_empty((1, n), np.float32, fill=np.float32(np.nan))
+            parts[i] = Part(Ref(yb, 0), Ref(wb, 0), Ref(sb, 0), Ref(bb, 0), n)
+            outs.append(yv); wts.append((w, sc, bi))
+        c = be.cmd_begin()
+        assert be.lib.qw_op_qmv_q4_multi(c, Ref(xb, 0), k, group, len(ns), C.addressof(parts))
+        assert not be.lib.qw_op_qmv_q4_multi(c, Ref(xb, 0), 1024, group, len(ns), C.addressof(parts))
+        be.cmd_wait(c); be.cmd_free(c)
+        for yv, (w, sc, bi) in zip(outs, wts):
+            assert worst_rel_err(np.array(yv), x, dequant(w, sc, bi, k, group)) < 2e-6

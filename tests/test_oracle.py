@@ -268,3 +268,20 @@ def test_qsa_select_known_answers(oracle):
         assert np.all(mask[r, base + r + 1:] == 255)                     # positions the row cannot see: not written
         n = int(lists[r, 0])
         assert list(lists[r, 1:1 + n]) == vis(r)
+
+
+def q4_weights(rng, n, k, group):
+    """MLX affine 4-bit: U32 [n, k/8] nibbles, bf16 scales (both signs) and biases [n, k/group]."""
+    w = rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32)
+    sc = synth.f32_to_bf16_bits((0.02 * rng.standard_normal((n, k // group))).astype(np.float32))
+    bi = synth.f32_to_bf16_bits((0.1 * rng.standard_normal((n, k // group))).astype(np.float32))
+    return w, sc, bi
+
+
+@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (512, 48, 2, 64), (256, 5, 3, 32), (1024, 17, 1, 32)])
+def test_q4_product_is_the_reference_function(oracle, refcpu, k, n, rows, group):
+    """orc_qmv_q4 against the compiled qw_cpu_qmv_q4 (qwasar_cpu.c:36-63): bit for bit."""
+    rng = np.random.default_rng(k + n)
+    w, sc, bi = q4_weights(rng, n, k, group)
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    assert np.array_equal(oracle.qmv_q4(x, w, sc, bi, k, n, rows, group), refcpu.qmv_q4(x, w, sc, bi, k, n, rows, group))

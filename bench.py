@@ -357,6 +357,66 @@ def prefill_extra(be, torch, peaks, device):
             "frac_of_bf16_peak": round(tf / peaks["tf"], 4), "peak_tflops": peaks["tf"], "peak": peaks["which"]}
 
 
+def next_rows_extra(be, torch, peaks, device):
+    """Side measurements of the ops either side of the node (first correct versions, not tuned):
+    the 4-bit affine product at a one-token q_proj shape (weight bytes per second, eight weight
+    sets in rotation so that L2 cannot serve the repeats), and one QSA step at 262 144 cached
+    positions (block scores from stored keys, selection of 512 blocks of 4, masked attention of
+    16 query / 2 KV heads over the 2 052 listed positions)."""
+    from qwasar_b200.backend import QwRef
+    out = {}
+    wrap = lambda t: be.buf_wrap_device(t.data_ptr(), t.numel() * t.element_size())
+    g = torch.Generator(device=device); g.manual_seed(5)
+    # ---- q4 product, rows = 1
+    k, n, group, sets = 5120, 12288, 64, 8
+    w = torch.randint(0, 2 ** 31 - 1, (sets, n, k // 8), generator=g, device=device, dtype=torch.int32)
+    sc = (0.02 * torch.randn((sets, n, k // group), generator=g, device=device)).to(torch.bfloat16)
+    bi = (0.1 * torch.randn((sets, n, k // group), generator=g, device=device)).to(torch.bfloat16)
+    x = torch.randn((1, k), generator=g, device=device, dtype=torch.float32)
+    y = torch.empty((1, n), device=device, dtype=torch.float32)
+    bw, bs, bb, bx, by = wrap(w), wrap(sc), wrap(bi), wrap(x), wrap(y)
+    w_bytes, s_bytes = n * (k // 8) * 4, n * (k // group) * 2
+
+    def q4(c):
+        for i in range(sets):
+            be.op_qmat_q4(c, QwRef(by, 0), QwRef(bx, 0), QwRef(bw, i * w_bytes), QwRef(bs, i * s_bytes), QwRef(bb, i * s_bytes), k, n, 1, group)
+    ms = time_device(be, torch, q4, 5, 3, lambda: None) / sets
+    per = w_bytes + 2 * s_bytes
+    out["qmat_q4_decode"] = {"k": k, "n": n, "group": group, "us": round(ms * 1e3, 2), "weight_gbs": round(per / 1e9 / (ms * 1e-3), 1),
+                             "frac_of_hbm": round(per / 1e9 / (ms * 1e-3) / peaks["hbm"], 4), "peak": peaks["which"]}
+    for b in (bw, bs, bb, bx, by):
+        be.buf_free(b)
+    del w, sc, bi
+    # ---- one QSA step at 262 144 positions
+    ctx, ratio, topk, nq, d, qh, kvh = 262144 + 64, 4, 512, 4, 128, 16, 2
+    base, max_blocks, cap = 262144, (262144 + 64) // 4, 512 * 4 + 4
+    pool = torch.randn((max_blocks, d), generator=g, device=device, dtype=torch.float32)
+    qn = torch.randn((1, nq, d), generator=g, device=device, dtype=torch.float32)
+    scores = torch.zeros((1, max_blocks), device=device, dtype=torch.float32)
+    mask = torch.zeros((1, ctx), device=device, dtype=torch.uint8)
+    lst = torch.zeros((1, 1 + cap), device=device, dtype=torch.int32)
+    q = torch.randn((1, qh, 256), generator=g, device=device, dtype=torch.float32)
+    o = torch.empty((1, qh, 256), device=device, dtype=torch.float32)
+    kc = torch.randn((kvh, ctx, 256), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    vc = torch.randn((kvh, ctx, 256), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    bufs = [wrap(t) for t in (pool, qn, scores, mask, lst, q, o, kc, vc)]
+    bp, bq, bsco, bm, bl, bqq, bo, bk, bv = bufs
+    stages = {
+        "scores_us": lambda c: be.op_qsa_scores_pooled(c, QwRef(bsco, 0), QwRef(bq, 0), QwRef(bp, 0), 1, nq, d, ratio, base, max_blocks),
+        "select_us": lambda c: be.op_qsa_select(c, QwRef(bm, 0), QwRef(bl, 0), QwRef(bsco, 0), 1, ratio, base, topk, ctx, max_blocks),
+        "attend_us": lambda c: be.op_attn_masked(c, QwRef(bo, 0), QwRef(bqq, 0), QwRef(bk, 0), QwRef(bv, 0), QwRef(bl, 0), 1, qh, kvh, 256,
+                                                 ctx, base, 0.0625, topk, ratio),
+    }
+    step = {}
+    for name, fn in stages.items():
+        step[name] = round(time_device(be, torch, fn, 10, 3, lambda: None) * 1e3, 2)
+    step["listed_kv_bytes"] = int(lst[0, 0].item()) * kvh * 1024
+    out["qsa_step_262k"] = step
+    for b in bufs:
+        be.buf_free(b)
+    return out
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -432,6 +492,10 @@ def run_ours(args):
             extra["prefill"] = prefill_extra(be, torch, peaks, device)
         except Exception as e:   # the side measurement must not lose the headline line
             extra["prefill"] = {"error": str(e)[:200]}
+        try:
+            extra.update(next_rows_extra(be, torch, peaks, device))
+        except Exception as e:
+            extra["next_rows"] = {"error": str(e)[:200]}
         try:
             b1 = DecodeBench(be, torch, wl, 1, wl["q_heads"], wl["kv_heads"], layers, device, host_io=False)
             ms1 = time_device(be, torch, b1.encode_step, max(20, args.steps), 5, barrier)

@@ -92,75 +92,119 @@ __global__ void __launch_bounds__(256) qsa_scores_kernel(float *__restrict__ sco
     if (lane == 0) scores[(size_t)r * max_blocks + b] = __fdiv_rn(s, sqrtf((float)d));
 }
 
-// One CTA per row.  taken[]: one bit per complete block, in dynamic shared memory.
+// One CTA per row.  The reference finds the block_topk best blocks one at a time (the largest score
+// above -FLT_MAX, the lowest index among equals): that is the first `take` blocks in the order
+// (score descending, index ascending).  Found here without sorting: the scores map to unsigned
+// keys that order the same way (-0 and +0 share a key, as they compare equal), a radix select of
+// four 8-bit passes finds the key of the take-th best, every block with a larger key is taken, and
+// of the blocks with exactly that key the lowest-indexed ones until the count is reached.  Every
+// pass is one sweep over the row's scores, each thread over a contiguous run of blocks, which is
+// also what orders the equals and the list.
 constexpr int SEL_THREADS = 256;
+__device__ __forceinline__ bool sel_key(float v, uint32_t &key) {
+    if (!(v > -FLT_MAX)) return false;                            // -FLT_MAX, -inf and NaN are never selected
+    if (v == 0.0f) v = 0.0f;                                      // -0 -> +0
+    const uint32_t u = __float_as_uint(v);
+    key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return true;
+}
 __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ list,
                                                                  const float *__restrict__ scores, int ratio, int base_pos,
                                                                  int block_topk, int max_ctx, int max_blocks, int list_stride) {
-    extern __shared__ uint32_t taken[];
-    __shared__ float red_v[SEL_THREADS / 32];
-    __shared__ int red_i[SEL_THREADS / 32];
-    __shared__ int chosen;
+    __shared__ int hist[256];
     __shared__ int counts[SEL_THREADS];
-    const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_remaining, s_total;
+    const int r = blockIdx.x, tid = threadIdx.x;
     const int n_keys = base_pos + r + 1, n_blocks = n_keys / ratio;
     const float *sc = scores + (size_t)r * max_blocks;
     uint8_t *m = mask + (size_t)r * max_ctx;
     uint32_t *l = list + (size_t)r * list_stride;
-    for (int t = tid; t < n_keys; t += SEL_THREADS) m[t] = t >= n_blocks * ratio;
-    for (int w = tid; w < (n_blocks + 31) / 32; w += SEL_THREADS) taken[w] = 0;
-    __syncthreads();
-    const int take = min(block_topk, n_blocks);
-    for (int n = 0; n < take; n++) {
-        // the best block not yet taken: the largest score above -FLT_MAX, the lowest index among equals
-        float bv = 0.0f;
-        int bi = -1;
-        for (int b = tid; b < n_blocks; b += SEL_THREADS) {
-            if ((taken[b >> 5] >> (b & 31)) & 1u) continue;
-            const float v = sc[b];
-            if (v > -FLT_MAX && (bi < 0 || v > bv)) { bv = v; bi = b; }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-        }
-        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
-        __syncthreads();
-        if (tid == 0) {
-            float v = red_v[0];
-            int i = red_i[0];
-            for (int w = 1; w < SEL_THREADS / 32; w++)
-                if (red_i[w] >= 0 && (i < 0 || red_v[w] > v || (red_v[w] == v && red_i[w] < i))) { v = red_v[w]; i = red_i[w]; }
-            chosen = i;
-            if (i >= 0) taken[i >> 5] |= 1u << (i & 31);
-        }
-        __syncthreads();
-        if (chosen < 0) break;                                    // nothing above -FLT_MAX is left (block-uniform)
-    }
-    // mask of the taken blocks, and the list: taken blocks in ascending order, then the tail
     const int per = (n_blocks + SEL_THREADS - 1) / SEL_THREADS;
     const int lo = min(tid * per, n_blocks), hi = min(lo + per, n_blocks);
+    for (int t = tid; t < n_keys; t += SEL_THREADS) m[t] = t >= n_blocks * ratio;
+
+    // how many blocks can be selected at all
+    int eligible = 0;
+    for (int b = lo; b < hi; b++) { uint32_t key; eligible += sel_key(sc[b], key); }
+    counts[tid] = eligible;
+    __syncthreads();
+    if (tid == 0) {
+        int e = 0;
+        for (int i = 0; i < SEL_THREADS; i++) e += counts[i];
+        s_remaining = min(min(block_topk, n_blocks), e);          // take
+        s_prefix = 0;
+    }
+    __syncthreads();
+    const int take = s_remaining;
+
+    // radix select: after the pass over byte `shift`, s_prefix holds the top bytes of the key of
+    // the take-th best block and s_remaining how many blocks with that prefix are still wanted
+    if (take > 0) {
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            hist[tid] = 0;                                        // SEL_THREADS == 256 bins
+            __syncthreads();
+            const uint32_t prefix = s_prefix, high = shift == 24 ? 0u : 0xFFFFFFFFu << (shift + 8);
+            for (int b = lo; b < hi; b++) {
+                uint32_t key;
+                if (sel_key(sc[b], key) && (key & high) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int want = s_remaining, bin = 255;
+                for (; bin > 0 && hist[bin] < want; bin--) want -= hist[bin];
+                s_remaining = want;                               // still wanted among the keys of this bin
+                s_prefix = prefix | ((uint32_t)bin << shift);
+            }
+            __syncthreads();
+        }
+    }
+    const uint32_t kth = s_prefix;                                // the key of the take-th best block
+    const int need_eq = s_remaining;                              // blocks with exactly that key to take, lowest index first
+
+    // equals before this thread's run, then the verdict per block; taken blocks counted for the list
+    int eq = 0;
+    if (take > 0)
+        for (int b = lo; b < hi; b++) { uint32_t key; eq += sel_key(sc[b], key) && key == kth; }
+    counts[tid] = eq;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < SEL_THREADS; i++) { const int c2 = counts[i]; counts[i] = run; run += c2; }
+    }
+    __syncthreads();
+    const int eq_base = counts[tid];
+    __syncthreads();
     int cnt = 0;
-    for (int b = lo; b < hi; b++) cnt += (taken[b >> 5] >> (b & 31)) & 1u;
+    if (take > 0) {
+        int rank = eq_base;
+        for (int b = lo; b < hi; b++) {
+            uint32_t key;
+            if (sel_key(sc[b], key)) cnt += key > kth || (key == kth && rank++ < need_eq);
+        }
+    }
     counts[tid] = cnt;
     __syncthreads();
     if (tid == 0) {
         int run = 0;
         for (int i = 0; i < SEL_THREADS; i++) { const int c2 = counts[i]; counts[i] = run; run += c2; }
-        chosen = run;                                             // blocks taken in all
+        s_total = run;                                            // blocks taken in all (== take)
     }
     __syncthreads();
-    int at = counts[tid] * ratio;
-    for (int b = lo; b < hi; b++) {
-        if (!((taken[b >> 5] >> (b & 31)) & 1u)) continue;
-        for (int t = 0; t < ratio; t++) {
-            m[b * ratio + t] = 1;
-            l[1 + at++] = (uint32_t)(b * ratio + t);
+    // the mask of the taken blocks, and the list: taken blocks in ascending order, then the tail
+    if (take > 0) {
+        int at = counts[tid] * ratio, rank = eq_base;
+        for (int b = lo; b < hi; b++) {
+            uint32_t key;
+            if (!sel_key(sc[b], key)) continue;
+            if (!(key > kth || (key == kth && rank++ < need_eq))) continue;
+            for (int t = 0; t < ratio; t++) {
+                m[b * ratio + t] = 1;
+                l[1 + at++] = (uint32_t)(b * ratio + t);
+            }
         }
     }
-    const int tail0 = n_blocks * ratio, total = chosen * ratio;
+    const int tail0 = n_blocks * ratio, total = s_total * ratio;
     for (int t = tail0 + tid; t < n_keys; t += SEL_THREADS) l[1 + total + (t - tail0)] = (uint32_t)t;
     if (tid == 0) l[0] = (uint32_t)(total + (n_keys - tail0));
 }
@@ -183,8 +227,7 @@ void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const flo
 void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const float *scores, int rows, int ratio, int base_pos,
                        int block_topk, int max_ctx, int max_blocks) {
     if (rows <= 0) return;
-    const size_t smem = (size_t)((max_blocks + 31) / 32 + 1) * sizeof(uint32_t);
-    qsa_select_kernel<<<rows, SEL_THREADS, smem, s>>>(mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
+    qsa_select_kernel<<<rows, SEL_THREADS, 0, s>>>(mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
                                                       1 + block_topk * ratio + ratio);
     g_launches++;
 }

@@ -57,11 +57,99 @@ __global__ void __launch_bounds__(256) qmat_q4_kernel(float *__restrict__ y, con
     }
 }
 
+// One or two tokens: the product is a stream of weight bytes, so the kernel is built around the
+// loads.  A lane fetches 16 bytes of a weight row (4 words = 32 elements, inside one scale group)
+// per step, four steps of a 4096-element chunk of k in flight at once; the tokens' chunk of x sits
+// in shared memory, 32 floats per 36-float slot so that the lanes' 16-byte reads of their slots
+// fall on different banks; a warp takes QV_OUTS output rows one after the other over the same
+// staged chunk.
+constexpr int QV_ROWS = 2, QV_OUTS = 4, QV_KC = 4096, QV_SLOTS = QV_KC / 32, QV_PAD = 36;
+__global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
+                                                     const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
+                                                     int n, int rows, int group) {
+    __shared__ __align__(16) float xs[QV_ROWS][QV_SLOTS][QV_PAD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int o0 = (blockIdx.x * 8 + warp) * QV_OUTS;
+    const int r0 = blockIdx.y * QV_ROWS, nr = min(QV_ROWS, rows - r0);
+    const int words = k >> 3, groups = k / group;
+    float acc[QV_OUTS][QV_ROWS];
+#pragma unroll
+    for (int j = 0; j < QV_OUTS; j++)
+#pragma unroll
+        for (int r = 0; r < QV_ROWS; r++) acc[j][r] = 0.0f;
+    for (int kc0 = 0; kc0 < k; kc0 += QV_KC) {
+        const int kc = min(QV_KC, k - kc0), slots = kc >> 5, q4 = kc >> 2;      // k is a multiple of 32
+        __syncthreads();                                                        // the chunk before has been consumed
+        for (int idx = threadIdx.x; idx < nr * q4; idx += 256) {
+            const int r = idx / q4, e = (idx - r * q4) * 4;
+            *reinterpret_cast<float4 *>(&xs[r][e >> 5][e & 31]) = *reinterpret_cast<const float4 *>(x + (size_t)(r0 + r) * k + kc0 + e);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int j = 0; j < QV_OUTS; j++) {
+            const int o = o0 + j;
+            if (o >= n) continue;                                               // warp-uniform
+            const uint4 *wr = reinterpret_cast<const uint4 *>(w + (size_t)o * words + (kc0 >> 3));
+            const uint16_t *sr = scales + (size_t)o * groups, *br = biases + (size_t)o * groups;
+            uint4 wv[4];
+            float sc[4], bi[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int q = lane + 32 * i;
+                wv[i] = make_uint4(0, 0, 0, 0); sc[i] = 0.0f; bi[i] = 0.0f;
+                if (q < slots) {
+                    wv[i] = __ldg(wr + q);
+                    const int gi = (kc0 + q * 32) / group;
+                    sc[i] = bf16_bits_to_f32(sr[gi]); bi[i] = bf16_bits_to_f32(br[gi]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int q = lane + 32 * i;
+                if (q >= slots) continue;
+                const uint32_t ww[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+#pragma unroll
+                for (int r = 0; r < QV_ROWS; r++) {
+                    if (r >= nr) continue;
+                    float t = acc[j][r];
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const float4 a = *reinterpret_cast<const float4 *>(&xs[r][q][u * 8]);
+                        const float4 b = *reinterpret_cast<const float4 *>(&xs[r][q][u * 8 + 4]);
+                        const uint32_t word = ww[u];
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)(word & 0xFu)), bi[i]), a.x));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 4) & 0xFu)), bi[i]), a.y));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 8) & 0xFu)), bi[i]), a.z));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 12) & 0xFu)), bi[i]), a.w));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 16) & 0xFu)), bi[i]), b.x));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 20) & 0xFu)), bi[i]), b.y));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 24) & 0xFu)), bi[i]), b.z));
+                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)(word >> 28)), bi[i]), b.w));
+                    }
+                    acc[j][r] = t;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QV_OUTS; j++)
+#pragma unroll
+        for (int r = 0; r < QV_ROWS; r++) {
+            const float t = warp_sum(acc[j][r]);
+            if (lane == 0 && r < nr && o0 + j < n) y[(size_t)(r0 + r) * n + o0 + j] = t;
+        }
+}
+
 }  // namespace
 
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
                     int n, int rows, int group) {
     if (n <= 0 || rows <= 0) return;
+    if (rows <= QV_ROWS && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
+        qmv_q4_kernel<<<dim3((n + 8 * QV_OUTS - 1) / (8 * QV_OUTS), 1), 256, 0, s>>>(y, x, w, scales, biases, k, n, rows, group);
+        g_launches++;
+        return;
+    }
     qmat_q4_kernel<<<dim3((n + 7) / 8, (rows + QM_ROWS - 1) / QM_ROWS), 256, 0, s>>>(y, x, w, scales, biases, k, n, rows, group);
     g_launches++;
 }

@@ -31,7 +31,7 @@ def worst_rel_err(got, x, deq):
 
 
 @pytest.mark.parametrize("op", ["op_qmat_q4", "op_qmv_q4", "op_qmm_q4"])
-@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32)])
+@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (8192, 70, 2, 64), (5120, 33, 1, 32), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32)])
 def test_q4_product(be, oracle, op, k, n, rows, group):
     rng = np.random.default_rng(k + n + rows)
     w, sc, bi = q4_weights(rng, n, k, group)

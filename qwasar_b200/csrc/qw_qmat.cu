@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(256) qmat_q4_kernel(float *__restrict__ y, con
 // per step, four steps of a 4096-element chunk of k in flight at once; the tokens' chunk of x sits
 // in shared memory, 32 floats per 36-float slot so that the lanes' 16-byte reads of their slots
 // fall on different banks; a warp takes QV_OUTS output rows one after the other over the same
-// staged chunk.
+// staged chunk.  What the SMs pay for here is the unpacking, so scale and bias stay outside the
+// sum over a slot (a slot lies inside one scale group).
 constexpr int QV_ROWS = 2, QV_OUTS = 4, QV_KC = 4096, QV_SLOTS = QV_KC / 32, QV_PAD = 36;
 __global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
                                                      const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
@@ -83,6 +84,16 @@ __global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, cons
         for (int idx = threadIdx.x; idx < nr * q4; idx += 256) {
             const int r = idx / q4, e = (idx - r * q4) * 4;
             *reinterpret_cast<float4 *>(&xs[r][e >> 5][e & 31]) = *reinterpret_cast<const float4 *>(x + (size_t)(r0 + r) * k + kc0 + e);
+        }
+        __syncthreads();
+        // the sum of every slot's 32 inputs, kept in the slot's padding: scale and bias then come
+        // out of the inner sum, sum_e (sc * nib_e + bi) * x_e = sc * sum_e nib_e * x_e + bi * sum_e x_e
+        for (int idx = threadIdx.x; idx < nr * slots; idx += 256) {
+            const int r = idx / slots, q = idx - r * slots;
+            float sum = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 32; e++) sum += xs[r][q][e];
+            xs[r][q][32] = sum;
         }
         __syncthreads();
 #pragma unroll
@@ -111,21 +122,24 @@ __global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, cons
 #pragma unroll
                 for (int r = 0; r < QV_ROWS; r++) {
                     if (r >= nr) continue;
-                    float t = acc[j][r];
+                    float s1 = 0.0f;
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
                         const float4 a = *reinterpret_cast<const float4 *>(&xs[r][q][u * 8]);
                         const float4 b = *reinterpret_cast<const float4 *>(&xs[r][q][u * 8 + 4]);
                         const uint32_t word = ww[u];
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)(word & 0xFu)), bi[i]), a.x));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 4) & 0xFu)), bi[i]), a.y));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 8) & 0xFu)), bi[i]), a.z));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 12) & 0xFu)), bi[i]), a.w));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 16) & 0xFu)), bi[i]), b.x));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 20) & 0xFu)), bi[i]), b.y));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)((word >> 24) & 0xFu)), bi[i]), b.z));
-                        t = __fadd_rn(t, __fmul_rn(__fadd_rn(__fmul_rn(sc[i], (float)(word >> 28)), bi[i]), b.w));
+                        s1 = fmaf((float)(word & 0xFu), a.x, s1);
+                        s1 = fmaf((float)((word >> 4) & 0xFu), a.y, s1);
+                        s1 = fmaf((float)((word >> 8) & 0xFu), a.z, s1);
+                        s1 = fmaf((float)((word >> 12) & 0xFu), a.w, s1);
+                        s1 = fmaf((float)((word >> 16) & 0xFu), b.x, s1);
+                        s1 = fmaf((float)((word >> 20) & 0xFu), b.y, s1);
+                        s1 = fmaf((float)((word >> 24) & 0xFu), b.z, s1);
+                        s1 = fmaf((float)(word >> 28), b.w, s1);
                     }
+                    float t = acc[j][r];
+                    t = fmaf(sc[i], s1, t);
+                    t = fmaf(bi[i], xs[r][q][32], t);
                     acc[j][r] = t;
                 }
             }

@@ -98,9 +98,13 @@ __global__ void __launch_bounds__(256) qsa_scores_kernel(float *__restrict__ sco
 // keys that order the same way (-0 and +0 share a key, as they compare equal), a radix select of
 // four 8-bit passes finds the key of the take-th best, every block with a larger key is taken, and
 // of the blocks with exactly that key the lowest-indexed ones until the count is reached.  Every
-// pass is one sweep over the row's scores, each thread over a contiguous run of blocks, which is
-// also what orders the equals and the list.
-constexpr int SEL_THREADS = 256;
+// sweep reads the row with consecutive lanes on consecutive scores (a warp whose lanes each walk a
+// run of their own costs one cache-line look-up per lane and load, which was the whole run time).
+// The two ordered sweeps give every warp one contiguous stretch of blocks; ballots rank the equals
+// and place the taken blocks inside each group of 32.
+// SEL_BATCH loads are in flight per thread before the first is used: the branches and the
+// shared-memory updates of a sweep otherwise keep the compiler from overlapping them.
+constexpr int SEL_THREADS = 1024, SEL_WARPS = SEL_THREADS / 32, SEL_BATCH = 8;
 __device__ __forceinline__ bool sel_key(float v, uint32_t &key) {
     if (!(v > -FLT_MAX)) return false;                            // -FLT_MAX, -inf and NaN are never selected
     if (v == 0.0f) v = 0.0f;                                      // -0 -> +0
@@ -112,99 +116,160 @@ __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__rest
                                                                  const float *__restrict__ scores, int ratio, int base_pos,
                                                                  int block_topk, int max_ctx, int max_blocks, int list_stride) {
     __shared__ int hist[256];
-    __shared__ int counts[SEL_THREADS];
+    __shared__ int w_gt[SEL_WARPS], w_eq[SEL_WARPS];
     __shared__ uint32_t s_prefix;
-    __shared__ int s_remaining, s_total;
-    const int r = blockIdx.x, tid = threadIdx.x;
+    __shared__ int s_remaining, s_take, s_total;
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t below = (1u << lane) - 1u;
     const int n_keys = base_pos + r + 1, n_blocks = n_keys / ratio;
     const float *sc = scores + (size_t)r * max_blocks;
     uint8_t *m = mask + (size_t)r * max_ctx;
     uint32_t *l = list + (size_t)r * list_stride;
-    const int per = (n_blocks + SEL_THREADS - 1) / SEL_THREADS;
-    const int lo = min(tid * per, n_blocks), hi = min(lo + per, n_blocks);
-    for (int t = tid; t < n_keys; t += SEL_THREADS) m[t] = t >= n_blocks * ratio;
-
-    // how many blocks can be selected at all
-    int eligible = 0;
-    for (int b = lo; b < hi; b++) { uint32_t key; eligible += sel_key(sc[b], key); }
-    counts[tid] = eligible;
-    __syncthreads();
-    if (tid == 0) {
-        int e = 0;
-        for (int i = 0; i < SEL_THREADS; i++) e += counts[i];
-        s_remaining = min(min(block_topk, n_blocks), e);          // take
-        s_prefix = 0;
-    }
-    __syncthreads();
-    const int take = s_remaining;
+    // the mask starts as 0 over the blocks and 1 over the tail; 16 bytes per store where the row allows
+    const int tail0 = n_blocks * ratio;
+    const int head = min((int)((16 - ((uintptr_t)m & 15)) & 15), n_keys);
+    const int vec_end = tail0 > head ? head + ((tail0 - head) & ~15) : head;
+    for (int t = tid; t < head; t += SEL_THREADS) m[t] = t >= tail0;
+    for (int t = head + 16 * tid; t < vec_end; t += 16 * SEL_THREADS) *reinterpret_cast<uint4 *>(m + t) = make_uint4(0, 0, 0, 0);
+    for (int t = vec_end + tid; t < n_keys; t += SEL_THREADS) m[t] = t >= tail0;
+    if (tid == 0) { s_prefix = 0; s_remaining = 0; s_take = 0; }
 
     // radix select: after the pass over byte `shift`, s_prefix holds the top bytes of the key of
-    // the take-th best block and s_remaining how many blocks with that prefix are still wanted
-    if (take > 0) {
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            hist[tid] = 0;                                        // SEL_THREADS == 256 bins
-            __syncthreads();
-            const uint32_t prefix = s_prefix, high = shift == 24 ? 0u : 0xFFFFFFFFu << (shift + 8);
-            for (int b = lo; b < hi; b++) {
-                uint32_t key;
-                if (sel_key(sc[b], key) && (key & high) == prefix) atomicAdd(&hist[(key >> shift) & 0xFF], 1);
+    // the take-th best block and s_remaining how many blocks with that prefix are still wanted.
+    // The first pass sees every block that can be selected at all, which fixes `take`.
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix, high = shift == 24 ? 0u : 0xFFFFFFFFu << (shift + 8);
+        // scores of one row mostly share their top bytes: count a run of one bin in a register
+        // and add it once, or the whole row queues up on one shared-memory word
+        int cur = 0, run = 0;
+        for (int b0 = tid; b0 < n_blocks; b0 += SEL_BATCH * SEL_THREADS) {
+            float v[SEL_BATCH];
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                const int b = b0 + j * SEL_THREADS;
+                v[j] = b < n_blocks ? sc[b] : -FLT_MAX;
             }
-            __syncthreads();
-            if (tid == 0) {
-                int want = s_remaining, bin = 255;
-                for (; bin > 0 && hist[bin] < want; bin--) want -= hist[bin];
-                s_remaining = want;                               // still wanted among the keys of this bin
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                uint32_t key;
+                if (!(sel_key(v[j], key) && (key & high) == prefix)) continue;
+                const int bin = (key >> shift) & 0xFF;
+                if (bin == cur) { run++; continue; }
+                if (run) atomicAdd(&hist[cur], run);
+                cur = bin; run = 1;
+            }
+        }
+        if (run) atomicAdd(&hist[cur], run);
+        __syncthreads();
+        // Walking down from bin 255, the first bin at which the count reaches `want` (bin 0 if none
+        // does) holds the key looked for.  One warp: lane l sums bins 255-8l .. 248-8l, a scan over
+        // the lanes finds the lane in whose bins the count is reached, that lane walks its eight.
+        if (warp == 0) {
+            int want = s_remaining;
+            __syncwarp();
+            int h[8], mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { h[j] = hist[255 - 8 * lane - j]; mine += h[j]; }
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const int all = __shfl_sync(0xffffffffu, incl, 31);
+            if (shift == 24) {
+                want = min(min(block_topk, n_blocks), all);       // every block that can be selected is in this histogram
+                if (lane == 0) s_take = want;
+            }
+            const uint32_t reached = __ballot_sync(0xffffffffu, incl >= want);
+            if (reached == 0u) {
+                if (lane == 31) { s_remaining = want - (all - h[7]); s_prefix = prefix; }   // bin 0
+            } else if (lane == __ffs(reached) - 1) {
+                int run = incl - mine, bin = 0, rem = 0;
+                bool done = false;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (!done && (run + h[j] >= want || 8 * lane + j == 255)) { bin = 255 - 8 * lane - j; rem = want - run; done = true; }
+                    run += h[j];
+                }
+                s_remaining = rem;                                // still wanted among the keys of this bin
                 s_prefix = prefix | ((uint32_t)bin << shift);
             }
-            __syncthreads();
         }
+        __syncthreads();
+        if (s_take <= 0) break;
     }
+    const int take = s_take;
     const uint32_t kth = s_prefix;                                // the key of the take-th best block
     const int need_eq = s_remaining;                              // blocks with exactly that key to take, lowest index first
 
-    // equals before this thread's run, then the verdict per block; taken blocks counted for the list
-    int eq = 0;
+    // this warp's stretch of blocks, a multiple of 32 long
+    const int chunk = (n_blocks + SEL_THREADS - 1) / SEL_THREADS * 32;
+    const int w_lo = min(warp * chunk, n_blocks), w_hi = min(w_lo + chunk, n_blocks);
+    int gt = 0, eq = 0;
     if (take > 0)
-        for (int b = lo; b < hi; b++) { uint32_t key; eq += sel_key(sc[b], key) && key == kth; }
-    counts[tid] = eq;
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int i = 0; i < SEL_THREADS; i++) { const int c2 = counts[i]; counts[i] = run; run += c2; }
-    }
-    __syncthreads();
-    const int eq_base = counts[tid];
-    __syncthreads();
-    int cnt = 0;
-    if (take > 0) {
-        int rank = eq_base;
-        for (int b = lo; b < hi; b++) {
-            uint32_t key;
-            if (sel_key(sc[b], key)) cnt += key > kth || (key == kth && rank++ < need_eq);
+        for (int b0 = w_lo + lane; b0 < w_hi; b0 += SEL_BATCH * 32) {
+            float v[SEL_BATCH];
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                const int b = b0 + j * 32;
+                v[j] = b < w_hi ? sc[b] : -FLT_MAX;
+            }
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                uint32_t key;
+                if (sel_key(v[j], key)) { gt += key > kth; eq += key == kth; }
+            }
         }
-    }
-    counts[tid] = cnt;
+    gt = (int)__reduce_add_sync(0xffffffffu, (unsigned)gt);
+    eq = (int)__reduce_add_sync(0xffffffffu, (unsigned)eq);
+    if (lane == 0) { w_gt[warp] = gt; w_eq[warp] = eq; }
     __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int i = 0; i < SEL_THREADS; i++) { const int c2 = counts[i]; counts[i] = run; run += c2; }
-        s_total = run;                                            // blocks taken in all (== take)
+    if (tid == 0) {                                               // per warp: equals before it, taken blocks before it
+        int eq_run = 0, out_run = 0;
+        for (int w = 0; w < SEL_WARPS; w++) {
+            const int e = w_eq[w], g = w_gt[w];
+            w_eq[w] = eq_run; w_gt[w] = out_run;
+            out_run += g + min(max(need_eq - eq_run, 0), e);
+            eq_run += e;
+        }
+        s_total = out_run;                                        // blocks taken in all (== take)
     }
     __syncthreads();
     // the mask of the taken blocks, and the list: taken blocks in ascending order, then the tail
     if (take > 0) {
-        int at = counts[tid] * ratio, rank = eq_base;
-        for (int b = lo; b < hi; b++) {
-            uint32_t key;
-            if (!sel_key(sc[b], key)) continue;
-            if (!(key > kth || (key == kth && rank++ < need_eq))) continue;
-            for (int t = 0; t < ratio; t++) {
-                m[b * ratio + t] = 1;
-                l[1 + at++] = (uint32_t)(b * ratio + t);
+        int eq_rank = w_eq[warp], at = w_gt[warp];
+        for (int b0 = w_lo + lane; b0 < w_hi + lane; b0 += SEL_BATCH * 32) {   // the same trip count on every lane
+            float v[SEL_BATCH];
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                const int b = b0 + j * 32;
+                v[j] = b < w_hi ? sc[b] : -FLT_MAX;
+            }
+#pragma unroll
+            for (int j = 0; j < SEL_BATCH; j++) {
+                const int b = b0 + j * 32;
+                bool is_gt = false, is_eq = false;
+                uint32_t key;
+                if (sel_key(v[j], key)) { is_gt = key > kth; is_eq = key == kth; }
+                const uint32_t eq_bits = __ballot_sync(0xffffffffu, is_eq);
+                const bool taken = is_gt || (is_eq && eq_rank + __popc(eq_bits & below) < need_eq);
+                const uint32_t t_bits = __ballot_sync(0xffffffffu, taken);
+                if (taken) {
+                    const int pos = (at + __popc(t_bits & below)) * ratio;
+                    for (int t = 0; t < ratio; t++) {
+                        m[b * ratio + t] = 1;
+                        l[1 + pos + t] = (uint32_t)(b * ratio + t);
+                    }
+                }
+                eq_rank += __popc(eq_bits);
+                at += __popc(t_bits);
             }
         }
     }
-    const int tail0 = n_blocks * ratio, total = s_total * ratio;
+    const int total = s_total * ratio;
     for (int t = tail0 + tid; t < n_keys; t += SEL_THREADS) l[1 + total + (t - tail0)] = (uint32_t)t;
     if (tid == 0) l[0] = (uint32_t)(total + (n_keys - tail0));
 }

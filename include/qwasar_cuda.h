@@ -27,6 +27,7 @@
 #include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdio.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -46,6 +47,8 @@ static inline qw_ref qw_ref_at(qw_buf b, size_t off) { qw_ref r = { b, off }; re
 static inline qw_ref qw_ref_offset(qw_ref r, size_t off) { r.off += off; return r; }
 /* qwasar_gpu.h:54 -- one command buffer under construction. */
 typedef struct qw_cmd_s *qw_cmd;
+/* qwasar_gpu.h:105-109 -- one of the products of qw_op_qmv_q4_multi. */
+typedef struct { qw_ref y, w, scales, biases; int32_t n; } qw_qmv_part;
 #endif
 
 /* qwasar_gpu.h:18-23.  Idempotent; false + message in err on failure (no
@@ -87,12 +90,14 @@ void   qw_cmd_parallel(qw_cmd c, bool on);
 void   qw_cmd_free(qw_cmd c);
 const char *qw_cmd_error(qw_cmd c);
 
-/* qwasar_gpu.h:77-81.  QWASAR_PROFILE=1: qw_cmd_mark times the work since the
+/* qwasar_gpu.h:77-82.  QWASAR_PROFILE=1: qw_cmd_mark times the work since the
  * previous mark with a pair of CUDA events and charges it to `label`;
- * qw_prof_report prints the table to stderr (qwasar_metal.m:396-450). */
+ * qw_prof_report prints the table to `out`, per token when tokens > 0, and
+ * qw_prof_reset empties it (qwasar_metal.m:396-450). */
 bool qw_prof_enabled(void);
 void qw_cmd_mark(qw_cmd c, const char *label);
-void qw_prof_report(void);
+void qw_prof_report(FILE *out, long tokens);
+void qw_prof_reset(void);
 
 /* qwasar_gpu.h:391-393.  [rows, heads, 2*dim] f32 -> two [rows, heads, dim]. */
 void qw_op_split_heads2(qw_cmd c, qw_ref a, qw_ref b, qw_ref src,
@@ -167,7 +172,6 @@ void qw_op_qmv_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref 
                   int32_t k, int32_t n, int32_t rows, int32_t group);
 void qw_op_qmm_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases,
                   int32_t k, int32_t n, int32_t rows, int32_t group);
-typedef struct { qw_ref y, w, scales, biases; int32_t n; } qw_qmv_part;
 bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group, int32_t count, const qw_qmv_part *parts);
 /* qwasar_gpu.h:620-634 -- QSA's indexer.  qn f32 [rows, nq, d] are the normed + rotated index
  * queries, ikeys f32 [positions, d] a layer's raw index keys, k_norm bf16 [d] (or a null ref),
@@ -208,6 +212,20 @@ typedef enum { QW_F32 = 0, QW_BF16 = 1 } qw_dtype;
  * arena, init), or NULL. */
 const char *qw_gpu_last_error(void);
 int32_t     qw_gpu_sm_count(void);
+
+/* ---- several GPUs in one process -------------------------------------------
+ * qw_gpu_init brings up the calling thread's current CUDA device.  qw_gpu_init_multi brings up
+ * devices 0 .. n_dev-1 and lets each read and write the others' memory (needed by the exchange of
+ * partials below); device 0 is current afterwards.  qw_gpu_select makes a device current for the
+ * calls that allocate (qw_buf_*, qw_kv_*, qw_xchg_create, qw_cmd_begin); a command buffer stays on
+ * the device it was begun on, and ops encoded on it switch to that device by themselves, so a host
+ * thread drives several GPUs by alternating between their command buffers.  Like the reference's
+ * backend state (qwasar_metal.m:24-33) all of this is process-global and unsynchronised: one
+ * thread at a time. */
+int32_t     qw_gpu_device_count(void);
+bool        qw_gpu_init_multi(int32_t n_dev, char *err, size_t errcap);
+bool        qw_gpu_select(int32_t dev);
+int32_t     qw_gpu_current(void);            /* -1 before init */
 
 /* Kernels this library has launched since qw_gpu_init (every __global__ launch counts one). */
 uint64_t    qw_gpu_launch_count(void);
@@ -263,6 +281,16 @@ void   qw_op_copy(qw_cmd c, qw_ref dst, qw_ref src, size_t n);
 qw_buf  qw_kv_arena_alloc(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
 qw_buf  qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
                              uint32_t shuffle_seed);
+/* A page pool that several arenas share: max_bytes of device addresses are reserved, memory is
+ * committed as the arenas' tokens arrive.  This is the layout for serving many sequences on one
+ * GPU -- one pool per GPU, one K and one V arena per sequence inside it: pages go where the
+ * tokens are, and because arenas of one pool share its tensor maps, one attention launch carries
+ * all their sequences (a launch holds at most 8 distinct maps; an arena from qw_kv_arena_alloc has
+ * a private pool and so a map of its own).  Freeing an arena returns its pages to the pool; the
+ * pool's memory goes when the pool handle and every arena in it have been freed. */
+qw_buf  qw_kv_pool_alloc(size_t max_bytes, uint32_t shuffle_seed);
+qw_buf  qw_kv_arena_alloc_in(qw_buf pool, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim);
+int64_t qw_kv_pool_bytes_committed(qw_buf pool);
 /* Gather / scatter of n token rows of one (layer, head) starting at pos0,
  * to / from packed host memory (n * head_dim * 2 bytes) -- what
  * qw_session_pack / qw_session_unpack (qwasar_graph.c:320-393) need in place
@@ -312,8 +340,9 @@ bool qw_op_attn_layer_fused(qw_cmd c, qw_ref out, qw_ref qg, qw_ref k, qw_ref v,
 
 /* The same for n_seq independent sequences (one qw_session each in the
  * reference, which has no batch dimension): arrays of n_seq refs and base
- * positions; every sequence has `rows` rows.  Sequences are processed by one
- * launch per 16. */
+ * positions; every sequence has `rows` rows.  One launch of each kernel carries
+ * up to 64 sequences whose caches lie in at most 8 distinct buffers or pools
+ * (arenas of one pool count once); more are taken in further launches. */
 bool qw_op_attn_layer_fused_batch(qw_cmd c, int32_t n_seq, const qw_ref *out, const qw_ref *qg,
                                   const qw_ref *k, const qw_ref *v, qw_ref q_norm_w, qw_ref k_norm_w,
                                   const qw_ref *pos, qw_ref axis, qw_ref inv_freq,
@@ -349,6 +378,48 @@ bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q, qw_ref kc
 void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat, qw_ref gate,
                       int32_t rows, int32_t q_heads, int32_t head_dim, int32_t parts,
                       int32_t gate_stride, qw_dtype out_dtype, qw_dtype gate_dtype, int64_t part_stride);
+
+/* ---- the exchange of partials between GPUs ---------------------------------
+ * For a sequence whose positions are split over n_ranks GPUs (2 to 8; one process per GPU, or one
+ * process that holds them all).  Each rank creates one qw_xchg on its device: a gather buffer with
+ * a slot and a flag per (rank, row, head) for rows * q_heads <= max_rows_heads.  The ranks swap
+ * handles once -- qw_xchg_export writes qw_xchg_handle_bytes() (64) bytes to pass to the other
+ * processes by any means, qw_xchg_attach maps a peer's buffer from its handle (CUDA IPC),
+ * qw_xchg_attach_local takes the peer's object directly when it lives in this process (after
+ * qw_gpu_init_multi).  After that no library call and no host synchronisation is involved:
+ * qw_op_attn_exchange attends this rank's rows to its own key range [key_lo, key_hi) like
+ * qw_op_attn_partial, then its combine kernel stores the (acc, max, sum) record of every (row,
+ * head) straight into every rank's gather buffer (peer stores over NVLink) and raises the flags
+ * beside them, waits until the flags of all ranks are in, merges by log-sum-exp, applies the gate
+ * and writes out -- on every rank the full result (metal/attn.metal:273-331 is the arithmetic; the
+ * exchange itself is new).  Two kernels per call.  phase 0 does all of it; phase 1 stops after
+ * publishing and phase 2 only waits, merges and writes (1 then 2 equals 0: for hosts that want
+ * other work between the halves, and the only form in which several ranks may share ONE GPU,
+ * where a kernel must never wait for a kernel launched after it).
+ * Every rank must make the same sequence of calls on its exchange.  The wait is bounded
+ * (qw_xchg_set_timeout_ms, default 2000): a rank whose peers' records do not arrive gives up,
+ * writes no output, and qw_cmd_error reports it after qw_cmd_wait. */
+typedef struct qw_xchg_s *qw_xchg;
+qw_xchg qw_xchg_create(int32_t n_ranks, int32_t rank, int32_t max_rows_heads);
+void    qw_xchg_free(qw_xchg x);
+size_t  qw_xchg_handle_bytes(void);
+bool    qw_xchg_export(qw_xchg x, void *handle);
+bool    qw_xchg_attach(qw_xchg x, int32_t peer_rank, const void *handle);
+bool    qw_xchg_attach_local(qw_xchg x, int32_t peer_rank, qw_xchg peer);
+void    qw_xchg_set_timeout_ms(qw_xchg x, int32_t ms);
+bool    qw_op_attn_exchange(qw_cmd c, qw_xchg x, int32_t phase, qw_ref out, qw_ref gate, qw_ref q,
+                            qw_ref kcache, qw_ref vcache, int32_t rows, int32_t q_heads, int32_t kv_heads,
+                            int32_t head_dim, int32_t max_ctx, int32_t base_pos, int32_t key_lo, int32_t key_hi,
+                            float scale, qw_dtype q_dtype, qw_dtype out_dtype, qw_dtype gate_dtype,
+                            int32_t gate_stride);
+/* The same round for n_seq (<= 64) sequences of equal shape in the same two kernels: arrays of
+ * n_seq refs, positions and key ranges; gate may be NULL; n_seq * rows * q_heads <= max_rows_heads. */
+bool    qw_op_attn_exchange_batch(qw_cmd c, qw_xchg x, int32_t phase, int32_t n_seq, const qw_ref *out,
+                                  const qw_ref *gate, const qw_ref *q, const qw_ref *kcache, const qw_ref *vcache,
+                                  const int32_t *base_pos, const int32_t *key_lo, const int32_t *key_hi,
+                                  int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                  float scale, qw_dtype q_dtype, qw_dtype out_dtype, qw_dtype gate_dtype,
+                                  int32_t gate_stride);
 
 /* The pre-op half of the fused node alone (split, norm, RoPE, append; q_out
  * receives the normed + roped query as bf16 [rows, q_heads, head_dim]), for
@@ -387,7 +458,13 @@ bool qw_op_attn_preop(qw_cmd c, qw_ref q_out, qw_ref qg, qw_ref k, qw_ref v,
  *
  * The first call on each device (made with that device current) resolves the
  * array's device address and sets a kernel attribute; make that call before
- * any stream capture begins.  All calls on a device share the one array: two
+ * any stream capture begins, and from one thread: that first-call set-up is not
+ * guarded against two threads entering it at once.  The call returns when its
+ * kernels are queued.  A kernel whose bounded internal wait runs out (a fault
+ * of the device, not of the arguments) cannot be reported through the return
+ * value: after synchronising, qw_attn_decode_noalloc_status() returns, and
+ * clears, the code it left (0 = none; the output of such a call is not valid).
+ * All calls on a device share the one array: two
  * calls whose kernels overlap on the GPU (different streams, no dependency)
  * race on it -- order them on one stream or with events.  Nothing in the array
  * needs clearing between calls; stale contents are never read. */
@@ -396,6 +473,7 @@ bool   qw_attn_decode_noalloc(void *out, const void *q, const void *gate, const 
                               int32_t max_ctx, int32_t base_pos, float scale, qw_dtype io, void *cuda_stream,
                               char *err, size_t errcap);
 size_t qw_attn_decode_noalloc_scratch_bytes(void);
+int32_t qw_attn_decode_noalloc_status(void);
 
 #ifdef __cplusplus
 }

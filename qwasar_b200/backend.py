@@ -47,7 +47,8 @@ SIGNATURES = {
     "qw_cmd_error": (C.c_char_p, [_vp]),
     "qw_prof_enabled": (_b, []),
     "qw_cmd_mark": (None, [_vp, C.c_char_p]),
-    "qw_prof_report": (None, []),
+    "qw_prof_report": (None, [_vp, C.c_long]),      # FILE *out, long tokens
+    "qw_prof_reset": (None, []),
     "qw_op_split_heads2": (None, [_vp, QwRef, QwRef, QwRef, _i32, _i32, _i32]),
     "qw_op_rms_norm": (None, [_vp, QwRef, QwRef, QwRef, _i32, _i32, _f32, _f32]),
     "qw_op_rope_partial": (None, [_vp, QwRef, QwRef, QwRef, QwRef, _i32, _i32, _i32, _i32]),
@@ -70,6 +71,22 @@ SIGNATURES = {
     "qw_op_qmv_q4": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 4),
     "qw_op_qmm_q4": (None, [_vp, QwRef, QwRef, QwRef, QwRef, QwRef] + [_i32] * 4),
     "qw_op_qmv_q4_multi": (_b, [_vp, QwRef, _i32, _i32, _i32, _vp]),
+    "qw_gpu_device_count": (_i32, []),
+    "qw_gpu_init_multi": (_b, [_i32, C.c_char_p, _sz]),
+    "qw_gpu_select": (_b, [_i32]),
+    "qw_gpu_current": (_i32, []),
+    "qw_kv_pool_alloc": (_vp, [_sz, C.c_uint32]),
+    "qw_kv_arena_alloc_in": (_vp, [_vp, _i32, _i32, _i32, _i32]),
+    "qw_kv_pool_bytes_committed": (C.c_int64, [_vp]),
+    "qw_xchg_create": (_vp, [_i32, _i32, _i32]),
+    "qw_xchg_free": (None, [_vp]),
+    "qw_xchg_handle_bytes": (_sz, []),
+    "qw_xchg_export": (_b, [_vp, _vp]),
+    "qw_xchg_attach": (_b, [_vp, _i32, _vp]),
+    "qw_xchg_attach_local": (_b, [_vp, _i32, _vp]),
+    "qw_xchg_set_timeout_ms": (None, [_vp, _i32]),
+    "qw_op_attn_exchange": (_b, [_vp, _vp, _i32] + [QwRef] * 5 + [_i32] * 8 + [_f32, C.c_int, C.c_int, C.c_int, _i32]),
+    "qw_op_attn_exchange_batch": (_b, [_vp, _vp, _i32, _i32] + [_vp] * 8 + [_i32] * 5 + [_f32, C.c_int, C.c_int, C.c_int, _i32]),
     "qw_gpu_last_error": (C.c_char_p, []),
     "qw_gpu_sm_count": (_i32, []),
     "qw_gpu_launch_count": (C.c_uint64, []),
@@ -103,6 +120,7 @@ SIGNATURES = {
     "qw_op_attn_preop": (_b, [_vp] + [QwRef] * 11 + [_i32] * 7 + [_f32, C.c_int, _b]),
     "qw_attn_decode_noalloc": (_b, [_vp] * 5 + [_i32] * 6 + [_f32, C.c_int, _vp, C.c_char_p, _sz]),
     "qw_attn_decode_noalloc_scratch_bytes": (_sz, []),
+    "qw_attn_decode_noalloc_status": (_i32, []),
 }
 
 
@@ -221,6 +239,36 @@ class Backend:
             raise MemoryError(self.last_error())
         return b
 
+    def kv_pool_alloc(self, max_bytes, shuffle_seed=0):
+        b = self.lib.qw_kv_pool_alloc(max_bytes, shuffle_seed)
+        if not b:
+            raise MemoryError(self.last_error())
+        return b
+
+    def kv_arena_alloc_in(self, pool, n_layers, kv_heads, max_ctx, head_dim=256):
+        b = self.lib.qw_kv_arena_alloc_in(pool, n_layers, kv_heads, max_ctx, head_dim)
+        if not b:
+            raise MemoryError(self.last_error())
+        return b
+
+    # -- the exchange of partials between GPUs
+    def xchg_create(self, n_ranks, rank, max_rows_heads):
+        x = self.lib.qw_xchg_create(n_ranks, rank, max_rows_heads)
+        if not x:
+            raise RuntimeError(self.last_error())
+        return x
+
+    def xchg_export(self, x) -> bytes:
+        h = C.create_string_buffer(int(self.lib.qw_xchg_handle_bytes()))
+        if not self.lib.qw_xchg_export(x, h):
+            raise RuntimeError(self.last_error())
+        return h.raw
+
+    def xchg_attach(self, x, peer_rank, handle: bytes):
+        h = C.create_string_buffer(handle, len(handle))
+        if not self.lib.qw_xchg_attach(x, peer_rank, h):
+            raise RuntimeError(self.last_error())
+
     def kv_read(self, cache, layer, head, pos0, n, kv_heads, max_ctx, head_dim=256):
         import numpy as np
         out = np.empty((n, head_dim), np.uint16)
@@ -276,7 +324,9 @@ class Backend:
     def __getattr__(self, name):
         if name.startswith("op_") or name in ("rope_tables", "cmd_commit", "cmd_flush", "cmd_parallel", "cmd_mark",
                                                "kv_arena_trim", "kv_arena_pages_in_use", "kv_arena_bytes_committed",
-                                               "prof_report"):
+                                               "kv_pool_bytes_committed", "xchg_free", "xchg_attach_local", "xchg_set_timeout_ms",
+                                               "gpu_device_count", "gpu_init_multi", "gpu_select", "gpu_current",
+                                               "prof_report", "prof_reset"):
             return getattr(self.lib, "qw_" + name)
         raise AttributeError(name)
 
@@ -289,6 +339,16 @@ class Backend:
             c, n, C.addressof(arrs[0]), C.addressof(arrs[1]), C.addressof(arrs[2]), C.addressof(arrs[3]), qw, kw,
             C.addressof(arrs[4]), axis, inv_freq, C.addressof(arrs[5]), C.addressof(arrs[6]), C.addressof(bp),
             rows, q_heads, kv_heads, head_dim, rotary_dim, max_ctx, eps, scale, io)
+
+    def op_attn_exchange_batch(self, c, x, phase, outs, gates, qs, kcs, vcs, base_pos, key_lo, key_hi, rows, q_heads, kv_heads,
+                               head_dim, max_ctx, scale, q_dtype, out_dtype, gate_dtype, gate_stride):
+        n = len(outs)
+        ints = [(C.c_int32 * n)(*v) for v in (base_pos, key_lo, key_hi)]
+        arrs = [_ref_array(v) for v in (outs, gates if gates else [NULL_REF] * n, qs, kcs, vcs)]
+        return self.lib.qw_op_attn_exchange_batch(
+            c, x, phase, n, C.addressof(arrs[0]), C.addressof(arrs[1]) if gates else None, C.addressof(arrs[2]),
+            C.addressof(arrs[3]), C.addressof(arrs[4]), C.addressof(ints[0]), C.addressof(ints[1]), C.addressof(ints[2]),
+            rows, q_heads, kv_heads, head_dim, max_ctx, scale, q_dtype, out_dtype, gate_dtype, gate_stride)
 
     def op_attn_batch(self, c, outs, qs, kcs, vcs, base_pos, rows, q_heads, kv_heads, head_dim, max_ctx, scale, io):
         n = len(outs)

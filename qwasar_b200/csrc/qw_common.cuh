@@ -7,7 +7,9 @@
 
 #define QW_HEAD_DIM 256          // the only head width the reference builds for (qwasar_metal.m:1359-1363)
 #define QW_PAGE_TOKENS 64        // tokens per arena page: 64 x 512 B = 32 KB, 128 B-aligned rows
-#define QW_MAX_SEQ 16            // sequences (or row chunks) one launch carries
+#define QW_MAX_SEQ 64            // sequences (or row chunks) one launch carries
+#define QW_XCHG_REC 264          // floats per exchanged partial: acc[256], max, sum, padding to 16 bytes
+#define QW_MAX_MAPS 8            // distinct cache tensor maps one launch carries (arenas of one pool share theirs)
 
 // Status codes a kernel leaves in the backend's status word (first one wins).
 enum : int {
@@ -17,6 +19,7 @@ enum : int {
     QW_ST_MMA_TIMEOUT = 3,       // a wait on a tcgen05 commit barrier ran out
     QW_ST_BAD_PAGE = 4,          // a page-table entry was unmapped where a key was needed
     QW_ST_BAD_SMEM = 5,          // the dynamic shared-memory window was not 1024-byte aligned
+    QW_ST_PEER_TIMEOUT = 6,      // a partial from another GPU did not arrive within the exchange's time limit
 };
 
 namespace qw {
@@ -31,6 +34,21 @@ __device__ __forceinline__ void report(int *status, int code) {
     volatile int *s = status;
     if (s && *s == 0) *s = code;
 }
+
+// ---- programmatic dependent launch -----------------------------------------------
+// Kernels of one stream that are launched with the programmatic-serialization attribute may
+// start while the kernel before them still runs.  The rules every such kernel here keeps:
+//   * nothing produced by the kernel directly before it is read, and nothing any earlier
+//     kernel may still read is written, before pdl_wait() has returned (it returns when all
+//     earlier kernels have completed and their writes are visible);
+//   * pdl_launch_next() is called only after this kernel's own pdl_wait() where the next kernel
+//     reads anything before its wait -- so what that kernel finds on starting is at least
+//     everything that was complete before this one;
+//   * every CTA calls pdl_wait() before it exits, so "this kernel has completed" always implies
+//     "every kernel before it has completed".
+// Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- mbarrier -----------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {

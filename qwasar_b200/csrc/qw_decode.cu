@@ -157,10 +157,19 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
         mbar_fence_init();
     }
     __syncthreads();
-    if (lo >= hi) return;
+    // Dependent launch.  With p.early the kernel in front is this node's own K/V append, which
+    // waited for everything before it and touches only the rows [fresh_pos, ...) of each cache: what
+    // this kernel reads before its wait -- cached keys, page tables, raw query rows -- was complete
+    // before that kernel started, and the partial scratch is no longer in use, so only the tiles that
+    // hold appended rows wait.  Otherwise the whole kernel waits here.  The kernel behind (the
+    // merge) may be brought in right away: it touches nothing of ours before its own wait.
+    if (!p.early) pdl_wait();
+    pdl_launch_next();
+    if (lo >= hi) { pdl_wait(); return; }
 
     if (warp == NW) {
         // ---------------- producer warp (lane 0 issues the TMA loads) ----------------
+        bool waited = !p.early;
         Cursor pc = locate(p, lo);
         // page ids of 32 consecutive tiles, one per lane, fetched together: one global-memory
         // latency per 32 tiles instead of one per tile in front of every issue
@@ -185,6 +194,8 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
             if (lane == 0) {
                 const AttnSeq &sq = p.seq[pc.s];
                 const int t_abs = (sq.tile0 + pc.t) * TILE_KEYS;
+                // rows from fresh_pos on were appended by the kernel in front of this one
+                if (!waited && t_abs + TILE_KEYS > sq.fresh_pos) { pdl_wait(); waited = true; }
                 int64_t kr, vr;
                 if (sq.kc.table) {
                     if (kp < 0 || vp < 0) report(p.status, QW_ST_BAD_PAGE);
@@ -197,15 +208,16 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 uint8_t *st = smem + slot * STAGE_BYTES;
                 mbar_expect_tx(&full[slot], STAGE_BYTES);
 #pragma unroll
-                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.kmap[pc.s], b * 64, (int32_t)kr, &full[slot]);
+                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.maps[sq.kmap], b * 64, (int32_t)kr, &full[slot]);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
-                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.vmap[pc.s], b * 64, (int32_t)vr, &full[slot]);
+                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.maps[sq.vmap], b * 64, (int32_t)vr, &full[slot]);
             }
             advance(p, pc);
             __syncwarp();
         }
         // falls through to the end: consumers wait for every stage that was issued.
+        if (lane == 0 && !waited) pdl_wait();      // every CTA has waited before it exits
     } else {
         // ---------------- consumers ----------------
         const int mt = warp / KG, kg = warp % KG;
@@ -226,6 +238,65 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
             const int head0 = c.h * p.gqa;
 
             // Q of this group -> bf16, swizzled: 4 boxes of [MT*16 rows, 64 dims].
+            if (p.q_raw) {
+                // Raw rows of the [q|gate] projection: per-head RMS norm and partial RoPE here, in the
+                // arithmetic of the pre-op kernel (qwasar_cpu.c:68-82, 304-319), one warp per row, lane l
+                // holding dims 8l .. 8l+7.  The rows' cos / sin (one angle per lane) go through the
+                // reduction buffer, which is idle until the segment ends.
+                float *cs = red;
+                for (int r = warp; r < sq.rows; r += NW) {
+                    const int ax = p.axis[lane];
+                    const float ang = __fmul_rn((float)sq.pos[(size_t)ax * sq.pos_stride + r], p.inv_freq[lane]);
+                    float sn, cn;
+                    sincosf(ang, &sn, &cn);
+                    cs[r * 64 + lane] = cn; cs[r * 64 + 32 + lane] = sn;
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+                uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
+                if (p.q_norm_w) w4 = __ldg(reinterpret_cast<const uint4 *>(p.q_norm_w) + lane);
+                const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+                for (int row = warp; row < MT * 16; row += NW) {
+                    uint4 val = make_uint4(0, 0, 0, 0);
+                    if (row < valid_rows) {
+                        const int r = row / p.gqa, g = row - r * p.gqa;
+                        const size_t src = ((size_t)r * p.q_heads + head0 + g) * 512 + lane * 8;
+                        float x[8];
+                        if (p.q_dtype == DT_BF16) {
+                            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(sq.q) + src));
+                            const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                            for (int i = 0; i < 4; i++) { x[2 * i] = __uint_as_float(xw[i] << 16); x[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u); }
+                        } else {
+                            const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src));
+                            const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src + 4));
+                            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+                        }
+                        float ss = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+                        ss = warp_sum(ss);
+                        const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            x[i] = __fmul_rn(x[i], inv);
+                            if (p.q_norm_w) x[i] = __fmul_rn(x[i], __uint_as_float((i & 1) ? (ww[i >> 1] & 0xffff0000u) : (ww[i >> 1] << 16)));
+                        }
+                        // dims d < 32 sit in lanes 0-3, their partners d + 32 in lanes 4-7
+                        const float *cr = cs + r * 64 + 8 * (lane & 3);
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            const float other = __shfl_xor_sync(0xffffffffu, x[i], 4);
+                            if (lane < 8) {
+                                const float cn = cr[i], sn = cr[32 + i];
+                                x[i] = lane < 4 ? __fsub_rn(__fmul_rn(x[i], cn), __fmul_rn(other, sn))
+                                                : __fadd_rn(__fmul_rn(x[i], cn), __fmul_rn(other, sn));
+                            }
+                        }
+                        val = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
+                    }
+                    *reinterpret_cast<uint4 *>(q_s + (lane >> 3) * (MT * 16 * 128) + swz128(row, (lane & 7) * 8)) = val;
+                }
+            } else
             for (int idx = warp * 32 + lane; idx < MT * 16 * 32; idx += NW * 32) {
                 const int row = idx >> 5, chunk = idx & 31;           // 16-byte chunk = 8 dims
                 uint4 val = make_uint4(0, 0, 0, 0);
@@ -473,6 +544,97 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
     }
 }
 
+// ---- the exchange of partials between GPUs (a sequence split by position) ----------------
+// A record is one (row, head)'s combined partial: acc[256], max (natural units), sum, padded to
+// XCHG_REC floats so that records stay 16-byte aligned.  Rank a's record of epoch e goes to slot
+// [e & 1][a][rh] of EVERY rank's gather buffer by plain stores (peer stores over NVLink for the
+// others), then, after a system-wide fence, the epoch number goes into the flag beside it.  A rank
+// merges when the flags of all ranks show the epoch.  Two parities suffice: a rank can only publish
+// epoch e + 2 after it has merged epoch e + 1, which needed every rank's record of e + 1, which
+// those ranks published after they had merged epoch e.
+constexpr int XCHG_REC = QW_XCHG_REC;
+
+__device__ __forceinline__ void st_release_sys(int *p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int *p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Threads 0-63 of a block, each holding four dims (d4 ..) of the combined partial of (row, head) rh.
+__device__ __forceinline__ void xchg_publish(const XchgDev &x, size_t ci, int tid, int d4, float4 acc, float m, float den) {
+    const size_t slot = (size_t)((x.epoch & 1) * x.n_ranks + x.rank) * x.max_rh + ci;
+    for (int i = 0; i < x.n_ranks; i++) {
+        float *rec = x.gather[i] + slot * XCHG_REC;
+        *reinterpret_cast<float4 *>(rec + d4) = acc;
+        if (tid == 0) { rec[256] = den > 0.0f ? m : -3.0e38f; rec[257] = den; }
+    }
+    __threadfence_system();
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (tid < x.n_ranks) st_release_sys(x.flags[tid] + slot, x.epoch);
+}
+
+// Waits (bounded) for every rank's record of this epoch, merges them by log-sum-exp, applies the
+// gate and writes the output row.  Threads 0-63 of a block.
+__device__ __forceinline__ void xchg_collect(const AttnParams &p, const AttnSeq &sq, size_t ci, size_t rh, int tid, int d4, int *late_s) {
+    const XchgDev &x = p.x;
+    const size_t slot0 = (size_t)((x.epoch & 1) * x.n_ranks) * x.max_rh + ci;
+    float gate4[4] = {0.f, 0.f, 0.f, 0.f};
+    if (sq.gate) {
+        const size_t gi = rh * p.gate_stride + d4;
+#pragma unroll
+        for (int i = 0; i < 4; i++) gate4[i] = load_gate(sq.gate, gi + i, p.gate_dtype);
+    }
+    if (tid < x.n_ranks) {
+        const int *f = x.flags[x.rank] + slot0 + (size_t)tid * x.max_rh;
+        const uint64_t t0 = global_ns();
+        while (ld_acquire_sys(f) != x.epoch) {
+            if ((int64_t)(global_ns() - t0) > x.timeout_ns) { *late_s = 1; break; }
+            __nanosleep(100);
+        }
+    }
+    asm volatile("bar.sync 1, 64;" ::: "memory");
+    if (*reinterpret_cast<volatile int *>(late_s)) {
+        if (tid == 0) report(p.status, QW_ST_PEER_TIMEOUT);
+        return;
+    }
+    const float *mine = x.gather[x.rank] + slot0 * XCHG_REC;
+    float m = -3.0e38f;
+    for (int i = 0; i < x.n_ranks; i++) {
+        const float2 st = __ldcg(reinterpret_cast<const float2 *>(mine + (size_t)i * x.max_rh * XCHG_REC + 256));
+        if (st.y > 0.0f) m = fmaxf(m, st.x);
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.0f;
+    for (int i = 0; i < x.n_ranks; i++) {
+        const float *rec = mine + (size_t)i * x.max_rh * XCHG_REC;
+        const float2 st = __ldcg(reinterpret_cast<const float2 *>(rec + 256));
+        const float w = st.y > 0.0f ? __expf(st.x - m) : 0.0f;
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(rec + d4));
+        den += st.y * w;
+        acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+    }
+    const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+    acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+    if (sq.gate) {
+        acc.x *= sigmoidf(gate4[0]); acc.y *= sigmoidf(gate4[1]); acc.z *= sigmoidf(gate4[2]); acc.w *= sigmoidf(gate4[3]);
+    }
+    if (p.out_dtype == DT_BF16) {
+        uint2 v;
+        v.x = pack_bf16(acc.x, acc.y); v.y = pack_bf16(acc.z, acc.w);
+        *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(sq.out) + rh * 256 + d4) = v;
+    } else {
+        *reinterpret_cast<float4 *>(reinterpret_cast<float *>(sq.out) + rh * 256 + d4) = acc;
+    }
+}
+
 // One block per (group, row i): combine the group's partials.  A group cut over many CTAs (one
 // long sequence: up to one partial per SM) must not be walked one partial at a time -- every
 // step of such a walk is a trip to L2 -- so the block reads all (max, sum) pairs at once, one per
@@ -484,29 +646,47 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
     __shared__ float w_s[MERGE_THREADS];                      // weight of partial q (0 for an empty one)
     __shared__ float red_s[2][8];
     __shared__ __align__(16) float acc_s[3][256];
+    __shared__ int late_s;
+    // Dependent launch: the kernel behind this one touches nothing before its own wait, so it may
+    // be brought in at once; this kernel reads partials, and writes, only after its wait.  Every
+    // block waits before it exits.
+    pdl_launch_next();
     const int gidx = blockIdx.x / max_valid_rows;            // sequence * kv_heads + head
     const int row = blockIdx.x - gidx * max_valid_rows;
     const int s = gidx / p.kv_heads, h = gidx - s * p.kv_heads;
-    if (s >= p.n_seq) return;
+    if (s >= p.n_seq) { pdl_wait(); return; }
     const AttnSeq &sq = p.seq[s];
-    if (row >= sq.rows * p.gqa) return;
+    if (row >= sq.rows * p.gqa) { pdl_wait(); return; }
     const int64_t G0 = (int64_t)sq.cum_tiles + (int64_t)h * sq.n_tiles, G1 = G0 + sq.n_tiles;
     int c_first, c_last;
     group_ctas(p, G0, G1, c_first, c_last);
     const int parts = c_last - c_first + 1;                   // <= n_cta <= MERGE_THREADS
-    if (parts == 1 && p.mode == 0) return;                     // the split kernel wrote the output itself
+    if (parts == 1 && p.mode == 0) { pdl_wait(); return; }    // the split kernel wrote the output itself
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const size_t pi0 = (size_t)(c_first + gidx) * (MT * 16) + row;      // partial q sits MT*16 rows further per q
     // the gate of the row is fetched now, by the quarter that will use it: it depends on nothing here
     const int r = row / p.gqa, g = row - r * p.gqa;
     const size_t rh = (size_t)r * p.q_heads + h * p.gqa + g;
+    if (tid == 0) late_s = 0;
+    if (p.mode == 4 || (p.mode >= 2 && p.x.empty)) {
+        // the second half of an exchange alone (the records are already on their way), or a rank
+        // whose range holds no visible key: it publishes an empty record (sum 0 drops out of the merge)
+        pdl_wait();
+        if (tid >= 64) return;
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+        const size_t ci = (size_t)sq.row_slot0 * p.q_heads + rh;
+        if (p.mode != 4) xchg_publish(p.x, ci, tid, tid * 4, make_float4(0.f, 0.f, 0.f, 0.f), -3.0e38f, 0.0f);
+        if (p.mode != 3) xchg_collect(p, sq, ci, rh, tid, tid * 4, &late_s);
+        return;
+    }
     float gate4[4] = {0.f, 0.f, 0.f, 0.f};
     if (sq.gate && p.mode == 0 && tid < 64) {
         const size_t gi = rh * p.gate_stride + tid * 4;
 #pragma unroll
         for (int i = 0; i < 4; i++) gate4[i] = load_gate(sq.gate, gi + i, p.gate_dtype);
     }
+    pdl_wait();
     // max over the non-empty partials, then each partial's weight and the denominator
     float mq = -3.0e38f, lq = 0.0f;
     if (tid < parts) {
@@ -563,6 +743,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
         float *ca = p.comb_acc, *cs = p.comb_stat;
         *reinterpret_cast<float4 *>(ca + ci * 256 + d4) = acc;
         if (threadIdx.x == 0) { cs[ci * 2] = den > 0.0f ? m : -3.0e38f; cs[ci * 2 + 1] = den; }
+        return;
+    }
+    if (p.mode >= 2) {
+        const size_t ci = (size_t)sq.row_slot0 * p.q_heads + rh;
+        xchg_publish(p.x, ci, tid, d4, acc, m, den);
+        if (p.mode == 2) xchg_collect(p, sq, ci, rh, tid, d4, &late_s);
         return;
     }
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
@@ -698,6 +884,16 @@ __global__ void __launch_bounds__(256) attn_per_query_kernel(AttnSeq sq, int q_h
     if (threadIdx.x == 0) { pstat[pi * 2] = M; pstat[pi * 2 + 1] = L; }
 }
 
+// Launch attribute of every kernel of the decode chain: it may start while the kernel in front of
+// it on the stream still runs, and orders itself with pdl_wait() (qw_common.cuh).
+void pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute &attr, unsigned grid, unsigned block, size_t smem, cudaStream_t s) {
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg = cudaLaunchConfig_t();
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+}
+
 template <int MT, int KG>
 void launch_split_t(cudaStream_t s, const AttnParams &p) {
     using Cfg = SplitCfg<MT, KG>;
@@ -708,7 +904,10 @@ void launch_split_t(cudaStream_t s, const AttnParams &p) {
         cudaFuncSetAttribute(qw_attn_split_kernel<MT, KG>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
         configured[dev] = true;
     }
-    qw_attn_split_kernel<MT, KG><<<p.n_cta, Cfg::THREADS, Cfg::SMEM, s>>>(p);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    pdl_config(cfg, attr, (unsigned)p.n_cta, Cfg::THREADS, Cfg::SMEM, s);
+    cudaLaunchKernelEx(&cfg, qw_attn_split_kernel<MT, KG>, p);
     g_launches++;
 }
 
@@ -725,14 +924,15 @@ int g_tune_prefill_tc = 1;
 int g_tune_prefill_fuse_q = 1;
 
 int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
+    static int n[64] = {0};                    // per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!n[dev]) {
+        cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+        if (n[dev] <= 0) n[dev] = 148;
     }
-    return n;
+    return n[dev];
 }
 
 size_t attn_split_scratch_bytes(const AttnParams &p, int max_rows) {
@@ -773,11 +973,15 @@ bool attn_split_needs_merge(const AttnParams &p) {
 void launch_attn_merge(cudaStream_t s, const AttnParams &p, int max_rows) {
     const int vr = max_rows * p.gqa;
     const unsigned blocks = (unsigned)(p.n_seq * p.kv_heads * vr);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    pdl_config(cfg, attr, blocks, MERGE_THREADS, 0, s);
     switch (row_tiles(max_rows, p.gqa)) {
-        case 1: qw_attn_merge_kernel<1><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
-        case 2: qw_attn_merge_kernel<2><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
-        default: qw_attn_merge_kernel<4><<<blocks, MERGE_THREADS, 0, s>>>(p, vr); g_launches++; break;
+        case 1: cudaLaunchKernelEx(&cfg, qw_attn_merge_kernel<1>, p, vr); break;
+        case 2: cudaLaunchKernelEx(&cfg, qw_attn_merge_kernel<2>, p, vr); break;
+        default: cudaLaunchKernelEx(&cfg, qw_attn_merge_kernel<4>, p, vr); break;
     }
+    g_launches++;
 }
 
 void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,

@@ -65,27 +65,55 @@ void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows);
 
 // ---- attention ------------------------------------------------------------------------
 struct AttnSeq {
-    const void *q;           // [rows, q_heads, 256] f32 or bf16
+    const void *q;           // [rows, q_heads, 256] f32 or bf16; with q_raw the [q|gate] rows [rows, q_heads, 512]
     void *out;               // [rows, q_heads, 256] f32 or bf16
     const void *gate;        // nullptr, or element (r, h, d) at gate[(r*q_heads + h)*gate_stride + d]
+    const int32_t *pos;      // q_raw: positions of this sequence's first row, axis a of row r at pos[a*pos_stride + r]
     KvLayer kc, vc;
     int32_t rows, base_pos;  // row r reads keys [key_lo, min(key_hi, base_pos + r + 1))
     int32_t key_lo, key_hi;  // this launch's share of the sequence (whole: 0, base_pos + rows)
     int32_t tile0, n_tiles;  // first 32-key tile and tile count per kv head, from key_lo/key_hi
     int32_t cum_tiles;       // tiles of all earlier sequences times kv_heads
     int32_t row_slot0;       // first row of this sequence in the partial buffers
+    int32_t pos_stride;      // q_raw: rows of the call the positions belong to
+    int32_t fresh_pos;       // early: first cache position the kernel in front of this launch appends
+    uint8_t kmap, vmap;      // which of the launch's tensor maps cover this sequence's K and V rows
+};
+// Partials that cross GPUs (a sequence split by position): every rank stores its combined
+// (acc, max, sum) record of each (row, head) straight into every rank's gather buffer and raises
+// a flag beside it; a rank merges once the flags of all ranks are in.
+struct XchgDev {
+    float *gather[8];        // rank i's buffer [2 parities][n_ranks][max_rh][258] (acc[256], max, sum), as seen from this GPU
+    int *flags[8];           // rank i's flags  [2 parities][n_ranks][max_rh]: the epoch of the record beside it
+    int32_t n_ranks, rank, max_rh, epoch;
+    int32_t empty;           // no sequence of this launch has a visible key in this rank's range: empty records go out
+    int64_t timeout_ns;      // how long a rank waits for the others' records before it reports QW_ST_PEER_TIMEOUT
 };
 struct AttnParams {
+    CUtensorMap maps[QW_MAX_MAPS];
     AttnSeq seq[QW_MAX_SEQ];
-    CUtensorMap kmap[QW_MAX_SEQ], vmap[QW_MAX_SEQ];
     int32_t n_seq, q_heads, kv_heads, gqa;
     int32_t q_dtype, out_dtype, gate_dtype, gate_stride;
     int32_t total_tiles, n_cta;
-    int32_t mode;            // 0: write normalised (gated) output; 1: always leave partials (m, l, acc)
+    // 0: write normalised (gated) output; 1: leave one combined partial (m, l, acc) per (row, head);
+    // 2: publish that partial to all ranks of an exchange, wait for theirs, merge and write the output;
+    // 3: publish only; 4: wait + merge + output only (3 then 4 is 2 in two launches)
+    int32_t mode;
+    // q_raw: the kernel applies the per-head RMS norm (weights q_norm_w, bf16 [256] or nullptr) and the
+    // partial RoPE (axis uint8 [32], inv_freq f32 [32]) to the raw query rows itself
+    int32_t q_raw;
+    // early: launched directly behind this node's own K/V append kernel; only the tiles from each
+    // sequence's fresh_pos on wait for it (see pdl_wait in qw_common.cuh)
+    int32_t early;
+    const uint16_t *q_norm_w;
+    const uint8_t *axis;
+    const float *inv_freq;
+    float eps;
     float scale;
     float *pacc, *pstat;     // partial scratch: [slot, MT*16, 256] and [slot, MT*16, 2]
     float *comb_acc, *comb_stat;   // mode 1: where the one combined partial per (row, head) goes
     int *status;
+    XchgDev x;               // modes 2-4
 };
 // rows_per_seq * gqa <= 64.  The number of partial slots a launch may write: a (CTA, group)
 // segment uses slot cta + group.

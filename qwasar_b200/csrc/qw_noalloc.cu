@@ -19,6 +19,9 @@ using namespace qw;
 // It holds one (max, sum, acc[256]) partial per (CTA or kv head, query row) -- 258 floats each.
 #define QW_NOALLOC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) unsigned char g_noalloc_scratch[QW_NOALLOC_SCRATCH_BYTES];
+// Where this entry point's kernels leave a status code when one of their bounded waits runs out
+// (the regular ops report through their command buffer; this one has none).  0 = nothing happened.
+static __device__ int g_noalloc_status;
 
 namespace {
 
@@ -30,6 +33,7 @@ constexpr int MAX_DEVICES = 64;
 struct PerDevice {
     bool ready;
     float *scratch;      // device address of g_noalloc_scratch on that device
+    int *status;         // device address of g_noalloc_status on that device
     int sms;
 };
 PerDevice g_dev[MAX_DEVICES];
@@ -64,7 +68,11 @@ bool setup_device(int dev, char *err, size_t cap) {
             return fail(err, cap, "qw_attn_decode_noalloc: driver lacks cuTensorMapEncodeTiled");
         g_encode = reinterpret_cast<PFN_encodeTiled>(fn);
     }
+    void *st = nullptr;
+    e = cudaGetSymbolAddress(&st, g_noalloc_status);
+    if (e != cudaSuccess || !st) return fail(err, cap, "qw_attn_decode_noalloc: cudaGetSymbolAddress failed for the status word");
     d.scratch = reinterpret_cast<float *>(ptr);
+    d.status = reinterpret_cast<int *>(st);
     d.ready = true;
     return true;
 }
@@ -120,15 +128,17 @@ extern "C" bool qw_attn_decode_noalloc(void *out, const void *q, const void *gat
                  need, QW_NOALLOC_SCRATCH_BYTES);
         return fail(err, errcap, msg);
     }
-    if (!rows_map(&p.kmap[0], kcache, (uint64_t)kv_heads * max_ctx) || !rows_map(&p.vmap[0], vcache, (uint64_t)kv_heads * max_ctx))
+    s.kmap = 0; s.vmap = 1;
+    if (!rows_map(&p.maps[0], kcache, (uint64_t)kv_heads * max_ctx) || !rows_map(&p.maps[1], vcache, (uint64_t)kv_heads * max_ctx))
         return fail(err, errcap, "qw_attn_decode_noalloc: cuTensorMapEncodeTiled failed");
     // partial slots first, their (max, sum) pairs after them -- the layout the kernels expect.  Nothing
     // in the array has to start at zero: every slot the merge reads was written by this call's launch.
     const size_t part_rows = (size_t)attn_split_slots(p) * 16 + (size_t)rows * q_heads;
     p.pacc = g_dev[dev].scratch;
     p.pstat = g_dev[dev].scratch + part_rows * 256;
-    p.status = nullptr;
+    p.status = g_dev[dev].status;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    cudaGetLastError();        // an error left behind by earlier, unrelated work is not this call's
     launch_attn_split(stream, p, rows);
     launch_attn_merge(stream, p, rows);
     cudaError_t e = cudaGetLastError();
@@ -138,4 +148,15 @@ extern "C" bool qw_attn_decode_noalloc(void *out, const void *q, const void *gat
         return fail(err, errcap, msg);
     }
     return true;
+}
+
+// The status word of the calling thread's current device, and cleared: 0 when every kernel of the
+// earlier calls ran to its end, else the code of the wait that gave up (1 TMA load, 2 pipeline
+// stage, 4 unmapped page).  Blocks until the device is idle of this module's copies only in the
+// sense of cudaMemcpyFromSymbol: synchronise the streams of the calls first.  Allocates nothing.
+extern "C" int32_t qw_attn_decode_noalloc_status(void) {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_noalloc_status, sizeof v) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_noalloc_status, &zero, sizeof zero);
+    return v;
 }

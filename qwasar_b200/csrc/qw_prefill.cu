@@ -69,7 +69,7 @@ constexpr float NEG_BIG = -1.0e30f;
 constexpr float RESCALE_AT = 8.0f;                    // log2 units
 
 enum Bar { Q_READY = 0, Q_FULL, G_FULL, K_FULL0, K_FULL1, K_FREE0, K_FREE1, V_FULL0, V_FULL1, V_FREE0, V_FREE1,
-           S_READY, S_FREE, P_READY, PV_DONE, PV_ISSUED, N_BARS };
+           S_READY, S_FREE, P_READY, PV_DONE, PV_ISSUED, V_TAIL, N_BARS };
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
 
     // first row of the tensor map that holds page `pg` of this kv head (or a row past the map: zero fill)
     auto page_row = [&](const KvLayer &L, int pg) -> int32_t {
+        if (pg * QW_PAGE_TOKENS >= n_keys) return p.oob_row;       // nothing of this page is visible: zeros, whatever memory holds
         if (L.table) {
             const int id = pg < L.pt_stride ? __ldg(L.table + (size_t)kvh * L.pt_stride + pg) : -1;
             return id >= 0 ? id * QW_PAGE_TOKENS : p.oob_row;
@@ -258,6 +259,24 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                     tma_load_2d(smem + OFF_V + st * V_BYTES + b * VBOX, &p.vmap, b * 64, r, &bars[V_FULL0 + st]);
             }
         }
+        __syncwarp();
+        // The page that holds the last key: its rows past that key may hold anything (a recycled
+        // page, a caller's own buffer), and although their softmax weights are exactly 0, 0 x NaN
+        // would still poison the whole output tile.  The warp clears those rows in shared memory
+        // once the page has landed, and the P V issuer waits for that before it uses the page.
+        // (The page is one of the last two of this tile, so its stage is not filled again.)
+        const int pg_r = n_keys >> 6;
+        if ((n_keys & 63) && pg_r < 2 * n_t) {
+            mbar_wait(&bars[V_FULL0 + (pg_r & 1)], (pg_r >> 1) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+            uint8_t *stg = smem + OFF_V + (pg_r & 1) * V_BYTES;
+#pragma unroll
+            for (int b = 0; b < 4; b++)
+                for (int off = (n_keys & 63) * 128 + lane * 16; off < 64 * 128; off += 32 * 16)
+                    *reinterpret_cast<uint4 *>(stg + b * VBOX + off) = make_uint4(0, 0, 0, 0);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars[V_TAIL]);
+        }
     } else if (warp == W_MMA) {
         // ---------------- tensor-core issue, S = Q K^T ----------------
         // The two products are issued by two threads (this one and warp W_PV): a thread that has
@@ -308,6 +327,10 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 for (int h = 0; h < 2; h++) {                  // the two 64-key pages of the step
                     if (h == 1) {
                         mbar_wait_hot(&bars[V_FULL1], j & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                        tc_fence_after();
+                    }
+                    if ((n_keys & 63) && 2 * j + h == (n_keys >> 6)) {      // the page with the last key: cleared past it first
+                        mbar_wait(&bars[V_TAIL], 0, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                         tc_fence_after();
                     }
                     const uint32_t v_lo = desc_lo(v_a + h * V_BYTES, VBOX);
@@ -602,10 +625,12 @@ bool attn_prefill_io_ok(const void *out, int out_dtype, const void *gate, int ga
 }
 
 void launch_attn_prefill(cudaStream_t s, const PrefillParams &p) {
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {false};      // the attribute is per device
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
         cudaFuncSetAttribute(qw_attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        configured = true;
+        configured[dev] = true;
     }
     qw_attn_prefill_kernel<<<p.n_q_tiles * p.q_heads, THREADS, SMEM_BYTES, s>>>(p);
     g_launches++;

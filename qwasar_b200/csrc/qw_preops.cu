@@ -6,8 +6,12 @@
 //
 // Arithmetic follows the reference's scalar twins operation for operation
 // (qwasar_cpu.c:68-82, 304-319, 344-355) with contraction switched off through
-// the _rn intrinsics, so results differ from the CPU code only by the order of
-// the 256-term sum of squares and by the last bit of cosf/sinf.
+// the _rn intrinsics.  In the fused kernel the key rows -- whose bits end up in
+// the cache -- also keep the twins' order of the 256-term sum of squares (left to
+// right) and take cos / sin from the double-precision functions rounded once to
+// float, which is what a correctly rounded cosf / sinf returns; so the appended K
+// equals the CPU code's bit for bit.  Query rows (rounded to bf16 for the tensor
+// cores anyway) and the stand-alone norm op sum as a tree.
 #include "qw_kernels.h"
 
 namespace qw {
@@ -142,6 +146,11 @@ __global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, ui
 constexpr int PRE_ROWS = QW_PRE_ROWS;
 __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
+    // Dependent launch: this kernel reads the projections and writes the cache, so it waits for
+    // everything in front of it first; the attention kernel behind it may then start at once (it
+    // waits itself before it touches the rows appended here).
+    pdl_wait();
+    pdl_launch_next();
     const PreopSeq &s = p.seq[blockIdx.z];
     const int qh = p.q_heads, kvh = p.kv_heads;
     const int qs = p.skip_q ? 0 : qh;                    // query slots this launch handles
@@ -187,8 +196,11 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
             const int32_t p0 = s.pos[r], p1 = s.pos[(size_t)s.rows + r], p2 = s.pos[(size_t)2 * s.rows + r];
             const int ax = p.axis[lane];
             const float ang = __fmul_rn((float)(ax == 0 ? p0 : ax == 1 ? p1 : p2), p.inv_freq[lane]);
-            float sn, cs;
-            sincosf(ang, &sn, &cs);
+            // cosf / sinf of the fp32 angle (qwasar_cpu.c:312-315), correctly rounded: the double
+            // functions are exact far beyond float precision, so one rounding gives the float result
+            double snd, csd;
+            sincos((double)ang, &snd, &csd);
+            const float sn = (float)snd, cs = (float)csd;
             cs_s[warp][lane] = cs; cs_s[warp][32 + lane] = sn;
             if (s.cs_out && slot0 <= qs && qs < slot0 + 8) {          // the block with key head 0 publishes the table
                 s.cs_out[(size_t)r * 64 + lane] = cs; s.cs_out[(size_t)r * 64 + 32 + lane] = sn;
@@ -220,9 +232,27 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
         if (is_q || is_k) {
             // RMS norm (qwasar_cpu.c:68-82), then the weight
             float ss = 0.0f;
+            if (is_k) {
+                // key rows: the squares are added left to right over the 256 dims like the CPU loop --
+                // lane l continues the sum of lane l - 1 with its own eight
+                float sq[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
-            ss = warp_sum(ss);
+                for (int i = 0; i < 8; i++) sq[i] = __fmul_rn(x[i], x[i]);
+#pragma unroll 1
+                for (int st = 0; st < 32; st++) {
+                    const float carry = __shfl_sync(0xffffffffu, ss, (st + 31) & 31);
+                    if (lane == st) {
+                        ss = st ? carry : 0.0f;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, sq[i]);
+                    }
+                }
+                ss = __shfl_sync(0xffffffffu, ss, 31);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
+                ss = warp_sum(ss);
+            }
             const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -293,8 +323,15 @@ void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, in
 void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
     const int slots = (p.skip_q ? 0 : p.q_heads) + 2 * p.kv_heads;
     if (slots == 0) return;
-    dim3 grid((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
-    preop_kernel<<<grid, 256, 0, s>>>(p);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = cudaLaunchConfig_t();
+    cfg.gridDim = dim3((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, preop_kernel, p);
     g_launches++;
 }
 

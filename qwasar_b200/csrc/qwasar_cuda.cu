@@ -28,9 +28,10 @@ using namespace qw;
 // ---------------------------------------------------------------------------------------
 namespace {
 
-enum BufKind { BUF_SHARED, BUF_DEVICE, BUF_ARENA };
+enum BufKind { BUF_SHARED, BUF_DEVICE, BUF_ARENA, BUF_POOL };
 
 struct Arena;
+struct Pool;
 
 }  // namespace
 
@@ -41,6 +42,8 @@ struct qw_buf_s {
     void *dev;           // device side (shared mirror, device buffer, or arena pool)
     bool own_host, own_dev, registered;
     Arena *arena;
+    Pool *pool = nullptr;   // BUF_POOL: the page pool this handle stands for
+    int device = 0;      // the CUDA device the buffer lives on
 };
 
 namespace {
@@ -58,6 +61,8 @@ struct KTime { cudaEvent_t t0, t1; const char *kernel; };
 
 struct qw_cmd_s {
     cudaStream_t stream;
+    int device = 0;                 // the CUDA device of the stream; ops switch to it before they launch
+    int status_slot = 0;            // this command buffer's kernel status word (slot 0 is shared when all are taken)
     bool own_stream;
     bool failed;
     char err[256];
@@ -83,13 +88,19 @@ typedef CUresult (*PFN_memUnmap)(CUdeviceptr, size_t);
 typedef CUresult (*PFN_memSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc *, size_t);
 typedef CUresult (*PFN_memGetGranularity)(size_t *, const CUmemAllocationProp *, CUmemAllocationGranularity_flags);
 
+// One of these per CUDA device (qw_gpu_init brings up the current device, qw_gpu_init_multi
+// several); G is the state of the device that is current for this library.
+constexpr int MAX_DEVICES = 16;
+constexpr int STATUS_SLOTS = 64, STATUS_STRIDE = 16;     // status words, 64 bytes apart
 struct Globals {
     bool up = false;
     int device = 0;
+    int sms = 0;
     cudaDeviceProp prop;
     char name[300] = "";
-    int *status_host = nullptr;    // pinned + mapped: kernels record a status code here
+    int *status_host = nullptr;    // pinned + mapped: kernels record a status code in their command buffer's word
     int *status_dev = nullptr;
+    uint64_t status_used = 1;      // bit i: slot i belongs to a live command buffer (slot 0: the shared one)
     PFN_encodeTiled encodeTiled = nullptr;
     PFN_memAddressReserve memAddressReserve = nullptr;
     PFN_memAddressFree memAddressFree = nullptr;
@@ -103,20 +114,36 @@ struct Globals {
     std::vector<cudaStream_t> stream_pool;    // streams of freed command buffers, reused
     cudaStream_t copy_stream = nullptr;       // first-touch uploads of shared buffers, see dev_range
     std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows * 128 + box rows) -> map
+};
+Globals g_devs[MAX_DEVICES];
+Globals *g_cur = &g_devs[0];
+#define G (*g_cur)
+
+// Process-wide: the last error of a call without a command buffer, and the profiling tables.
+struct Shared {
     char last_error[256] = "";
     bool has_error = false;
     int prof = -1;
     std::map<std::string, std::pair<double, long>> prof_ms;
     bool time_kernels = false;
     std::map<std::string, std::pair<double, long long>> kernel_ms;
-} G;
+} SH;
+
+// Makes `dev` the current device of this library and of the calling thread.
+void use_device(int dev) {
+    if (dev < 0 || dev >= MAX_DEVICES || g_cur == &g_devs[dev]) return;
+    cudaSetDevice(dev);
+    g_cur = &g_devs[dev];
+}
+
+int *cmd_status(qw_cmd c) { return G.status_dev + (size_t)c->status_slot * STATUS_STRIDE; }
 
 void set_error(const char *fmt, ...) {
     va_list ap;
     va_start(ap, fmt);
-    vsnprintf(G.last_error, sizeof G.last_error, fmt, ap);
+    vsnprintf(SH.last_error, sizeof SH.last_error, fmt, ap);
     va_end(ap);
-    G.has_error = true;
+    SH.has_error = true;
 }
 
 void cmd_fail(qw_cmd c, const char *fmt, ...) {
@@ -151,6 +178,7 @@ const char *status_text(int code) {
         case QW_ST_MMA_TIMEOUT: return "kernel gave up waiting for a tensor-core commit";
         case QW_ST_BAD_PAGE: return "attention reached a cache position whose page was never mapped";
         case QW_ST_BAD_SMEM: return "the prefill kernel's shared-memory window was not 1024-byte aligned";
+        case QW_ST_PEER_TIMEOUT: return "the partial of another GPU did not arrive within the exchange's time limit";
         default: return "unknown kernel status";
     }
 }
@@ -162,22 +190,31 @@ constexpr size_t PAGE_BYTES = (size_t)QW_PAGE_TOKENS * QW_HEAD_DIM * 2;   // 32 
 constexpr size_t CHUNK_BYTES = (size_t)64 << 20;                           // physical growth step
 constexpr int PAGES_PER_CHUNK = (int)(CHUNK_BYTES / PAGE_BYTES);
 
-struct Arena {
-    int n_layers, kv_heads, max_ctx, head_dim;
-    int pages_per_head;
-    int64_t max_pages;
+// A pool is a reserved range of device addresses that fills with 32 KB pages as tokens arrive;
+// arenas (one per cache buffer of the reference) draw their pages from a pool.  Arenas that share
+// a pool share its tensor maps, so one attention launch can carry any number of their sequences.
+struct Pool {
+    int device;
     bool vmm;
     CUdeviceptr va;
     size_t va_size;
     std::vector<CUmemGenericAllocationHandle> chunks;
+    int64_t max_pages;
     int64_t mapped_pages;                 // pool pages backed by physical memory
-    std::vector<int32_t> table_host;      // [n_layers, kv_heads, pages_per_head], -1 = unmapped
-    int32_t *table_dev;
     std::vector<int32_t> free_pages;
-    int64_t in_use;
     uint32_t shuffle;
+    int refs;                             // arenas (and the pool's own handle) that keep it alive
     CUtensorMap map;                      // 32-row boxes (split-KV kernel)
     CUtensorMap map64;                    // 64-row boxes (prefill kernel)
+};
+struct Arena {
+    Pool *pool;
+    int n_layers, kv_heads, max_ctx, head_dim;
+    int pages_per_head;
+    int64_t max_pages;
+    std::vector<int32_t> table_host;      // [n_layers, kv_heads, pages_per_head], -1 = unmapped
+    int32_t *table_dev;
+    int64_t in_use;
 };
 
 bool encode_rows_map(CUtensorMap *m, void *base, uint64_t rows, uint32_t box_rows) {
@@ -206,15 +243,15 @@ bool encode_tile_map(CUtensorMap *m, const void *base, int dtype, uint64_t row_e
     return true;
 }
 
-bool arena_grow(Arena *a, cudaStream_t stream) {
-    if (a->mapped_pages >= a->max_pages) return false;
+bool pool_grow(Pool *a) {
+    if (a->mapped_pages >= a->max_pages) { set_error("page pool exhausted (%lld pages)", (long long)a->max_pages); return false; }
     const int64_t first = a->mapped_pages;
     const int64_t n = std::min<int64_t>(PAGES_PER_CHUNK, a->max_pages - first);
     if (a->vmm) {
         CUmemAllocationProp prop = {};
         prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
         prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-        prop.location.id = G.device;
+        prop.location.id = a->device;
         CUmemGenericAllocationHandle h;
         // the reserved range is a whole number of chunks, so a full chunk is always mapped
         if (G.memCreate(&h, CHUNK_BYTES, &prop, 0) != CUDA_SUCCESS) { set_error("arena: out of device memory"); return false; }
@@ -227,8 +264,14 @@ bool arena_grow(Arena *a, cudaStream_t stream) {
             G.memUnmap(at, CHUNK_BYTES); G.memRelease(h); set_error("arena: cuMemSetAccess failed"); return false;
         }
         a->chunks.push_back(h);
-        // zeroed in the order of the stream whose kernels will write the new pages
-        cudaMemsetAsync(reinterpret_cast<void *>(at), 0, CHUNK_BYTES, stream);
+        // The new pages start as zeros, and the fill has finished before any stream can be handed
+        // one of them: command streams do not order with one another, so a fill left pending on one
+        // stream could land on rows that another stream has already appended.  Growth is rare
+        // (64 MB steps), so the wait costs nothing that matters.
+        if (cudaMemset(reinterpret_cast<void *>(at), 0, CHUNK_BYTES) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+            set_error("arena: clearing a new chunk failed");
+            return false;
+        }
     }
     // hand the new pages to the free list, permuted when asked to
     std::vector<int32_t> ids((size_t)n);
@@ -253,14 +296,15 @@ bool arena_ensure(Arena *a, int layer, int first_token, int n_tokens, cudaStream
     const int need = (n_tokens + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
     const int first_page = std::max(first_token, 0) / QW_PAGE_TOKENS;
     if (need > a->pages_per_head) { set_error("arena: %d tokens exceed max_ctx %d", n_tokens, a->max_ctx); return false; }
+    Pool *pl = a->pool;
     for (int h = 0; h < a->kv_heads; h++) {
         int32_t *row = a->table_host.data() + ((size_t)layer * a->kv_heads + h) * a->pages_per_head;
         int first_new = -1, last_new = -1;
         for (int pg = first_page; pg < need; pg++) {
             if (row[pg] >= 0) continue;
-            if (a->free_pages.empty() && !arena_grow(a, stream)) return false;
-            row[pg] = a->free_pages.back();
-            a->free_pages.pop_back();
+            if (pl->free_pages.empty() && !pool_grow(pl)) return false;
+            row[pg] = pl->free_pages.back();
+            pl->free_pages.pop_back();
             a->in_use++;
             if (first_new < 0) first_new = pg;
             last_new = pg;
@@ -279,19 +323,64 @@ bool arena_ensure(Arena *a, int layer, int first_token, int n_tokens, cudaStream
     return true;
 }
 
+void pool_release(Pool *pl) {
+    if (!pl || --pl->refs > 0) return;
+    use_device(pl->device);
+    cudaDeviceSynchronize();
+    if (pl->vmm) {
+        for (size_t i = 0; i < pl->chunks.size(); i++) {
+            G.memUnmap(pl->va + i * CHUNK_BYTES, CHUNK_BYTES);
+            G.memRelease(pl->chunks[i]);
+        }
+        if (pl->va) G.memAddressFree(pl->va, pl->va_size);
+    } else if (pl->va) {
+        cudaFree(reinterpret_cast<void *>(pl->va));
+    }
+    delete pl;
+}
+
+// A pool able to hold max_bytes of pages (rounded up to whole 64 MB chunks); nothing is committed yet.
+Pool *pool_create(size_t max_bytes, uint32_t shuffle) {
+    Pool *pl = new Pool();
+    pl->device = G.device;
+    const size_t n_chunks = std::max<size_t>(1, (max_bytes + CHUNK_BYTES - 1) / CHUNK_BYTES);
+    pl->va_size = n_chunks * CHUNK_BYTES;
+    pl->max_pages = (int64_t)(pl->va_size / PAGE_BYTES);
+    pl->mapped_pages = 0; pl->shuffle = shuffle; pl->refs = 1; pl->va = 0; pl->vmm = false;
+    if (G.memAddressReserve) {
+        CUmemAllocationProp prop = {};
+        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        prop.location.id = G.device;
+        size_t gran = 0;
+        if (G.memGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) == CUDA_SUCCESS && gran && CHUNK_BYTES % gran == 0 &&
+            G.memAddressReserve(&pl->va, pl->va_size, CHUNK_BYTES, 0, 0) == CUDA_SUCCESS)
+            pl->vmm = true;
+    }
+    if (!pl->vmm) {
+        // no virtual-memory management on this platform: the pool is allocated whole
+        void *p = nullptr;
+        if (cudaMalloc(&p, pl->va_size) != cudaSuccess) { set_error("arena: cannot allocate %zu bytes", pl->va_size); delete pl; cudaGetLastError(); return nullptr; }
+        cudaMemset(p, 0, pl->va_size);
+        cudaDeviceSynchronize();
+        pl->va = (CUdeviceptr)p;
+        pl->mapped_pages = 0;             // pages still enter the free list chunk by chunk (pool_grow)
+    }
+    // the tensor maps span the whole reserved range; rows of unmapped pages are never addressed
+    if (!encode_rows_map(&pl->map, reinterpret_cast<void *>(pl->va), (uint64_t)(pl->va_size / 512), 32) ||
+        !encode_rows_map(&pl->map64, reinterpret_cast<void *>(pl->va), (uint64_t)(pl->va_size / 512), 64)) { pool_release(pl); return nullptr; }
+    return pl;
+}
+
 void arena_destroy(Arena *a) {
     if (!a) return;
+    use_device(a->pool->device);
     cudaDeviceSynchronize();
-    if (a->vmm) {
-        for (size_t i = 0; i < a->chunks.size(); i++) {
-            G.memUnmap(a->va + i * CHUNK_BYTES, CHUNK_BYTES);
-            G.memRelease(a->chunks[i]);
-        }
-        if (a->va) G.memAddressFree(a->va, a->va_size);
-    } else if (a->va) {
-        cudaFree(reinterpret_cast<void *>(a->va));
-    }
+    // the arena's pages go back to its pool (they keep their contents: an arena that is handed a
+    // recycled page owns every row of it only after it has appended that row)
+    for (int32_t id : a->table_host) if (id >= 0) a->pool->free_pages.push_back(id);
     if (a->table_dev) cudaFree(a->table_dev);
+    pool_release(a->pool);
     delete a;
 }
 
@@ -307,7 +396,7 @@ void arena_destroy(Arena *a) {
 void *dev_range(qw_cmd c, qw_ref r, size_t bytes, bool write, size_t align = 16) {
     qw_buf b = r.buf;
     if (!b) return nullptr;
-    if (b->kind == BUF_ARENA) { cmd_fail(c, "an arena can only be a cache operand"); return nullptr; }
+    if (b->kind == BUF_ARENA || b->kind == BUF_POOL) { cmd_fail(c, "an arena can only be a cache operand"); return nullptr; }
     if (r.off + bytes > b->len) { cmd_fail(c, "operand [%zu, %zu) exceeds its buffer (%zu bytes)", r.off, r.off + bytes, b->len); return nullptr; }
     if ((reinterpret_cast<uintptr_t>(b->dev) + r.off) & (align - 1)) {
         cmd_fail(c, "operand at byte offset %zu of its buffer is not %zu-byte aligned", r.off, align);
@@ -385,6 +474,7 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
                    int64_t *map_rows = nullptr, int32_t first_token = 0) {
     qw_buf b = ref.buf;
     if (!b) { cmd_fail(c, "cache operand is null"); return false; }
+    if (b->kind == BUF_POOL) { cmd_fail(c, "a page pool is not a cache: allocate an arena in it"); return false; }
     const size_t layer_bytes = (size_t)kv_heads * max_ctx * head_dim * 2;
     if (b->kind == BUF_ARENA) {
         Arena *a = b->arena;
@@ -396,13 +486,13 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
         if (ref.off % layer_bytes) { cmd_fail(c, "arena offset %zu is not a layer boundary", ref.off); return false; }
         const int layer = (int)(ref.off / layer_bytes);
         if (layer >= a->n_layers) { cmd_fail(c, "arena layer %d out of range", layer); return false; }
-        if (append && !arena_ensure(a, layer, first_token, n_tokens, c->stream)) { cmd_fail(c, "%s", G.last_error); return false; }
-        out->base = reinterpret_cast<__nv_bfloat16 *>(a->va);
+        if (append && !arena_ensure(a, layer, first_token, n_tokens, c->stream)) { cmd_fail(c, "%s", SH.last_error); return false; }
+        out->base = reinterpret_cast<__nv_bfloat16 *>(a->pool->va);
         out->table = a->table_dev + (size_t)layer * a->kv_heads * a->pages_per_head;
         out->pt_stride = a->pages_per_head;
         out->max_ctx = max_ctx;
-        if (map) *map = box_rows == 64 ? a->map64 : a->map;
-        if (map_rows) *map_rows = (int64_t)(a->va_size / 512);
+        if (map) *map = box_rows == 64 ? a->pool->map64 : a->pool->map;
+        if (map_rows) *map_rows = (int64_t)(a->pool->va_size / 512);
         return true;
     }
     void *d = dev_range(c, ref, layer_bytes, will_write);
@@ -418,7 +508,7 @@ bool resolve_cache(qw_cmd c, qw_ref ref, int32_t kv_heads, int32_t max_ctx, int3
         auto it = G.map_cache.find(key);
         if (it == G.map_cache.end()) {
             CUtensorMap m;
-            if (!encode_rows_map(&m, d, rows, box_rows)) { cmd_fail(c, "%s", G.last_error); return false; }
+            if (!encode_rows_map(&m, d, rows, box_rows)) { cmd_fail(c, "%s", SH.last_error); return false; }
             it = G.map_cache.emplace(key, m).first;
         }
         *map = it->second;
@@ -453,14 +543,14 @@ bool launch_split_merge(qw_cmd c, AttnParams &p, int max_rows, float *scr) {
     const size_t n_part_rows = (size_t)attn_split_slots(p) * mt16 + rows_total * p.q_heads;
     p.pacc = scr;
     p.pstat = scr + n_part_rows * 256;
-    p.status = G.status_dev;
+    p.status = cmd_status(c);
     KTime kt = {nullptr, nullptr, "qw_attn_split"};
-    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    const bool timed = SH.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
     launch_attn_split(c->stream, p, max_rows);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
     // a group is written directly only when one CTA's share covers it whole
-    if (p.mode == 1 || attn_split_needs_merge(p)) launch_attn_merge(c->stream, p, max_rows);
+    if (p.mode != 0 || attn_split_needs_merge(p)) launch_attn_merge(c->stream, p, max_rows);
     return cuda_ok(c, cudaGetLastError(), "attention launch");
 }
 
@@ -472,6 +562,50 @@ bool run_split(qw_cmd c, AttnParams &p, int max_rows) {
     if (!scr) return false;
     return launch_split_merge(c, p, max_rows, scr);
 }
+
+// Collects sequences (or row chunks) for split-KV launches: one launch carries up to QW_MAX_SEQ of
+// them over up to QW_MAX_MAPS distinct cache tensor maps (arenas of one pool share one map, plain
+// cache buffers have one each); a sequence that does not fit starts the next launch.
+struct SplitBatch {
+    qw_cmd c;
+    AttnParams p;
+    int n = 0, n_maps = 0, max_rows = 0;
+    bool early_next = false;       // the next launch goes directly behind this node's K/V append kernel
+
+    int map_slot(const CUtensorMap &m) {
+        for (int i = 0; i < n_maps; i++)
+            if (!memcmp(&p.maps[i], &m, sizeof m)) return i;
+        if (n_maps == QW_MAX_MAPS) return -1;
+        p.maps[n_maps] = m;
+        return n_maps++;
+    }
+    bool flush() {
+        if (!n) return true;
+        p.n_seq = n;
+        p.early = early_next ? 1 : 0;
+        early_next = false;
+        const bool ok = run_split(c, p, max_rows);
+        n = 0; n_maps = 0; max_rows = 0;
+        return ok;
+    }
+    bool add(const AttnSeq &sq, const CUtensorMap &km, const CUtensorMap &vm) {
+        for (int attempt = 0; attempt < 2; attempt++) {
+            const int saved = n_maps;
+            const int k = n < QW_MAX_SEQ ? map_slot(km) : -1;
+            const int v = k >= 0 ? map_slot(vm) : -1;
+            if (k >= 0 && v >= 0) {
+                p.seq[n] = sq;
+                p.seq[n].kmap = (uint8_t)k; p.seq[n].vmap = (uint8_t)v;
+                max_rows = std::max(max_rows, sq.rows);
+                n++;
+                return true;
+            }
+            n_maps = saved;
+            if (!flush()) return false;
+        }
+        return false;
+    }
+};
 
 // The tcgen05 prefill kernel over one sequence: q_bf16 is [rows, q_heads, 256] in device memory.
 // With cs_table != nullptr, q_bf16 is instead the raw [rows, q_heads, 512] bf16 [q|gate] input: the kernel
@@ -492,7 +626,7 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
     p.n_q_tiles = (rows + 127) / 128;
     p.oob_row = (int32_t)std::min<int64_t>(std::max(k_rows, v_rows), 0x7fffffff);
     p.scale = scale;
-    p.status = G.status_dev;
+    p.status = cmd_status(c);
     const uint64_t row = (uint64_t)q_heads * 256;
     p.fuse_q = cs_table != nullptr; p.q_norm_w = q_norm_w; p.eps = eps;
     if (p.fuse_q && !encode_tile_map(&p.csmap, cs_table, DT_F32, 64, 64, rows)) return cmd_fail(c, "%s", "prefill: tensor map encoding failed"), false;
@@ -501,68 +635,148 @@ bool run_prefill(qw_cmd c, const __nv_bfloat16 *q_bf16, void *out, int out_dtype
         (gate && !encode_tile_map(&p.gmap, gate, gate_dtype, (uint64_t)(q_heads - 1) * gate_stride + 256, (uint64_t)q_heads * gate_stride, rows)))
         return cmd_fail(c, "%s", "prefill: tensor map encoding failed"), false;
     KTime kt = {nullptr, nullptr, "qw_attn_prefill"};
-    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    const bool timed = SH.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
     launch_attn_prefill(c->stream, p);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
     return cuda_ok(c, cudaGetLastError(), "prefill launch");
 }
 
-bool live(qw_cmd c) { return G.up && c && !c->failed; }
+// An op may encode on c: the backend is up and c has not failed.  The command buffer's device
+// becomes the current one (a host that drives several GPUs alternates between their command buffers).
+bool live(qw_cmd c) {
+    if (!c || c->failed || !g_devs[c->device].up) return false;
+    use_device(c->device);
+    return true;
+}
+
 
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
 // lifecycle
 // ---------------------------------------------------------------------------------------
-extern "C" bool qw_gpu_init(char *err, size_t errcap) {
-    if (G.up) return true;
+// Brings up CUDA device `dev` (made current) as g_devs[dev].
+static bool init_device(int dev, char *err, size_t errcap) {
     auto fail = [&](const char *fmt, const char *arg) {
         if (err && errcap) snprintf(err, errcap, fmt, arg);
         set_error(fmt, arg);
         return false;
     };
-    int n = 0;
-    cudaError_t e = cudaGetDeviceCount(&n);
-    if (e != cudaSuccess || n == 0) return fail("no CUDA device: %s", e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0");
-    if (cudaGetDevice(&G.device) != cudaSuccess) return fail("%s", "cudaGetDevice failed");
-    if (cudaGetDeviceProperties(&G.prop, G.device) != cudaSuccess) return fail("%s", "cudaGetDeviceProperties failed");
-    if (G.prop.major != 10) return fail("device %s is not compute capability 10.x (this backend is sm_100a only)", G.prop.name);
-    snprintf(G.name, sizeof G.name, "%s", G.prop.name);
-    if (!entry("cuTensorMapEncodeTiled", &G.encodeTiled)) return fail("%s", "driver lacks cuTensorMapEncodeTiled");
-    const bool vmm = entry("cuMemAddressReserve", &G.memAddressReserve) && entry("cuMemAddressFree", &G.memAddressFree) &&
-                     entry("cuMemCreate", &G.memCreate) && entry("cuMemRelease", &G.memRelease) &&
-                     entry("cuMemMap", &G.memMap) && entry("cuMemUnmap", &G.memUnmap) &&
-                     entry("cuMemSetAccess", &G.memSetAccess) && entry("cuMemGetAllocationGranularity", &G.memGetGranularity);
-    if (!vmm) G.memAddressReserve = nullptr;
-    if (cudaHostAlloc((void **)&G.status_host, 64, cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer((void **)&G.status_dev, G.status_host, 0) != cudaSuccess)
-        return fail("%s", "cannot allocate the status word");
-    memset(G.status_host, 0, 64);
-    if (cudaStreamCreateWithFlags(&G.copy_stream, cudaStreamNonBlocking) != cudaSuccess) G.copy_stream = nullptr;
-    G.up = true;
-    G.has_error = false;
+    if (dev < 0 || dev >= MAX_DEVICES) return fail("%s", "device index out of range");
+    if (cudaSetDevice(dev) != cudaSuccess) return fail("%s", "cudaSetDevice failed");
+    Globals &g = g_devs[dev];
+    g_cur = &g;
+    if (g.up) return true;
+    g.device = dev;
+    if (cudaGetDeviceProperties(&g.prop, dev) != cudaSuccess) return fail("%s", "cudaGetDeviceProperties failed");
+    if (g.prop.major != 10) return fail("device %s is not compute capability 10.x (this backend is sm_100a only)", g.prop.name);
+    snprintf(g.name, sizeof g.name, "%s", g.prop.name);
+    g.sms = g.prop.multiProcessorCount > 0 ? g.prop.multiProcessorCount : 148;
+    if (!entry("cuTensorMapEncodeTiled", &g.encodeTiled)) return fail("%s", "driver lacks cuTensorMapEncodeTiled");
+    const bool vmm = entry("cuMemAddressReserve", &g.memAddressReserve) && entry("cuMemAddressFree", &g.memAddressFree) &&
+                     entry("cuMemCreate", &g.memCreate) && entry("cuMemRelease", &g.memRelease) &&
+                     entry("cuMemMap", &g.memMap) && entry("cuMemUnmap", &g.memUnmap) &&
+                     entry("cuMemSetAccess", &g.memSetAccess) && entry("cuMemGetAllocationGranularity", &g.memGetGranularity);
+    if (!vmm) g.memAddressReserve = nullptr;
+    const size_t st_bytes = (size_t)STATUS_SLOTS * STATUS_STRIDE * sizeof(int);
+    if (cudaHostAlloc((void **)&g.status_host, st_bytes, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer((void **)&g.status_dev, g.status_host, 0) != cudaSuccess)
+        return fail("%s", "cannot allocate the status words");
+    memset(g.status_host, 0, st_bytes);
+    g.status_used = 1;
+    if (cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking) != cudaSuccess) g.copy_stream = nullptr;
+    g.up = true;
     return true;
 }
 
+extern "C" bool qw_gpu_init(char *err, size_t errcap) {
+    if (G.up) return true;
+    int n = 0, dev = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        const char *why = e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0";
+        if (err && errcap) snprintf(err, errcap, "no CUDA device: %s", why);
+        set_error("no CUDA device: %s", why);
+        return false;
+    }
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        if (err && errcap) snprintf(err, errcap, "cudaGetDevice failed");
+        set_error("cudaGetDevice failed");
+        return false;
+    }
+    if (!init_device(dev, err, errcap)) return false;
+    SH.has_error = false;
+    return true;
+}
+
+extern "C" int32_t qw_gpu_device_count(void) {
+    int n = 0;
+    return cudaGetDeviceCount(&n) == cudaSuccess ? n : 0;
+}
+
+// Devices 0 .. n_dev-1 of this process, each able to read and write the others' memory (the
+// exchange of partials stores straight into a peer's buffer).  Device 0 is current afterwards.
+extern "C" bool qw_gpu_init_multi(int32_t n_dev, char *err, size_t errcap) {
+    const int have = qw_gpu_device_count();
+    if (n_dev <= 0 || n_dev > have || n_dev > MAX_DEVICES) {
+        if (err && errcap) snprintf(err, errcap, "%d devices asked for, %d present (at most %d)", n_dev, have, MAX_DEVICES);
+        set_error("%d devices asked for, %d present", n_dev, have);
+        return false;
+    }
+    for (int d = 0; d < n_dev; d++)
+        if (!init_device(d, err, errcap)) return false;
+    for (int d = 0; d < n_dev; d++) {
+        cudaSetDevice(d);
+        for (int o = 0; o < n_dev; o++) {
+            if (o == d) continue;
+            int can = 0;
+            cudaDeviceCanAccessPeer(&can, d, o);
+            cudaError_t e = can ? cudaDeviceEnablePeerAccess(o, 0) : cudaErrorPeerAccessUnsupported;
+            if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+            if (e != cudaSuccess) {
+                if (err && errcap) snprintf(err, errcap, "device %d cannot reach device %d: %s", d, o, cudaGetErrorString(e));
+                set_error("device %d cannot reach device %d: %s", d, o, cudaGetErrorString(e));
+                cudaGetLastError();
+                return false;
+            }
+        }
+    }
+    cudaSetDevice(0);
+    g_cur = &g_devs[0];
+    SH.has_error = false;
+    return true;
+}
+
+extern "C" bool qw_gpu_select(int32_t dev) {
+    if (dev < 0 || dev >= MAX_DEVICES || !g_devs[dev].up) { set_error("qw_gpu_select: device %d was not initialised", dev); return false; }
+    use_device(dev);
+    return true;
+}
+extern "C" int32_t qw_gpu_current(void) { return G.up ? G.device : -1; }
+
 extern "C" void qw_gpu_shutdown(void) {
-    if (!G.up) return;
-    cudaDeviceSynchronize();
-    for (auto &s : G.scratch_pool) cudaFree(s.p);
-    G.scratch_pool.clear();
-    for (auto &st : G.stream_pool) cudaStreamDestroy(st);
-    G.stream_pool.clear();
-    if (G.copy_stream) { cudaStreamDestroy(G.copy_stream); G.copy_stream = nullptr; }
-    G.map_cache.clear();
-    if (G.status_host) cudaFreeHost(G.status_host);
-    G.status_host = G.status_dev = nullptr;
-    G.up = false;
+    for (int d = 0; d < MAX_DEVICES; d++) {
+        Globals &g = g_devs[d];
+        if (!g.up) continue;
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+        for (auto &s : g.scratch_pool) cudaFree(s.p);
+        g.scratch_pool.clear();
+        for (auto &st : g.stream_pool) cudaStreamDestroy(st);
+        g.stream_pool.clear();
+        if (g.copy_stream) { cudaStreamDestroy(g.copy_stream); g.copy_stream = nullptr; }
+        g.map_cache.clear();
+        if (g.status_host) cudaFreeHost(g.status_host);
+        g.status_host = g.status_dev = nullptr;
+        g.up = false;
+    }
 }
 
 extern "C" const char *qw_gpu_name(void) { return G.up ? G.name : "(no device)"; }
 extern "C" uint64_t qw_gpu_working_set_limit(void) { return G.up ? (uint64_t)G.prop.totalGlobalMem : 0; }
 extern "C" uint64_t qw_gpu_max_buffer_length(void) { return G.up ? (uint64_t)G.prop.totalGlobalMem : 0; }
-extern "C" const char *qw_gpu_last_error(void) { return G.has_error ? G.last_error : nullptr; }
+extern "C" const char *qw_gpu_last_error(void) { return SH.has_error ? SH.last_error : nullptr; }
 extern "C" int32_t qw_gpu_sm_count(void) { return G.up ? sm_count() : 0; }
 extern "C" uint64_t qw_gpu_launch_count(void) { return (uint64_t)qw::g_launches; }
 extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
@@ -591,13 +805,13 @@ extern "C" int32_t qw_attn_split_plan(int32_t n_seq, int32_t kv_heads, const int
     if (needs_merge) *needs_merge = attn_split_needs_merge(p) ? 1 : 0;
     return p.n_cta;
 }
-extern "C" void qw_prof_kernels(bool on) { G.time_kernels = on; }
+extern "C" void qw_prof_kernels(bool on) { SH.time_kernels = on; }
 extern "C" bool qw_prof_kernel_read(const char *kernel, double *ms_total, int64_t *launches, bool reset) {
-    auto it = G.kernel_ms.find(kernel ? kernel : "");
-    if (it == G.kernel_ms.end()) { if (ms_total) *ms_total = 0; if (launches) *launches = 0; return false; }
+    auto it = SH.kernel_ms.find(kernel ? kernel : "");
+    if (it == SH.kernel_ms.end()) { if (ms_total) *ms_total = 0; if (launches) *launches = 0; return false; }
     if (ms_total) *ms_total = it->second.first;
     if (launches) *launches = it->second.second;
-    if (reset) G.kernel_ms.erase(it);
+    if (reset) SH.kernel_ms.erase(it);
     return true;
 }
 
@@ -607,6 +821,7 @@ extern "C" bool qw_prof_kernel_read(const char *kernel, double *ms_total, int64_
 extern "C" qw_buf qw_buf_alloc(size_t len) {
     if (!G.up) { set_error("qw_buf_alloc before qw_gpu_init"); return nullptr; }
     qw_buf b = new qw_buf_s{BUF_SHARED, len, nullptr, nullptr, true, true, false, nullptr};
+    b->device = G.device;
     const size_t n = std::max<size_t>(len, 16);
     if (cudaHostAlloc(&b->host, n, cudaHostAllocDefault) != cudaSuccess || cudaMalloc(&b->dev, n) != cudaSuccess) {
         set_error("cannot allocate a %zu-byte shared buffer", len);
@@ -624,6 +839,7 @@ extern "C" qw_buf qw_buf_alloc(size_t len) {
 extern "C" qw_buf qw_buf_wrap(void *ptr, size_t len) {
     if (!G.up || !ptr) return nullptr;
     qw_buf b = new qw_buf_s{BUF_SHARED, len, ptr, nullptr, false, true, false, nullptr};
+    b->device = G.device;
     if (cudaMalloc(&b->dev, std::max<size_t>(len, 16)) != cudaSuccess) { set_error("cannot mirror a %zu-byte wrapped buffer", len); delete b; cudaGetLastError(); return nullptr; }
     if (cudaHostRegister(ptr, len, cudaHostRegisterDefault) == cudaSuccess) b->registered = true;
     else cudaGetLastError();   // pageable memory still works, copies are just staged
@@ -633,6 +849,7 @@ extern "C" qw_buf qw_buf_wrap(void *ptr, size_t len) {
 extern "C" qw_buf qw_buf_alloc_device(size_t len) {
     if (!G.up) { set_error("qw_buf_alloc_device before qw_gpu_init"); return nullptr; }
     qw_buf b = new qw_buf_s{BUF_DEVICE, len, nullptr, nullptr, false, true, false, nullptr};
+    b->device = G.device;
     if (cudaMalloc(&b->dev, std::max<size_t>(len, 16)) != cudaSuccess) { set_error("cannot allocate %zu bytes of device memory", len); delete b; cudaGetLastError(); return nullptr; }
     cudaMemset(b->dev, 0, std::max<size_t>(len, 16));
     cudaStreamSynchronize(0);
@@ -641,14 +858,21 @@ extern "C" qw_buf qw_buf_alloc_device(size_t len) {
 
 extern "C" qw_buf qw_buf_wrap_device(void *device_ptr, size_t len) {
     if (!G.up || !device_ptr) return nullptr;
-    return new qw_buf_s{BUF_DEVICE, len, nullptr, device_ptr, false, false, false, nullptr};
+    qw_buf b = new qw_buf_s{BUF_DEVICE, len, nullptr, device_ptr, false, false, false, nullptr};
+    b->device = G.device;
+    return b;
 }
 
 extern "C" void qw_buf_free(qw_buf b) {
     if (!b) return;
     if (b->kind == BUF_ARENA) { arena_destroy(b->arena); delete b; return; }
-    cudaDeviceSynchronize();
-    G.map_cache.clear();
+    if (b->kind == BUF_POOL) { pool_release(b->pool); delete b; return; }      // the memory goes with its last arena
+    use_device(b->device);
+    // work that still uses the buffer must finish first; tensor maps built over it are dropped
+    if (b->own_dev || b->registered) cudaDeviceSynchronize();
+    const uintptr_t lo = (uintptr_t)b->dev, hi = lo + b->len;
+    for (auto it = G.map_cache.begin(); it != G.map_cache.end();)
+        it = (it->first.first >= lo && it->first.first < hi) ? G.map_cache.erase(it) : std::next(it);
     if (b->registered) cudaHostUnregister(b->host);
     if (b->own_host && b->host) cudaFreeHost(b->host);
     if (b->own_dev && b->dev) cudaFree(b->dev);
@@ -660,13 +884,15 @@ extern "C" size_t qw_buf_length(qw_buf b) { return b ? b->len : 0; }
 extern "C" void *qw_buf_device_ptr(qw_buf b) { return b ? b->dev : nullptr; }
 
 extern "C" bool qw_buf_upload(qw_buf b, size_t off, const void *src, size_t len) {
-    if (!b || b->kind == BUF_ARENA || off + len > b->len) { set_error("qw_buf_upload: bad range"); return false; }
+    if (!b || b->kind == BUF_ARENA || b->kind == BUF_POOL || off + len > b->len) { set_error("qw_buf_upload: bad range"); return false; }
+    use_device(b->device);
     if (b->kind == BUF_SHARED) memcpy((char *)b->host + off, src, len);
     if (cudaMemcpy((char *)b->dev + off, src, len, cudaMemcpyHostToDevice) != cudaSuccess) { set_error("qw_buf_upload: copy failed"); return false; }
     return true;
 }
 extern "C" bool qw_buf_download(qw_buf b, size_t off, void *dst, size_t len) {
-    if (!b || b->kind == BUF_ARENA || off + len > b->len) { set_error("qw_buf_download: bad range"); return false; }
+    if (!b || b->kind == BUF_ARENA || b->kind == BUF_POOL || off + len > b->len) { set_error("qw_buf_download: bad range"); return false; }
+    use_device(b->device);
     if (cudaMemcpy(dst, (char *)b->dev + off, len, cudaMemcpyDeviceToHost) != cudaSuccess) { set_error("qw_buf_download: copy failed"); return false; }
     return true;
 }
@@ -674,49 +900,56 @@ extern "C" bool qw_buf_download(qw_buf b, size_t off, void *dst, size_t len) {
 // ---------------------------------------------------------------------------------------
 // arena API
 // ---------------------------------------------------------------------------------------
-extern "C" qw_buf qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
-                                       uint32_t shuffle_seed) {
-    if (!G.up) { set_error("qw_kv_arena_alloc before qw_gpu_init"); return nullptr; }
+static qw_buf arena_new(Pool *pool, bool private_pool, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                        uint32_t shuffle_seed) {
     if (n_layers <= 0 || kv_heads <= 0 || max_ctx <= 0 || head_dim != QW_HEAD_DIM) { set_error("arena: unsupported shape"); return nullptr; }
     Arena *a = new Arena();
     a->n_layers = n_layers; a->kv_heads = kv_heads; a->max_ctx = max_ctx; a->head_dim = head_dim;
     a->pages_per_head = (max_ctx + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
     a->max_pages = (int64_t)n_layers * kv_heads * a->pages_per_head;
-    a->mapped_pages = 0; a->in_use = 0; a->shuffle = shuffle_seed; a->table_dev = nullptr; a->va = 0;
-    const size_t n_chunks = ((size_t)a->max_pages * PAGE_BYTES + CHUNK_BYTES - 1) / CHUNK_BYTES;
-    a->va_size = n_chunks * CHUNK_BYTES;
-    a->vmm = false;
-    if (G.memAddressReserve) {
-        CUmemAllocationProp prop = {};
-        prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
-        prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
-        prop.location.id = G.device;
-        size_t gran = 0;
-        if (G.memGetGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) == CUDA_SUCCESS && gran && CHUNK_BYTES % gran == 0 &&
-            G.memAddressReserve(&a->va, a->va_size, CHUNK_BYTES, 0, 0) == CUDA_SUCCESS)
-            a->vmm = true;
+    a->in_use = 0; a->table_dev = nullptr;
+    if (private_pool) {
+        pool = pool_create((size_t)a->max_pages * PAGE_BYTES, shuffle_seed);
+        if (!pool) { delete a; return nullptr; }
+    } else {
+        pool->refs++;
     }
-    if (!a->vmm) {
-        // no virtual-memory management on this platform: the pool is allocated whole
-        void *p = nullptr;
-        if (cudaMalloc(&p, a->va_size) != cudaSuccess) { set_error("arena: cannot allocate %zu bytes", a->va_size); delete a; cudaGetLastError(); return nullptr; }
-        cudaMemset(p, 0, a->va_size);
-        cudaStreamSynchronize(0);
-        a->va = (CUdeviceptr)p;
-    }
+    a->pool = pool;
     a->table_host.assign((size_t)a->max_pages, -1);
     if (cudaMalloc(&a->table_dev, (size_t)a->max_pages * sizeof(int32_t)) != cudaSuccess) { set_error("arena: cannot allocate the page table"); arena_destroy(a); cudaGetLastError(); return nullptr; }
     cudaMemset(a->table_dev, 0xff, (size_t)a->max_pages * sizeof(int32_t));
     cudaStreamSynchronize(0);   // the fill must not trail kernels launched on other streams
-    // the tensor map spans the whole reserved range; rows of unmapped pages are never addressed
-    if (!encode_rows_map(&a->map, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 32) ||
-        !encode_rows_map(&a->map64, reinterpret_cast<void *>(a->va), (uint64_t)(a->va_size / 512), 64)) { arena_destroy(a); return nullptr; }
     qw_buf b = new qw_buf_s{BUF_ARENA, (size_t)n_layers * kv_heads * max_ctx * head_dim * 2, nullptr,
-                            reinterpret_cast<void *>(a->va), false, false, false, a};
+                            reinterpret_cast<void *>(pool->va), false, false, false, a};
+    b->device = G.device;
     return b;
+}
+extern "C" qw_buf qw_kv_arena_alloc_ex(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
+                                       uint32_t shuffle_seed) {
+    if (!G.up) { set_error("qw_kv_arena_alloc before qw_gpu_init"); return nullptr; }
+    return arena_new(nullptr, true, n_layers, kv_heads, max_ctx, head_dim, shuffle_seed);
 }
 extern "C" qw_buf qw_kv_arena_alloc(int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
     return qw_kv_arena_alloc_ex(n_layers, kv_heads, max_ctx, head_dim, 0);
+}
+extern "C" qw_buf qw_kv_pool_alloc(size_t max_bytes, uint32_t shuffle_seed) {
+    if (!G.up) { set_error("qw_kv_pool_alloc before qw_gpu_init"); return nullptr; }
+    if (!max_bytes) { set_error("qw_kv_pool_alloc: empty pool"); return nullptr; }
+    Pool *pl = pool_create(max_bytes, shuffle_seed);
+    if (!pl) return nullptr;
+    qw_buf b = new qw_buf_s{BUF_POOL, pl->va_size, nullptr, reinterpret_cast<void *>(pl->va), false, false, false, nullptr};
+    b->pool = pl;
+    b->device = G.device;
+    return b;
+}
+extern "C" qw_buf qw_kv_arena_alloc_in(qw_buf pool, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim) {
+    if (!pool || pool->kind != BUF_POOL) { set_error("qw_kv_arena_alloc_in: not a pool"); return nullptr; }
+    use_device(pool->device);
+    return arena_new(pool->pool, false, n_layers, kv_heads, max_ctx, head_dim, 0);
+}
+extern "C" int64_t qw_kv_pool_bytes_committed(qw_buf pool) {
+    if (!pool || pool->kind != BUF_POOL) return -1;
+    return pool->pool->vmm ? (int64_t)(pool->pool->chunks.size() * CHUNK_BYTES) : (int64_t)pool->pool->va_size;
 }
 
 static bool kv_rw(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32_t n, void *host, bool store,
@@ -729,6 +962,7 @@ static bool kv_rw(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32
     if (cache->kind == BUF_ARENA) {
         Arena *a = cache->arena;
         if (a->kv_heads != kv_heads || a->max_ctx != max_ctx || layer < 0 || layer >= a->n_layers) { set_error("qw_kv_read/store: shape differs from the arena's"); return false; }
+        use_device(cache->device);
         if (store && !arena_ensure(a, layer, pos0, pos0 + n, 0)) return false;
         const int32_t *tab = a->table_host.data() + ((size_t)layer * a->kv_heads + head) * a->pages_per_head;
         int t = pos0;
@@ -740,7 +974,7 @@ static bool kv_rw(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int32
                 if (store) { set_error("qw_kv_store: page not mapped"); return false; }
                 memset(hp, 0, (size_t)cnt * row);   // never written: reads as zeros
             } else {
-                char *dp = (char *)a->va + ((size_t)tab[pg] * QW_PAGE_TOKENS + in) * row;
+                char *dp = (char *)a->pool->va + ((size_t)tab[pg] * QW_PAGE_TOKENS + in) * row;
                 if (cudaMemcpy(store ? (void *)dp : (void *)hp, store ? (void *)hp : (void *)dp, (size_t)cnt * row,
                                store ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost) != cudaSuccess) {
                     set_error("qw_kv_read/store: copy failed");
@@ -771,6 +1005,7 @@ extern "C" bool qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t p
 // kernel and one copy per layer through a staging buffer.
 static bool kv_pack_io(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
                        int32_t n_tokens, void *host, size_t len, bool unpack) {
+    if (kcache) use_device(kcache->device);
     if (!G.up || !kcache || !vcache || n_layers <= 0 || kv_heads <= 0 || head_dim != QW_HEAD_DIM || n_tokens < 0 || n_tokens > max_ctx || !host) {
         set_error("qw_kv_pack/unpack: bad arguments");
         return false;
@@ -818,13 +1053,14 @@ extern "C" bool qw_kv_unpack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int
 extern "C" void qw_kv_arena_trim(qw_buf cache, int32_t n_tokens) {
     if (!cache || cache->kind != BUF_ARENA) return;
     Arena *a = cache->arena;
+    use_device(cache->device);
     cudaDeviceSynchronize();
     const int keep = (std::max(n_tokens, 0) + QW_PAGE_TOKENS - 1) / QW_PAGE_TOKENS;
     for (size_t lh = 0; lh < (size_t)a->n_layers * a->kv_heads; lh++) {
         int32_t *row = a->table_host.data() + lh * a->pages_per_head;
         bool any = false;
         for (int pg = keep; pg < a->pages_per_head; pg++)
-            if (row[pg] >= 0) { a->free_pages.push_back(row[pg]); row[pg] = -1; a->in_use--; any = true; }
+            if (row[pg] >= 0) { a->pool->free_pages.push_back(row[pg]); row[pg] = -1; a->in_use--; any = true; }
         if (any && keep < a->pages_per_head)
             cudaMemcpy(a->table_dev + lh * a->pages_per_head + keep, row + keep, (size_t)(a->pages_per_head - keep) * sizeof(int32_t),
                        cudaMemcpyHostToDevice);
@@ -833,8 +1069,8 @@ extern "C" void qw_kv_arena_trim(qw_buf cache, int32_t n_tokens) {
 extern "C" int64_t qw_kv_arena_pages_in_use(qw_buf cache) { return cache && cache->kind == BUF_ARENA ? cache->arena->in_use : -1; }
 extern "C" int64_t qw_kv_arena_bytes_committed(qw_buf cache) {
     if (!cache || cache->kind != BUF_ARENA) return -1;
-    Arena *a = cache->arena;
-    return a->vmm ? (int64_t)(a->chunks.size() * CHUNK_BYTES) : (int64_t)a->va_size;
+    Pool *pl = cache->arena->pool;
+    return pl->vmm ? (int64_t)(pl->chunks.size() * CHUNK_BYTES) : (int64_t)pl->va_size;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -843,6 +1079,12 @@ extern "C" int64_t qw_kv_arena_bytes_committed(qw_buf cache) {
 static qw_cmd cmd_new(cudaStream_t s, bool own) {
     qw_cmd c = new qw_cmd_s();
     c->stream = s; c->own_stream = own; c->failed = false; c->err[0] = 0; c->parallel = 0;
+    c->device = G.device;
+    // a status word of its own, so that a kernel's bounded wait that ran out is reported on the
+    // command buffer that launched it; with every slot taken the shared word 0 serves
+    c->status_slot = 0;
+    for (int i = 1; i < STATUS_SLOTS; i++)
+        if (!(G.status_used >> i & 1)) { G.status_used |= (uint64_t)1 << i; c->status_slot = i; G.status_host[i * STATUS_STRIDE] = 0; break; }
     return c;
 }
 extern "C" qw_cmd qw_cmd_begin(void) {
@@ -869,21 +1111,25 @@ extern "C" void qw_cmd_parallel(qw_cmd c, bool on) { if (c) c->parallel += on ? 
 
 extern "C" void qw_cmd_wait(qw_cmd c) {
     if (!c) return;
+    use_device(c->device);
     for (auto &t : c->touched)
         if (t.whi > t.wlo)
             cuda_ok(c, cudaMemcpyAsync((char *)t.b->host + t.wlo, (char *)t.b->dev + t.wlo, t.whi - t.wlo, cudaMemcpyDeviceToHost, c->stream), "download");
     c->touched.clear();
     cudaError_t e = cudaStreamSynchronize(c->stream);
     if (e != cudaSuccess) cmd_fail(c, "GPU fault: %s", cudaGetErrorString(e));
-    if (G.status_host && G.status_host[0] != 0) {
-        cmd_fail(c, "%s", status_text(G.status_host[0]));
-        G.status_host[0] = 0;
+    if (G.status_host) {
+        volatile int *st = G.status_host + (size_t)c->status_slot * STATUS_STRIDE;
+        if (*st != 0) {
+            cmd_fail(c, "%s", status_text(*st));
+            *st = 0;
+        }
     }
     if (c->marks.size() > 1) {
         for (size_t i = 1; i < c->marks.size(); i++) {
             float ms = 0;
             if (c->marks[i].label && cudaEventElapsedTime(&ms, c->marks[i - 1].ev, c->marks[i].ev) == cudaSuccess) {
-                auto &slot = G.prof_ms[c->marks[i].label];
+                auto &slot = SH.prof_ms[c->marks[i].label];
                 slot.first += ms; slot.second++;
             }
         }
@@ -893,7 +1139,7 @@ extern "C" void qw_cmd_wait(qw_cmd c) {
     for (auto &k : c->ktimes) {
         float ms = 0;
         if (cudaEventElapsedTime(&ms, k.t0, k.t1) == cudaSuccess) {
-            auto &slot = G.kernel_ms[k.kernel];
+            auto &slot = SH.kernel_ms[k.kernel];
             slot.first += ms; slot.second++;
         }
         cudaEventDestroy(k.t0); cudaEventDestroy(k.t1);
@@ -903,6 +1149,8 @@ extern "C" void qw_cmd_wait(qw_cmd c) {
 
 extern "C" void qw_cmd_free(qw_cmd c) {
     if (!c) return;
+    use_device(c->device);
+    if (c->status_slot) G.status_used &= ~((uint64_t)1 << c->status_slot);
     if (!c->touched.empty() || !c->scratch.empty()) cudaStreamSynchronize(c->stream);
     for (auto &s : c->scratch) G.scratch_pool.push_back(s);
     if (c->uploaded) cudaEventDestroy(c->uploaded);
@@ -919,8 +1167,8 @@ extern "C" void qw_cmd_free(qw_cmd c) {
 extern "C" const char *qw_cmd_error(qw_cmd c) { return c && c->failed ? c->err : nullptr; }
 
 extern "C" bool qw_prof_enabled(void) {
-    if (G.prof < 0) { const char *v = getenv("QWASAR_PROFILE"); G.prof = (v && *v && strcmp(v, "0")) ? 1 : 0; }
-    return G.prof == 1;
+    if (SH.prof < 0) { const char *v = getenv("QWASAR_PROFILE"); SH.prof = (v && *v && strcmp(v, "0")) ? 1 : 0; }
+    return SH.prof == 1;
 }
 extern "C" void qw_cmd_mark(qw_cmd c, const char *label) {
     if (!c || !qw_prof_enabled()) return;
@@ -929,28 +1177,30 @@ extern "C" void qw_cmd_mark(qw_cmd c, const char *label) {
     cudaEventRecord(m.ev, c->stream);
     c->marks.push_back(m);
 }
-extern "C" void qw_prof_report(void) {
+// The table of qwasar_metal.m:435-447: one line per label, milliseconds per token when a token
+// count is given, the share of the total, the marks counted, then the total.
+extern "C" void qw_prof_report(FILE *out, long tokens) {
+    if (!out || SH.prof_ms.empty()) return;
     double total = 0;
-    for (auto &kv : G.prof_ms) total += kv.second.first;
-    for (auto &kv : G.prof_ms)
-        fprintf(stderr, "  %-28s %9.3f ms  %6ld marks  %5.1f%%\n", kv.first.c_str(), kv.second.first, kv.second.second,
-                total > 0 ? 100.0 * kv.second.first / total : 0.0);
+    for (auto &kv : SH.prof_ms) total += kv.second.first;
+    const double per = tokens > 0 ? (double)tokens : 1.0;
+    fprintf(out, "GPU time by section%s:\n", tokens > 0 ? ", per decoded token" : "");
+    for (auto &kv : SH.prof_ms)
+        fprintf(out, "  %-22s %8.3f ms  %5.1f%%  (%ld marks)\n", kv.first.c_str(), kv.second.first / per,
+                100.0 * kv.second.first / (total > 0 ? total : 1.0), kv.second.second);
+    fprintf(out, "  %-22s %8.3f ms\n", "total", total / per);
 }
+extern "C" void qw_prof_reset(void) { SH.prof_ms.clear(); }
 
 extern "C" void qw_op_copy(qw_cmd c, qw_ref dst, qw_ref src, size_t n) {
     if (!live(c) || !n) return;
-    // a shared source is read straight from its host side; a shared destination is written on
-    // its device side and copied back at wait like any op output
-    void *d = dev_range(c, dst, n, true);
-    const void *s = nullptr;
-    if (src.buf && src.buf->kind == BUF_SHARED) {
-        if (src.off + n > src.buf->len) { cmd_fail(c, "copy source out of range"); return; }
-        s = (char *)src.buf->host + src.off;
-    } else {
-        s = dev_range(c, src, n, false);
-    }
+    // Both sides are taken on the device: an earlier op of this command buffer may have written the
+    // source, and then only its device mirror is current until qw_cmd_wait.  A shared destination
+    // is copied back at wait like any op output.
+    void *d = dev_range(c, dst, n, true, 1);
+    const void *s = dev_range(c, src, n, false, 1);
     if (!d || !s) return;
-    cuda_ok(c, cudaMemcpyAsync(d, s, n, cudaMemcpyDefault, c->stream), "copy");
+    cuda_ok(c, cudaMemcpyAsync(d, s, n, cudaMemcpyDeviceToDevice, c->stream), "copy");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -1032,18 +1282,19 @@ struct AttnArgs {
 };
 
 // Rows of one call cut into chunks of at most 64 / gqa rows, each chunk a "sequence" of a
-// split-KV launch; launches carry up to QW_MAX_SEQ chunks.
+// split-KV launch.
 bool attn_rows_split(qw_cmd c, const AttnArgs *seqs, int n_seq, int32_t q_heads, int32_t kv_heads, int32_t max_ctx,
                      float scale, int q_dtype, int out_dtype, int gate_dtype, int gate_stride) {
     const int gqa = q_heads / kv_heads;
     if (gqa > 64) return false;
     const int chunk_rows = std::max(1, 64 / gqa);
     const size_t q_el = q_dtype == DT_BF16 ? 2 : 4, o_el = out_dtype == DT_BF16 ? 2 : 4, g_el = gate_dtype == DT_BF16 ? 2 : 4;
-    AttnParams p;
+    SplitBatch b;
+    b.c = c;
+    AttnParams &p = b.p;
     memset(&p, 0, sizeof p);
     p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = q_dtype; p.out_dtype = out_dtype;
     p.gate_dtype = gate_dtype; p.gate_stride = gate_stride; p.scale = scale; p.mode = 0;
-    int n = 0, max_rows = 0;
     for (int s = 0; s < n_seq; s++) {
         const AttnArgs &a = seqs[s];
         KvLayer kc, vc;
@@ -1056,7 +1307,8 @@ bool attn_rows_split(qw_cmd c, const AttnArgs *seqs, int n_seq, int32_t q_heads,
         const char *gp = a.gate.buf ? (const char *)dev_range(c, a.gate, ((size_t)a.rows * q_heads - 1) * gate_stride * g_el + 256 * g_el, false) : nullptr;
         if (!qp || !op || (a.gate.buf && !gp)) return false;
         for (int r0 = 0; r0 < a.rows; r0 += chunk_rows) {
-            AttnSeq &sq = p.seq[n];
+            AttnSeq sq;
+            memset(&sq, 0, sizeof sq);
             const int rr = std::min(chunk_rows, a.rows - r0);
             sq.q = qp + (size_t)r0 * q_heads * 256 * q_el;
             sq.out = op + (size_t)r0 * q_heads * 256 * o_el;
@@ -1064,20 +1316,10 @@ bool attn_rows_split(qw_cmd c, const AttnArgs *seqs, int n_seq, int32_t q_heads,
             sq.kc = kc; sq.vc = vc;
             sq.rows = rr; sq.base_pos = a.base_pos + r0;
             sq.key_lo = 0; sq.key_hi = a.base_pos + r0 + rr;
-            p.kmap[n] = km; p.vmap[n] = vm;
-            max_rows = std::max(max_rows, rr);
-            if (++n == QW_MAX_SEQ) {
-                p.n_seq = n;
-                if (!run_split(c, p, max_rows)) return false;
-                n = 0; max_rows = 0;
-            }
+            if (!b.add(sq, km, vm)) return false;
         }
     }
-    if (n) {
-        p.n_seq = n;
-        if (!run_split(c, p, max_rows)) return false;
-    }
-    return true;
+    return b.flush();
 }
 
 }  // namespace
@@ -1250,7 +1492,7 @@ extern "C" bool qw_op_attn_decode_tensor(qw_cmd c, qw_ref out, qw_ref q, qw_ref 
                                          int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
                                          int32_t base_pos, float scale) {
     if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
-    if (rows * (q_heads / kv_heads) > 64) return false;
+    if (q_heads / kv_heads > 64) return false;            // rows beyond 64 / grouping are taken in chunks
     AttnArgs a = {out, q, qw_ref{nullptr, 0}, kcache, vcache, rows, base_pos};
     return attn_rows_split(c, &a, 1, q_heads, kv_heads, max_ctx, scale, DT_F32, DT_F32, DT_F32, 256);
 }
@@ -1304,12 +1546,13 @@ bool fused_check(int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_d
 
 struct FusedSeq { qw_ref out, qg, k, v, pos, kcache, vcache; int32_t base_pos; };
 
-// pre-op for up to QW_MAX_SEQ sequences; q_out[i] receives each sequence's bf16 query
-// cs_out != nullptr: the query heads are left alone and the rotation angles' cos / sin of every row
-// go to cs_out[i] ([rows, 64] f32) -- for the prefill kernel that norms and rotates its own tiles.
+// pre-op for up to QW_MAX_SEQ sequences; q_out[i] receives each sequence's bf16 query.
+// skip_q: the query heads are left alone (the attention kernel norms and rotates them itself) and
+// q_out may be nullptr; cs_out != nullptr: the rotation angles' cos / sin of every row also go to
+// cs_out[i] ([rows, 64] f32) -- the prefill kernel reads its angles from there.
 bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_out, qw_ref q_norm_w, qw_ref k_norm_w,
                qw_ref axis, qw_ref inv_freq, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t max_ctx,
-               float eps, int io, bool append, float *const *cs_out = nullptr) {
+               float eps, int io, bool append, float *const *cs_out = nullptr, bool skip_q = false) {
     PreopParams p;
     memset(&p, 0, sizeof p);
     const size_t el = io == DT_BF16 ? 2 : 4;
@@ -1331,13 +1574,13 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
             if (!resolve_cache(c, s[i].kcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.kc, nullptr, 32, nullptr, s[i].base_pos)) return false;
             if (!resolve_cache(c, s[i].vcache, kv_heads, max_ctx, QW_HEAD_DIM, s[i].base_pos + rows, true, true, &ps.vc, nullptr, 32, nullptr, s[i].base_pos)) return false;
         }
-        ps.q_out = q_out[i];
+        ps.q_out = q_out ? q_out[i] : nullptr;
         ps.cs_out = cs_out ? cs_out[i] : nullptr;
         ps.rows = rows; ps.base_pos = s[i].base_pos;
     }
-    p.skip_q = cs_out != nullptr;
+    p.skip_q = skip_q || cs_out != nullptr;
     KTime kt = {nullptr, nullptr, "qw_attn_preop"};
-    const bool timed = G.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
+    const bool timed = SH.time_kernels && cudaEventCreate(&kt.t0) == cudaSuccess && cudaEventCreate(&kt.t1) == cudaSuccess;
     if (timed) cudaEventRecord(kt.t0, c->stream);
     launch_preop(c->stream, p, rows);
     if (timed) { cudaEventRecord(kt.t1, c->stream); c->ktimes.push_back(kt); }
@@ -1347,20 +1590,12 @@ bool run_preop(qw_cmd c, const FusedSeq *s, int n_seq, __nv_bfloat16 *const *q_o
 bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_ref k_norm_w, qw_ref axis, qw_ref inv_freq,
                  int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t max_ctx, float eps, float scale, int io) {
     const size_t el = io == DT_BF16 ? 2 : 4;
+    const int gqa = q_heads / kv_heads;
+    const int chunk_rows = std::max(1, 64 / gqa);
     for (int s0 = 0; s0 < n_seq; s0 += QW_MAX_SEQ) {
         const int ns = std::min(QW_MAX_SEQ, n_seq - s0);
         for (int i = 0; i < ns; i++)
             if ((int64_t)seqs[s0 + i].base_pos + rows > max_ctx || seqs[s0 + i].base_pos < 0) { cmd_fail(c, "fused attention: positions outside the cache"); return false; }
-        // scratch: the bf16 queries of this group of sequences, then the attention partials (sized generously)
-        const size_t q_bytes = (size_t)rows * q_heads * 256 * 2;
-        const size_t q_total = ((size_t)ns * q_bytes + 1023) & ~(size_t)1023;
-        const int gqa = q_heads / kv_heads;
-        const int chunk_rows = std::max(1, 64 / gqa);
-        const size_t part_rows = (size_t)(sm_count() + QW_MAX_SEQ * kv_heads) * 64 + (size_t)QW_MAX_SEQ * chunk_rows * q_heads;
-        char *scr = (char *)cmd_scratch(c, q_total + part_rows * 258 * 4);
-        if (!scr) return false;
-        __nv_bfloat16 *qo[QW_MAX_SEQ];
-        for (int i = 0; i < ns; i++) qo[i] = reinterpret_cast<__nv_bfloat16 *>(scr + (size_t)i * q_bytes);
         if (rows * gqa > 64 && g_tune_prefill_tc) {
             // many rows: the tcgen05 kernel, one launch per sequence (operands that its tile maps
             // cannot describe, e.g. an output that is not 16-byte aligned, take the chunked path below)
@@ -1374,46 +1609,48 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
                 if (!op[i] || !gp[i]) return false;
                 tiles_ok = tiles_ok && attn_prefill_io_ok(op[i], io, gp[i] + 256 * el, io, 512);
             }
-            if (tiles_ok && io == DT_BF16 && g_tune_prefill_fuse_q) {
-                // bf16 rows: the kernel norms and rotates its own query tiles; the pre-op only appends
-                // K and V and leaves the rows' cos / sin (in the scratch the bf16 queries would have taken)
+            if (tiles_ok) {
+                // scratch: per sequence the bf16 queries, or (bf16 rows: the kernel norms and rotates its
+                // own query tiles, the pre-op only appends K and V) the rows' cos / sin in the same place
+                const size_t q_bytes = (size_t)rows * q_heads * 256 * 2;
+                char *scr = (char *)cmd_scratch(c, (size_t)ns * q_bytes);
+                if (!scr) return false;
+                __nv_bfloat16 *qo[QW_MAX_SEQ];
                 float *cs[QW_MAX_SEQ];
-                for (int i = 0; i < ns; i++) cs[i] = reinterpret_cast<float *>(scr + (size_t)i * q_bytes);
+                for (int i = 0; i < ns; i++) { qo[i] = reinterpret_cast<__nv_bfloat16 *>(scr + (size_t)i * q_bytes); cs[i] = reinterpret_cast<float *>(qo[i]); }
+                const bool fuse_q = io == DT_BF16 && g_tune_prefill_fuse_q;
                 const uint16_t *wq = q_norm_w.buf ? (const uint16_t *)dev_range(c, q_norm_w, 512, false) : nullptr;
                 if (q_norm_w.buf && !wq) return false;
-                if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true, cs)) return false;
+                if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true,
+                               fuse_q ? cs : nullptr)) return false;
                 for (int i = 0; i < ns; i++) {
                     const FusedSeq &fs = seqs[s0 + i];
-                    if (!run_prefill(c, reinterpret_cast<const __nv_bfloat16 *>(gp[i]), op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache,
-                                     rows, q_heads, kv_heads, max_ctx, fs.base_pos, scale, cs[i], wq, eps)) return false;
-                }
-                continue;
-            }
-            if (tiles_ok) {
-                if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
-                for (int i = 0; i < ns; i++) {
-                    const FusedSeq &fs = seqs[s0 + i];
-                    if (!run_prefill(c, qo[i], op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
-                                     max_ctx, fs.base_pos, scale)) return false;
+                    const bool ok = fuse_q
+                        ? run_prefill(c, reinterpret_cast<const __nv_bfloat16 *>(gp[i]), op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache,
+                                      rows, q_heads, kv_heads, max_ctx, fs.base_pos, scale, cs[i], wq, eps)
+                        : run_prefill(c, qo[i], op[i], io, gp[i] + 256 * el, io, 512, fs.kcache, fs.vcache, rows, q_heads, kv_heads,
+                                      max_ctx, fs.base_pos, scale);
+                    if (!ok) return false;
                 }
                 continue;
             }
         }
-        if (!run_preop(c, seqs + s0, ns, qo, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true)) return false;
-
-        AttnParams p;
+        // few rows (decode, verify), or rows in chunks: one kernel appends K and V, the split-KV
+        // kernel norms and rotates the raw query rows itself and starts under the append
+        if (!run_preop(c, seqs + s0, ns, nullptr, q_norm_w, k_norm_w, axis, inv_freq, rows, q_heads, kv_heads, max_ctx, eps, io, true,
+                       nullptr, true)) return false;
+        SplitBatch b;
+        b.c = c;
+        AttnParams &p = b.p;
         memset(&p, 0, sizeof p);
-        p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = DT_BF16; p.out_dtype = io;
+        p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = io; p.out_dtype = io;
         p.gate_dtype = io; p.gate_stride = 512; p.scale = scale; p.mode = 0;
-        int n = 0, max_rows = 0;
-        auto flush = [&]() -> bool {
-            if (!n) return true;
-            p.n_seq = n;
-            plan_split(p);
-            const bool ok = launch_split_merge(c, p, max_rows, reinterpret_cast<float *>(scr + q_total));
-            n = 0; max_rows = 0;
-            return ok;
-        };
+        p.q_raw = 1; p.eps = eps;
+        p.q_norm_w = q_norm_w.buf ? (const uint16_t *)dev_range(c, q_norm_w, 512, false) : nullptr;
+        p.axis = (const uint8_t *)dev_range(c, axis, 32, false, 1);
+        p.inv_freq = (const float *)dev_range(c, inv_freq, 128, false, 4);
+        if (!p.axis || !p.inv_freq || (q_norm_w.buf && !p.q_norm_w)) return false;
+        b.early_next = !SH.time_kernels;        // (event records between the kernels would serialise them anyway)
         for (int i = 0; i < ns; i++) {
             const FusedSeq &fs = seqs[s0 + i];
             KvLayer kc, vc;
@@ -1422,22 +1659,24 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
             if (!resolve_cache(c, fs.vcache, kv_heads, max_ctx, QW_HEAD_DIM, fs.base_pos + rows, false, false, &vc, &vm)) return false;
             char *op = (char *)dev_range(c, fs.out, (size_t)rows * q_heads * 256 * el, true);
             const char *gp = (const char *)dev_range(c, fs.qg, (size_t)rows * q_heads * 512 * el, false);
-            if (!op || !gp) return false;
+            const int32_t *pp = (const int32_t *)dev_range(c, fs.pos, (size_t)3 * rows * 4, false, 4);
+            if (!op || !gp || !pp) return false;
             for (int r0 = 0; r0 < rows; r0 += chunk_rows) {
-                AttnSeq &sq = p.seq[n];
+                AttnSeq sq;
+                memset(&sq, 0, sizeof sq);
                 const int rr = std::min(chunk_rows, rows - r0);
-                sq.q = qo[i] + (size_t)r0 * q_heads * 256;
+                sq.q = gp + (size_t)r0 * q_heads * 512 * el;               // the q half of each [q|gate] head
                 sq.out = op + (size_t)r0 * q_heads * 256 * el;
-                sq.gate = gp + ((size_t)r0 * q_heads * 512 + 256) * el;    // the gate half of each [q|gate] head
+                sq.gate = gp + ((size_t)r0 * q_heads * 512 + 256) * el;    // the gate half
+                sq.pos = pp + r0; sq.pos_stride = rows;
                 sq.kc = kc; sq.vc = vc;
                 sq.rows = rr; sq.base_pos = fs.base_pos + r0;
+                sq.fresh_pos = fs.base_pos;
                 sq.key_lo = 0; sq.key_hi = fs.base_pos + r0 + rr;
-                p.kmap[n] = km; p.vmap[n] = vm;
-                max_rows = std::max(max_rows, rr);
-                if (++n == QW_MAX_SEQ && !flush()) return false;
+                if (!b.add(sq, km, vm)) return false;
             }
         }
-        if (!flush()) return false;
+        if (!b.flush()) return false;
     }
     return true;
 }
@@ -1495,8 +1734,10 @@ extern "C" bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q
                                    int32_t key_lo, int32_t key_hi, float scale, qw_dtype q_dtype) {
     if (!live(c) || !shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos)) return false;
     const int gqa = q_heads / kv_heads;
-    if (rows * gqa > 64 || key_lo < 0 || (key_lo & 63)) return false;
+    if (rows * gqa > 64 || key_lo < 0) return false;
     key_hi = std::min(key_hi, base_pos + rows);
+    // an empty range needs no alignment (a trailing shard of a short sequence starts where the keys end)
+    if (key_hi > key_lo && (key_lo & 63)) return false;
     const size_t n_rh = (size_t)rows * q_heads;
     float *pa = (float *)dev_range(c, pacc, n_rh * 256 * 4, true), *ps = (float *)dev_range(c, pstat, n_rh * 2 * 4, true);
     if (!pa || !ps) return false;
@@ -1511,8 +1752,9 @@ extern "C" bool qw_op_attn_partial(qw_cmd c, qw_ref pacc, qw_ref pstat, qw_ref q
     p.n_seq = 1; p.q_heads = q_heads; p.kv_heads = kv_heads; p.gqa = gqa; p.q_dtype = (int)q_dtype; p.out_dtype = DT_F32;
     p.gate_dtype = DT_F32; p.gate_stride = 256; p.scale = scale; p.mode = 1;
     AttnSeq &sq = p.seq[0];
-    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.kc, &p.kmap[0])) return false;
-    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.vc, &p.vmap[0])) return false;
+    if (!resolve_cache(c, kcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.kc, &p.maps[0])) return false;
+    if (!resolve_cache(c, vcache, kv_heads, max_ctx, head_dim, key_hi, false, false, &sq.vc, &p.maps[1])) return false;
+    sq.kmap = 0; sq.vmap = 1;
     sq.q = dev_range(c, q, n_rh * 256 * (q_dtype == QW_BF16 ? 2 : 4), false);
     if (!sq.q) return false;
     sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = key_lo; sq.key_hi = key_hi;
@@ -1536,4 +1778,179 @@ extern "C" void qw_op_attn_merge(qw_cmd c, qw_ref out, qw_ref pacc, qw_ref pstat
     launch_merge_parts(c->stream, po, (int)out_dtype, pa, ps, pg, (int)gate_dtype, gate_stride, (int)n_rh, parts, nullptr, nullptr,
                        a_stride, s_stride);
     cuda_ok(c, cudaGetLastError(), "merge launch");
+}
+
+// ---------------------------------------------------------------------------------------
+// additive: the exchange of partials between the GPUs that hold one sequence
+// ---------------------------------------------------------------------------------------
+struct qw_xchg_s {
+    int device, n_ranks, rank, max_rh;
+    void *base;                 // one allocation: the gather buffer, then the flags
+    size_t gather_bytes, flags_bytes;
+    float *peer_gather[8];      // every rank's buffer as this process addresses it ([rank] = own)
+    int *peer_flags[8];
+    void *opened[8];            // mappings of other processes' buffers, closed by qw_xchg_free
+    int epoch;
+    int64_t timeout_ns;
+};
+
+extern "C" qw_xchg qw_xchg_create(int32_t n_ranks, int32_t rank, int32_t max_rows_heads) {
+    if (!G.up) { set_error("qw_xchg_create before qw_gpu_init"); return nullptr; }
+    if (n_ranks < 1 || n_ranks > 8 || rank < 0 || rank >= n_ranks || max_rows_heads <= 0) { set_error("qw_xchg_create: 1 to 8 ranks, a rank among them, a positive row count"); return nullptr; }
+    qw_xchg x = new qw_xchg_s();
+    memset(x, 0, sizeof *x);
+    x->device = G.device; x->n_ranks = n_ranks; x->rank = rank; x->max_rh = max_rows_heads;
+    x->gather_bytes = (size_t)2 * n_ranks * max_rows_heads * QW_XCHG_REC * sizeof(float);
+    x->flags_bytes = (size_t)2 * n_ranks * max_rows_heads * sizeof(int);
+    if (cudaMalloc(&x->base, x->gather_bytes + x->flags_bytes) != cudaSuccess) { set_error("qw_xchg_create: out of device memory"); cudaGetLastError(); delete x; return nullptr; }
+    cudaMemset(x->base, 0, x->gather_bytes + x->flags_bytes);       // no flag shows an epoch yet
+    cudaDeviceSynchronize();
+    x->peer_gather[rank] = (float *)x->base;
+    x->peer_flags[rank] = (int *)((char *)x->base + x->gather_bytes);
+    x->timeout_ns = (int64_t)2000 * 1000 * 1000;
+    return x;
+}
+
+extern "C" void qw_xchg_free(qw_xchg x) {
+    if (!x) return;
+    use_device(x->device);
+    cudaDeviceSynchronize();
+    for (int i = 0; i < 8; i++) if (x->opened[i]) cudaIpcCloseMemHandle(x->opened[i]);
+    cudaFree(x->base);
+    delete x;
+}
+
+extern "C" size_t qw_xchg_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+extern "C" bool qw_xchg_export(qw_xchg x, void *handle) {
+    if (!x || !handle) return false;
+    use_device(x->device);
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, x->base) != cudaSuccess) { set_error("qw_xchg_export: %s", cudaGetErrorString(cudaGetLastError())); return false; }
+    memcpy(handle, &h, sizeof h);
+    return true;
+}
+
+extern "C" bool qw_xchg_attach(qw_xchg x, int32_t peer_rank, const void *handle) {
+    if (!x || !handle || peer_rank < 0 || peer_rank >= x->n_ranks || peer_rank == x->rank) { set_error("qw_xchg_attach: bad rank"); return false; }
+    use_device(x->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void *p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        set_error("qw_xchg_attach: cannot map rank %d's buffer: %s", peer_rank, cudaGetErrorString(cudaGetLastError()));
+        return false;
+    }
+    if (x->opened[peer_rank]) cudaIpcCloseMemHandle(x->opened[peer_rank]);
+    x->opened[peer_rank] = p;
+    x->peer_gather[peer_rank] = (float *)p;
+    x->peer_flags[peer_rank] = (int *)((char *)p + x->gather_bytes);
+    return true;
+}
+
+extern "C" bool qw_xchg_attach_local(qw_xchg x, int32_t peer_rank, qw_xchg peer) {
+    if (!x || !peer || peer_rank < 0 || peer_rank >= x->n_ranks || peer_rank == x->rank || peer->rank != peer_rank ||
+        peer->n_ranks != x->n_ranks || peer->max_rh != x->max_rh) { set_error("qw_xchg_attach_local: the two ends do not match"); return false; }
+    x->peer_gather[peer_rank] = (float *)peer->base;
+    x->peer_flags[peer_rank] = (int *)((char *)peer->base + peer->gather_bytes);
+    return true;
+}
+
+extern "C" void qw_xchg_set_timeout_ms(qw_xchg x, int32_t ms) { if (x && ms > 0) x->timeout_ns = (int64_t)ms * 1000 * 1000; }
+
+// One exchange round for n_seq sequences of equal shape.  Sequences whose range on this rank is
+// empty publish empty records from a launch of the second kernel alone; the others go through the
+// split-KV kernel first.  Slot numbers follow the sequence's place in the call on every rank.
+static bool attn_exchange(qw_cmd c, qw_xchg x, int32_t phase, int32_t n_seq, const qw_ref *out, const qw_ref *gate, const qw_ref *q,
+                          const qw_ref *kcache, const qw_ref *vcache, const int32_t *base_pos, const int32_t *key_lo,
+                          const int32_t *key_hi, int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                          int32_t max_ctx, float scale, qw_dtype q_dtype, qw_dtype out_dtype, qw_dtype gate_dtype,
+                          int32_t gate_stride) {
+    if (!live(c) || !x || phase < 0 || phase > 2 || n_seq <= 0 || n_seq > QW_MAX_SEQ) return false;
+    if (rows <= 0 || kv_heads <= 0 || q_heads <= 0 || q_heads % kv_heads || head_dim != QW_HEAD_DIM) return false;
+    const int gqa = q_heads / kv_heads;
+    const size_t n_rh = (size_t)rows * q_heads;
+    if (rows * gqa > 64 || (size_t)n_seq * n_rh > (size_t)x->max_rh || x->device != c->device) {
+        cmd_fail(c, "attn_exchange: shape does not fit the exchange (rows * grouping <= 64, sequences * rows * q_heads <= %d, same device)", x->max_rh);
+        return false;
+    }
+    for (int i = 0; i < x->n_ranks; i++)
+        if (!x->peer_gather[i]) { cmd_fail(c, "attn_exchange: rank %d was never attached", i); return false; }
+    AttnParams base;
+    memset(&base, 0, sizeof base);
+    base.q_heads = q_heads; base.kv_heads = kv_heads; base.gqa = gqa; base.q_dtype = (int)q_dtype; base.out_dtype = (int)out_dtype;
+    base.gate_dtype = (int)gate_dtype; base.gate_stride = gate_stride; base.scale = scale;
+    base.mode = phase == 0 ? 2 : phase == 1 ? 3 : 4;
+    if (phase != 2) x->epoch++;               // a new round: every rank must make the same calls in the same order
+    for (int i = 0; i < x->n_ranks; i++) { base.x.gather[i] = x->peer_gather[i]; base.x.flags[i] = x->peer_flags[i]; }
+    base.x.n_ranks = x->n_ranks; base.x.rank = x->rank; base.x.max_rh = x->max_rh; base.x.epoch = x->epoch;
+    base.x.timeout_ns = x->timeout_ns;
+    // two launches at most: the sequences with keys here, and the ones without (or, in phase 2, all)
+    for (int pass = 0; pass < 2; pass++) {
+        AttnParams p = base;
+        int slot0[QW_MAX_SEQ];
+        int n = 0, n_maps = 0;
+        for (int i = 0; i < n_seq; i++) {
+            if (!shape_ok(rows, q_heads, kv_heads, head_dim, max_ctx, base_pos[i]) || key_lo[i] < 0) return false;
+            const int hi = std::min(key_hi[i], base_pos[i] + rows);
+            const bool empty = hi <= key_lo[i] || phase == 2;
+            if (empty != (pass == 1)) continue;
+            if (!empty && (key_lo[i] & 63)) return false;
+            AttnSeq &sq = p.seq[n];
+            sq.rows = rows; sq.base_pos = base_pos[i]; sq.key_lo = empty ? 0 : key_lo[i]; sq.key_hi = empty ? 1 : hi;
+            if (phase != 1) {
+                const size_t g_el = gate_dtype == QW_BF16 ? 2 : 4;
+                sq.out = dev_range(c, out[i], n_rh * 256 * (out_dtype == QW_BF16 ? 2 : 4), true);
+                sq.gate = gate && gate[i].buf ? dev_range(c, gate[i], ((n_rh - 1) * gate_stride + 256) * g_el, false) : nullptr;
+                if (!sq.out || (gate && gate[i].buf && !sq.gate)) return false;
+            }
+            if (!empty) {
+                CUtensorMap km, vm;
+                if (!resolve_cache(c, kcache[i], kv_heads, max_ctx, head_dim, hi, false, false, &sq.kc, &km)) return false;
+                if (!resolve_cache(c, vcache[i], kv_heads, max_ctx, head_dim, hi, false, false, &sq.vc, &vm)) return false;
+                int k = -1, v = -1;
+                for (int m = 0; m < n_maps; m++) { if (!memcmp(&p.maps[m], &km, sizeof km)) k = m; if (!memcmp(&p.maps[m], &vm, sizeof vm)) v = m; }
+                if (k < 0 && n_maps < QW_MAX_MAPS) { p.maps[n_maps] = km; k = n_maps++; }
+                if (v < 0 && !memcmp(&km, &vm, sizeof km)) v = k;
+                if (v < 0 && n_maps < QW_MAX_MAPS) { p.maps[n_maps] = vm; v = n_maps++; }
+                if (k < 0 || v < 0) { cmd_fail(c, "attn_exchange: the sequences' caches lie in more than %d buffers or pools", QW_MAX_MAPS); return false; }
+                sq.kmap = (uint8_t)k; sq.vmap = (uint8_t)v;
+                sq.q = dev_range(c, q[i], n_rh * 256 * (q_dtype == QW_BF16 ? 2 : 4), false);
+                if (!sq.q) return false;
+            }
+            slot0[n++] = i * rows;
+        }
+        if (!n) continue;
+        p.n_seq = n;
+        p.x.empty = pass;
+        plan_split(p);
+        for (int i = 0; i < n; i++) p.seq[i].row_slot0 = slot0[i];
+        if (pass == 1) {
+            p.status = cmd_status(c);
+            launch_attn_merge(c->stream, p, rows);
+            if (!cuda_ok(c, cudaGetLastError(), "exchange launch")) return false;
+        } else {
+            float *scr = (float *)cmd_scratch(c, attn_split_scratch_bytes(p, rows));
+            if (!scr || !launch_split_merge(c, p, rows, scr)) return false;
+        }
+    }
+    return true;
+}
+
+extern "C" bool qw_op_attn_exchange(qw_cmd c, qw_xchg x, int32_t phase, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcache, qw_ref vcache,
+                                    int32_t rows, int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t max_ctx,
+                                    int32_t base_pos, int32_t key_lo, int32_t key_hi, float scale, qw_dtype q_dtype,
+                                    qw_dtype out_dtype, qw_dtype gate_dtype, int32_t gate_stride) {
+    return attn_exchange(c, x, phase, 1, &out, &gate, &q, &kcache, &vcache, &base_pos, &key_lo, &key_hi, rows, q_heads, kv_heads,
+                         head_dim, max_ctx, scale, q_dtype, out_dtype, gate_dtype, gate_stride);
+}
+
+extern "C" bool qw_op_attn_exchange_batch(qw_cmd c, qw_xchg x, int32_t phase, int32_t n_seq, const qw_ref *out, const qw_ref *gate,
+                                          const qw_ref *q, const qw_ref *kcache, const qw_ref *vcache, const int32_t *base_pos,
+                                          const int32_t *key_lo, const int32_t *key_hi, int32_t rows, int32_t q_heads,
+                                          int32_t kv_heads, int32_t head_dim, int32_t max_ctx, float scale, qw_dtype q_dtype,
+                                          qw_dtype out_dtype, qw_dtype gate_dtype, int32_t gate_stride) {
+    if (!out || !q || !kcache || !vcache || !base_pos || !key_lo || !key_hi) return false;
+    return attn_exchange(c, x, phase, n_seq, out, gate, q, kcache, vcache, base_pos, key_lo, key_hi, rows, q_heads, kv_heads,
+                         head_dim, max_ctx, scale, q_dtype, out_dtype, gate_dtype, gate_stride);
 }

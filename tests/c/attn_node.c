@@ -58,7 +58,7 @@ static const any_fn all_symbols[] = {
     (any_fn)qw_gpu_max_buffer_length, (any_fn)qw_buf_alloc, (any_fn)qw_buf_wrap, (any_fn)qw_buf_free,
     (any_fn)qw_buf_contents, (any_fn)qw_buf_length, (any_fn)qw_cmd_begin, (any_fn)qw_cmd_commit,
     (any_fn)qw_cmd_wait, (any_fn)qw_cmd_flush, (any_fn)qw_cmd_parallel, (any_fn)qw_cmd_free,
-    (any_fn)qw_cmd_error, (any_fn)qw_prof_enabled, (any_fn)qw_prof_report, (any_fn)qw_cmd_mark, (any_fn)qw_op_split_heads2,
+    (any_fn)qw_cmd_error, (any_fn)qw_prof_enabled, (any_fn)qw_prof_report, (any_fn)qw_prof_reset, (any_fn)qw_cmd_mark, (any_fn)qw_op_split_heads2,
     (any_fn)qw_op_rms_norm, (any_fn)qw_op_rope_partial, (any_fn)qw_rope_tables, (any_fn)qw_op_kv_write,
     (any_fn)qw_op_attn, (any_fn)qw_op_attn_decode, (any_fn)qw_op_attn_prefill, (any_fn)qw_op_attn_prefill_as,
     (any_fn)qw_op_attn_decode_split, (any_fn)qw_op_attn_decode_tensor, (any_fn)qw_op_mul_sigmoid,
@@ -73,7 +73,11 @@ static const any_fn all_symbols[] = {
     (any_fn)qw_kv_pack, (any_fn)qw_kv_unpack, (any_fn)qw_kv_arena_trim, (any_fn)qw_kv_arena_pages_in_use,
     (any_fn)qw_kv_arena_bytes_committed, (any_fn)qw_op_attn_layer_fused, (any_fn)qw_op_attn_layer_fused_batch,
     (any_fn)qw_op_attn_batch, (any_fn)qw_op_attn_partial, (any_fn)qw_op_attn_merge, (any_fn)qw_op_attn_preop,
-    (any_fn)qw_attn_decode_noalloc, (any_fn)qw_attn_decode_noalloc_scratch_bytes,
+    (any_fn)qw_attn_decode_noalloc, (any_fn)qw_attn_decode_noalloc_scratch_bytes, (any_fn)qw_attn_decode_noalloc_status,
+    (any_fn)qw_gpu_device_count, (any_fn)qw_gpu_init_multi, (any_fn)qw_gpu_select, (any_fn)qw_gpu_current,
+    (any_fn)qw_kv_pool_alloc, (any_fn)qw_kv_arena_alloc_in, (any_fn)qw_kv_pool_bytes_committed,
+    (any_fn)qw_xchg_create, (any_fn)qw_xchg_free, (any_fn)qw_xchg_handle_bytes, (any_fn)qw_xchg_export,
+    (any_fn)qw_xchg_attach, (any_fn)qw_xchg_attach_local, (any_fn)qw_xchg_set_timeout_ms, (any_fn)qw_op_attn_exchange, (any_fn)qw_op_attn_exchange_batch,
 };
 
 int main(int argc, char **argv) {

@@ -41,6 +41,25 @@ def test_header_compiles_as_c99_and_every_entry_point_links(attn_node):
     assert "device:" in r.stdout or "qw_gpu_init:" in r.stdout    # a device, or the library's refusal without one
 
 
+REF_HEADER = os.path.join(os.environ.get("QWASAR_REF", "/root/reference"), "qwasar_gpu.h")
+
+
+@pytest.mark.skipif(not os.path.exists(REF_HEADER), reason="the reference checkout is not present on this machine")
+def test_header_coexists_with_the_reference_header(tmp_path):
+    """A translation unit of the reference includes qwasar_gpu.h first; this header must then add
+    only what is new: every declaration the two share has to match, or -Werror stops the compile."""
+    src = tmp_path / "both.c"
+    src.write_text('#include "qwasar_gpu.h"\n#include "qwasar_cuda.h"\n'
+                   "int main(void) { qw_qmv_part p; qw_ref r = qw_ref_at(NULL, 0); (void)p; (void)r;\n"
+                   "  qw_prof_report(stderr, 0); qw_prof_reset(); return qw_gpu_sm_count(); }\n")
+    libdir = os.path.join(ROOT, "qwasar_b200")
+    cmd = ["gcc", "-std=c99", "-pedantic", "-Wall", "-Wextra", "-Werror", "-I" + os.path.dirname(REF_HEADER),
+           "-I" + os.path.join(ROOT, "include"), str(src), "-o", str(tmp_path / "both"), "-L" + libdir, "-lqwasar_cuda",
+           "-Wl,-rpath," + libdir]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("args", [[], ["1", "16", "4", "4096", "1"], ["40", "8", "2", "70", "3"], ["200", "16", "4", "0", "1"]],
                          ids=["verify-3-rows", "decode-4k", "chunk-40", "prefill-200"])

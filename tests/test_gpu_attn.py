@@ -86,6 +86,15 @@ def test_split(be, oracle, kind, base, rows):
     assert max_rel_err(got, want) <= 1e-2 and rel_l2(got, want) < 5e-3
 
 
+@pytest.mark.parametrize("kind", [SPLIT_TENSOR, DISPATCH])
+@pytest.mark.parametrize("base,rows", [(500, 6), (1200, 9)])
+def test_verify_rows_of_a_12_to_1_grouping(be, oracle, kind, base, rows):
+    """A Flash-Next-shaped verify block (24 query / 2 KV heads): 6 to 9 rows x 12 heads exceed one
+    64-row tile, so the split-KV kernel takes the rows in chunks instead of declining."""
+    got, want = run_case(be, oracle, kind, base, rows, qh=24, kvh=2, ctx=1536)
+    assert max_rel_err(got, want) <= 1e-2 and rel_l2(got, want) < 5e-3
+
+
 @pytest.mark.parametrize("qh,kvh", [(16, 4), (16, 2), (24, 2), (8, 8)])
 @pytest.mark.parametrize("base,rows", [(0, 1), (97, 1), (700, 3), (10, 20)])
 def test_dispatch_other_groupings(be, oracle, qh, kvh, base, rows):
@@ -142,3 +151,45 @@ def test_gqa_and_normalisation(be, oracle, kind, qh, kvh):
         want = (np.arange(qh) // (qh // kvh) + 1).astype(np.float32)
         dev = np.abs(ov[0] - want[:, None]).max()
         assert dev < (1e-4 if kind == PER_QUERY else 1e-2)
+
+
+@pytest.mark.parametrize("kind,rows,base", [(TILED, 70, 30), (TILED, 200, 0), (SPLIT_TENSOR, 3, 97), (PER_QUERY, 2, 50)])
+def test_tail_of_a_caller_owned_cache_may_hold_anything(be, oracle, kind, rows, base):
+    """Cache rows past the last query position never matter (tests/test_attn.c:148-194), even when
+    they hold NaN or infinity bit patterns -- a caller-owned buffer promises nothing about them."""
+    qh, kvh, ctx, hd = 16, 4, 512, 256
+    rng = np.random.default_rng(rows)
+    n = base + rows
+    kc = synth.cache_bits(rng, kvh, ctx); vc = synth.cache_bits(rng, kvh, ctx)
+    kc[:, n:] = 0x7FC0; vc[:, n:] = 0x7FC0                       # quiet NaN
+    kc[:, n + 1::2] = 0x7F80; vc[:, n + 1::2] = 0xFF80           # +inf / -inf
+    q = synth.normal_bf16(rng, (rows, qh, hd))
+    with Bufs(be) as B:
+        qb, _ = B.shared(q)
+        ob, ov = B.shared_empty((rows, qh, hd), np.float32)
+        kcb = B.device(kc); vcb = B.device(vc)
+        c = be.cmd_begin()
+        encode(be, c, kind, QwRef(ob, 0), QwRef(qb, 0), QwRef(kcb, 0), QwRef(vcb, 0), rows, qh, kvh, ctx, base, 0.0625)
+        be.cmd_wait(c); be.cmd_free(c)
+        got = np.array(ov)
+    assert np.isfinite(got).all(), "a NaN from beyond the last key reached the output"
+    kc[:, n:] = 0; vc[:, n:] = 0
+    want = oracle.attn_decode(q, kc, vc, rows, qh, kvh, hd, ctx, base, 0.0625)
+    assert max_rel_err(got, want) <= 1e-2
+
+
+def test_copy_reads_what_an_earlier_op_wrote(be):
+    """qw_op_copy inside a command buffer sees the output of the op encoded before it (ops run in
+    encoding order and each sees everything before it, qwasar_gpu.h:63-65)."""
+    x = np.linspace(-3, 3, 1024).astype(np.float32)
+    g = np.ones(1024, np.float32) * 0.5
+    with Bufs(be) as B:
+        yb, yv = B.shared(x.copy()); gb, _ = B.shared(g)
+        db, dv = B.shared_empty((1024,), np.float32, fill=0.0)
+        c = be.cmd_begin()
+        be.op_mul_sigmoid(c, QwRef(yb, 0), QwRef(gb, 0), 1024)
+        be.op_copy(c, QwRef(db, 0), QwRef(yb, 0), 4096)
+        be.cmd_wait(c); be.cmd_free(c)
+        want = x * (1.0 / (1.0 + np.exp(-0.5)))
+        assert np.allclose(np.array(dv), want, rtol=1e-6)
+        assert np.array_equal(np.array(dv), np.array(yv))

@@ -51,3 +51,31 @@ def test_partials_merge_to_whole(be, oracle, rows, qh, kvh, base, cuts):
         if st[1] > 0:
             # compare the normalised partial (the max each side subtracts may differ)
             assert rel_l2(np.array(pav[i, 0]) / stats[i, 0, 1], acc / st[1]) < 6e-3
+
+
+def test_cuts_from_seq_range_at_an_unaligned_length(be, oracle):
+    """Trailing shards of a short sequence are empty and start where the keys end, which need not be
+    a multiple of 64 (sharding.seq_range): the op takes them and leaves an empty partial."""
+    from qwasar_b200 import sharding
+    rows, qh, kvh, base, shards = 1, 16, 2, 99, 4          # 100 keys
+    ctx = base + rows + 3
+    rng = np.random.default_rng(4)
+    q = synth.normal_bf16(rng, (rows, qh, 256)); gate = synth.normal_bf16(rng, (rows, qh, 256))
+    kc = synth.cache_bits(rng, kvh, ctx); vc = synth.cache_bits(rng, kvh, ctx)
+    n_rh = rows * qh
+    with Bufs(be) as B:
+        qb, _ = B.shared(q); gb, _ = B.shared(gate)
+        kcb = B.device(kc); vcb = B.device(vc)
+        pa, _ = B.shared_empty((shards, n_rh, 256), np.float32); ps, psv = B.shared_empty((shards, n_rh, 2), np.float32)
+        ob, ov = B.shared_empty((rows, qh, 256), np.float32)
+        c = be.cmd_begin()
+        for i in range(shards):
+            lo, hi = sharding.seq_range(i, shards, base + rows)
+            assert be.op_attn_partial(c, QwRef(pa, i * n_rh * 256 * 4), QwRef(ps, i * n_rh * 2 * 4), QwRef(qb, 0), QwRef(kcb, 0),
+                                      QwRef(vcb, 0), rows, qh, kvh, 256, ctx, base, lo, hi, 0.0625, F32), (i, lo, hi)
+        be.op_attn_merge(c, QwRef(ob, 0), QwRef(pa, 0), QwRef(ps, 0), QwRef(gb, 0), rows, qh, 256, shards, 256, F32, F32, 0)
+        be.cmd_wait(c); be.cmd_free(c)
+        assert np.all(np.array(psv)[2:, :, 1] == 0.0)
+        got = np.array(ov)
+    want = oracle.mul_sigmoid(oracle.attn_decode(q, kc, vc, rows, qh, kvh, 256, ctx, base, 0.0625), gate)
+    assert max_rel_err(got, want) <= 1e-2

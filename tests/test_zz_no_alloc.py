@@ -22,7 +22,7 @@ from qwasar_b200 import synth
 pytestmark = pytest.mark.gpu
 
 
-def both_ways(be, B, q, kc, vc, rows, qh, kvh, ctx, base):
+def both_ways(be, B, q, kc, vc, rows, qh, kvh, ctx, base, use_stream=False):
     """(existing entry point's output, new entry point's output) for one decode step."""
     qb = B.device(q)
     kcb = B.device(kc); vcb = B.device(vc)
@@ -34,11 +34,13 @@ def both_ways(be, B, q, kc, vc, rows, qh, kvh, ctx, base):
     be.cmd_wait(c); be.cmd_free(c)
     err = C.create_string_buffer(256)
     dp = be.lib.qw_buf_device_ptr
-    ok = be.lib.qw_attn_decode_noalloc(dp(o_new), dp(qb), None, dp(kcb), dp(vcb), rows, qh, kvh, 256, ctx, base,
-                                       synth.SCALE, F32, None, err, 256)
-    assert ok, err.value.decode()
     import torch
+    stream = torch.cuda.Stream() if use_stream else None
+    ok = be.lib.qw_attn_decode_noalloc(dp(o_new), dp(qb), None, dp(kcb), dp(vcb), rows, qh, kvh, 256, ctx, base,
+                                       synth.SCALE, F32, stream.cuda_stream if stream else None, err, 256)
+    assert ok, err.value.decode()
     torch.cuda.synchronize()
+    assert be.lib.qw_attn_decode_noalloc_status() == 0          # no kernel gave up on a wait
     a = np.empty((rows, qh, 256), np.float32); b = np.empty_like(a)
     be.buf_download(o_old, 0, a); be.buf_download(o_new, 0, b)
     return a, b
@@ -49,11 +51,12 @@ def test_noalloc_matches_pooled_entry_point_twice(be, oracle):
     rng = np.random.default_rng(2024)
     with Bufs(be) as B:
         # first call: one token deep in a 27B-shaped cache; second call: other depth, grouping and rows
-        for rows, qh, kvh, base in ((1, 24, 4, 5000), (2, 16, 2, 777)):
+        # (the second on a stream of the caller's instead of the default stream)
+        for call, (rows, qh, kvh, base) in enumerate(((1, 24, 4, 5000), (2, 16, 2, 777))):
             ctx = base + rows + 5
             q = synth.normal_bf16(rng, (rows, qh, 256))
             kc = synth.cache_bits(rng, kvh, ctx); vc = synth.cache_bits(rng, kvh, ctx)
-            old, new = both_ways(be, B, q, kc, vc, rows, qh, kvh, ctx, base)
+            old, new = both_ways(be, B, q, kc, vc, rows, qh, kvh, ctx, base, use_stream=call == 1)
             assert np.isfinite(new).all()
             assert max_rel_err(new, old) <= 1e-2 and rel_l2(new, old) < 5e-3
             want = oracle.attn_decode(q, kc, vc, rows, qh, kvh, 256, ctx, base, synth.SCALE)
@@ -95,3 +98,6 @@ def test_noalloc_rejects_what_does_not_fit(be):
         assert b"head_dim" in err.value
         assert not be.lib.qw_attn_decode_noalloc(p, p, None, p, p, 1, 24, 4, 256, 64, 64, 0.0625, F32, None, err, 256)
         assert b"outside the cache" in err.value
+        # 128 kv heads: one partial slot per (SM or kv head) x 16 rows of 1032 bytes no longer fits the 4 MiB
+        assert not be.lib.qw_attn_decode_noalloc(p, p, None, p, p, 1, 128, 128, 256, 64, 0, 0.0625, F32, None, err, 256)
+        assert b"bytes of scratch" in err.value

@@ -297,3 +297,65 @@ class RefCpu:
         out = self.attn_decode(q, kc, vc, rows, q_heads, kv_heads, head_dim, max_ctx, base_pos,
                                scale, threads=threads or self.max_threads)
         return out, gate, q, kk
+
+
+class RefFlash:
+    """One synthetic attention layer run by the reference's own qwasar_flash_cpu.c
+    (oracle/_ref/libqwflashcpu.so, built by oracle/Makefile around ref_flash_driver.c): its block
+    selection `qsa_select` (qwasar_flash_cpu.c:346-418) and its composed gated-attention layer
+    `qsa_step` (:422-488), fed through 4-bit affine projections as in a bound engine."""
+
+    @staticmethod
+    def available() -> bool:
+        return os.path.exists(os.path.join(HERE, "_ref", "libqwflashcpu.so"))
+
+    def __init__(self, *, hidden, hidden_out, q_heads, kv_heads, head_dim, idx_heads, idx_dim, budget, ratio, max_ctx,
+                 proj, norms, rotary_dim=64, theta=1e7, section=(11, 11, 10), eps=1e-6, group=64):
+        """proj: dict name -> (weight uint32 [out, in/8], scales uint16 [out, in/group], biases uint16) for
+        q_proj, k_proj, v_proj, o_proj, qk_proj; norms: dict name -> uint16 [dim] or None for q_norm, k_norm,
+        idx_q_norm, idx_k_norm."""
+        L = self.lib = _load(os.path.join(HERE, "_ref", "libqwflashcpu.so"))
+        self.keep = []
+        ptrs = []
+        for name in ("q_proj", "k_proj", "v_proj", "o_proj", "qk_proj"):
+            for a, dt in zip(proj[name], (np.uint32, np.uint16, np.uint16)):
+                a = np.ascontiguousarray(a, dt); self.keep.append(a); ptrs.append(a.ctypes.data)
+        nptrs = []
+        for name in ("q_norm", "k_norm", "idx_q_norm", "idx_k_norm"):
+            a = norms.get(name)
+            if a is None:
+                nptrs.append(None)
+            else:
+                a = np.ascontiguousarray(a, np.uint16); self.keep.append(a); nptrs.append(a.ctypes.data)
+        P = (C.c_void_p * 15)(*ptrs); N = (C.c_void_p * 4)(*nptrs)
+        sec = np.asarray(section, np.int32)
+        L.qwflash_new.restype = C.c_void_p
+        L.qwflash_new.argtypes = [C.c_int] * 6 + [C.c_float, C.c_void_p] + [C.c_int] * 4 + [C.c_float, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        self.h = L.qwflash_new(hidden, hidden_out, q_heads, kv_heads, head_dim, rotary_dim, theta, sec.ctypes.data, idx_heads, idx_dim,
+                               budget, ratio, eps, max_ctx, group, P, N)
+        L.qwflash_free.argtypes = [C.c_void_p]
+        L.qwflash_select.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.qwflash_step.argtypes = [C.c_void_p, C.c_void_p, C.c_int] + [C.c_void_p] * 4
+        self.dims = dict(hidden=hidden, hidden_out=hidden_out, q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim,
+                         idx_heads=idx_heads, idx_dim=idx_dim)
+
+    def select(self, x, pos):
+        """(allowed uint8 [pos + 1], qk f32 [(idx_heads + 1) * idx_dim]) for the token at pos; feed positions in order."""
+        d = self.dims
+        x = np.ascontiguousarray(x, np.float32)
+        allowed = np.zeros(pos + 1, np.uint8); qk = np.zeros((d["idx_heads"] + 1) * d["idx_dim"], np.float32)
+        self.lib.qwflash_select(self.h, x.ctypes.data, pos, allowed.ctypes.data, qk.ctypes.data)
+        return allowed, qk
+
+    def step(self, x, pos):
+        """(out [hidden_out], qg [q_heads, 2 * head_dim], k, v [kv_heads, head_dim]) for the token at pos, in order."""
+        d = self.dims
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.zeros(d["hidden_out"], np.float32); qg = np.zeros((d["q_heads"], 2 * d["head_dim"]), np.float32)
+        k = np.zeros((d["kv_heads"], d["head_dim"]), np.float32); v = np.zeros_like(k)
+        self.lib.qwflash_step(self.h, x.ctypes.data, pos, out.ctypes.data, qg.ctypes.data, k.ctypes.data, v.ctypes.data)
+        return out, qg, k, v
+
+    def close(self):
+        if self.h:
+            self.lib.qwflash_free(self.h); self.h = None

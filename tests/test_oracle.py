@@ -285,3 +285,86 @@ def test_q4_product_is_the_reference_function(oracle, refcpu, k, n, rows, group)
     w, sc, bi = q4_weights(rng, n, k, group)
     x = rng.standard_normal((rows, k)).astype(np.float32)
     assert np.array_equal(oracle.qmv_q4(x, w, sc, bi, k, n, rows, group), refcpu.qmv_q4(x, w, sc, bi, k, n, rows, group))
+
+
+# ---- the reference's own block selection and composed layer (qwasar_flash_cpu.c) ------------------
+def _q4(rng, n, k, group=64, scale=0.02):
+    w = rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32)
+    sc = synth.f32_to_bf16_bits((scale * rng.standard_normal((n, k // group))).astype(np.float32))
+    bi = synth.f32_to_bf16_bits((-7.5 * scale * (1 + 0.1 * rng.standard_normal((n, k // group)))).astype(np.float32))
+    return w, sc, bi
+
+
+def _identity_q4(n, group=64):
+    """A 4-bit affine matrix that is exactly the identity: nibble 1 on the diagonal, scale 1, bias 0."""
+    w = np.zeros((n, n // 8), np.uint32)
+    for i in range(n):
+        w[i, i // 8] = np.uint32(1) << np.uint32(4 * (i % 8))
+    return w, np.full((n, n // group), 0x3F80, np.uint16), np.zeros((n, n // group), np.uint16)
+
+
+def _flash_layer(rng, *, q_heads, kv_heads, idx_heads, idx_dim, budget, ratio, max_ctx, hidden=256):
+    from oracle.oracle import RefFlash
+    if not RefFlash.available():
+        pytest.skip("oracle/_ref/libqwflashcpu.so not built (needs the reference checkout at build time)")
+    norm = lambda n: synth.f32_to_bf16_bits((1.0 + 0.2 * rng.standard_normal(n)).astype(np.float32))
+    proj = {"q_proj": _q4(rng, q_heads * 512, hidden), "k_proj": _q4(rng, kv_heads * 256, hidden),
+            "v_proj": _q4(rng, kv_heads * 256, hidden), "o_proj": _identity_q4(q_heads * 256),
+            "qk_proj": _q4(rng, (idx_heads + 1) * idx_dim, hidden)}
+    norms = {"q_norm": norm(256), "k_norm": norm(256), "idx_q_norm": norm(idx_dim), "idx_k_norm": norm(idx_dim)}
+    fl = RefFlash(hidden=hidden, hidden_out=q_heads * 256, q_heads=q_heads, kv_heads=kv_heads, head_dim=256, idx_heads=idx_heads,
+                  idx_dim=idx_dim, budget=budget, ratio=ratio, max_ctx=max_ctx, proj=proj, norms=norms)
+    return fl, norms
+
+
+@pytest.mark.parametrize("ratio,topk,idx_dim", [(4, 3, 128), (2, 5, 64), (8, 2, 128)])
+def test_qsa_select_is_the_reference_function(oracle, refcpu, ratio, topk, idx_dim):
+    """orc_qsa_scores + orc_qsa_select against the reference's own qsa_select, token by token over a
+    growing context: the same mask of visible positions at every step.  The reference's selection is
+    a repeated arg-max with the lowest index among equals; blocks whose heads all score <= 0 tie at
+    exactly 0, and the last tokens here are zero vectors, which ties every block."""
+    rng = np.random.default_rng(ratio * 100 + topk)
+    nq, P, hidden = 4, 70, 256
+    fl, norms = _flash_layer(rng, q_heads=2, kv_heads=1, idx_heads=nq, idx_dim=idx_dim, budget=topk * ratio, ratio=ratio, max_ctx=P)
+    axis, inv = refcpu.rope_tables(64, 1e7, (11, 11, 10))
+    ikeys = np.zeros((P, idx_dim), np.float32)
+    ties = 0
+    for pos in range(P):
+        x = rng.standard_normal(hidden).astype(np.float32) if pos < P - 6 else np.zeros(hidden, np.float32)
+        allowed, qk = fl.select(x, pos)
+        ikeys[pos] = qk[nq * idx_dim:]
+        qn = refcpu.rms_norm(qk[:nq * idx_dim].reshape(nq, idx_dim), norms["idx_q_norm"], idx_dim, nq, 1e-6)
+        qn = refcpu.rope_partial(qn, np.full((3, 1), pos, np.int32), axis, inv, 1, nq, idx_dim, 64)
+        max_blocks = (P + ratio - 1) // ratio
+        scores, _ = oracle.qsa_scores(qn, ikeys[:pos + 1], norms["idx_k_norm"], inv, 1, nq, idx_dim, ratio, pos, 64, max_blocks, 1e-6)
+        mask, lists = oracle.qsa_select(scores, 1, ratio, pos, topk, P)
+        assert np.array_equal(mask[0, :pos + 1], allowed), f"position {pos}"
+        n_blocks = (pos + 1) // ratio
+        ties += int(n_blocks > topk and len(np.unique(scores[0, :n_blocks])) < n_blocks)
+        cnt = int(lists[0, 0])
+        assert np.array_equal(lists[0, 1:1 + cnt], np.flatnonzero(allowed))
+    assert ties > 3, "the case was meant to contain tied block scores"
+    fl.close()
+
+
+def test_attn_layer_is_the_reference_composition(oracle):
+    """orc_attn_layer against the reference's own composed gated-attention layer, qsa_step, one token
+    at a time (its cached path): projections -> split [q|gate] -> norms -> RoPE -> append -> attention
+    over every position (the budget covers them all) -> sigmoid gate, read through an identity o_proj.
+    qsa_step keeps its K/V cache in fp32 where this build rounds to bf16, hence a tolerance."""
+    rng = np.random.default_rng(31)
+    qh, kvh, P, hidden = 4, 2, 40, 256
+    fl, norms = _flash_layer(rng, q_heads=qh, kv_heads=kvh, idx_heads=2, idx_dim=64, budget=4096, ratio=4, max_ctx=P)
+    axis, inv = oracle.rope_tables()
+    kc = np.zeros((kvh, P, 256), np.uint16); vc = np.zeros((kvh, P, 256), np.uint16)
+    worst = 0.0
+    for pos in range(P):
+        x = rng.standard_normal(hidden).astype(np.float32)
+        out, qg, k, v = fl.step(x, pos)
+        got = oracle.attn_layer(qg[None], k[None], v[None], norms["q_norm"], norms["k_norm"], np.full((3, 1), pos, np.int32), axis, inv,
+                                kc, vc, 1, qh, kvh, 256, 64, P, pos, 1e-6, 0.0625)
+        want = out.reshape(1, qh, 256)
+        err = np.sqrt(np.sum((got - want) ** 2) / np.sum(want ** 2))
+        worst = max(worst, float(err))
+    assert worst < 4e-3, worst
+    fl.close()

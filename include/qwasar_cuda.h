@@ -115,6 +115,10 @@ void qw_rope_tables(uint8_t *axis, float *inv_freq, int32_t rotary_dim,
 /* qwasar_gpu.h:385.  y[i] *= sigmoid(gate[i]). */
 void qw_op_mul_sigmoid(qw_cmd c, qw_ref y, qw_ref gate, int32_t n);
 
+/* qwasar_gpu.h:387-389.  dst[r, 0:len] = src[r, offset:offset+len], f32 rows of src_stride floats:
+ * how the Flash-Next attention layer takes the indexer's key and query heads out of their joint
+ * projection (qwasar_flash_graph.c:446-452). */
+void qw_op_slice_rows(qw_cmd c, qw_ref dst, qw_ref src, int32_t rows, int32_t src_stride, int32_t offset, int32_t len);
 /* qwasar_gpu.h:402-406.  Appends rows of K and V at base_pos, rounding to the
  * cache type (bf16, round-to-nearest-even).  The cache refs address one layer:
  * either a plain buffer holding the reference's head-major
@@ -233,8 +237,9 @@ uint64_t    qw_gpu_launch_count(void);
  * qwasar_metal.m:1513-1516): "split_kg" = 4 | 6, consumer warps per 16-row tile of the
  * split-KV kernel; "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
  * split-KV kernel over row chunks; "prefill_fuse_q" = 1 | 0, with bf16 rows the tcgen05 prefill norms and
- * rotates its own query tiles (default) or the pre-op kernel does.  Returns false for an unknown
- * knob or value. */
+ * rotates its own query tiles (default) or the pre-op kernel does; "pdl" = 1 | 0, the kernels of the
+ * decode chain start under the kernel in front of them (programmatic dependent launch, default) or in
+ * plain stream order.  Returns false for an unknown knob or value. */
 bool        qw_gpu_tune(const char *knob, int32_t value);
 /* How the split-KV decode kernel divides a launch of n_seq sequences (n_keys[i] keys each, kv_heads
  * heads) over at most n_cta_max CTAs: all (sequence, kv head) groups are laid end to end as one line

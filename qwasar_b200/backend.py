@@ -54,6 +54,7 @@ SIGNATURES = {
     "qw_op_rope_partial": (None, [_vp, QwRef, QwRef, QwRef, QwRef, _i32, _i32, _i32, _i32]),
     "qw_rope_tables": (None, [_vp, _vp, _i32, _f32, _vp]),
     "qw_op_mul_sigmoid": (None, [_vp, QwRef, QwRef, _i32]),
+    "qw_op_slice_rows": (None, [_vp, QwRef, QwRef, _i32, _i32, _i32, _i32]),
     "qw_op_kv_write": (None, [_vp, QwRef, QwRef, QwRef, QwRef, _i32, _i32, _i32, _i32, _i32]),
     "qw_op_attn_decode": (None, _ATTN),
     "qw_op_attn_prefill": (_b, _ATTN),

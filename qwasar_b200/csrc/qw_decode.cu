@@ -242,34 +242,59 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 // Raw rows of the [q|gate] projection: per-head RMS norm and partial RoPE here, in the
                 // arithmetic of the pre-op kernel (qwasar_cpu.c:68-82, 304-319), one warp per row, lane l
                 // holding dims 8l .. 8l+7.  The rows' cos / sin (one angle per lane) go through the
-                // reduction buffer, which is idle until the segment ends.
+                // reduction buffer, which is idle until the segment ends.  The first rows are requested
+                // before the angles are worked out, so the two trips to memory overlap.
+                constexpr int PF = 4;                              // rows a warp has in flight
                 float *cs = red;
-                for (int r = warp; r < sq.rows; r += NW) {
-                    const int ax = p.axis[lane];
-                    const float ang = __fmul_rn((float)sq.pos[(size_t)ax * sq.pos_stride + r], p.inv_freq[lane]);
-                    float sn, cn;
-                    sincosf(ang, &sn, &cn);
-                    cs[r * 64 + lane] = cn; cs[r * 64 + 32 + lane] = sn;
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+                uint4 raw[PF][2];
+                auto fetch = [&](int row, uint4 (&r2)[2]) {
+                    r2[0] = make_uint4(0, 0, 0, 0); r2[1] = r2[0];
+                    if (row >= valid_rows) return;
+                    const int r = row / p.gqa, g = row - r * p.gqa;
+                    const size_t src = ((size_t)r * p.q_heads + head0 + g) * 512 + lane * 8;
+                    if (p.q_dtype == DT_BF16) {
+                        r2[0] = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(sq.q) + src));
+                    } else {
+                        const uint4 *g4 = reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(sq.q) + src);
+                        r2[0] = __ldg(g4); r2[1] = __ldg(g4 + 1);
+                    }
+                };
+#pragma unroll
+                for (int u = 0; u < PF; u++) fetch(warp + u * NW, raw[u]);
                 uint4 w4 = make_uint4(0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u);
                 if (p.q_norm_w) w4 = __ldg(reinterpret_cast<const uint4 *>(p.q_norm_w) + lane);
+                {
+                    // the token's position on all three axes and the dim's axis side by side (a position
+                    // looked up through the axis would be a second trip to memory)
+                    const int ax = p.axis[lane];
+                    const float fr = p.inv_freq[lane];
+                    for (int r = warp; r < sq.rows; r += NW) {
+                        const int32_t p0 = sq.pos[r], p1 = sq.pos[(size_t)sq.pos_stride + r], p2 = sq.pos[(size_t)2 * sq.pos_stride + r];
+                        const float ang = __fmul_rn((float)(ax == 0 ? p0 : ax == 1 ? p1 : p2), fr);
+                        // cos / sin of the fp32 angle (it reaches 2^18 rad): the remainder modulo 2 pi in
+                        // double precision, good to 1e-10, then the fast functions on [-pi, pi] (2^-21) --
+                        // far below the bf16 rounding the query gets next
+                        const double turns = rint((double)ang * 0.15915494309189535);
+                        const float rem = (float)fma(turns, -6.283185307179586, (double)ang);
+                        float sn, cn;
+                        __sincosf(rem, &sn, &cn);
+                        cs[r * 64 + lane] = cn; cs[r * 64 + 32 + lane] = sn;
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
                 const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
-                for (int row = warp; row < MT * 16; row += NW) {
+                auto finish = [&](int row, const uint4 (&r2)[2]) {
                     uint4 val = make_uint4(0, 0, 0, 0);
                     if (row < valid_rows) {
-                        const int r = row / p.gqa, g = row - r * p.gqa;
-                        const size_t src = ((size_t)r * p.q_heads + head0 + g) * 512 + lane * 8;
+                        const int r = row / p.gqa;
                         float x[8];
                         if (p.q_dtype == DT_BF16) {
-                            const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(sq.q) + src));
-                            const uint32_t xw[4] = {raw.x, raw.y, raw.z, raw.w};
+                            const uint32_t xw[4] = {r2[0].x, r2[0].y, r2[0].z, r2[0].w};
 #pragma unroll
                             for (int i = 0; i < 4; i++) { x[2 * i] = __uint_as_float(xw[i] << 16); x[2 * i + 1] = __uint_as_float(xw[i] & 0xffff0000u); }
                         } else {
-                            const float4 a = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src));
-                            const float4 b = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(sq.q) + src + 4));
-                            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+                            x[0] = __uint_as_float(r2[0].x); x[1] = __uint_as_float(r2[0].y); x[2] = __uint_as_float(r2[0].z); x[3] = __uint_as_float(r2[0].w);
+                            x[4] = __uint_as_float(r2[1].x); x[5] = __uint_as_float(r2[1].y); x[6] = __uint_as_float(r2[1].z); x[7] = __uint_as_float(r2[1].w);
                         }
                         float ss = 0.0f;
 #pragma unroll
@@ -295,6 +320,15 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                         val = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
                     }
                     *reinterpret_cast<uint4 *>(q_s + (lane >> 3) * (MT * 16 * 128) + swz128(row, (lane & 7) * 8)) = val;
+                };
+                for (int row0 = warp; row0 < MT * 16; row0 += NW * PF) {
+                    if (row0 != warp) {
+#pragma unroll
+                        for (int u = 0; u < PF; u++) fetch(row0 + u * NW, raw[u]);
+                    }
+#pragma unroll
+                    for (int u = 0; u < PF; u++)
+                        if (row0 + u * NW < MT * 16) finish(row0 + u * NW, raw[u]);
                 }
             } else
             for (int idx = warp * 32 + lane; idx < MT * 16 * 32; idx += NW * 32) {
@@ -891,7 +925,7 @@ void pdl_config(cudaLaunchConfig_t &cfg, cudaLaunchAttribute &attr, unsigned gri
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg = cudaLaunchConfig_t();
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(block); cfg.dynamicSmemBytes = smem; cfg.stream = s;
-    cfg.attrs = &attr; cfg.numAttrs = 1;
+    cfg.attrs = &attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
 }
 
 template <int MT, int KG>
@@ -922,6 +956,7 @@ unsigned long long g_launches = 0;
 int g_tune_split_kg = 6;
 int g_tune_prefill_tc = 1;
 int g_tune_prefill_fuse_q = 1;
+int g_tune_pdl = 1;
 
 int sm_count() {
     static int n[64] = {0};                    // per device

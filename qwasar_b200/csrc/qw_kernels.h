@@ -40,6 +40,7 @@ void launch_mul_sigmoid(cudaStream_t s, float *y, const float *gate, int64_t n);
 // One layer between the cache and the packed layout [kv_heads][K rows | V rows][n_tokens][256] bf16.
 void launch_kv_pack(cudaStream_t s, KvLayer kc, KvLayer vc, void *packed, int kv_heads, int n_tokens, bool unpack);
 void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, int64_t n);
+void launch_slice_rows(cudaStream_t s, float *dst, const float *src, int rows, int src_stride, int offset, int len);
 
 // One sequence of the fused pre-op: split [q|gate], RMS-norm q and k, partial RoPE,
 // round and append K/V, leave the normed+roped query as bf16.
@@ -188,5 +189,8 @@ extern int g_tune_split_kg;
 extern int g_tune_prefill_tc;
 // 1: with bf16 rows the tcgen05 prefill norms and rotates its own query tiles; 0: the pre-op does.
 extern int g_tune_prefill_fuse_q;
+// 1: the kernels of the decode chain are launched as programmatic dependents (they may start under
+// the kernel in front of them); 0: plain stream order, for comparison.
+extern int g_tune_pdl;
 
 }  // namespace qw

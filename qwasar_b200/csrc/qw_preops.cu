@@ -90,6 +90,14 @@ __global__ void mul_sigmoid_kernel(float *__restrict__ y, const float *__restric
     if (i < n) y[i] = __fmul_rn(y[i], __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g[i]))));
 }
 
+// dst[r, 0:len] = src[r, offset:offset+len] over rows of src_stride floats (qwasar_gpu.h:387-389)
+__global__ void slice_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, int64_t n, int src_stride, int offset, int len) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t r = i / len;
+    dst[i] = src[r * src_stride + offset + (i - r * len)];
+}
+
 __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float *__restrict__ src, int64_t n) {
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i + 3 < n) {
@@ -146,6 +154,7 @@ __global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, ui
 constexpr int PRE_ROWS = QW_PRE_ROWS;
 __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
+    __shared__ __align__(16) float sq_s[8][PRE_ROWS][260];   // squares of the key rows (row stride 260: lanes on distinct banks)
     // Dependent launch: this kernel reads the projections and writes the cache, so it waits for
     // everything in front of it first; the attention kernel behind it may then start at once (it
     // waits itself before it touches the rows appended here).
@@ -215,12 +224,7 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
 #pragma unroll
         for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(ww[i] << 16); w[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }
     }
-#pragma unroll
-    for (int u = 0; u < PRE_ROWS; u++) {
-        if (u >= n || dst_row[u] < 0) continue;          // warp-uniform
-        uint4 *out = reinterpret_cast<uint4 *>(dst + dst_row[u] * 256) + lane;
-        if (!is_q && !is_k && p.io_dtype == DT_BF16) { *out = raw[u][0]; continue; }      // V, already bf16: a copy
-        float x[8];
+    auto unpack = [&](int u, float (&x)[8]) {
         if (p.io_dtype == DT_BF16) {
             const uint32_t xw[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
 #pragma unroll
@@ -229,25 +233,44 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
             x[0] = __uint_as_float(raw[u][0].x); x[1] = __uint_as_float(raw[u][0].y); x[2] = __uint_as_float(raw[u][0].z); x[3] = __uint_as_float(raw[u][0].w);
             x[4] = __uint_as_float(raw[u][1].x); x[5] = __uint_as_float(raw[u][1].y); x[6] = __uint_as_float(raw[u][1].z); x[7] = __uint_as_float(raw[u][1].w);
         }
+    };
+    // Key rows: the squares are added left to right over the 256 dims like the CPU loop
+    // (qwasar_cpu.c:70-72).  A row's squares go through shared memory so that ONE lane walks them in
+    // order -- lane u takes row u of this warp, the warp's rows side by side -- which costs a
+    // fraction of the instructions of a sum handed from lane to lane.
+    float ss_k[PRE_ROWS];
+    if (is_k) {
+#pragma unroll
+        for (int u = 0; u < PRE_ROWS; u++) {
+            if (u >= n || dst_row[u] < 0) continue;      // warp-uniform
+            float x[8];
+            unpack(u, x);
+            float4 *sq = reinterpret_cast<float4 *>(&sq_s[warp][u][lane * 8]);
+            sq[0] = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]), __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+            sq[1] = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]), __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
+        }
+        __syncwarp();
+        float acc = 0.0f;
+        if (lane < n) {
+            const float *sq = sq_s[warp][lane];
+#pragma unroll 16
+            for (int i = 0; i < 256; i++) acc = __fadd_rn(acc, sq[i]);
+        }
+#pragma unroll
+        for (int u = 0; u < PRE_ROWS; u++) ss_k[u] = __shfl_sync(0xffffffffu, acc, u);
+    }
+#pragma unroll
+    for (int u = 0; u < PRE_ROWS; u++) {
+        if (u >= n || dst_row[u] < 0) continue;          // warp-uniform
+        uint4 *out = reinterpret_cast<uint4 *>(dst + dst_row[u] * 256) + lane;
+        if (!is_q && !is_k && p.io_dtype == DT_BF16) { *out = raw[u][0]; continue; }      // V, already bf16: a copy
+        float x[8];
+        unpack(u, x);
         if (is_q || is_k) {
             // RMS norm (qwasar_cpu.c:68-82), then the weight
             float ss = 0.0f;
             if (is_k) {
-                // key rows: the squares are added left to right over the 256 dims like the CPU loop --
-                // lane l continues the sum of lane l - 1 with its own eight
-                float sq[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) sq[i] = __fmul_rn(x[i], x[i]);
-#pragma unroll 1
-                for (int st = 0; st < 32; st++) {
-                    const float carry = __shfl_sync(0xffffffffu, ss, (st + 31) & 31);
-                    if (lane == st) {
-                        ss = st ? carry : 0.0f;
-#pragma unroll
-                        for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, sq[i]);
-                    }
-                }
-                ss = __shfl_sync(0xffffffffu, ss, 31);
+                ss = ss_k[u];
             } else {
 #pragma unroll
                 for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
@@ -315,6 +338,12 @@ void launch_mul_sigmoid(cudaStream_t s, float *y, const float *gate, int64_t n) 
     mul_sigmoid_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, gate, n);
     g_launches++;
 }
+void launch_slice_rows(cudaStream_t s, float *dst, const float *src, int rows, int src_stride, int offset, int len) {
+    const int64_t n = (int64_t)rows * len;
+    if (n <= 0) return;
+    slice_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(dst, src, n, src_stride, offset, len);
+    g_launches++;
+}
 void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, int64_t n) {
     if (n <= 0) return;
     f32_to_bf16_kernel<<<(unsigned)((n + 1023) / 1024), 256, 0, s>>>(dst, src, n);
@@ -330,7 +359,7 @@ void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
     cfg.gridDim = dim3((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
     cfg.blockDim = dim3(256);
     cfg.stream = s;
-    cfg.attrs = &attr; cfg.numAttrs = 1;
+    cfg.attrs = &attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, preop_kernel, p);
     g_launches++;
 }

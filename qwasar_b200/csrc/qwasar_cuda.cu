@@ -783,6 +783,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "split_kg") && (value == 4 || value == 6)) { qw::g_tune_split_kg = value; return true; }
     if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
+    if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     return false;
 }
 // How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
@@ -1257,6 +1258,15 @@ extern "C" void qw_op_mul_sigmoid(qw_cmd c, qw_ref y, qw_ref gate, int32_t n) {
     launch_mul_sigmoid(c->stream, py, pg, n);
 }
 
+extern "C" void qw_op_slice_rows(qw_cmd c, qw_ref dst, qw_ref src, int32_t rows, int32_t src_stride, int32_t offset, int32_t len) {
+    if (!live(c) || rows <= 0 || len <= 0) return;
+    if (offset < 0 || offset + len > src_stride) { cmd_fail(c, "slice_rows: columns [%d, %d) outside rows of %d", offset, offset + len, src_stride); return; }
+    float *pd = (float *)dev_range(c, dst, (size_t)rows * len * 4, true, 4);
+    const float *ps = (const float *)dev_range(c, src, ((size_t)(rows - 1) * src_stride + offset + len) * 4, false, 4);
+    if (!pd || !ps) return;
+    launch_slice_rows(c->stream, pd, ps, rows, src_stride, offset, len);
+}
+
 extern "C" void qw_op_kv_write(qw_cmd c, qw_ref kcache, qw_ref vcache, qw_ref k, qw_ref v, int32_t rows, int32_t kv_heads,
                                int32_t head_dim, int32_t max_ctx, int32_t base_pos) {
     if (!live(c) || rows <= 0) return;
@@ -1650,7 +1660,7 @@ bool fused_batch(qw_cmd c, const FusedSeq *seqs, int n_seq, qw_ref q_norm_w, qw_
         p.axis = (const uint8_t *)dev_range(c, axis, 32, false, 1);
         p.inv_freq = (const float *)dev_range(c, inv_freq, 128, false, 4);
         if (!p.axis || !p.inv_freq || (q_norm_w.buf && !p.q_norm_w)) return false;
-        b.early_next = !SH.time_kernels;        // (event records between the kernels would serialise them anyway)
+        b.early_next = !SH.time_kernels && g_tune_pdl;        // (event records between the kernels would serialise them anyway)
         for (int i = 0; i < ns; i++) {
             const FusedSeq &fs = seqs[s0 + i];
             KvLayer kc, vc;

@@ -59,7 +59,7 @@ static const any_fn all_symbols[] = {
     (any_fn)qw_buf_contents, (any_fn)qw_buf_length, (any_fn)qw_cmd_begin, (any_fn)qw_cmd_commit,
     (any_fn)qw_cmd_wait, (any_fn)qw_cmd_flush, (any_fn)qw_cmd_parallel, (any_fn)qw_cmd_free,
     (any_fn)qw_cmd_error, (any_fn)qw_prof_enabled, (any_fn)qw_prof_report, (any_fn)qw_prof_reset, (any_fn)qw_cmd_mark, (any_fn)qw_op_split_heads2,
-    (any_fn)qw_op_rms_norm, (any_fn)qw_op_rope_partial, (any_fn)qw_rope_tables, (any_fn)qw_op_kv_write,
+    (any_fn)qw_op_rms_norm, (any_fn)qw_op_rope_partial, (any_fn)qw_rope_tables, (any_fn)qw_op_kv_write, (any_fn)qw_op_slice_rows,
     (any_fn)qw_op_attn, (any_fn)qw_op_attn_decode, (any_fn)qw_op_attn_prefill, (any_fn)qw_op_attn_prefill_as,
     (any_fn)qw_op_attn_decode_split, (any_fn)qw_op_attn_decode_tensor, (any_fn)qw_op_mul_sigmoid,
     (any_fn)qw_op_attn_masked, (any_fn)qw_op_attn_masked_gated, (any_fn)qw_op_qsa_scores, (any_fn)qw_op_qsa_pool,

@@ -14,7 +14,10 @@ STUB(qw_op_silu_scale) STUB(qw_op_rms_norm_gated_sigmoid) STUB(qw_op_rms_norm_ga
 STUB(qw_op_repeat_cols) STUB(qw_op_qmv_q4_bank2) STUB(qw_op_ple_gate) STUB(qw_op_moe_route) STUB(qw_op_moe_group)
 STUB(qw_op_moe_combine_shared) STUB(qw_op_hc_mix_up) STUB(qw_op_hc_mix) STUB(qw_op_hc_inject_norm) STUB(qw_op_hc_inject)
 STUB(qw_op_gdn_gates) STUB(qw_op_gated_delta_prep) STUB(qw_op_gated_delta) STUB(qw_op_conv1d_dilated_silu)
-STUB(qw_op_conv1d_causal_silu) STUB(qw_moe_max_tiles)
+STUB(qw_op_conv1d_causal_silu)
+/* Only sizes a scratch buffer of the MoE layers at session creation (qwasar_flash_graph.c:122): an
+ * upper bound for any tile height is one tile per pair plus one per expert. */
+int qw_moe_max_tiles(int pairs, int experts) { return pairs + experts; }
 void *qw_residency_new(void *bufs, int n) { (void)bufs; (void)n; return NULL; }
 void qw_residency_free(void *r) { (void)r; }
 

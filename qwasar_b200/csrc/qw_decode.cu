@@ -799,33 +799,84 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
     }
 }
 
-// ---- merge of partials that arrive from outside (other GPUs) ---------------------------
-// pacc [parts, n_rh, 256], pstat [parts, n_rh, 2] (max in natural units, sum).
-__global__ void __launch_bounds__(64) merge_parts_kernel(void *out, int out_dtype, const float *__restrict__ pacc,
-                                                         const float *__restrict__ pstat, const void *gate,
-                                                         int gate_dtype, int gate_stride, int n_rh, int parts,
-                                                         float *pacc_out, float *pstat_out, size_t acc_stride,
-                                                         size_t stat_stride) {
+// ---- merge of partials laid out by part ------------------------------------------------------
+// pacc [parts, n_rh, 256], pstat [parts, n_rh, 2] (max in natural units, sum): partials gathered
+// from other GPUs, the slices of the per-query kernel, the chunks of the masked kernel.  One block
+// per (row, head); like qw_attn_merge_kernel it reads every (max, sum) pair at once -- one per
+// thread, in rounds of 256 -- and its four quarters of 64 threads x float4 each take every fourth
+// part with four loads in flight, because a walk through the parts is a trip to L2 per step.  A part
+// with sum 0 is not read at all (its accumulator may hold anything).
+__global__ void __launch_bounds__(256) merge_parts_kernel(void *out, int out_dtype, const float *__restrict__ pacc,
+                                                          const float *__restrict__ pstat, const void *gate,
+                                                          int gate_dtype, int gate_stride, int n_rh, int parts,
+                                                          float *pacc_out, float *pstat_out, size_t acc_stride,
+                                                          size_t stat_stride) {
+    __shared__ float red_s[2][8];
+    __shared__ __align__(16) float acc_s[3][256];
+    extern __shared__ float w_dyn[];                          // parts weights
     const int rh = blockIdx.x;
-    const int d4 = threadIdx.x * 4;
-    float m = -3.0e38f;
-    for (int q = 0; q < parts; q++) {
-        const float *st = pstat + (size_t)q * stat_stride + (size_t)rh * 2;
-        if (st[1] > 0.0f) m = fmaxf(m, st[0]);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_launch_next();
+    pdl_wait();
+    float mq = -3.0e38f;
+    for (int q = tid; q < parts; q += 256) {
+        const float2 st = *reinterpret_cast<const float2 *>(pstat + (size_t)q * stat_stride + (size_t)rh * 2);
+        w_dyn[q] = st.y > 0.0f ? st.x : -3.0e38f;             // the part's max for now
+        if (st.y > 0.0f) mq = fmaxf(mq, st.x);
     }
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float m = warp_max(mq);
+    if (lane == 0) red_s[0][warp] = m;
+    __syncthreads();
+    m = red_s[0][0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) m = fmaxf(m, red_s[0][i]);
     float den = 0.0f;
-    for (int q = 0; q < parts; q++) {
-        const float *st = pstat + (size_t)q * stat_stride + (size_t)rh * 2;
-        const float l = st[1];
-        const float w = l > 0.0f ? __expf(st[0] - m) : 0.0f;
-        const float4 a = *reinterpret_cast<const float4 *>(pacc + (size_t)q * acc_stride + (size_t)rh * 256 + d4);
+    for (int q = tid; q < parts; q += 256) {
+        const float l = pstat[(size_t)q * stat_stride + (size_t)rh * 2 + 1];
+        const float w = l > 0.0f ? __expf(w_dyn[q] - m) : 0.0f;
+        w_dyn[q] = w;
         den += l * w;
-        acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+    }
+    den = warp_sum(den);
+    if (lane == 0) red_s[1][warp] = den;
+    __syncthreads();
+    den = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) den += red_s[1][i];
+
+    const int quarter = tid >> 6, d4 = (tid & 63) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *base = pacc + (size_t)rh * 256 + d4;
+    int q = quarter;
+    for (; q + 12 < parts; q += 16) {
+        float4 a[4];
+        float w[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            w[u] = w_dyn[q + 4 * u];
+            a[u] = w[u] > 0.0f ? *reinterpret_cast<const float4 *>(base + (size_t)(q + 4 * u) * acc_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) { acc.x += a[u].x * w[u]; acc.y += a[u].y * w[u]; acc.z += a[u].z * w[u]; acc.w += a[u].w * w[u]; }
+    }
+    for (; q < parts; q += 4) {
+        const float w = w_dyn[q];
+        if (w > 0.0f) {
+            const float4 a = *reinterpret_cast<const float4 *>(base + (size_t)q * acc_stride);
+            acc.x += a.x * w; acc.y += a.y * w; acc.z += a.z * w; acc.w += a.w * w;
+        }
+    }
+    if (quarter > 0) *reinterpret_cast<float4 *>(&acc_s[quarter - 1][d4]) = acc;
+    __syncthreads();
+    if (quarter > 0) return;
+#pragma unroll
+    for (int i = 0; i < 3; i++) {
+        const float4 o = *reinterpret_cast<const float4 *>(&acc_s[i][d4]);
+        acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
     }
     if (pacc_out) {
         *reinterpret_cast<float4 *>(pacc_out + (size_t)rh * 256 + d4) = acc;
-        if (threadIdx.x == 0) { pstat_out[rh * 2] = den > 0.0f ? m : -3.0e38f; pstat_out[rh * 2 + 1] = den; }
+        if (tid == 0) { pstat_out[rh * 2] = den > 0.0f ? m : -3.0e38f; pstat_out[rh * 2 + 1] = den; }
         return;
     }
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
@@ -843,6 +894,184 @@ __global__ void __launch_bounds__(64) merge_parts_kernel(void *out, int out_dtyp
         *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(out) + (size_t)rh * 256 + d4) = v;
     } else {
         *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + (size_t)rh * 256 + d4) = acc;
+    }
+}
+
+// ---- masked attention on tensor ops: the listed positions, gathered -----------------------------
+// What qw_op_attn_masked runs when a selection exists (qwasar_gpu.h:635-651; the reference's tensor
+// form is metal4/attn_tensor.metal:482-591): row r attends only the positions of its list.  The
+// list's capacity is cut into chunks of 64 entries; one CTA of four warps per (chunk, kv head, row),
+// a warp per 16 listed keys.  The keys' K and V rows are gathered from wherever they lie (plain
+// cache or paged arena) by 16-byte asynchronous copies -- all 32 rows of a warp in flight at once,
+// entries past the count or outside the cache arrive as zeros -- into the swizzled layout the
+// ldmatrix fragments expect; S = Q K^T and O = P V are m16n8k16 bf16 tensor ops for all query heads
+// of the kv head (rows 0 .. gqa-1 of the 16-row tile), the softmax is fp32, the four warps' (m, l, O)
+// are combined through shared memory, and the CTA leaves one partial per query head for
+// merge_parts_kernel.  The whole step is a few microseconds of latency, not bandwidth: 2 052 keys
+// are 4 MB.
+constexpr int AM_WARPS = 4, AM_KEYS = 16 * AM_WARPS;
+constexpr int AM_BOX = 16 * 128;                          // 16 keys x 64 dims bf16
+constexpr int AM_OFF_K = 0, AM_OFF_V = AM_WARPS * 4 * AM_BOX, AM_OFF_Q = 2 * AM_WARPS * 4 * AM_BOX;
+constexpr int AM_OFF_RED = AM_OFF_Q + 16 * 512, AM_OFF_M = AM_OFF_RED + 16 * RED_LD * 4, AM_OFF_L = AM_OFF_M + AM_WARPS * 16 * 4;
+constexpr int AM_SMEM = AM_OFF_L + 16 * 4 + 1024;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;                         // 0 bytes read: the 16 bytes arrive as zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+__global__ void __launch_bounds__(AM_WARPS * 32) attn_masked_mma_kernel(AttnSeq sq, int q_heads, int kv_heads, int gqa, float scale,
+                                                                         const uint32_t *__restrict__ list, int list_stride,
+                                                                         float *__restrict__ pacc, float *__restrict__ pstat) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem + AM_OFF_Q;
+    float *red = reinterpret_cast<float *>(smem + AM_OFF_RED);
+    float *sm_m = reinterpret_cast<float *>(smem + AM_OFF_M);
+    float *sm_l = reinterpret_cast<float *>(smem + AM_OFF_L);
+    const int chunk = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int n_rh = sq.rows * q_heads;
+    const uint32_t *row_list = list + (size_t)r * list_stride;
+    pdl_launch_next();
+    pdl_wait();
+    const int count = (int)min(row_list[0], (uint32_t)(list_stride - 1));
+    const size_t part0 = ((size_t)chunk * n_rh + (size_t)r * q_heads + h * gqa) ;   // first of this CTA's gqa partial rows
+    if (chunk * AM_KEYS >= count) {
+        // nothing listed here: empty partials (sum 0 drops out of the merge)
+        if (threadIdx.x < gqa) { pstat[(part0 + threadIdx.x) * 2] = -3.0e38f; pstat[(part0 + threadIdx.x) * 2 + 1] = 0.0f; }
+        return;
+    }
+    // ---- gather: this warp's 16 keys
+    const int e0 = chunk * AM_KEYS + warp * 16;
+    uint32_t pos = 0xffffffffu;
+    if (lane < 16 && e0 + lane < count) pos = row_list[1 + e0 + lane];
+    const bool ok = pos < (uint32_t)sq.kc.max_ctx;
+    int64_t kr = -1, vr = -1;
+    if (ok) { kr = kv_row(sq.kc, h, (int)pos); vr = kv_row(sq.vc, h, (int)pos); }
+    const uint32_t k_base = smem_u32(smem + AM_OFF_K + warp * 4 * AM_BOX), v_base = smem_u32(smem + AM_OFF_V + warp * 4 * AM_BOX);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        const int64_t kri = __shfl_sync(0xffffffffu, kr, i), vri = __shfl_sync(0xffffffffu, vr, i);
+        const uint32_t off = (lane >> 3) * AM_BOX + swz128(i, (lane & 7) * 8);
+        cp_async16(k_base + off, sq.kc.base + max(kri, (int64_t)0) * 256 + lane * 8, kri >= 0);
+        cp_async16(v_base + off, sq.vc.base + max(vri, (int64_t)0) * 256 + lane * 8, vri >= 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const uint32_t valid = __ballot_sync(0xffffffffu, kr >= 0 && vr >= 0) & 0xffffu;     // bit i: key i of this warp counts
+    // ---- Q of this (row, kv head): gqa rows of 256 fp32 -> bf16, swizzled (rows past gqa are zeros)
+    for (int idx = threadIdx.x; idx < 16 * 32; idx += AM_WARPS * 32) {
+        const int row = idx >> 5, ch = idx & 31;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < gqa) {
+            const float *src = reinterpret_cast<const float *>(sq.q) + ((size_t)r * q_heads + h * gqa + row) * 256 + ch * 8;
+            const float4 a = *reinterpret_cast<const float4 *>(src), b = *reinterpret_cast<const float4 *>(src + 4);
+            val.x = pack_bf16(a.x, a.y); val.y = pack_bf16(a.z, a.w); val.z = pack_bf16(b.x, b.y); val.w = pack_bf16(b.z, b.w);
+        }
+        *reinterpret_cast<uint4 *>(q_s + (ch >> 3) * AM_BOX + swz128(row, (ch & 7) * 8)) = val;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+
+    // ---- S = Q K^T for the warp's 16 keys
+    const uint32_t q_base = smem_u32(q_s);
+    const float sc2 = scale * LOG2E;
+    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+    {
+        const int mi = lane >> 3;
+        const uint32_t q_row = (mi & 1) * 8 + (lane & 7), k_row = (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int ks = 0; ks < 16; ks++) {
+            uint32_t a[4], b[4];
+            const uint32_t qc = ks * 2 + (mi >> 1), kc = ks * 2 + (mi & 1);
+            ldsm_x4(a[0], a[1], a[2], a[3], q_base + (qc >> 3) * AM_BOX + swz128(q_row, (qc & 7) * 8));
+            ldsm_x4(b[0], b[1], b[2], b[3], k_base + (kc >> 3) * AM_BOX + swz128(k_row, (kc & 7) * 8));
+            mma_bf16(s[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+            mma_bf16(s[1], a[0], a[1], a[2], a[3], b[2], b[3]);
+        }
+    }
+    float m0, m1, l0, l1;
+    uint32_t pa[4];
+    {
+#pragma unroll
+        for (int n = 0; n < 2; n++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int key = n * 8 + tig * 2 + (e & 1);
+                s[n][e] = (valid >> key & 1u) ? s[n][e] * sc2 : -INFINITY;
+            }
+        float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        m0 = fmaxf(mx0, NEG_BIG); m1 = fmaxf(mx1, NEG_BIG);
+        const float p00 = ex2(s[0][0] - m0), p01 = ex2(s[0][1] - m0), p02 = ex2(s[0][2] - m1), p03 = ex2(s[0][3] - m1);
+        const float p10 = ex2(s[1][0] - m0), p11 = ex2(s[1][1] - m0), p12 = ex2(s[1][2] - m1), p13 = ex2(s[1][3] - m1);
+        l0 = (p00 + p01) + (p10 + p11); l1 = (p02 + p03) + (p12 + p13);
+        pa[0] = pack_bf16(p00, p01); pa[1] = pack_bf16(p02, p03); pa[2] = pack_bf16(p10, p11); pa[3] = pack_bf16(p12, p13);
+    }
+    // ---- O = P V
+    float o[32][4];
+#pragma unroll
+    for (int n = 0; n < 32; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    {
+        const int mi = lane >> 3;
+        const uint32_t v_row = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+        for (int np = 0; np < 16; np++) {
+            uint32_t b[4];
+            const uint32_t vc = np * 2 + (mi >> 1);
+            ldsm_x4_t(b[0], b[1], b[2], b[3], v_base + (vc >> 3) * AM_BOX + swz128(v_row, (vc & 7) * 8));
+            mma_bf16(o[np * 2], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+            mma_bf16(o[np * 2 + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+        }
+    }
+    // ---- the four warps' (m, l, O) combined through shared memory, one round per warp
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (tig == 0) { sm_m[warp * 16 + gid] = m0; sm_m[warp * 16 + gid + 8] = m1; }
+    __syncthreads();
+    float M0 = NEG_BIG, M1 = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < AM_WARPS; w++) { M0 = fmaxf(M0, sm_m[w * 16 + gid]); M1 = fmaxf(M1, sm_m[w * 16 + gid + 8]); }
+    {
+        const float f0 = ex2(m0 - M0), f1 = ex2(m1 - M1);
+        const bool v0 = gid < gqa, v1 = gid + 8 < gqa;
+        float2 *r0 = reinterpret_cast<float2 *>(red + (size_t)gid * RED_LD + tig * 2);
+        float2 *r1 = r0 + 8 * (RED_LD / 2);
+#pragma unroll 1
+        for (int round = 0; round < AM_WARPS; round++) {
+            if (warp == round) {
+                if (v0) {
+#pragma unroll
+                    for (int n = 0; n < 32; n++) {
+                        const float2 t = round ? r0[n * 4] : make_float2(0.f, 0.f);
+                        r0[n * 4] = make_float2(fmaf(o[n][0], f0, t.x), fmaf(o[n][1], f0, t.y));
+                    }
+                }
+                if (v1) {
+#pragma unroll
+                    for (int n = 0; n < 32; n++) {
+                        const float2 t = round ? r1[n * 4] : make_float2(0.f, 0.f);
+                        r1[n * 4] = make_float2(fmaf(o[n][2], f1, t.x), fmaf(o[n][3], f1, t.y));
+                    }
+                }
+                if (tig == 0) {
+                    sm_l[gid] = (round ? sm_l[gid] : 0.0f) + l0 * f0;
+                    sm_l[gid + 8] = (round ? sm_l[gid + 8] : 0.0f) + l1 * f1;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    for (int idx = threadIdx.x; idx < gqa * 64; idx += AM_WARPS * 32) {
+        const int row = idx >> 6, d4 = (idx & 63) * 4;
+        float Mrow = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < AM_WARPS; w++) Mrow = fmaxf(Mrow, sm_m[w * 16 + row]);
+        *reinterpret_cast<float4 *>(pacc + (part0 + row) * 256 + d4) = *reinterpret_cast<const float4 *>(red + (size_t)row * RED_LD + d4);
+        if ((idx & 63) == 0) { pstat[(part0 + row) * 2] = Mrow * LN2; pstat[(part0 + row) * 2 + 1] = sm_l[row]; }
     }
 }
 
@@ -957,6 +1186,7 @@ int g_tune_split_kg = 6;
 int g_tune_prefill_tc = 1;
 int g_tune_prefill_fuse_q = 1;
 int g_tune_pdl = 1;
+int g_tune_masked_tc = 1;
 
 int sm_count() {
     static int n[64] = {0};                    // per device
@@ -1025,8 +1255,32 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
     if (n_rows_heads <= 0) return;
     if (!acc_stride) acc_stride = (size_t)n_rows_heads * 256;
     if (!stat_stride) stat_stride = (size_t)n_rows_heads * 2;
-    merge_parts_kernel<<<n_rows_heads, 64, 0, s>>>(out, out_dtype, pacc, pstat, gate, gate_dtype, gate_stride,
-                                                   n_rows_heads, parts, pacc_out, pstat_out, acc_stride, stat_stride);
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    pdl_config(cfg, attr, (unsigned)n_rows_heads, 256, (size_t)parts * sizeof(float), s);
+    cudaLaunchKernelEx(&cfg, merge_parts_kernel, out, out_dtype, pacc, pstat, gate, gate_dtype, gate_stride, n_rows_heads, parts,
+                       pacc_out, pstat_out, acc_stride, stat_stride);
+    g_launches++;
+}
+
+// Masked attention of `rows` rows over their position lists on tensor ops: n_chunks = ceil(cap / 64)
+// partials per (row, head) into pacc [n_chunks, rows * q_heads, 256] / pstat, for launch_merge_parts.
+int attn_masked_chunks(int cap) { return (cap + AM_KEYS - 1) / AM_KEYS; }
+void launch_attn_masked_mma(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
+                            int list_stride, float *pacc, float *pstat) {
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        cudaFuncSetAttribute(attn_masked_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AM_SMEM);
+        configured[dev] = true;
+    }
+    const int gqa = q_heads / kv_heads;
+    cudaLaunchConfig_t cfg;
+    cudaLaunchAttribute attr;
+    pdl_config(cfg, attr, 1, AM_WARPS * 32, AM_SMEM, s);
+    cfg.gridDim = dim3((unsigned)attn_masked_chunks(list_stride - 1), (unsigned)kv_heads, (unsigned)seq.rows);
+    cudaLaunchKernelEx(&cfg, attn_masked_mma_kernel, seq, q_heads, kv_heads, gqa, scale, list, list_stride, pacc, pstat);
     g_launches++;
 }
 

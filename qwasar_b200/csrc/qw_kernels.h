@@ -160,6 +160,12 @@ void launch_attn_per_query(cudaStream_t s, const AttnSeq &seq, int q_heads, int 
 size_t attn_per_query_scratch_bytes(int rows, int q_heads, int splits);
 int attn_per_query_splits(int rows, int q_heads, int n_keys);
 
+// Masked attention on tensor ops over each row's position list (q f32; grouping <= 16): one partial
+// per 64 list entries into pacc [chunks, rows * q_heads, 256] / pstat [chunks, rows * q_heads, 2].
+int attn_masked_chunks(int cap);
+void launch_attn_masked_mma(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
+                            int list_stride, float *pacc, float *pstat);
+
 // Merge of externally supplied partials (the cross-GPU exchange): pacc [parts, rows*q_heads, 256],
 // pstat [parts, rows*q_heads, 2] -> out (gated when gate != nullptr).
 void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *pacc, const float *pstat,
@@ -169,6 +175,17 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
 // ---- 4-bit affine product (qw_qmat.cu): y [rows, n] = x [rows, k] . dequant(w [n, k/8])^T ----
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
                     int n, int rows, int group);
+
+// Up to four one-token products sharing x (and k, group) in one launch; w rows 16-byte aligned.
+struct QmvMulti {
+    float *y[4];
+    const uint32_t *w[4];
+    const uint16_t *scales[4], *biases[4];
+    const float *x;
+    int32_t n[4], blocks[4];
+    int32_t count, k, group;
+};
+void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m);
 
 // ---- QSA indexer (qw_qsa.cu) ----------------------------------------------------------------
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
@@ -192,5 +209,7 @@ extern int g_tune_prefill_fuse_q;
 // 1: the kernels of the decode chain are launched as programmatic dependents (they may start under
 // the kernel in front of them); 0: plain stream order, for comparison.
 extern int g_tune_pdl;
+// 1: masked attention (position lists) on tensor ops where the grouping allows; 0: the fp32 per-query kernel.
+extern int g_tune_masked_tc;
 
 }  // namespace qw

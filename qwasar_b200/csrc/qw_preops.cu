@@ -154,7 +154,9 @@ __global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, ui
 constexpr int PRE_ROWS = QW_PRE_ROWS;
 __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
-    __shared__ __align__(16) float sq_s[8][PRE_ROWS][260];   // squares of the key rows (row stride 260: lanes on distinct banks)
+    // squares of the key rows, [key warps of the block][PRE_ROWS][260] (row stride 260: lanes on
+    // distinct banks); sized by the launch for the key heads a block can hold
+    extern __shared__ __align__(16) float sq_dyn[];
     // Dependent launch: this kernel reads the projections and writes the cache, so it waits for
     // everything in front of it first; the attention kernel behind it may then start at once (it
     // waits itself before it touches the rows appended here).
@@ -239,20 +241,22 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
     // order -- lane u takes row u of this warp, the warp's rows side by side -- which costs a
     // fraction of the instructions of a sum handed from lane to lane.
     float ss_k[PRE_ROWS];
+    // this warp's rows of the buffer: key heads of a block are consecutive, the first one is head max(slot0, qs) - qs
+    float *sq_mine = sq_dyn + (size_t)(is_k ? h - (max(slot0, qs) - qs) : 0) * PRE_ROWS * 260;
     if (is_k) {
 #pragma unroll
         for (int u = 0; u < PRE_ROWS; u++) {
             if (u >= n || dst_row[u] < 0) continue;      // warp-uniform
             float x[8];
             unpack(u, x);
-            float4 *sq = reinterpret_cast<float4 *>(&sq_s[warp][u][lane * 8]);
+            float4 *sq = reinterpret_cast<float4 *>(sq_mine + u * 260 + lane * 8);
             sq[0] = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]), __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
             sq[1] = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]), __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
         }
         __syncwarp();
         float acc = 0.0f;
         if (lane < n) {
-            const float *sq = sq_s[warp][lane];
+            const float *sq = sq_mine + lane * 260;
 #pragma unroll 16
             for (int i = 0; i < 256; i++) acc = __fadd_rn(acc, sq[i]);
         }
@@ -358,6 +362,7 @@ void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t();
     cfg.gridDim = dim3((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
     cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = (size_t)(p.kv_heads < 8 ? p.kv_heads : 8) * PRE_ROWS * 260 * sizeof(float);
     cfg.stream = s;
     cfg.attrs = &attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, preop_kernel, p);

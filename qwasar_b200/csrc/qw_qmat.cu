@@ -65,13 +65,13 @@ __global__ void __launch_bounds__(256) qmat_q4_kernel(float *__restrict__ y, con
 // staged chunk.  What the SMs pay for here is the unpacking, so scale and bias stay outside the
 // sum over a slot (a slot lies inside one scale group).
 constexpr int QV_ROWS = 2, QV_OUTS = 4, QV_KC = 4096, QV_SLOTS = QV_KC / 32, QV_PAD = 36;
-__global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
-                                                     const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
-                                                     int n, int rows, int group) {
+__device__ __forceinline__ void qmv_q4_block(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
+                                             const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
+                                             int n, int rows, int group, int block, int row_block) {
     __shared__ __align__(16) float xs[QV_ROWS][QV_SLOTS][QV_PAD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int o0 = (blockIdx.x * 8 + warp) * QV_OUTS;
-    const int r0 = blockIdx.y * QV_ROWS, nr = min(QV_ROWS, rows - r0);
+    const int o0 = (block * 8 + warp) * QV_OUTS;
+    const int r0 = row_block * QV_ROWS, nr = min(QV_ROWS, rows - r0);
     const int words = k >> 3, groups = k / group;
     float acc[QV_OUTS][QV_ROWS];
 #pragma unroll
@@ -154,7 +154,29 @@ __global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, cons
         }
 }
 
+__global__ void __launch_bounds__(256) qmv_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
+                                                     const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
+                                                     int n, int rows, int group) {
+    qmv_q4_block(y, x, w, scales, biases, k, n, rows, group, blockIdx.x, blockIdx.y);
+}
+
+// Up to four one-token products that share their input (the q, k, v and indexer projections of one
+// token, qwasar_gpu.h:105-109) as ONE launch: the blocks of all parts laid end to end.
+__global__ void __launch_bounds__(256) qmv_q4_multi_kernel(const __grid_constant__ QmvMulti m) {
+    int part = 0, block = blockIdx.x;
+    while (part + 1 < m.count && block >= m.blocks[part]) { block -= m.blocks[part]; part++; }
+    qmv_q4_block(m.y[part], m.x, m.w[part], m.scales[part], m.biases[part], m.k, m.n[part], 1, m.group, block, 0);
+}
+
 }  // namespace
+
+void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m) {
+    int total = 0;
+    for (int i = 0; i < m.count; i++) { m.blocks[i] = (m.n[i] + 8 * QV_OUTS - 1) / (8 * QV_OUTS); total += m.blocks[i]; }
+    if (total <= 0) return;
+    qmv_q4_multi_kernel<<<total, 256, 0, s>>>(m);
+    g_launches++;
+}
 
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
                     int n, int rows, int group) {

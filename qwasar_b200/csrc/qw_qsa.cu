@@ -14,6 +14,7 @@
 // through the _rn intrinsics.  These are small kernels: first correct versions, not tuned.
 #include <float.h>
 #include <algorithm>
+#include <cooperative_groups.h>
 
 #include "qw_kernels.h"
 
@@ -274,6 +275,192 @@ __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__rest
     if (tid == 0) l[0] = (uint32_t)(total + (n_keys - tail0));
 }
 
+
+// ---- the selection of a long row, spread over a cluster of eight CTAs --------------------------------
+// The same selection as qsa_select_kernel (same keys, same radix select, same order of the list),
+// for rows of thousands of blocks, where one CTA sweeping the row six times from L2 is all latency:
+// 65 536 scores took 67 us.  Here a cluster of SC_CTAS CTAs (distributed shared memory) takes one row;
+// CTA q reads its contiguous share of the scores ONCE, as order-preserving keys into shared memory
+// (0 = not selectable), and every later pass runs from there.  A radix pass builds a 256-bin
+// histogram per CTA (warp-aggregated adds), the cluster synchronises, every CTA sums the eight
+// histograms through distributed shared memory and takes the same decision; the ordered passes need
+// only each CTA's counts of larger and equal keys, read the same way.  The mask is cleared and the
+// list written by the CTAs in parallel, each for its own stretch of blocks.
+namespace cg = cooperative_groups;
+constexpr int SC_CTAS = 8, SC_THREADS = 1024, SC_WARPS = SC_THREADS / 32;
+
+__global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
+qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ list, const float *__restrict__ scores, int ratio,
+                          int base_pos, int block_topk, int max_ctx, int max_blocks, int list_stride, int per_cta) {
+    extern __shared__ uint32_t keys[];                            // per_cta keys of this CTA's blocks
+    __shared__ int hist[256];
+    __shared__ int tot[256];
+    __shared__ int w_gt[SC_WARPS], w_eq[SC_WARPS];
+    __shared__ int cta_cnt[2];                                    // this CTA's blocks with a larger / an equal key
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_remaining, s_take;
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const int r = blockIdx.x / SC_CTAS, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t below = (1u << lane) - 1u;
+    const int n_keys = base_pos + r + 1, n_blocks = n_keys / ratio;
+    const float *sc = scores + (size_t)r * max_blocks;
+    uint8_t *m = mask + (size_t)r * max_ctx;
+    uint32_t *l = list + (size_t)r * list_stride;
+    const int tail0 = n_blocks * ratio;
+    const int lo = min(rank * per_cta, n_blocks), hi = min(lo + per_cta, n_blocks);
+
+    // this CTA's share of the mask, [m_lo, m_hi): 0 over the blocks, 1 over the tail; 16 bytes per
+    // store where the addresses allow (shares are cut at multiples of 16 bytes of the row's address)
+    {
+        const uintptr_t a0 = (uintptr_t)m;
+        const int64_t span = ((int64_t)n_keys + SC_CTAS - 1) / SC_CTAS;
+        int64_t c0 = (int64_t)rank * span, c1 = c0 + span;
+        c0 = rank == 0 ? 0 : (int64_t)(((a0 + c0 + 15) & ~(uintptr_t)15) - a0);
+        c1 = rank == SC_CTAS - 1 ? n_keys : (int64_t)(((a0 + c1 + 15) & ~(uintptr_t)15) - a0);
+        const int m_lo = (int)(c0 < n_keys ? c0 : n_keys), m_hi = (int)(c1 < n_keys ? c1 : n_keys);
+        const int head = min(m_lo + (int)((16 - ((a0 + m_lo) & 15)) & 15), m_hi);
+        const int zero_end = min(m_hi, tail0);
+        const int vec_end = zero_end > head ? head + ((zero_end - head) & ~15) : head;
+        for (int t = m_lo + tid; t < head; t += SC_THREADS) m[t] = t >= tail0;
+        for (int t = head + 16 * tid; t < vec_end; t += 16 * SC_THREADS) *reinterpret_cast<uint4 *>(m + t) = make_uint4(0, 0, 0, 0);
+        for (int t = vec_end + tid; t < m_hi; t += SC_THREADS) m[t] = t >= tail0;
+    }
+    // the scores of this CTA's blocks, once, as keys
+    for (int i = tid; i < per_cta; i += SC_THREADS) {
+        uint32_t key = 0;
+        const int b = lo + i;
+        if (b < hi) { uint32_t k2; if (sel_key(sc[b], k2)) key = k2; }
+        keys[i] = key;
+    }
+    if (tid == 0) { s_prefix = 0; s_remaining = 0; s_take = 0; }
+    __syncthreads();
+
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix, high = shift == 24 ? 0u : 0xFFFFFFFFu << (shift + 8);
+        for (int i = tid; i < per_cta; i += SC_THREADS) {        // the same trip count on every lane
+            const uint32_t key = keys[i];
+            const bool in = key != 0u && (key & high) == prefix;
+            const int bin = in ? (int)((key >> shift) & 0xFF) : -1;
+            // lanes of one bin add once: scores of a row mostly share their top bytes
+            const uint32_t same = __match_any_sync(0xffffffffu, bin);
+            if (in && (same & below) == 0u) atomicAdd(&hist[bin], __popc(same));
+        }
+        cluster.sync();                                           // every CTA's histogram is complete
+        if (tid < 256) {
+            int sum = 0;
+#pragma unroll
+            for (int q = 0; q < SC_CTAS; q++) sum += cluster.map_shared_rank(hist, q)[tid];
+            tot[tid] = sum;
+        }
+        __syncthreads();
+        // as in qsa_select_kernel: walking down from bin 255, the first bin at which the count reaches
+        // `want` holds the key looked for (every CTA computes the same)
+        if (warp == 0) {
+            int want = s_remaining;
+            __syncwarp();
+            int h[8], mine = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) { h[j] = tot[255 - 8 * lane - j]; mine += h[j]; }
+            int incl = mine;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += up;
+            }
+            const int all = __shfl_sync(0xffffffffu, incl, 31);
+            if (shift == 24) {
+                want = min(min(block_topk, n_blocks), all);
+                if (lane == 0) s_take = want;
+            }
+            const uint32_t reached = __ballot_sync(0xffffffffu, incl >= want);
+            if (reached == 0u) {
+                if (lane == 31) { s_remaining = want - (all - h[7]); s_prefix = prefix; }
+            } else if (lane == __ffs(reached) - 1) {
+                int run = incl - mine, bin = 0, rem = 0;
+                bool done = false;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    if (!done && (run + h[j] >= want || 8 * lane + j == 255)) { bin = 255 - 8 * lane - j; rem = want - run; done = true; }
+                    run += h[j];
+                }
+                s_remaining = rem;
+                s_prefix = prefix | ((uint32_t)bin << shift);
+            }
+        }
+        cluster.sync();                                           // all have read the histograms; the decision is visible
+        if (s_take <= 0) break;                                   // (the same on every CTA)
+    }
+    const int take = s_take;
+    const uint32_t kth = s_prefix;
+    const int need_eq = s_remaining;
+
+    // this warp's stretch of this CTA's keys (per_cta is a multiple of 1024, so a multiple of 32 per warp)
+    const int chunk = per_cta / SC_WARPS;
+    const int w_lo = warp * chunk, w_hi = w_lo + chunk;
+    int gt = 0, eq = 0;
+    if (take > 0)
+        for (int i = w_lo + lane; i < w_hi; i += 32) {
+            const uint32_t key = keys[i];
+            gt += key != 0u && key > kth; eq += key != 0u && key == kth;
+        }
+    gt = (int)__reduce_add_sync(0xffffffffu, (unsigned)gt);
+    eq = (int)__reduce_add_sync(0xffffffffu, (unsigned)eq);
+    if (lane == 0) { w_gt[warp] = gt; w_eq[warp] = eq; }
+    __syncthreads();
+    if (tid == 0) {
+        int g = 0, e = 0;
+        for (int w = 0; w < SC_WARPS; w++) { g += w_gt[w]; e += w_eq[w]; }
+        cta_cnt[0] = g; cta_cnt[1] = e;
+    }
+    cluster.sync();
+    // equals and taken blocks in the CTAs before this one, then in the warps before this one
+    int eq_before = 0, out_before = 0, total_taken = 0;
+    {
+        int e_run = 0, o_run = 0;
+        for (int q = 0; q < SC_CTAS; q++) {
+            const int *cnt = cluster.map_shared_rank(cta_cnt, q);
+            const int g = cnt[0], e = cnt[1];
+            if (q == rank) { eq_before = e_run; out_before = o_run; }
+            o_run += g + min(max(need_eq - e_run, 0), e);
+            e_run += e;
+        }
+        total_taken = o_run;
+    }
+    int eq_rank = eq_before, at = out_before;
+    for (int w = 0; w < warp; w++) {
+        at += w_gt[w] + min(max(need_eq - eq_rank, 0), w_eq[w]);
+        eq_rank += w_eq[w];
+    }
+    if (take > 0) {
+        for (int i = w_lo + lane; i < w_hi; i += 32) {
+            const uint32_t key = keys[i];
+            const int b = lo + i;
+            const bool is_gt = key != 0u && key > kth, is_eq = key != 0u && key == kth;
+            const uint32_t eq_bits = __ballot_sync(0xffffffffu, is_eq);
+            const bool taken = is_gt || (is_eq && eq_rank + __popc(eq_bits & below) < need_eq);
+            const uint32_t t_bits = __ballot_sync(0xffffffffu, taken);
+            if (taken) {
+                const int pos = (at + __popc(t_bits & below)) * ratio;
+                for (int t = 0; t < ratio; t++) {
+                    m[b * ratio + t] = 1;
+                    l[1 + pos + t] = (uint32_t)(b * ratio + t);
+                }
+            }
+            eq_rank += __popc(eq_bits);
+            at += __popc(t_bits);
+        }
+    }
+    if (rank == 0) {
+        const int total = total_taken * ratio;
+        for (int t = tail0 + tid; t < n_keys; t += SC_THREADS) l[1 + total + (t - tail0)] = (uint32_t)t;
+        if (tid == 0) l[0] = (uint32_t)(total + (n_keys - tail0));
+    }
+    cluster.sync();                                               // no CTA leaves while another may still read its counts
+}
+
 }  // namespace
 
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
@@ -292,6 +479,23 @@ void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const flo
 void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const float *scores, int rows, int ratio, int base_pos,
                        int block_topk, int max_ctx, int max_blocks) {
     if (rows <= 0) return;
+    // long rows: a cluster of eight CTAs per row with the row's keys resident in their shared memory
+    const int most = std::min((base_pos + rows) / ratio, max_blocks);
+    const int per_cta = ((most + SC_CTAS - 1) / SC_CTAS + 1023) / 1024 * 1024;
+    if (most >= 8192 && per_cta * 4 <= 200 * 1024) {
+        static bool configured[64] = {false};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !configured[dev]) {
+            cudaFuncSetAttribute(qsa_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            configured[dev] = true;
+        }
+        qsa_select_cluster_kernel<<<rows * SC_CTAS, SC_THREADS, (size_t)per_cta * 4, s>>>(mask, list, scores, ratio, base_pos, block_topk,
+                                                                                         max_ctx, max_blocks, 1 + block_topk * ratio + ratio,
+                                                                                         per_cta);
+        g_launches++;
+        return;
+    }
     qsa_select_kernel<<<rows, SEL_THREADS, 0, s>>>(mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
                                                       1 + block_topk * ratio + ratio);
     g_launches++;

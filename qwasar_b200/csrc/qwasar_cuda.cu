@@ -784,6 +784,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
+    if (knob && !strcmp(knob, "masked_tc") && (value == 0 || value == 1)) { qw::g_tune_masked_tc = value; return true; }
     return false;
 }
 // How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
@@ -1387,9 +1388,30 @@ extern "C" void qw_op_qmm_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scal
 }
 extern "C" bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group, int32_t count, const qw_qmv_part *parts) {
     if (!live(c) || !parts || count <= 0 || count > 4 || k < 2048) return false;        // the reference's limits (qwasar_gpu.h:105-109)
-    for (int32_t i = 0; i < count; i++)
-        if (!qmat_q4(c, "qmv_q4_multi", parts[i].y, x, parts[i].w, parts[i].scales, parts[i].biases, k, parts[i].n, 1, group)) return false;
-    return true;
+    if ((group != 32 && group != 64) || k % group) { cmd_fail(c, "qmv_q4_multi: k %d, group %d not supported", k, group); return false; }
+    QmvMulti m;
+    memset(&m, 0, sizeof m);
+    m.count = count; m.k = k; m.group = group;
+    m.x = (const float *)dev_range(c, x, (size_t)k * 4, false, 16);
+    if (!m.x) return false;
+    bool aligned = true;
+    for (int32_t i = 0; i < count; i++) {
+        const int32_t n = parts[i].n;
+        if (n <= 0) { cmd_fail(c, "qmv_q4_multi: part %d has no rows", i); return false; }
+        m.n[i] = n;
+        m.y[i] = (float *)dev_range(c, parts[i].y, (size_t)n * 4, true, 4);
+        m.w[i] = (const uint32_t *)dev_range(c, parts[i].w, (size_t)n * (k / 8) * 4, false, 4);
+        m.scales[i] = (const uint16_t *)dev_range(c, parts[i].scales, (size_t)n * (k / group) * 2, false, 2);
+        m.biases[i] = (const uint16_t *)dev_range(c, parts[i].biases, (size_t)n * (k / group) * 2, false, 2);
+        if (!m.y[i] || !m.w[i] || !m.scales[i] || !m.biases[i]) return false;
+        aligned = aligned && ((uintptr_t)m.w[i] & 15) == 0;
+    }
+    if (aligned) {
+        launch_qmv_q4_multi(c->stream, m);               // one dispatch for all parts
+    } else {
+        for (int32_t i = 0; i < count; i++) launch_qmat_q4(c->stream, m.y[i], m.x, m.w[i], m.scales[i], m.biases[i], k, m.n[i], 1, group);
+    }
+    return cuda_ok(c, cudaGetLastError(), "qmv_q4_multi launch");
 }
 
 // ---- QSA indexer: block keys, block scores, selection (qwasar_gpu.h:620-639) ----
@@ -1478,6 +1500,17 @@ static void attn_masked(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcac
     const uint32_t *pl = (const uint32_t *)dev_range(c, list, (size_t)rows * (1 + cap) * 4, false, 4);
     if (!sq.q || !po || !pl || (gate.buf && !pg)) return;
     sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = 0; sq.key_hi = base_pos + rows;
+    if (g_tune_masked_tc && q_heads / kv_heads <= 16) {
+        // tensor ops over the gathered rows: a partial per 64 list entries, then the merge (and gate)
+        const int chunks = attn_masked_chunks(cap);
+        float *scr = (float *)cmd_scratch(c, attn_per_query_scratch_bytes(rows, q_heads, chunks));
+        if (!scr) return;
+        float *pstat = scr + (size_t)chunks * rows * q_heads * 256;
+        launch_attn_masked_mma(c->stream, sq, q_heads, kv_heads, scale, pl, 1 + cap, scr, pstat);
+        launch_merge_parts(c->stream, po, DT_F32, scr, pstat, pg, DT_F32, 256, rows * q_heads, chunks, nullptr, nullptr);
+        cuda_ok(c, cudaGetLastError(), "attn_masked launch");
+        return;
+    }
     const int splits = attn_per_query_splits(rows, q_heads, cap);
     float *scr = (float *)cmd_scratch(c, attn_per_query_scratch_bytes(rows, q_heads, splits));
     if (!scr) return;

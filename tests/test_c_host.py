@@ -66,3 +66,37 @@ def test_header_coexists_with_the_reference_header(tmp_path):
 def test_node_from_c_matches_oracle(attn_node, args):
     r = subprocess.run([attn_node] + args, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.fixture(scope="module")
+def two_gpu_node(tmp_path_factory):
+    import qwasar_b200  # noqa: F401
+    from oracle import oracle as orc
+    orc.Oracle()
+    exe = str(tmp_path_factory.mktemp("c2") / "two_gpu_node")
+    libdir, ordir = os.path.join(ROOT, "qwasar_b200"), os.path.join(ROOT, "oracle", "_build")
+    cmd = ["gcc", "-std=c99", "-pedantic", "-Wall", "-Wextra", "-Werror", "-O1", "-I" + os.path.join(ROOT, "include"),
+           os.path.join(ROOT, "tests", "c", "two_gpu_node.c"), "-o", exe, "-L" + libdir, "-lqwasar_cuda", "-L" + ordir, "-lqworacle", "-lm",
+           "-Wl,-rpath," + libdir, "-Wl,-rpath," + ordir]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return exe
+
+
+def test_multi_gpu_host_compiles_as_c99(two_gpu_node):
+    """tests/c/two_gpu_node.c -- one C99 thread driving several GPUs through the header -- builds
+    -pedantic -Werror and, where fewer devices exist than it asks for, says so and exits 0."""
+    r = subprocess.run([two_gpu_node], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("args", [["2", "3000", "16", "2"], ["2", "100", "24", "4"], ["4", "5000", "16", "2"]], ids=["2-gpus", "2-gpus-short", "4-gpus"])
+def test_one_c_thread_drives_several_gpus(two_gpu_node, args):
+    """A sequence split by position over the GPUs of one process: per-device arenas, the partials
+    exchanged by peer stores (qw_op_attn_exchange), every device ends with the oracle's output."""
+    import torch
+    if torch.cuda.device_count() < int(args[0]):
+        pytest.skip(f"needs {args[0]} GPUs")
+    r = subprocess.run([two_gpu_node] + args, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout + r.stderr

@@ -2,13 +2,17 @@
 shape of the reference's own test (tests/test_sparse.c:1036-1122): 24 query / 2 KV heads, 64 rows
 at base 6000, per row about a third of the positions plus the newest four, every 16th row only a
 handful, the list poisoned past its count; as one chunk and a row at a time; plain and gated;
-over a plain cache and over the paged arena.  The kernel is fp32 throughout, so the bound is the
-reference's for its fp32 path: rel-L2 < 1e-4 (tests/test_sparse.c:1115-1119), and it is also
-held to 2e-5 here."""
+over a plain cache and over the paged arena.  Two forms, as in the reference: the fp32 per-query
+kernel, held to the reference's bound for its fp32 path (rel-L2 < 1e-4, tests/test_sparse.c:1115-1119)
+and to 2e-5 here; and the tensor-op kernel over the gathered rows (the default where the grouping is
+at most 16), which rounds q and the softmax weights to bf16 -- rel-L2 < 6e-3 (the reference gives its
+half-precision tensor form 1e-3, and bf16 keeps three bits fewer) and max relative error per output
+vector <= 2e-2: the queries here are three times the N(0,1) of the benchmark configurations, as in
+the reference's test, which sharpens the softmax and the effect of rounding q with it."""
 import numpy as np
 import pytest
 
-from conftest import rel_l2
+from conftest import max_rel_err, rel_l2
 from gpu_util import Bufs, QwRef, arena_fill
 from qwasar_b200 import synth
 
@@ -34,8 +38,21 @@ def make_lists(rows, base, cap, seed=5):
     return lists
 
 
+@pytest.fixture(params=["fp32", "tensor"])
+def form(request, be):
+    assert be.tune("masked_tc", 1 if request.param == "tensor" else 0)
+    yield request.param
+    be.tune("masked_tc", 1)
+
+
+def close_enough(got, want, form):
+    if form == "fp32":
+        return rel_l2(got, want) < 2e-5
+    return max_rel_err(got, want) <= 2e-2 and rel_l2(got, want) < 6e-3
+
+
 @pytest.mark.parametrize("paged", [False, True], ids=["linear", "arena"])
-def test_masked_chunk_and_rows_plain_and_gated(be, oracle, paged):
+def test_masked_chunk_and_rows_plain_and_gated(be, oracle, paged, form):
     rows, qh, kvh, base, topk, ratio = 64, 24, 2, 6000, 576, 4
     ctx = base + rows + 8
     cap = topk * ratio + ratio
@@ -72,12 +89,12 @@ def test_masked_chunk_and_rows_plain_and_gated(be, oracle, paged):
         for name, got, ref in (("chunk", v_chunk, want), ("row at a time", v_rows, want), ("gated chunk", w_chunk, want_gated),
                                ("gated rows", w_rows, want_gated)):
             e = rel_l2(np.array(got), ref)
-            assert e < 2e-5, f"attn_masked, {name}: rel-L2 {e:.3e}"
+            assert close_enough(np.array(got), ref, form), f"attn_masked, {name}: rel-L2 {e:.3e}, max rel {max_rel_err(np.array(got), ref):.3e}"
         # the same kernel either way; only the number of list slices per row differs with the row count
         assert rel_l2(np.array(v_chunk), np.array(v_rows)) < 1e-6
 
 
-def test_masked_edge_lists(be, oracle):
+def test_masked_edge_lists(be, oracle, form):
     """A list of one position, a full list, and a position outside the cache (skipped, no fault)."""
     rows, qh, kvh, base, topk, ratio = 3, 8, 2, 100, 8, 4
     ctx, cap = 128, topk * ratio + ratio
@@ -99,4 +116,4 @@ def test_masked_edge_lists(be, oracle):
         be.op_attn_masked(c, QwRef(ob, 0), QwRef(qb, 0), QwRef(kb, 0), QwRef(vb, 0), QwRef(lb, 0), rows, qh, kvh, 256, ctx, base,
                           0.0625, topk, ratio)
         be.cmd_wait(c); be.cmd_free(c)
-        assert rel_l2(np.array(ov), want) < 2e-5
+        assert close_enough(np.array(ov), want, form)

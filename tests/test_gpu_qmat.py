@@ -70,7 +70,9 @@ def test_q4_multi(be, oracle):
             parts[i] = Part(Ref(yb, 0), Ref(wb, 0), Ref(sb, 0), Ref(bb, 0), n)
             outs.append(yv); wts.append((w, sc, bi))
         c = be.cmd_begin()
+        n0 = be.launch_count()
         assert be.lib.qw_op_qmv_q4_multi(c, Ref(xb, 0), k, group, len(ns), C.addressof(parts))
+        assert be.launch_count() - n0 == 1, "the parts share one dispatch (qwasar_gpu.h:105-109)"
         assert not be.lib.qw_op_qmv_q4_multi(c, Ref(xb, 0), 1024, group, len(ns), C.addressof(parts))
         be.cmd_wait(c); be.cmd_free(c)
         for yv, (w, sc, bi) in zip(outs, wts):

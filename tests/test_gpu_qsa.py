@@ -95,6 +95,22 @@ def test_select_long_context(be, oracle):
     check_select(be, oracle, scores, rows, ratio, base, topk, max_ctx)
 
 
+@pytest.mark.parametrize("rows,ratio,base,topk", [(1, 4, 65535 * 4 + 2, 512), (3, 2, 20000, 300), (2, 4, 40000, 0), (1, 8, 70000, 20000)])
+def test_select_rows_of_thousands_of_blocks(be, oracle, rows, ratio, base, topk):
+    """Rows long enough for the eight-CTA cluster kernel: random scores with stretches of equal ones
+    (also across the boundary between two CTAs' shares), zeros of both signs, unselectable entries; a
+    budget of zero blocks; a budget larger than the number of blocks."""
+    rng = np.random.default_rng(base % 1000 + rows)
+    max_ctx = base + rows + 5
+    nb = max_ctx // ratio
+    scores = rng.standard_normal((rows, nb)).astype(np.float32)
+    scores[:, 50:90] = scores[:, 49:50]
+    scores[:, nb // 8 - 20: nb // 8 + 20] = 9.5                           # a tie among the very best, across a share boundary
+    scores[:, 1000:1100:3] = 0.0; scores[:, 1001:1100:3] = -0.0
+    scores[0, 2000:2100] = np.nan; scores[0, 2100:2200] = -3.4028235e38; scores[0, 2200:2210] = -np.inf
+    check_select(be, oracle, scores, rows, ratio, base, topk, max_ctx)
+
+
 def test_scores_select_attend_chain(be, oracle):
     """Raw index keys -> scores -> selection -> masked attention, every stage on the device, against
     the oracle's chain fed with the device's scores (so that a last-bit difference of a score cannot
@@ -127,4 +143,4 @@ def test_scores_select_attend_chain(be, oracle):
         n = int(want_list[r, 0])
         assert int(lists[r, 0]) == n and np.array_equal(lists[r, 1:1 + n], want_list[r, 1:1 + n])
     want = oracle.attn_masked(q, kc, vc, want_list, rows, qh, kvh, 256, max_ctx, 0.0625)
-    assert rel_l2(got, want) < 2e-5
+    assert rel_l2(got, want) < 5e-3          # the masked attention's tensor-op form (bf16 q and weights)

@@ -316,6 +316,11 @@ bool    qw_kv_store(qw_buf cache, int32_t layer, int32_t head, int32_t pos0, int
  * by the other build must be refused by the file header, which is the
  * caller's (qwasar_kvstore.c:52-63 records no dtype yet). */
 size_t  qw_kv_state_bytes(int32_t n_layers, int32_t kv_heads, int32_t head_dim, int32_t n_tokens);
+/* What a checkpoint header should record beside its dims so that a payload written by a build with
+ * another cache element type is rejected rather than misread: the four characters "BF16" as a
+ * little-endian word (0x36314642).  The reference's header (qwasar_kvstore.c:52-63) has a `reserved`
+ * word for it; a build that stores IEEE half would write "F16 ". */
+uint32_t qw_kv_element_tag(void);
 bool    qw_kv_pack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx,
                    int32_t head_dim, int32_t n_tokens, void *dst, size_t cap);
 bool    qw_kv_unpack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx,

@@ -107,6 +107,7 @@ SIGNATURES = {
     "qw_kv_read": (_b, [_vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32]),
     "qw_kv_store": (_b, [_vp, _i32, _i32, _i32, _i32, _vp, _i32, _i32, _i32]),
     "qw_kv_state_bytes": (_sz, [_i32, _i32, _i32, _i32]),
+    "qw_kv_element_tag": (C.c_uint32, []),
     "qw_kv_pack": (_b, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz]),
     "qw_kv_unpack": (_b, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _sz]),
     "qw_kv_arena_trim": (None, [_vp, _i32]),

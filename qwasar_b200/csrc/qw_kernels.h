@@ -211,5 +211,7 @@ extern int g_tune_prefill_fuse_q;
 extern int g_tune_pdl;
 // 1: masked attention (position lists) on tensor ops where the grouping allows; 0: the fp32 per-query kernel.
 extern int g_tune_masked_tc;
+// 1: a one-token 4-bit product keeps x in registers (qmv1_q4_kernel); 0: the shared-memory kernel.
+extern int g_tune_qmv_regs;
 
 }  // namespace qw

@@ -219,6 +219,10 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
     if (warp == W_K) {
         // ---------------- K tiles: two pages each, rows 0-63 and 64-127 of every 64-dim box ----------------
         if (lane == 0) {
+            // Dependent launch: the cache rows of this chunk (and the rows' cos / sin) come from the
+            // append kernel in front; everything a CTA does before this point -- barriers, tensor
+            // memory, the raw query tile, which is an input of the node -- runs under that kernel's tail.
+            pdl_wait();
             for (int j = 0; j < n_t; j++) {
                 const int st = j & 1;
                 const int32_t r0 = page_row(p.kc, 2 * j), r1 = page_row(p.kc, 2 * j + 1);
@@ -248,6 +252,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
             // the Q tile (raw q rows of the [q|gate] input when the kernel norms and rotates them
             // itself, then together with the rows' cos / sin, parked in the P region)
             mbar_expect_tx(&bars[Q_FULL], (p.fuse_q ? 6 : 4) * IO_BOX);
+            if (!p.fuse_q) pdl_wait();                     // ready-made queries are written by the kernel in front
             // ready-made queries: dims 0-127 to the staging area (they move on to tensor memory),
             // dims 128-255 straight to where the tensor core reads them; raw rows: all four boxes to
             // the staging area, their cos / sin to K stage 1
@@ -256,6 +261,7 @@ __global__ void __launch_bounds__(THREADS, 1) qw_attn_prefill_kernel(const __gri
                 tma_load_2d(smem + ((p.fuse_q || b < 2) ? OFF_STAGE_Q + b * IO_BOX : OFF_QHI + (b - 2) * IO_BOX), &p.qmap,
                             head * (p.fuse_q ? 512 : 256) + b * 64, q0, &bars[Q_FULL]);
             if (p.fuse_q) {
+                pdl_wait();                                // the raw rows above are inputs; the angles are not
                 tma_load_2d(smem + OFF_CS, &p.csmap, 0, q0, &bars[Q_FULL]);
                 tma_load_2d(smem + OFF_CS + IO_BOX, &p.csmap, 32, q0, &bars[Q_FULL]);
             }
@@ -671,7 +677,13 @@ void launch_attn_prefill(cudaStream_t s, const PrefillParams &p) {
         cudaFuncSetAttribute(qw_attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         configured[dev] = true;
     }
-    qw_attn_prefill_kernel<<<p.n_q_tiles * p.q_heads, THREADS, SMEM_BYTES, s>>>(p);
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = cudaLaunchConfig_t();
+    cfg.gridDim = dim3((unsigned)(p.n_q_tiles * p.q_heads)); cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = s;
+    cfg.attrs = &attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, qw_attn_prefill_kernel, p);
     g_launches++;
 }
 

@@ -138,10 +138,10 @@ __global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, ui
 }
 
 // ---- the fused pre-op ---------------------------------------------------------------------
-// grid = (ceil(max_rows / PRE_ROWS) * ceil(slots / 8), 1, n_seq) with slots = q_heads + 2 * kv_heads
-// (the query heads are left out when the prefill kernel norms its own tiles).  A block covers
-// PRE_ROWS consecutive tokens and eight slots, one warp per slot: slot < q_heads is a query head,
-// then the key heads, then the value heads.
+// grid = (ceil(max_rows / PRE_ROWS) * ceil(slots / PRE_WARPS), 1, n_seq) with slots = q_heads + 2 *
+// kv_heads (the query heads are left out when the attention kernel norms its own rows).  A block
+// covers PRE_ROWS consecutive tokens and PRE_WARPS slots, one warp per slot: slot < q_heads is a
+// query head, then the key heads, then the value heads.
 //
 // Lane l holds the eight consecutive dims 8l .. 8l+7 of a head row: one 16-byte load and one
 // 16-byte store per bf16 row and lane, no staging.  The RoPE pair (d, d + 32), d < 32, then sits
@@ -152,7 +152,12 @@ __global__ void __launch_bounds__(256) kv_pack_kernel(KvLayer kc, KvLayer vc, ui
 #define QW_PRE_ROWS 4
 #endif
 constexpr int PRE_ROWS = QW_PRE_ROWS;
-__global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ PreopParams p) {
+// Slots (warps) per block.  Four, not eight: the key warps live longest (their in-order sum), and a
+// block holds its SM resources until its last warp is done -- with small blocks the value and query
+// rows of other blocks stream under them.
+constexpr int PRE_WARPS = 4;
+static_assert(PRE_WARPS >= PRE_ROWS, "a block's first PRE_ROWS warps work out the rows' angles");
+__global__ void __launch_bounds__(PRE_WARPS * 32, 8) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
     // squares of the key rows, [key warps of the block][PRE_ROWS][260] (row stride 260: lanes on
     // distinct banks); sized by the launch for the key heads a block can hold
@@ -165,11 +170,11 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
     const PreopSeq &s = p.seq[blockIdx.z];
     const int qh = p.q_heads, kvh = p.kv_heads;
     const int qs = p.skip_q ? 0 : qh;                    // query slots this launch handles
-    const int nblk = (qs + 2 * kvh + 7) / 8;
+    const int nblk = (qs + 2 * kvh + PRE_WARPS - 1) / PRE_WARPS;
     const int r0 = (blockIdx.x / nblk) * PRE_ROWS;
     if (r0 >= s.rows) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slot0 = (blockIdx.x % nblk) * 8, slot = slot0 + warp;
+    const int slot0 = (blockIdx.x % nblk) * PRE_WARPS, slot = slot0 + warp;
     const int n = min(PRE_ROWS, s.rows - r0);
     const bool active = slot < qs + 2 * kvh;             // (idle warps still help with the angles below)
     const bool is_q = slot < qs, is_k = !is_q && slot < qs + kvh;
@@ -213,7 +218,7 @@ __global__ void __launch_bounds__(256, 4) preop_kernel(const __grid_constant__ P
             sincos((double)ang, &snd, &csd);
             const float sn = (float)snd, cs = (float)csd;
             cs_s[warp][lane] = cs; cs_s[warp][32 + lane] = sn;
-            if (s.cs_out && slot0 <= qs && qs < slot0 + 8) {          // the block with key head 0 publishes the table
+            if (s.cs_out && slot0 <= qs && qs < slot0 + PRE_WARPS) {          // the block with key head 0 publishes the table
                 s.cs_out[(size_t)r * 64 + lane] = cs; s.cs_out[(size_t)r * 64 + 32 + lane] = sn;
             }
         }
@@ -360,9 +365,9 @@ void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cudaLaunchConfig_t cfg = cudaLaunchConfig_t();
-    cfg.gridDim = dim3((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + 7) / 8), 1, p.n_seq);
-    cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = (size_t)(p.kv_heads < 8 ? p.kv_heads : 8) * PRE_ROWS * 260 * sizeof(float);
+    cfg.gridDim = dim3((unsigned)((max_rows + PRE_ROWS - 1) / PRE_ROWS) * ((slots + PRE_WARPS - 1) / PRE_WARPS), 1, p.n_seq);
+    cfg.blockDim = dim3(PRE_WARPS * 32);
+    cfg.dynamicSmemBytes = (size_t)(p.kv_heads < PRE_WARPS ? p.kv_heads : PRE_WARPS) * PRE_ROWS * 260 * sizeof(float);
     cfg.stream = s;
     cfg.attrs = &attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, preop_kernel, p);

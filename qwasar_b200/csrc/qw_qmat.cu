@@ -10,6 +10,7 @@
 // across the warp (the reference's test bounds that reordering at 2e-6 of the sum of absolute
 // terms, tests/test_qmv.c:31-50,129).  A first correct version: weight-bandwidth-bound at one
 // token, not on tensor cores for many.
+#include <algorithm>
 #include "qw_kernels.h"
 
 namespace qw {
@@ -168,6 +169,112 @@ __global__ void __launch_bounds__(256) qmv_q4_multi_kernel(const __grid_constant
     qmv_q4_block(m.y[part], m.x, m.w[part], m.scales[part], m.biases[part], m.k, m.n[part], 1, m.group, block, 0);
 }
 
+// One token, the weights streamed once: x lives in REGISTERS.  A block of W warps splits k: lane l of
+// warp w owns the 32-element slots (i * W + w) * 32 + l, i < NS (one 16-byte weight load per slot and
+// output row), and keeps those slots' inputs -- and their sums, so that scale and bias come out of
+// the inner product -- for every output row it walks.  Blocks are persistent: as many as fit the
+// GPU, each striding over chunks of OUTS output rows with the next chunk's weights already on their
+// way while the current one is multiplied, so x is fetched once per block and a row costs a lane one
+// load and 32 multiply-adds per slot with no shared-memory traffic.
+//
+// A nibble n becomes a float in ONE instruction: a byte permute drops it into mantissa bits 16-19
+// of 0.5f, which is 0.5 (1 + n / 128) exactly; sum_e f_e x_e = 0.5 sum x + (1 / 256) sum n_e x_e, so
+// with the slot's sum of x kept beside it the affine weights fold into two multiply-adds per slot:
+// y += (256 s) S + (b - 128 s) sum x.  (The products f x are rounded to 24 bits against a signal of
+// n x / 256: 1e-6 of a term each, random, far inside the reference's 2e-6 of the sum of absolute
+// terms.)  The kernel this replaces staged x in shared memory, read it back twice per weight word,
+// converted every nibble through the integer-to-float unit: 7 instructions per weight, a third of
+// the warp slots filled, 0.17 of the memory bandwidth.
+__device__ __forceinline__ float nib_f(uint32_t bytes, uint32_t sel) {
+    // byte `sel & 7` of `bytes` into byte 2 of 0x3F000000
+    return __uint_as_float(__byte_perm(bytes, 0x3F000000u, sel));
+}
+template <int NS, int OUTS>
+__global__ void __launch_bounds__(256) qmv1_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
+                                                      const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
+                                                      int n, int group) {
+    __shared__ float part[2][8][OUTS];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
+    const int words = k >> 3, groups = k / group;
+    float xv[NS][32], xsum[NS];
+    int slot[NS];
+#pragma unroll
+    for (int i = 0; i < NS; i++) {
+        slot[i] = (i * W + warp) * 32 + lane;
+        const bool ok = slot[i] * 32 < k;
+        float sum = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const float4 a = ok ? __ldg(reinterpret_cast<const float4 *>(x + (size_t)slot[i] * 32) + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+            xv[i][4 * u] = a.x; xv[i][4 * u + 1] = a.y; xv[i][4 * u + 2] = a.z; xv[i][4 * u + 3] = a.w;
+            sum += (a.x + a.y) + (a.z + a.w);
+        }
+        xsum[i] = sum;
+        if (!ok) slot[i] = -1;
+    }
+    const int n_chunks = (n + OUTS - 1) / OUTS;
+    uint4 wv[OUTS][NS];
+    uint32_t sb[OUTS][NS];                                    // scale (low half) and bias (high half), bf16 bits
+    auto fetch = [&](int chunk) {
+#pragma unroll
+        for (int j = 0; j < OUTS; j++)
+#pragma unroll
+            for (int i = 0; i < NS; i++) {
+                wv[j][i] = make_uint4(0, 0, 0, 0); sb[j][i] = 0u;
+                const int o = chunk * OUTS + j;
+                if (chunk < n_chunks && o < n && slot[i] >= 0) {
+                    wv[j][i] = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)o * words) + slot[i]);
+                    const int gi = slot[i] * 32 / group;
+                    sb[j][i] = (uint32_t)__ldg(scales + (size_t)o * groups + gi) | ((uint32_t)__ldg(biases + (size_t)o * groups + gi) << 16);
+                }
+            }
+    };
+    int chunk = blockIdx.x, it = 0;
+    fetch(chunk);
+    for (; chunk < n_chunks; chunk += gridDim.x, it++) {
+        uint4 cur[OUTS][NS];
+        uint32_t csb[OUTS][NS];
+#pragma unroll
+        for (int j = 0; j < OUTS; j++)
+#pragma unroll
+            for (int i = 0; i < NS; i++) { cur[j][i] = wv[j][i]; csb[j][i] = sb[j][i]; }
+        fetch(chunk + gridDim.x);                               // the next chunk travels under this one's arithmetic
+#pragma unroll
+        for (int j = 0; j < OUTS; j++) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NS; i++) {
+                const uint32_t ww[4] = {cur[j][i].x, cur[j][i].y, cur[j][i].z, cur[j][i].w};
+                float s1 = 0.0f, s2 = 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    // nibbles 0, 2, 4, 6 of the word as the four bytes of lo; 1, 3, 5, 7 as those of hi
+                    const uint32_t lo = ww[u] & 0x0F0F0F0Fu, hi = (ww[u] >> 4) & 0x0F0F0F0Fu;
+                    s1 = fmaf(nib_f(lo, 0x7044), xv[i][8 * u], s1);
+                    s2 = fmaf(nib_f(hi, 0x7044), xv[i][8 * u + 1], s2);
+                    s1 = fmaf(nib_f(lo, 0x7144), xv[i][8 * u + 2], s1);
+                    s2 = fmaf(nib_f(hi, 0x7144), xv[i][8 * u + 3], s2);
+                    s1 = fmaf(nib_f(lo, 0x7244), xv[i][8 * u + 4], s1);
+                    s2 = fmaf(nib_f(hi, 0x7244), xv[i][8 * u + 5], s2);
+                    s1 = fmaf(nib_f(lo, 0x7344), xv[i][8 * u + 6], s1);
+                    s2 = fmaf(nib_f(hi, 0x7344), xv[i][8 * u + 7], s2);
+                }
+                const float sc = __uint_as_float(csb[j][i] << 16), bi = __uint_as_float(csb[j][i] & 0xffff0000u);
+                acc = fmaf(256.0f * sc, s1 + s2, acc);
+                acc = fmaf(fmaf(-128.0f, sc, bi), xsum[i], acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) part[it & 1][warp][j] = acc;
+        }
+        __syncthreads();                                        // (the other half of `part` is written next round)
+        if (threadIdx.x < OUTS && chunk * OUTS + threadIdx.x < n) {
+            float t = 0.0f;
+            for (int q = 0; q < W; q++) t += part[it & 1][q][threadIdx.x];
+            y[chunk * OUTS + threadIdx.x] = t;
+        }
+    }
+}
+
 }  // namespace
 
 void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m) {
@@ -181,6 +288,24 @@ void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m) {
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
                     int n, int rows, int group) {
     if (n <= 0 || rows <= 0) return;
+    if (rows == 1 && k <= 16384 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && g_tune_qmv_regs) {
+        // one token: the register kernel; W warps so that a lane owns one slot (two for long rows)
+        const int slots = k / 32;
+        static int per_sm[2][9] = {{0}};                       // resident blocks per SM by (form, warps)
+        const int form = slots <= 256 ? 0 : 1, W = form == 0 ? (slots + 31) / 32 : (slots + 63) / 64;
+        if (!per_sm[form][W]) {
+            int nb = 0;
+            if (form == 0) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, qmv1_q4_kernel<1, 4>, W * 32, 0);
+            else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, qmv1_q4_kernel<2, 2>, W * 32, 0);
+            per_sm[form][W] = nb > 0 ? nb : 1;
+        }
+        const int outs = form == 0 ? 4 : 2;
+        const int grid = std::min((n + outs - 1) / outs, sm_count() * per_sm[form][W]);
+        if (form == 0) qmv1_q4_kernel<1, 4><<<grid, W * 32, 0, s>>>(y, x, w, scales, biases, k, n, group);
+        else qmv1_q4_kernel<2, 2><<<grid, W * 32, 0, s>>>(y, x, w, scales, biases, k, n, group);
+        g_launches++;
+        return;
+    }
     if (rows <= QV_ROWS && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         qmv_q4_kernel<<<dim3((n + 8 * QV_OUTS - 1) / (8 * QV_OUTS), 1), 256, 0, s>>>(y, x, w, scales, biases, k, n, rows, group);
         g_launches++;

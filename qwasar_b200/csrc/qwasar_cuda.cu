@@ -785,6 +785,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     if (knob && !strcmp(knob, "masked_tc") && (value == 0 || value == 1)) { qw::g_tune_masked_tc = value; return true; }
+    if (knob && !strcmp(knob, "qmv_regs") && (value == 0 || value == 1)) { qw::g_tune_qmv_regs = value; return true; }
     return false;
 }
 // How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
@@ -1041,6 +1042,7 @@ extern "C" size_t qw_kv_state_bytes(int32_t n_layers, int32_t kv_heads, int32_t 
     if (n_layers <= 0 || kv_heads <= 0 || head_dim <= 0 || n_tokens <= 0) return 0;
     return (size_t)n_layers * kv_heads * 2 * n_tokens * head_dim * 2;
 }
+extern "C" uint32_t qw_kv_element_tag(void) { return 0x36314642u; }     // "BF16"
 extern "C" bool qw_kv_pack(qw_buf kcache, qw_buf vcache, int32_t n_layers, int32_t kv_heads, int32_t max_ctx, int32_t head_dim,
                            int32_t n_tokens, void *dst, size_t cap) {
     const size_t need = qw_kv_state_bytes(n_layers, kv_heads, head_dim, n_tokens);

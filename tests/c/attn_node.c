@@ -69,7 +69,7 @@ static const any_fn all_symbols[] = {
     (any_fn)qw_attn_split_plan, (any_fn)qw_prof_kernels, (any_fn)qw_prof_kernel_read,
     (any_fn)qw_buf_alloc_device, (any_fn)qw_buf_wrap_device, (any_fn)qw_buf_device_ptr, (any_fn)qw_buf_upload,
     (any_fn)qw_buf_download, (any_fn)qw_cmd_begin_on_stream, (any_fn)qw_op_copy, (any_fn)qw_kv_arena_alloc,
-    (any_fn)qw_kv_arena_alloc_ex, (any_fn)qw_kv_read, (any_fn)qw_kv_store, (any_fn)qw_kv_state_bytes,
+    (any_fn)qw_kv_arena_alloc_ex, (any_fn)qw_kv_read, (any_fn)qw_kv_store, (any_fn)qw_kv_state_bytes, (any_fn)qw_kv_element_tag,
     (any_fn)qw_kv_pack, (any_fn)qw_kv_unpack, (any_fn)qw_kv_arena_trim, (any_fn)qw_kv_arena_pages_in_use,
     (any_fn)qw_kv_arena_bytes_committed, (any_fn)qw_op_attn_layer_fused, (any_fn)qw_op_attn_layer_fused_batch,
     (any_fn)qw_op_attn_batch, (any_fn)qw_op_attn_partial, (any_fn)qw_op_attn_merge, (any_fn)qw_op_attn_preop,

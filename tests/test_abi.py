@@ -56,6 +56,11 @@ def test_host_rope_tables_match_known_answers():
     assert abs(inv[1] - 0.6042963862) < 1e-7 and abs(inv[31] - 1.654816941254e-07) < 1e-13
 
 
+def test_cache_element_tag_spells_bf16():
+    lib = backend.load_library()
+    assert int(lib.qw_kv_element_tag()).to_bytes(4, "little") == b"BF16"
+
+
 def test_no_device_means_loud_failure():
     """Without a CUDA device init reports why, allocations return NULL and ops encode
     nothing -- there is no CPU path behind the ABI."""

@@ -398,10 +398,11 @@ def parity_block(be, torch, dist, world, rank, device):
     def gather(local):          # concatenation over ranks along the head axis, on rank 0's host
         if world == 1:
             return [local]
-        t = torch.from_numpy(np.ascontiguousarray(local)).to(device)
+        local = np.ascontiguousarray(local)
+        t = torch.from_numpy(local.view(np.uint8)).to(device)      # as bytes: NCCL carries no 16-bit unsigned type
         outs = [torch.empty_like(t) for _ in range(world)]
         dist.all_gather(outs, t)
-        return [o.cpu().numpy() for o in outs]
+        return [o.cpu().numpy().view(local.dtype).reshape(local.shape) for o in outs]
 
     # (1) KV heads sharded: the fused node on each rank's head slice
     for name in ("heads_decode", "heads_verify"):

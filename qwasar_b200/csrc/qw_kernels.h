@@ -174,7 +174,7 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
 
 // ---- 4-bit affine product (qw_qmat.cu): y [rows, n] = x [rows, k] . dequant(w [n, k/8])^T ----
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
-                    int n, int rows, int group);
+                    int n, int rows, int group, int *status);
 
 // Up to four one-token products sharing x (and k, group) in one launch; w rows 16-byte aligned.
 struct QmvMulti {
@@ -185,7 +185,7 @@ struct QmvMulti {
     int32_t n[4], blocks[4];
     int32_t count, k, group;
 };
-void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m);
+void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m, int *status);
 
 // ---- QSA indexer (qw_qsa.cu) ----------------------------------------------------------------
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
@@ -212,6 +212,6 @@ extern int g_tune_pdl;
 // 1: masked attention (position lists) on tensor ops where the grouping allows; 0: the fp32 per-query kernel.
 extern int g_tune_masked_tc;
 // 1: a one-token 4-bit product keeps x in registers (qmv1_q4_kernel); 0: the shared-memory kernel.
-extern int g_tune_qmv_regs;
+extern int g_tune_qmv_tc;
 
 }  // namespace qw

@@ -169,115 +169,370 @@ __global__ void __launch_bounds__(256) qmv_q4_multi_kernel(const __grid_constant
     qmv_q4_block(m.y[part], m.x, m.w[part], m.scales[part], m.biases[part], m.k, m.n[part], 1, m.group, block, 0);
 }
 
-// One token, the weights streamed once: x lives in REGISTERS.  A block of W warps splits k: lane l of
-// warp w owns the 32-element slots (i * W + w) * 32 + l, i < NS (one 16-byte weight load per slot and
-// output row), and keeps those slots' inputs -- and their sums, so that scale and bias come out of
-// the inner product -- for every output row it walks.  Blocks are persistent: as many as fit the
-// GPU, each striding over chunks of OUTS output rows with the next chunk's weights already on their
-// way while the current one is multiplied, so x is fetched once per block and a row costs a lane one
-// load and 32 multiply-adds per slot with no shared-memory traffic.
+// One or two tokens, the weights streamed once, the arithmetic on the INTEGER tensor path.
 //
-// A nibble n becomes a float in ONE instruction: a byte permute drops it into mantissa bits 16-19
-// of 0.5f, which is 0.5 (1 + n / 128) exactly; sum_e f_e x_e = 0.5 sum x + (1 / 256) sum n_e x_e, so
-// with the slot's sum of x kept beside it the affine weights fold into two multiply-adds per slot:
-// y += (256 s) S + (b - 128 s) sum x.  (The products f x are rounded to 24 bits against a signal of
-// n x / 256: 1e-6 of a term each, random, far inside the reference's 2e-6 of the sum of absolute
-// terms.)  The kernel this replaces staged x in shared memory, read it back twice per weight word,
-// converted every nibble through the integer-to-float unit: 7 instructions per weight, a third of
-// the warp slots filled, 0.17 of the memory bandwidth.
-__device__ __forceinline__ float nib_f(uint32_t bytes, uint32_t sel) {
-    // byte `sel & 7` of `bytes` into byte 2 of 0x3F000000
-    return __uint_as_float(__byte_perm(bytes, 0x3F000000u, sel));
+// Why integers: at one token the product is bound by instruction issue, not by memory -- turning a
+// nibble into a float costs the conversion unit a quarter-rate instruction (or a permute on the
+// half-rate logic pipe) and every weight one multiply-add: 5 to 7 instructions per weight, 0.17 to
+// 0.21 of the memory bandwidth however x is staged (shared memory, or registers with prefetch).
+// mma.sync.m16n8k32.u8.s8 takes the nibbles as they are -- `w & 0x0F0F0F0F` IS an A fragment
+// register, 3 instructions per 8 weights -- and adds in int32 without rounding.  x becomes integers
+// exactly: each token is scaled by a power of two so that max |x| lands in [2^28, 2^29), rounded to
+// an int32 q (every element within 2^-6 of the maximum keeps its full mantissa), and q is cut into
+// four balanced base-256 digits, one column of B each: a token owns four of the eight columns, so
+// one launch carries two tokens.  Per group of 64 weights the digit sums come out of the
+// accumulators exactly, are combined pairwise in int32, and meet the group's scale in one fp32
+// multiply-add per row; the bias meets the group's sum of q.  What is left of rounding is the fp32
+// sum over groups and warps, far inside the reference's bound (2e-6 of the sum of absolute terms,
+// tests/test_qmv.c:31-50,129).
+//
+// Layout of the work: a tile is 16 output rows by all of k.  One producer warp brings a tile's
+// rows (and their scales and biases) into shared memory with ten bulk copies -- long bursts for
+// DRAM, and no register or issue slot of the consumers is spent on loads; up to four tiles are in
+// flight per block.  The consumer warps split k, 8 groups each: a quad of lanes takes one group of
+// one row, so that an instruction's 32 k-positions lie in one group; a warp's fragments of x stay
+// in its registers for the whole launch, its 8 scales of a row are one 16-byte read.  A last warp
+// adds the consumers' partial sums of a tile up and writes y, behind a barrier of its own, so no
+// consumer ever waits for another.  Blocks are persistent, one per SM, tiles strided over them; x is
+// quantised while the first tiles travel (it is asked for before the second tile is, or it would
+// queue behind them).  A token with an infinity or a NaN in x yields NaN for all its outputs.
+//
+// What was measured on the way (k 5120, n 12288, one token, 35 MB per launch, back-to-back launches
+// over eight weight sets): lanes loading 8 bytes each, one group of one row per quad, 1.0 TB/s (the
+// memory system was handed 32-byte sectors of eight rows per request); one bulk copy per row, 48 a
+// tile, 2.5 TB/s with the arithmetic switched off (a copy costs the unit a fixed time); a block-wide
+// barrier per tile and x in shared memory, 2.3 TB/s; this form 3.3 TB/s, of which the stream itself
+// runs at DRAM speed (a tile per SM every 0.95 us) and the rest is the launch gap (2.2 us), the first
+// tile's latency (2.4 us) and the last tile's arithmetic (1.2 us).
+constexpr int QI_MAXW = 14, QI_MAXS = 4, QI_ITEMS = 4, QI_PER = 8, QI_SLOTS = 4;   // warps, stages, 8-element items per thread, groups per warp, slots of partial sums
+struct QmvJob {
+    float *y[4];
+    const uint32_t *w[4];
+    const uint16_t *scales[4], *biases[4];
+    const float *x;
+    int *status;
+    int32_t n[4], tile_end[4];                                 // running total of 16-row tiles over the parts
+    int32_t count, k, tokens, per, tiles, stages, w_stride;   // w_stride: bytes from one staged pair of rows to the next
+};
+
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-template <int NS, int OUTS>
-__global__ void __launch_bounds__(256) qmv1_q4_kernel(float *__restrict__ y, const float *__restrict__ x, const uint32_t *__restrict__ w,
-                                                      const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases, int k,
-                                                      int n, int group) {
-    __shared__ float part[2][8][OUTS];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, W = blockDim.x >> 5;
-    const int words = k >> 3, groups = k / group;
-    float xv[NS][32], xsum[NS];
-    int slot[NS];
-#pragma unroll
-    for (int i = 0; i < NS; i++) {
-        slot[i] = (i * W + warp) * 32 + lane;
-        const bool ok = slot[i] * 32 < k;
-        float sum = 0.0f;
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const float4 a = ok ? __ldg(reinterpret_cast<const float4 *>(x + (size_t)slot[i] * 32) + u) : make_float4(0.f, 0.f, 0.f, 0.f);
-            xv[i][4 * u] = a.x; xv[i][4 * u + 1] = a.y; xv[i][4 * u + 2] = a.z; xv[i][4 * u + 3] = a.w;
-            sum += (a.x + a.y) + (a.z + a.w);
-        }
-        xsum[i] = sum;
-        if (!ok) slot[i] = -1;
-    }
-    const int n_chunks = (n + OUTS - 1) / OUTS;
-    uint4 wv[OUTS][NS];
-    uint32_t sb[OUTS][NS];                                    // scale (low half) and bias (high half), bf16 bits
-    auto fetch = [&](int chunk) {
-#pragma unroll
-        for (int j = 0; j < OUTS; j++)
-#pragma unroll
-            for (int i = 0; i < NS; i++) {
-                wv[j][i] = make_uint4(0, 0, 0, 0); sb[j][i] = 0u;
-                const int o = chunk * OUTS + j;
-                if (chunk < n_chunks && o < n && slot[i] >= 0) {
-                    wv[j][i] = __ldg(reinterpret_cast<const uint4 *>(w + (size_t)o * words) + slot[i]);
-                    const int gi = slot[i] * 32 / group;
-                    sb[j][i] = (uint32_t)__ldg(scales + (size_t)o * groups + gi) | ((uint32_t)__ldg(biases + (size_t)o * groups + gi) << 16);
-                }
-            }
+// global -> shared bulk copy (untiled; both addresses and the size multiples of 16 bytes), completing on `bar`
+__device__ __forceinline__ void bulk_load(void *smem_dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint2 lds_u2(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u4(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void consumer_sync(int threads) { asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory"); }
+
+__global__ void __launch_bounds__((QI_MAXW + 2) * 32, 1) qmv_imma_q4_kernel(const __grid_constant__ QmvJob job) {
+    constexpr int GROUP = 64;
+    extern __shared__ __align__(128) unsigned char qmv_smem[];
+    __shared__ uint64_t full[QI_MAXS], empty[QI_MAXS], done[QI_SLOTS], pfree[QI_SLOTS];
+    __shared__ uint32_t s_max[QI_MAXW][2];
+    __shared__ int s_abort;
+    const int k = job.k, groups = k / GROUP, words = k >> 3, W = (blockDim.x >> 5) - 2, tokens = job.tokens, S = job.stages;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3, CT = W * 32;
+    float *xg = reinterpret_cast<float *>(qmv_smem);            // [4][groups] sums of q (rows >= tokens: 0)
+    float *part = xg + 4 * groups;                              // [slot][W][16 rows][4 column pairs]
+    float *pbias = part + QI_SLOTS * W * 64;                    // [slot][W][16 rows][4 tokens]
+    const uint32_t w_bytes = (uint32_t)(k >> 1), s_bytes = (uint32_t)(groups * 2), stage_bytes = 8u * job.w_stride + 32u * s_bytes;
+    unsigned char *stage0 = qmv_smem + (((size_t)groups * 16 + (size_t)W * 64 * 4 * 2 * QI_SLOTS + 127) & ~(size_t)127);
+    // the quantised x, [8 columns][k / 8 chunks of 8 elements, + 4] in fragment order (the + 4 puts the columns 8 banks
+    // apart: a fragment read then covers all banks, and a chunk's writer stores next to its neighbours'), borrows the
+    // LAST stage until the consumers hold their fragments in registers (a stage is larger: 9 k bytes against 8 k)
+    const int xcol = words + 4;
+    uint2 *xs = reinterpret_cast<uint2 *>(stage0 + (size_t)(S - 1) * stage_bytes);
+    const int tiles = job.tiles;
+    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    auto locate = [&](int tile, int &part_i, int &base) {
+        part_i = 0; base = 0;
+        while (part_i + 1 < job.count && tile >= job.tile_end[part_i]) { base = job.tile_end[part_i]; part_i++; }
     };
-    int chunk = blockIdx.x, it = 0;
-    fetch(chunk);
-    for (; chunk < n_chunks; chunk += gridDim.x, it++) {
-        uint4 cur[OUTS][NS];
-        uint32_t csb[OUTS][NS];
-#pragma unroll
-        for (int j = 0; j < OUTS; j++)
-#pragma unroll
-            for (int i = 0; i < NS; i++) { cur[j][i] = wv[j][i]; csb[j][i] = sb[j][i]; }
-        fetch(chunk + gridDim.x);                               // the next chunk travels under this one's arithmetic
-#pragma unroll
-        for (int j = 0; j < OUTS; j++) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NS; i++) {
-                const uint32_t ww[4] = {cur[j][i].x, cur[j][i].y, cur[j][i].z, cur[j][i].w};
-                float s1 = 0.0f, s2 = 0.0f;
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    // nibbles 0, 2, 4, 6 of the word as the four bytes of lo; 1, 3, 5, 7 as those of hi
-                    const uint32_t lo = ww[u] & 0x0F0F0F0Fu, hi = (ww[u] >> 4) & 0x0F0F0F0Fu;
-                    s1 = fmaf(nib_f(lo, 0x7044), xv[i][8 * u], s1);
-                    s2 = fmaf(nib_f(hi, 0x7044), xv[i][8 * u + 1], s2);
-                    s1 = fmaf(nib_f(lo, 0x7144), xv[i][8 * u + 2], s1);
-                    s2 = fmaf(nib_f(hi, 0x7144), xv[i][8 * u + 3], s2);
-                    s1 = fmaf(nib_f(lo, 0x7244), xv[i][8 * u + 4], s1);
-                    s2 = fmaf(nib_f(hi, 0x7244), xv[i][8 * u + 5], s2);
-                    s1 = fmaf(nib_f(lo, 0x7344), xv[i][8 * u + 6], s1);
-                    s2 = fmaf(nib_f(hi, 0x7344), xv[i][8 * u + 7], s2);
-                }
-                const float sc = __uint_as_float(csb[j][i] << 16), bi = __uint_as_float(csb[j][i] & 0xffff0000u);
-                acc = fmaf(256.0f * sc, s1 + s2, acc);
-                acc = fmaf(fmaf(-128.0f, sc, bi), xsum[i], acc);
+
+    if (tid == 0) {
+        s_abort = 0;
+        for (int i = 0; i < S; i++) { mbar_init(&full[i], 1); mbar_init(&empty[i], W); }
+        for (int i = 0; i < QI_SLOTS; i++) { mbar_init(&done[i], W); mbar_init(&pfree[i], 1); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_wait();                                                 // x may come from the kernel before; nothing is written yet
+    pdl_launch_next();
+
+    if (warp == W) {
+        // ---- producer: a tile's 16 rows of weights, 16 rows of scales, 16 of biases per stage -------
+        // Ten copies per tile: the rows of a tile follow one another in memory, so the weights go pair of
+        // rows by pair of rows (the pairs 8 banks apart in shared memory: the 8 rows a fragment load touches
+        // then cover all 32 banks in two passes, the least an 8-byte load per lane takes), scales and biases
+        // as one block each.  (One copy per row -- 48 a tile -- held the whole kernel to 2.5 TB/s with the
+        // arithmetic switched off: a copy costs the unit a fixed time whatever its size.)  Only a part's last
+        // tile, when it has fewer than 16 rows, is copied row by row, the missing rows filled with the last.
+        for (int it = 0; it < my_tiles; it++) {
+            const int st = it % S, tile = blockIdx.x + it * gridDim.x;
+            if (it == 1) asm volatile("bar.sync 2, %0;" ::"r"(CT + 32) : "memory");      // the consumers have asked for x
+            if (it == S - 1) asm volatile("bar.sync 3, %0;" ::"r"(CT + 32) : "memory");  // ... and are done with the borrowed stage
+            if (it >= S) mbar_wait_hot(&empty[st], ((it / S) - 1) & 1, &s_abort, job.status, QW_ST_SLOT_TIMEOUT);
+            int pi, base; locate(tile, pi, base);
+            const int row0 = (tile - base) * 16;
+            unsigned char *dst = stage0 + (size_t)st * stage_bytes, *dst_s = dst + 8u * job.w_stride;
+            if (lane == 0) mbar_expect_tx(&full[st], 16u * w_bytes + 32u * s_bytes);
+            __syncwarp();
+            if (row0 + 16 <= job.n[pi]) {
+                if (lane < 8) bulk_load(dst + (size_t)lane * job.w_stride, job.w[pi] + (size_t)(row0 + 2 * lane) * words, 2u * w_bytes, &full[st]);
+                else if (lane == 8) bulk_load(dst_s, job.scales[pi] + (size_t)row0 * groups, 16u * s_bytes, &full[st]);
+                else if (lane == 9) bulk_load(dst_s + 16u * s_bytes, job.biases[pi] + (size_t)row0 * groups, 16u * s_bytes, &full[st]);
+            } else {
+                const int row = min(row0 + (lane & 15), job.n[pi] - 1);
+                if (lane < 16) bulk_load(dst + (size_t)(lane >> 1) * job.w_stride + (lane & 1) * w_bytes, job.w[pi] + (size_t)row * words, w_bytes, &full[st]);
+                bulk_load(dst_s + (size_t)lane * s_bytes, (lane < 16 ? job.scales[pi] : job.biases[pi]) + (size_t)row * groups, s_bytes, &full[st]);
             }
-            acc = warp_sum(acc);
-            if (lane == 0) part[it & 1][warp][j] = acc;
         }
-        __syncthreads();                                        // (the other half of `part` is written next round)
-        if (threadIdx.x < OUTS && chunk * OUTS + threadIdx.x < n) {
-            float t = 0.0f;
-            for (int q = 0; q < W; q++) t += part[it & 1][q][threadIdx.x];
-            y[chunk * OUTS + threadIdx.x] = t;
+        if (my_tiles < 2) asm volatile("bar.sync 2, %0;" ::"r"(CT + 32) : "memory");
+        if (my_tiles < S) asm volatile("bar.sync 3, %0;" ::"r"(CT + 32) : "memory");
+        return;
+    }
+    if (warp == W + 1) {
+        // ---- the warp that adds a tile up: 16 rows x 2 tokens, one lane each, over the W warps' partial sums ----
+        const int row = lane >> 1, t = lane & 1;
+        float inv = 0.0f;
+        bool bad = false;
+        for (int it = 0; it < my_tiles; it++) {
+            const int st = it % QI_SLOTS, tile = blockIdx.x + it * gridDim.x;
+            mbar_wait_hot(&done[st], (it / QI_SLOTS) & 1, &s_abort, job.status, QW_ST_MMA_TIMEOUT);
+            if (it == 0) {                                       // (the consumers' maxima are complete once a tile is)
+                uint32_t m = 0;
+                for (int q = 0; q < W; q++) m = max(m, s_max[q][t]);
+                int e = (int)(m >> 23);
+                bad = e == 255;
+                inv = __uint_as_float((uint32_t)(min(max(e, 29), 254) - 28) << 23);
+            }
+            int pi, base; locate(tile, pi, base);
+            const int o = (tile - base) * 16 + row;
+            const float *a = part + (size_t)st * W * 64 + row * 4, *bq = pbias + (size_t)st * W * 64 + row * 4;
+            float lo = 0.0f, hi = 0.0f, bs = 0.0f;
+            for (int q = 0; q < W; q++) { lo += a[q * 64 + 2 * t]; hi += a[q * 64 + 2 * t + 1]; bs += bq[q * 64 + t]; }
+            if (t < tokens && o < job.n[pi])
+                job.y[pi][(size_t)t * job.n[pi] + o] = bad ? __uint_as_float(0x7fc00000u) : inv * (fmaf(65536.0f, hi, lo) + bs);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&pfree[st]);             // the slot of partial sums may be written again
         }
+        return;
+    }
+
+    // ---- x -> integers (the consumer warps, while the first tiles travel) -------------------------
+    // An item is 8 consecutive elements of one token (a chunk: what one lane feeds one instruction);
+    // a thread keeps its items in registers between the pass that finds max |x| and the one that cuts
+    // the digits, so x is read once.  (The host side checks that QI_ITEMS items per thread suffice.)
+    const int items = words * tokens;
+    float xv[QI_ITEMS][8];
+    uint32_t m0 = 0, m1 = 0;
+#pragma unroll
+    for (int i = 0; i < QI_ITEMS; i++) {
+        const int it = tid + i * CT;
+#pragma unroll
+        for (int j = 0; j < 8; j++) xv[i][j] = 0.0f;
+        if (it < items) {
+            const int t = it >= words, c = it - t * words;
+            const int e0 = (c >> 3) * GROUP + (c & 3) * 16 + ((c >> 2) & 1) * 8;   // chunk c = (group, word of the lane, lane-in-quad)
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(job.x + (size_t)t * k + e0));
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(job.x + (size_t)t * k + e0 + 4));
+            xv[i][0] = a.x; xv[i][1] = a.y; xv[i][2] = a.z; xv[i][3] = a.w; xv[i][4] = b.x; xv[i][5] = b.y; xv[i][6] = b.z; xv[i][7] = b.w;
+        }
+    }
+    // x is asked for before the weights: behind three stages of weight traffic it would arrive last
+    asm volatile("bar.arrive 2, %0;" ::"r"(CT + 32) : "memory");
+#pragma unroll
+    for (int i = 0; i < QI_ITEMS; i++) {
+        const int it = tid + i * CT;
+        if (it < items) {
+            uint32_t m = 0;
+#pragma unroll
+            for (int j = 0; j < 8; j++) m = max(m, __float_as_uint(xv[i][j]) & 0x7fffffffu);
+            if (it >= words) m1 = max(m1, m); else m0 = max(m0, m);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) { m0 = max(m0, __shfl_xor_sync(0xffffffffu, m0, o)); m1 = max(m1, __shfl_xor_sync(0xffffffffu, m1, o)); }
+    if (lane == 0) { s_max[warp][0] = m0; s_max[warp][1] = m1; }
+    for (int i = tokens * groups + tid; i < 4 * groups; i += CT) xg[i] = 0.0f;
+    consumer_sync(CT);
+    float scale[2];
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        uint32_t m = 0;
+        for (int q = 0; q < W; q++) m = max(m, s_max[q][t]);
+        const int e = min(max((int)(m >> 23), 29), 254);
+        scale[t] = __uint_as_float((uint32_t)(282 - e) << 23);  // max |x| * scale in [2^28, 2^29); the adding warp undoes it
+    }
+#pragma unroll
+    for (int i = 0; i < QI_ITEMS; i++) {
+        if (i * CT >= items) break;                              // (the same for every thread)
+        const int it = tid + i * CT;
+        const bool live = it < items;
+        const int t = live && it >= words, c = live ? it - t * words : 0;
+        // q + 0x00808080 has the balanced base-256 digits of q, each plus 128, as its low three bytes and the top
+        // digit as its (signed) high byte: the xor takes the 128s off again.  Then two 4 x 4 byte transposes put
+        // digit p of elements 0, 2, 4, 6 into one B register and of 1, 3, 5, 7 into the other.
+        uint32_t z[8];
+        int sum_hi = 0, sum_lo = 0;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int q = __float2int_rn(xv[i][j] * (t ? scale[1] : scale[0]));
+            sum_hi += q >> 8; sum_lo += q & 255;
+            z[j] = (uint32_t)(q + 0x00808080) ^ 0x00808080u;
+        }
+        uint2 col[4];
+        {
+            const uint32_t t0 = __byte_perm(z[0], z[2], 0x5140), t1 = __byte_perm(z[0], z[2], 0x7362);
+            const uint32_t u0 = __byte_perm(z[4], z[6], 0x5140), u1 = __byte_perm(z[4], z[6], 0x7362);
+            col[0].x = __byte_perm(t0, u0, 0x5410); col[1].x = __byte_perm(t0, u0, 0x7632);
+            col[2].x = __byte_perm(t1, u1, 0x5410); col[3].x = __byte_perm(t1, u1, 0x7632);
+        }
+        {
+            const uint32_t t0 = __byte_perm(z[1], z[3], 0x5140), t1 = __byte_perm(z[1], z[3], 0x7362);
+            const uint32_t u0 = __byte_perm(z[5], z[7], 0x5140), u1 = __byte_perm(z[5], z[7], 0x7362);
+            col[0].y = __byte_perm(t0, u0, 0x5410); col[1].y = __byte_perm(t0, u0, 0x7632);
+            col[2].y = __byte_perm(t1, u1, 0x5410); col[3].y = __byte_perm(t1, u1, 0x7632);
+        }
+        // the group's sum of q: its 8 chunks sit in 8 neighbouring lanes
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) { sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, o); sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, o); }
+        if (live) {
+#pragma unroll
+            for (int p = 0; p < 4; p++) xs[(size_t)(t * 4 + p) * xcol + c] = col[p];
+            if (tokens == 1) {
+#pragma unroll
+                for (int p = 4; p < 8; p++) xs[(size_t)p * xcol + c] = make_uint2(0u, 0u);
+            }
+            if ((c & 7) == 0) xg[t * groups + (c >> 3)] = fmaf((float)sum_hi, 256.0f, (float)sum_lo);
+        }
+    }
+    consumer_sync(CT);
+
+    // ---- the product ---------------------------------------------------------------------------
+    // A warp owns 8 consecutive groups of k for every tile: their B fragments (the digits of x) and sums
+    // of q stay in registers, its 8 scales and 8 biases of a row are one 16-byte read each, and shared
+    // memory is addressed through 32-bit window offsets (with generic pointers the address arithmetic of
+    // the reads outweighed the arithmetic they feed).  No block-wide barrier: a warp hands its partial
+    // sums to the adding warp through the stage's `done` barrier and goes on to the next tile.
+    const int g0 = warp * QI_PER;
+    uint2 bx[QI_PER][2];
+    float xsum[QI_PER];
+#pragma unroll
+    for (int i = 0; i < QI_PER; i++) {
+        const uint2 *xb = xs + (size_t)gid * xcol + (g0 + i) * 8 + tig;     // chunk (group, word 0 / 1 of the lane, lane-in-quad)
+        bx[i][0] = xb[0]; bx[i][1] = xb[4];
+        xsum[i] = xg[tig * groups + g0 + i];
+    }
+    fence_proxy_async();                                           // (our reads of it, before the bulk copies' writes)
+    asm volatile("bar.arrive 3, %0;" ::"r"(CT + 32) : "memory");     // the borrowed stage may be loaded
+    const uint32_t a_stage = smem_u32(stage0);
+    const uint32_t o_w = (uint32_t)(gid >> 1) * job.w_stride + (gid & 1) * w_bytes + tig * 8 + g0 * 32, o_s = 8u * job.w_stride + (uint32_t)gid * s_bytes + g0 * 2;
+    const uint32_t d_w = 4u * job.w_stride, d_s = 8u * s_bytes, d_b = 16u * s_bytes;
+    for (int it = 0; it < my_tiles; it++) {
+        const int st = it % S;
+        mbar_wait_hot(&full[st], (it / S) & 1, &s_abort, job.status, QW_ST_TMA_TIMEOUT);
+        const uint32_t a_w = a_stage + (uint32_t)st * stage_bytes + o_w, a_s = a_stage + (uint32_t)st * stage_bytes + o_s;
+        const uint4 sv0 = lds_u4(a_s), sv1 = lds_u4(a_s + d_s), bv0 = lds_u4(a_s + d_b), bv1 = lds_u4(a_s + d_b + d_s);
+        const uint32_t s0w[4] = {sv0.x, sv0.y, sv0.z, sv0.w}, s1w[4] = {sv1.x, sv1.y, sv1.z, sv1.w};
+        const uint32_t b0w[4] = {bv0.x, bv0.y, bv0.z, bv0.w}, b1w[4] = {bv1.x, bv1.y, bv1.z, bv1.w};
+        float ya0 = 0.0f, ya1 = 0.0f, yb0 = 0.0f, yb1 = 0.0f;  // rows gid, gid + 8: column-pair sums, bias sums (token tig)
+#pragma unroll
+        for (int i = 0; i < QI_PER; i++) {
+            const uint2 wa = lds_u2(a_w + 32 * i), wb = lds_u2(a_w + d_w + 32 * i);
+            int c[4] = {0, 0, 0, 0};
+            mma_u8s8(c, wa.x & 0x0F0F0F0Fu, wb.x & 0x0F0F0F0Fu, (wa.x >> 4) & 0x0F0F0F0Fu, (wb.x >> 4) & 0x0F0F0F0Fu, bx[i][0].x, bx[i][0].y);
+            mma_u8s8(c, wa.y & 0x0F0F0F0Fu, wb.y & 0x0F0F0F0Fu, (wa.y >> 4) & 0x0F0F0F0Fu, (wb.y >> 4) & 0x0F0F0F0Fu, bx[i][1].x, bx[i][1].y);
+            // bf16 pairs: the even group's value is the low half of its word
+            const float s_0 = __uint_as_float((i & 1) ? s0w[i >> 1] & 0xffff0000u : s0w[i >> 1] << 16);
+            const float s_1 = __uint_as_float((i & 1) ? s1w[i >> 1] & 0xffff0000u : s1w[i >> 1] << 16);
+            const float b_0 = __uint_as_float((i & 1) ? b0w[i >> 1] & 0xffff0000u : b0w[i >> 1] << 16);
+            const float b_1 = __uint_as_float((i & 1) ? b1w[i >> 1] & 0xffff0000u : b1w[i >> 1] << 16);
+            // columns 2 tig, 2 tig + 1 are digits (0, 1) or (2, 3) of token tig / 2
+            ya0 = fmaf(s_0, (float)(c[0] + (c[1] << 8)), ya0);
+            ya1 = fmaf(s_1, (float)(c[2] + (c[3] << 8)), ya1);
+            yb0 = fmaf(b_0, xsum[i], yb0);
+            yb1 = fmaf(b_1, xsum[i], yb1);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);                 // done with the staged tile
+        const int slot = it % QI_SLOTS;
+        if (it >= QI_SLOTS) mbar_wait_hot(&pfree[slot], ((it / QI_SLOTS) - 1) & 1, &s_abort, job.status, QW_ST_SLOT_TIMEOUT);
+        float *pp = part + (size_t)(slot * W + warp) * 64, *pq = pbias + (size_t)(slot * W + warp) * 64;
+        pp[gid * 4 + tig] = ya0; pp[(gid + 8) * 4 + tig] = ya1;
+        pq[gid * 4 + tig] = yb0; pq[(gid + 8) * 4 + tig] = yb1;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&done[slot]);                // partial sums are in place
     }
 }
 
 }  // namespace
 
-void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m) {
+// The tensor-path kernel's launch, or false where it does not apply (then the callers below use the
+// fp32 kernels): up to two tokens, groups of 64, k a multiple of 512 (so that a row of scales is a
+// whole number of 16-byte units), 16-byte aligned operands, at least two tiles staged beside the
+// quantised x in shared memory.
+static bool launch_qmv_imma(cudaStream_t s, QmvJob &job, int group) {
+    const int k = job.k;
+    if (!g_tune_qmv_tc || job.tokens < 1 || job.tokens > 2 || group != 64 || k <= 0 || (k & 511)) return false;
+    uintptr_t align = reinterpret_cast<uintptr_t>(job.x);
+    job.tiles = 0;
+    for (int i = 0; i < job.count; i++) {
+        if (job.n[i] <= 0) return false;
+        align |= reinterpret_cast<uintptr_t>(job.w[i]) | reinterpret_cast<uintptr_t>(job.scales[i]) | reinterpret_cast<uintptr_t>(job.biases[i]);
+        job.tiles += (job.n[i] + 15) / 16;
+        job.tile_end[i] = job.tiles;
+    }
+    if (align & 15) return false;
+    const int groups = k / group;
+    job.per = QI_PER;
+    const int W = groups / QI_PER;                              // (k is a multiple of 512)
+    if (W > QI_MAXW) return false;
+    // staged pairs of rows start 8 banks apart
+    int w_words = k / 4; w_words += ((8 - w_words % 32) + 32) % 32;
+    job.w_stride = w_words * 4;
+    const size_t fixed = (((size_t)groups * 16 + (size_t)W * 64 * 4 * 2 * QI_SLOTS + 127) & ~(size_t)127) + 128;
+    const size_t stage = 8 * (size_t)job.w_stride + 32 * (size_t)groups * 2, cap = 226 * 1024;
+    if (fixed + 2 * stage > cap) return false;
+    job.stages = (int)std::min<size_t>(QI_MAXS, (cap - fixed) / stage);
+    const size_t smem = fixed + job.stages * stage;
+    static bool configured[16] = {false};                       // per device
+    int dev = 0; cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) return false;
+    if (!configured[dev]) {
+        if (cudaFuncSetAttribute(qmv_imma_q4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cap) != cudaSuccess) return false;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min(job.tiles, sm_count())); cfg.blockDim = dim3((W + 2) * 32); cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, qmv_imma_q4_kernel, job) != cudaSuccess) return false;
+    g_launches++;
+    return true;
+}
+
+void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m, int *status) {
+    {
+        QmvJob job{};
+        for (int i = 0; i < m.count; i++) { job.y[i] = m.y[i]; job.w[i] = m.w[i]; job.scales[i] = m.scales[i]; job.biases[i] = m.biases[i]; job.n[i] = m.n[i]; }
+        job.x = m.x; job.count = m.count; job.k = m.k; job.tokens = 1; job.status = status;
+        if (m.count >= 1 && launch_qmv_imma(s, job, m.group)) return;
+    }
     int total = 0;
     for (int i = 0; i < m.count; i++) { m.blocks[i] = (m.n[i] + 8 * QV_OUTS - 1) / (8 * QV_OUTS); total += m.blocks[i]; }
     if (total <= 0) return;
@@ -286,25 +541,13 @@ void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m) {
 }
 
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
-                    int n, int rows, int group) {
+                    int n, int rows, int group, int *status) {
     if (n <= 0 || rows <= 0) return;
-    if (rows == 1 && k <= 16384 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) & 15) == 0 && g_tune_qmv_regs) {
-        // one token: the register kernel; W warps so that a lane owns one slot (two for long rows)
-        const int slots = k / 32;
-        static int per_sm[2][9] = {{0}};                       // resident blocks per SM by (form, warps)
-        const int form = slots <= 256 ? 0 : 1, W = form == 0 ? (slots + 31) / 32 : (slots + 63) / 64;
-        if (!per_sm[form][W]) {
-            int nb = 0;
-            if (form == 0) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, qmv1_q4_kernel<1, 4>, W * 32, 0);
-            else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, qmv1_q4_kernel<2, 2>, W * 32, 0);
-            per_sm[form][W] = nb > 0 ? nb : 1;
-        }
-        const int outs = form == 0 ? 4 : 2;
-        const int grid = std::min((n + outs - 1) / outs, sm_count() * per_sm[form][W]);
-        if (form == 0) qmv1_q4_kernel<1, 4><<<grid, W * 32, 0, s>>>(y, x, w, scales, biases, k, n, group);
-        else qmv1_q4_kernel<2, 2><<<grid, W * 32, 0, s>>>(y, x, w, scales, biases, k, n, group);
-        g_launches++;
-        return;
+    if (rows <= 2) {
+        QmvJob job{};
+        job.y[0] = y; job.w[0] = w; job.scales[0] = scales; job.biases[0] = biases; job.n[0] = n;
+        job.x = x; job.count = 1; job.k = k; job.tokens = rows; job.status = status;
+        if (launch_qmv_imma(s, job, group)) return;
     }
     if (rows <= QV_ROWS && (reinterpret_cast<uintptr_t>(w) & 15) == 0) {
         qmv_q4_kernel<<<dim3((n + 8 * QV_OUTS - 1) / (8 * QV_OUTS), 1), 256, 0, s>>>(y, x, w, scales, biases, k, n, rows, group);

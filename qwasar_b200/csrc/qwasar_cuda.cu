@@ -785,7 +785,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     if (knob && !strcmp(knob, "masked_tc") && (value == 0 || value == 1)) { qw::g_tune_masked_tc = value; return true; }
-    if (knob && !strcmp(knob, "qmv_regs") && (value == 0 || value == 1)) { qw::g_tune_qmv_regs = value; return true; }
+    if (knob && !strcmp(knob, "qmv_tc") && (value == 0 || value == 1)) { qw::g_tune_qmv_tc = value; return true; }
     return false;
 }
 // How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
@@ -1373,7 +1373,7 @@ static bool qmat_q4(qw_cmd c, const char *op, qw_ref y, qw_ref x, qw_ref w, qw_r
     const uint16_t *ps = (const uint16_t *)dev_range(c, scales, (size_t)n * (k / group) * 2, false, 2);
     const uint16_t *pb = (const uint16_t *)dev_range(c, biases, (size_t)n * (k / group) * 2, false, 2);
     if (!py || !px || !pw || !ps || !pb) return false;
-    launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group);
+    launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group, cmd_status(c));
     return cuda_ok(c, cudaGetLastError(), "qmat_q4 launch");
 }
 extern "C" void qw_op_qmat_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n, int32_t rows,
@@ -1409,9 +1409,9 @@ extern "C" bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group,
         aligned = aligned && ((uintptr_t)m.w[i] & 15) == 0;
     }
     if (aligned) {
-        launch_qmv_q4_multi(c->stream, m);               // one dispatch for all parts
+        launch_qmv_q4_multi(c->stream, m, cmd_status(c));               // one dispatch for all parts
     } else {
-        for (int32_t i = 0; i < count; i++) launch_qmat_q4(c->stream, m.y[i], m.x, m.w[i], m.scales[i], m.biases[i], k, m.n[i], 1, group);
+        for (int32_t i = 0; i < count; i++) launch_qmat_q4(c->stream, m.y[i], m.x, m.w[i], m.scales[i], m.biases[i], k, m.n[i], 1, group, cmd_status(c));
     }
     return cuda_ok(c, cudaGetLastError(), "qmv_q4_multi launch");
 }

@@ -31,7 +31,9 @@ def worst_rel_err(got, x, deq):
 
 
 @pytest.mark.parametrize("op", ["op_qmat_q4", "op_qmv_q4", "op_qmm_q4"])
-@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (8192, 70, 2, 64), (5120, 33, 1, 32), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32)])
+@pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (8192, 70, 2, 64), (5120, 33, 1, 32), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32),
+                                              (5120, 12288, 1, 64), (5120, 1000, 2, 64), (12288, 500, 1, 64), (4096, 257, 2, 64), (128, 16, 1, 64),
+                                              (640, 1, 1, 64), (16384, 40, 2, 64)])
 def test_q4_product(be, oracle, op, k, n, rows, group):
     rng = np.random.default_rng(k + n + rows)
     w, sc, bi = q4_weights(rng, n, k, group)
@@ -49,6 +51,49 @@ def test_q4_product(be, oracle, op, k, n, rows, group):
         want = oracle.qmv_q4(x, w, sc, bi, k, n, rows, group)
         assert worst_rel_err(want, x, dequant(w, sc, bi, k, group)) < 2e-5
         assert np.allclose(got, want, rtol=0, atol=2e-5 * np.abs(want).max() + 1e-6)
+
+
+@pytest.mark.parametrize("kind", ["positive", "outlier", "tiny", "huge", "zero", "nan"])
+def test_q4_product_input_ranges(be, kind):
+    """The one- and two-token product turns x into scaled integers: inputs that stress the scale --
+    one-signed (nothing cancels in the sums), a 1e4 outlier over unit noise, magnitudes near the
+    ends of the fp32 range, all zeros -- stay inside the reference's bound; a NaN in one token
+    poisons that token's outputs and leaves the other token's alone."""
+    k, n, rows, group = 5120, 300, 2, 64
+    rng = np.random.default_rng(len(kind))
+    w, sc, bi = q4_weights(rng, n, k, group)
+    x = rng.standard_normal((rows, k)).astype(np.float32)
+    if kind == "positive":
+        x = np.abs(x) + 1.0
+    elif kind == "outlier":
+        x[0, 77] = 1.0e4; x[1, 4000] = -3.0e4
+    elif kind == "tiny":
+        x *= np.float32(1e-30)
+    elif kind == "huge":
+        x *= np.float32(1e30)
+    elif kind == "zero":
+        x[0] = 0.0
+    elif kind == "nan":
+        x[1, 123] = np.nan
+    with Bufs(be) as B:
+        xb, _ = B.shared(x); wb, _ = B.shared(w); sb, _ = B.shared(sc); bb, _ = B.shared(bi)
+        yb, yv = B.shared_empty((rows, n), np.float32, fill=np.float32(7.0))
+        c = be.cmd_begin()
+        be.op_qmat_q4(c, QwRef(yb, 0), QwRef(xb, 0), QwRef(wb, 0), QwRef(sb, 0), QwRef(bb, 0), k, n, rows, group)
+        be.cmd_wait(c); be.cmd_free(c)
+        got = np.array(yv)
+    deq = dequant(w, sc, bi, k, group)
+    if kind == "nan":
+        assert np.all(np.isnan(got[1])) and np.all(np.isfinite(got[0]))
+        assert worst_rel_err(got[:1], x[:1], deq) < 2e-6
+        return
+    assert np.all(np.isfinite(got))
+    if kind == "zero":
+        assert np.all(got[0] == 0.0)
+        assert worst_rel_err(got[1:], x[1:], deq) < 2e-6
+        return
+    with np.errstate(over="ignore"):
+        assert worst_rel_err(got, x, deq) < 2e-6
 
 
 def test_q4_multi(be, oracle):

@@ -64,8 +64,13 @@ struct Cursor {      // position on the flattened tile line
 
 __device__ __forceinline__ Cursor locate(const AttnParams &p, int T) {
     Cursor c;
-    int s = 0;
-    while (s + 1 < p.n_seq && p.seq[s + 1].cum_tiles <= T) s++;
+    // the last sequence that starts at or before T, by bisection (every probe is an indexed read of the launch's
+    // table: a walk over 64 sequences at the head of every warp cost the kernel 10 us)
+    int s = 0, e = p.n_seq - 1;
+    while (s < e) {
+        const int m = (s + e + 1) >> 1;
+        if (p.seq[m].cum_tiles <= T) s = m; else e = m - 1;
+    }
     const int rel = T - p.seq[s].cum_tiles;
     c.s = s;
     c.h = rel / p.seq[s].n_tiles;
@@ -93,8 +98,11 @@ __host__ __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
     if (cta >= p.n_cta) return p.total_tiles;
     const int64_t v_total = (int64_t)p.total_tiles + (int64_t)SEG_COST * p.n_seq * p.kv_heads;
     const int64_t v = ((int64_t)cta * v_total) / p.n_cta;
-    int s = 0;
-    while (s + 1 < p.n_seq && (int64_t)p.seq[s + 1].cum_tiles + (int64_t)SEG_COST * (s + 1) * p.kv_heads <= v) s++;
+    int s = 0, e = p.n_seq - 1;
+    while (s < e) {
+        const int m = (s + e + 1) >> 1;
+        if ((int64_t)p.seq[m].cum_tiles + (int64_t)SEG_COST * m * p.kv_heads <= v) s = m; else e = m - 1;
+    }
     const int64_t rel = v - ((int64_t)p.seq[s].cum_tiles + (int64_t)SEG_COST * s * p.kv_heads);
     const int per = p.seq[s].n_tiles + SEG_COST;
     int h = (int)(rel / per);
@@ -171,20 +179,37 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
         // ---------------- producer warp (lane 0 issues the TMA loads) ----------------
         bool waited = !p.early;
         Cursor pc = locate(p, lo);
+        // the current sequence's entries of the launch table, re-read only when the cursor changes sequence
+        int cur_s = -1, s_tile0 = 0, s_ntiles = 1, s_fresh = 0, s_kctx = 0, s_vctx = 0, s_kmap = 0, s_vmap = 0, s_kstride = 0, s_vstride = 0;
+        const int32_t *s_ktab = nullptr, *s_vtab = nullptr;
         // page ids of 32 consecutive tiles, one per lane, fetched together: one global-memory
         // latency per 32 tiles instead of one per tile in front of every issue
         int win_k = 0, win_v = 0;
         for (int T = lo; T < hi; T++) {
             const int i = T - lo, slot = i % NST;
+            if (pc.s != cur_s) {
+                const AttnSeq &sq = p.seq[pc.s];
+                cur_s = pc.s; s_tile0 = sq.tile0; s_ntiles = sq.n_tiles; s_fresh = sq.fresh_pos;
+                s_ktab = sq.kc.table; s_vtab = sq.vc.table; s_kstride = sq.kc.pt_stride; s_vstride = sq.vc.pt_stride;
+                s_kctx = sq.kc.max_ctx; s_vctx = sq.vc.max_ctx; s_kmap = sq.kmap; s_vmap = sq.vmap;
+            }
             if ((i & 31) == 0) {
                 const int T2 = T + lane;
                 if (T2 < hi) {
-                    const Cursor c2 = locate(p, T2);
-                    const AttnSeq &s2 = p.seq[c2.s];
-                    if (s2.kc.table) {
-                        const int pg = ((s2.tile0 + c2.t) * TILE_KEYS) >> 6;
-                        win_k = __ldg(s2.kc.table + (size_t)c2.h * s2.kc.pt_stride + pg);
-                        win_v = __ldg(s2.vc.table + (size_t)c2.h * s2.vc.pt_stride + pg);
+                    if (pc.t + lane < s_ntiles) {                  // still in the cursor's group: no walk over the table
+                        if (s_ktab) {
+                            const int pg = ((s_tile0 + pc.t + lane) * TILE_KEYS) >> 6;
+                            win_k = __ldg(s_ktab + (size_t)pc.h * s_kstride + pg);
+                            win_v = __ldg(s_vtab + (size_t)pc.h * s_vstride + pg);
+                        }
+                    } else {
+                        const Cursor c2 = locate(p, T2);
+                        const AttnSeq &s2 = p.seq[c2.s];
+                        if (s2.kc.table) {
+                            const int pg = ((s2.tile0 + c2.t) * TILE_KEYS) >> 6;
+                            win_k = __ldg(s2.kc.table + (size_t)c2.h * s2.kc.pt_stride + pg);
+                            win_v = __ldg(s2.vc.table + (size_t)c2.h * s2.vc.pt_stride + pg);
+                        }
                     }
                 }
             }
@@ -192,28 +217,30 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
             const int vp = __shfl_sync(0xffffffffu, win_v, i & 31);
             if (i >= NST) mbar_wait(&empty[slot], ((i / NST) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
             if (lane == 0) {
-                const AttnSeq &sq = p.seq[pc.s];
-                const int t_abs = (sq.tile0 + pc.t) * TILE_KEYS;
+                const int t_abs = (s_tile0 + pc.t) * TILE_KEYS;
                 // rows from fresh_pos on were appended by the kernel in front of this one
-                if (!waited && t_abs + TILE_KEYS > sq.fresh_pos) { pdl_wait(); waited = true; }
+                if (!waited && t_abs + TILE_KEYS > s_fresh) { pdl_wait(); waited = true; }
                 int64_t kr, vr;
-                if (sq.kc.table) {
+                if (s_ktab) {
                     if (kp < 0 || vp < 0) report(p.status, QW_ST_BAD_PAGE);
                     kr = (int64_t)max(kp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
                     vr = (int64_t)max(vp, 0) * QW_PAGE_TOKENS + (t_abs & 63);
                 } else {
-                    kr = (int64_t)pc.h * sq.kc.max_ctx + t_abs;
-                    vr = (int64_t)pc.h * sq.vc.max_ctx + t_abs;
+                    kr = (int64_t)pc.h * s_kctx + t_abs;
+                    vr = (int64_t)pc.h * s_vctx + t_abs;
                 }
                 uint8_t *st = smem + slot * STAGE_BYTES;
                 mbar_expect_tx(&full[slot], STAGE_BYTES);
 #pragma unroll
-                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.maps[sq.kmap], b * 64, (int32_t)kr, &full[slot]);
+                for (int b = 0; b < 4; b++) tma_load_2d(st + b * BOX_BYTES, &p.maps[s_kmap], b * 64, (int32_t)kr, &full[slot]);
 #pragma unroll
                 for (int b = 0; b < 4; b++)
-                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.maps[sq.vmap], b * 64, (int32_t)vr, &full[slot]);
+                    tma_load_2d(st + (4 + b) * BOX_BYTES, &p.maps[s_vmap], b * 64, (int32_t)vr, &full[slot]);
             }
-            advance(p, pc);
+            if (++pc.t == s_ntiles) {                              // (advance(), on the cached tile count)
+                pc.t = 0;
+                if (++pc.h == p.kv_heads) { pc.h = 0; pc.s++; }
+            }
             __syncwarp();
         }
         // falls through to the end: consumers wait for every stage that was issued.
@@ -357,9 +384,14 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
 
             // causal limits of this thread's two rows (last readable key index)
             const int row0 = mt * 16 + gid, row1 = row0 + 8;
-            const int lim0 = min(sq.key_hi - 1, row0 < valid_rows ? sq.base_pos + row0 / p.gqa : 0x7fffffff);
-            const int lim1 = min(sq.key_hi - 1, row1 < valid_rows ? sq.base_pos + row1 / p.gqa : 0x7fffffff);
-            const int mask_from = min(sq.key_hi, sq.base_pos + 1);   // blocks reaching this key need masking
+            // The segment's constants are pinned in registers: read through `sq` inside the tile loop they are
+            // indexed loads from the launch's sequence table, which stops fitting the constant cache beyond a
+            // dozen sequences (the kernel lost 12 % at 32 sequences and 22 % at 64 before this).
+            int key_hi = sq.key_hi, seg_tile0 = sq.tile0 + seg_t0;
+            asm volatile("" : "+r"(key_hi), "+r"(seg_tile0));
+            const int lim0 = min(key_hi - 1, row0 < valid_rows ? sq.base_pos + row0 / p.gqa : 0x7fffffff);
+            const int lim1 = min(key_hi - 1, row1 < valid_rows ? sq.base_pos + row1 / p.gqa : 0x7fffffff);
+            const int mask_from = min(key_hi, sq.base_pos + 1);   // blocks reaching this key need masking
 
             for (int tt = 0; tt < seg_n; tt++, T++) {
                 const int i = T - lo, slot = i % NST;
@@ -373,8 +405,8 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
 #pragma unroll
                 for (int j = 0; j < 2; j++) {
                     if (((2 * i + j) % KG) != kg) continue;
-                    const int blk_t0 = (sq.tile0 + seg_t0 + tt) * TILE_KEYS + j * 16;
-                    if (blk_t0 >= sq.key_hi) continue;
+                    const int blk_t0 = (seg_tile0 + tt) * TILE_KEYS + j * 16;
+                    if (blk_t0 >= key_hi) continue;
 
                     // ---- S = Q K^T for 16 keys ----
                     // fragments of k-step ks+1 are requested before the tensor ops of step ks
@@ -453,10 +485,10 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                     {
                         const int mi = lane >> 3;
                         const uint32_t v_row = j * 16 + (mi & 1) * 8 + (lane & 7);
-                        const bool ragged = blk_t0 + 16 > sq.key_hi;   // keys past the end may hold anything
+                        const bool ragged = blk_t0 + 16 > key_hi;   // keys past the end may hold anything
                         const int k_a = blk_t0 + tig * 2;              // key of a b-register's low half (b0); +8 for b1
-                        const uint32_t keep_a = (k_a < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 1 < sq.key_hi ? 0xffff0000u : 0u);
-                        const uint32_t keep_b = (k_a + 8 < sq.key_hi ? 0x0000ffffu : 0u) | (k_a + 9 < sq.key_hi ? 0xffff0000u : 0u);
+                        const uint32_t keep_a = (k_a < key_hi ? 0x0000ffffu : 0u) | (k_a + 1 < key_hi ? 0xffff0000u : 0u);
+                        const uint32_t keep_b = (k_a + 8 < key_hi ? 0x0000ffffu : 0u) | (k_a + 9 < key_hi ? 0xffff0000u : 0u);
                         uint32_t vb[2][4];
                         auto fetch_v = [&](int np, uint32_t(&b)[4]) {
                             const uint32_t vc = np * 2 + (mi >> 1);

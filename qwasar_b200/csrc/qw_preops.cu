@@ -157,11 +157,13 @@ constexpr int PRE_ROWS = QW_PRE_ROWS;
 // rows of other blocks stream under them.
 constexpr int PRE_WARPS = 4;
 static_assert(PRE_WARPS >= PRE_ROWS, "a block's first PRE_ROWS warps work out the rows' angles");
-__global__ void __launch_bounds__(PRE_WARPS * 32, 8) preop_kernel(const __grid_constant__ PreopParams p) {
+__global__ void __launch_bounds__(PRE_WARPS * 32, 6) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
     // squares of the key rows, [key warps of the block][PRE_ROWS][260] (row stride 260: lanes on
     // distinct banks); sized by the launch for the key heads a block can hold
     extern __shared__ __align__(16) float sq_dyn[];
+    __shared__ float ss_s[PRE_WARPS * PRE_ROWS];         // the key rows' sums of squares, [key slot of the block][token]
+    static_assert(PRE_WARPS * PRE_ROWS <= 32, "one warp walks all key rows of a block");
     // Dependent launch: this kernel reads the projections and writes the cache, so it waits for
     // everything in front of it first; the attention kernel behind it may then start at once (it
     // waits itself before it touches the rows appended here).
@@ -224,13 +226,6 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, 8) preop_kernel(const __grid_c
         }
         __syncthreads();
     }
-    if (!active) return;
-    float w[8];
-    if (wn && (is_q || is_k)) {
-        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-        for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(ww[i] << 16); w[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }
-    }
     auto unpack = [&](int u, float (&x)[8]) {
         if (p.io_dtype == DT_BF16) {
             const uint32_t xw[4] = {raw[u][0].x, raw[u][0].y, raw[u][0].z, raw[u][0].w};
@@ -242,31 +237,52 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, 8) preop_kernel(const __grid_c
         }
     };
     // Key rows: the squares are added left to right over the 256 dims like the CPU loop
-    // (qwasar_cpu.c:70-72).  A row's squares go through shared memory so that ONE lane walks them in
-    // order -- lane u takes row u of this warp, the warp's rows side by side -- which costs a
-    // fraction of the instructions of a sum handed from lane to lane.
+    // (qwasar_cpu.c:70-72).  The rows' squares go through shared memory and ONE warp walks them, a lane
+    // per row -- all key rows of the block side by side (up to PRE_WARPS heads x PRE_ROWS tokens) -- so
+    // the 256 dependent additions are issued once per block, not once per key warp: with each key warp
+    // walking its own four rows the pre-op of a 4096-token prefill spent 8 of its 10 million
+    // instructions here.
     float ss_k[PRE_ROWS];
-    // this warp's rows of the buffer: key heads of a block are consecutive, the first one is head max(slot0, qs) - qs
-    float *sq_mine = sq_dyn + (size_t)(is_k ? h - (max(slot0, qs) - qs) : 0) * PRE_ROWS * 260;
-    if (is_k) {
 #pragma unroll
-        for (int u = 0; u < PRE_ROWS; u++) {
-            if (u >= n || dst_row[u] < 0) continue;      // warp-uniform
-            float x[8];
-            unpack(u, x);
-            float4 *sq = reinterpret_cast<float4 *>(sq_mine + u * 260 + lane * 8);
-            sq[0] = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]), __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
-            sq[1] = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]), __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
-        }
-        __syncwarp();
-        float acc = 0.0f;
-        if (lane < n) {
-            const float *sq = sq_mine + lane * 260;
-#pragma unroll 16
-            for (int i = 0; i < 256; i++) acc = __fadd_rn(acc, sq[i]);
-        }
+    for (int u = 0; u < PRE_ROWS; u++) ss_k[u] = 0.0f;
+    const int k_first = max(slot0, qs), k_last = min(slot0 + PRE_WARPS, qs + kvh);   // key slots of this block: [k_first, k_last)
+    if (k_first < k_last) {                              // (the same for the whole block)
+        float *sq_mine = sq_dyn + (size_t)(is_k ? slot - k_first : 0) * PRE_ROWS * 260;
+        if (is_k) {
 #pragma unroll
-        for (int u = 0; u < PRE_ROWS; u++) ss_k[u] = __shfl_sync(0xffffffffu, acc, u);
+            for (int u = 0; u < PRE_ROWS; u++) {
+                if (u >= n || dst_row[u] < 0) continue;      // warp-uniform
+                float x[8];
+                unpack(u, x);
+                float4 *sq = reinterpret_cast<float4 *>(sq_mine + u * 260 + lane * 8);
+                sq[0] = make_float4(__fmul_rn(x[0], x[0]), __fmul_rn(x[1], x[1]), __fmul_rn(x[2], x[2]), __fmul_rn(x[3], x[3]));
+                sq[1] = make_float4(__fmul_rn(x[4], x[4]), __fmul_rn(x[5], x[5]), __fmul_rn(x[6], x[6]), __fmul_rn(x[7], x[7]));
+            }
+        }
+        __syncthreads();
+        if (warp == 0 && lane < (k_last - k_first) * PRE_ROWS && (lane % PRE_ROWS) < n) {
+            const float4 *sq = reinterpret_cast<const float4 *>(sq_dyn + (size_t)lane * 260);   // row (slot lane / PRE_ROWS, token lane % PRE_ROWS)
+            float acc = 0.0f;
+#pragma unroll 4
+            for (int i = 0; i < 64; i++) {
+                const float4 v = sq[i];
+                acc = __fadd_rn(__fadd_rn(__fadd_rn(__fadd_rn(acc, v.x), v.y), v.z), v.w);
+            }
+            // ... and turns it into the row's norm factor here, once per row instead of once per lane of its warp
+            ss_s[lane] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(acc, 256.0f), p.eps)));
+        }
+        __syncthreads();
+        if (is_k) {
+#pragma unroll
+            for (int u = 0; u < PRE_ROWS; u++) ss_k[u] = ss_s[(slot - k_first) * PRE_ROWS + u];
+        }
+    }
+    if (!active) return;
+    float w[8];
+    if (wn && (is_q || is_k)) {
+        const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) { w[2 * i] = __uint_as_float(ww[i] << 16); w[2 * i + 1] = __uint_as_float(ww[i] & 0xffff0000u); }
     }
 #pragma unroll
     for (int u = 0; u < PRE_ROWS; u++) {
@@ -277,30 +293,32 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, 8) preop_kernel(const __grid_c
         unpack(u, x);
         if (is_q || is_k) {
             // RMS norm (qwasar_cpu.c:68-82), then the weight
-            float ss = 0.0f;
+            float inv;
             if (is_k) {
-                ss = ss_k[u];
+                inv = ss_k[u];                           // (already the factor, see above)
             } else {
+                float ss = 0.0f;
 #pragma unroll
                 for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(x[i], x[i]));
                 ss = warp_sum(ss);
+                inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
             }
-            const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, 256.0f), p.eps)));
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 x[i] = __fmul_rn(x[i], inv);
                 if (wn) x[i] = __fmul_rn(x[i], w[i]);
             }
             // partial RoPE (qwasar_cpu.c:304-319): dims d < 32 in lanes 0-3, their partners d + 32 in lanes 4-7
+            // (no branch: every lane does the arithmetic, lanes 8-31 on a dummy angle, and keeps its own value)
             const float *cr = cs_s[u] + 8 * (lane & 3);
+            const bool rot = lane < 8, lo = lane < 4;
 #pragma unroll
             for (int i = 0; i < 8; i++) {
                 const float other = __shfl_xor_sync(0xffffffffu, x[i], 4);
-                if (lane < 8) {
-                    const float c = cr[i], sn = cr[32 + i];
-                    x[i] = lane < 4 ? __fsub_rn(__fmul_rn(x[i], c), __fmul_rn(other, sn))      // lo' = lo c - hi s
-                                    : __fadd_rn(__fmul_rn(x[i], c), __fmul_rn(other, sn));     // hi' = hi c + lo s
-                }
+                const float c = cr[i], sn = lo ? -cr[32 + i] : cr[32 + i];
+                // lo' = lo c - hi s, hi' = hi c + lo s (the negation is exact, so the first is the same sum)
+                const float y = __fadd_rn(__fmul_rn(x[i], c), __fmul_rn(other, sn));
+                x[i] = rot ? y : x[i];
             }
         }
         *out = make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));

@@ -645,6 +645,10 @@ def next_rows_extra(be, torch, peaks, device):
     step = {}
     for name, fn in stages.items():
         step[name] = round(time_device(be, torch, fn, 10, 3, lambda: None)[0] * 1e3, 2)
+    def chain(c):                      # the three stages back to back, as a decode step encodes them
+        for fn in stages.values():
+            fn(c)
+    step["chain_us"] = round(time_device(be, torch, chain, 10, 3, lambda: None)[0] * 1e3, 2)
     step["listed_kv_bytes"] = int(lst[0, 0].item()) * kvh * 1024
     out["qsa_step_262k"] = step
     for b in bufs:
@@ -821,6 +825,14 @@ def run_ours(args):
         if not be.tune(k, int(v)):
             raise SystemExit(f"unknown knob {kv}")
     peaks = measured_peaks()
+    if args.only:                      # one side measurement alone: a short run for a profiler to sit on
+        fn = {"prefill": lambda: prefill_extra(be, torch, peaks, device),
+              "next": lambda: next_rows_extra(be, torch, peaks, device),
+              "c1": lambda: small_decode_extra(be, torch, peaks, device, "c1_9b_decode_4k", 16),
+              "c4": lambda: small_decode_extra(be, torch, peaks, device, "c4_27b_verify_32k", 8)}[args.only]
+        if rank == 0:
+            print(json.dumps({"only": args.only, "result": fn()}), flush=True)
+        return
     wl = synth.WORKLOADS[args.workload]
     warm = max(3, args.warmup)
 
@@ -937,6 +949,8 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="attention layers per step (default: the model's)")
     ap.add_argument("--seq-layers", type=int, default=4, help="layer caches the sequence-split side measurement walks")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--only", default="", choices=["", "prefill", "next", "c1", "c4"],
+                    help="run ONE of the single-GPU side measurements and print its block alone (for profiling that kernel)")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--cache", default="pool", choices=["pool", "arena", "linear"],
                     help="arenas in one page pool, an arena per sequence, or the reference's plain layout")

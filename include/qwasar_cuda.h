@@ -239,8 +239,9 @@ uint64_t    qw_gpu_launch_count(void);
  * split-KV kernel over row chunks; "prefill_fuse_q" = 1 | 0, with bf16 rows the tcgen05 prefill norms and
  * rotates its own query tiles (default) or the pre-op kernel does; "pdl" = 1 | 0, the kernels of the
  * decode chain start under the kernel in front of them (programmatic dependent launch, default) or in
- * plain stream order; "masked_tc" = 1 | 0, attention over a gathered row list on tensor-op tiles
- * (default, bf16 operands) or on the fp32 kernel; "qmv_tc" = 1 | 0, the one- and two-token 4-bit
+ * plain stream order; "masked_tc" = 1 | 2 | 0, attention over a gathered row list on tensor-op tiles
+ * (bf16 operands) as one launch on a thread-block cluster (default), as partials plus a merge launch, or on
+ * the fp32 kernel; "qmv_tc" = 1 | 0, the one- and two-token 4-bit
  * product on the integer tensor path (default) or on the fp32 kernel.  Returns false for an unknown
  * knob or value. */
 bool        qw_gpu_tune(const char *knob, int32_t value);

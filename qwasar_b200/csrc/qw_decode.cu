@@ -23,6 +23,7 @@
 // partials add (n_cta + groups) x rows x 1 KB.
 #include "qw_kernels.h"
 #include <algorithm>
+#include <cooperative_groups.h>
 
 namespace qw {
 
@@ -1211,6 +1212,232 @@ int row_tiles(int max_rows, int gqa) {
     return need <= 1 ? 1 : (need <= 2 ? 2 : 4);
 }
 
+// ---- masked attention of one (row, KV head) on a CLUSTER: no partials in memory, no merge launch -------
+// The row's list (at most a few thousand positions) is cut into steps of 16 keys, the steps dealt to the
+// CTAs of a cluster and, inside a CTA, to its warps: a warp gathers its 16 K and V rows with asynchronous
+// copies, computes S = Q K^T, the softmax weights and O = P V exactly as attn_masked_mma_kernel does, and
+// keeps (max, sum, O) in registers over the steps it owns.  The warps of a CTA then add their O through
+// the buffers the rows were gathered into, the CTAs add theirs through distributed shared memory -- each
+// CTA finishes an equal slice of the output dims, gate included -- so the whole op is one launch and the
+// only trips to memory are list -> rows -> output.  (As two launches with partials in between, the merge
+// was 6 of the op's 17 us and the partials another trip.)
+namespace cgx = cooperative_groups;
+constexpr int AC_WARPS = 12;
+constexpr int AC_OFF_KV = 0;                                   // per warp: K 8 KB | V 8 KB, later the warp's O [16][256] fp32
+constexpr int AC_OFF_Q = AC_WARPS * 16384;                     // Q tile, bf16 [16][256] swizzled
+constexpr int AC_OFF_ACC = AC_OFF_Q + 16 * 512;                // the CTA's O [16][256] fp32
+constexpr int AC_OFF_M = AC_OFF_ACC + 16 * 1024;               // per warp row maxima [AC_WARPS][16]
+constexpr int AC_OFF_L = AC_OFF_M + AC_WARPS * 64;             // per warp row sums   [AC_WARPS][16]
+constexpr int AC_OFF_CM = AC_OFF_L + AC_WARPS * 64;            // the CTA's row maxima [16] and sums [16]
+constexpr int AC_SMEM = AC_OFF_CM + 128 + 1024;
+__global__ void __launch_bounds__(AC_WARPS * 32, 1)
+attn_masked_cluster_kernel(AttnSeq sq, int q_heads, int kv_heads, int gqa, float scale, const uint32_t *__restrict__ list, int list_stride,
+                           float *__restrict__ out, const float *__restrict__ gate, int gate_stride) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *q_s = smem + AC_OFF_Q;
+    float *cta_acc = reinterpret_cast<float *>(smem + AC_OFF_ACC);
+    float *sm_m = reinterpret_cast<float *>(smem + AC_OFF_M), *sm_l = reinterpret_cast<float *>(smem + AC_OFF_L);
+    float *cta_ml = reinterpret_cast<float *>(smem + AC_OFF_CM);
+    cgx::cluster_group cluster = cgx::this_cluster();
+    const int C = (int)cluster.num_blocks(), rank = (int)cluster.block_rank();
+    const int h = blockIdx.y, r = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const uint32_t *row_list = list + (size_t)r * list_stride;
+    pdl_launch_next();
+    pdl_wait();
+    // the count and the first step's positions are asked for together (entries past the count are inside the
+    // row of the list and simply not used): one trip to memory instead of two
+    const int guess = (rank * AC_WARPS + warp) * 16 + lane;      // where this lane's first key sits if the list is full
+    uint32_t pos_guess = 0xffffffffu;
+    if (lane < 16 && guess < list_stride - 1) pos_guess = __ldg(row_list + 1 + guess);
+    const int count = (int)min(__ldg(row_list), (uint32_t)(list_stride - 1));
+    const int steps = (count + 15) >> 4, spc = (steps + C - 1) / C;   // steps per CTA
+    const int s0 = min(rank * spc, steps), s1 = min(s0 + spc, steps);
+
+    // ---- Q of this (row, kv head): gqa rows of 256 fp32 -> bf16, swizzled (rows past gqa are zeros)
+    for (int idx = threadIdx.x; idx < 16 * 32; idx += AC_WARPS * 32) {
+        const int row = idx >> 5, ch = idx & 31;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < gqa) {
+            const float *src = reinterpret_cast<const float *>(sq.q) + ((size_t)r * q_heads + h * gqa + row) * 256 + ch * 8;
+            const float4 a = __ldg(reinterpret_cast<const float4 *>(src)), b = __ldg(reinterpret_cast<const float4 *>(src + 4));
+            val.x = pack_bf16(a.x, a.y); val.y = pack_bf16(a.z, a.w); val.z = pack_bf16(b.x, b.y); val.w = pack_bf16(b.z, b.w);
+        }
+        *reinterpret_cast<uint4 *>(q_s + (ch >> 3) * AM_BOX + swz128(row, (ch & 7) * 8)) = val;
+    }
+    __syncthreads();
+
+    const uint32_t k_base = smem_u32(smem + AC_OFF_KV + warp * 16384), v_base = k_base + 4 * AM_BOX;
+    const uint32_t q_base = smem_u32(q_s);
+    const float sc2 = scale * LOG2E;
+    float o[32][4];
+#pragma unroll
+    for (int n = 0; n < 32; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.0f, l1 = 0.0f;
+    for (int st = s0 + warp; st < s1; st += AC_WARPS) {
+        // ---- gather: 16 keys
+        const int e0 = st * 16;
+        uint32_t pos = 0xffffffffu;
+        if (lane < 16 && e0 + lane < count) pos = (e0 + lane == guess) ? pos_guess : __ldg(row_list + 1 + e0 + lane);
+        const bool ok = pos < (uint32_t)sq.kc.max_ctx;
+        int kr = -1, vr = -1;                                   // rows of the cache arrays (below 2^31: 512 bytes each)
+        if (ok) { kr = (int)kv_row(sq.kc, h, (int)pos); vr = (int)kv_row(sq.vc, h, (int)pos); }
+#pragma unroll
+        for (int i = 0; i < 16; i++) {
+            const int kri = __shfl_sync(0xffffffffu, kr, i), vri = __shfl_sync(0xffffffffu, vr, i);
+            const uint32_t off = (lane >> 3) * AM_BOX + swz128(i, (lane & 7) * 8);
+            cp_async16(k_base + off, sq.kc.base + (size_t)max(kri, 0) * 256 + lane * 8, kri >= 0);
+            cp_async16(v_base + off, sq.vc.base + (size_t)max(vri, 0) * 256 + lane * 8, vri >= 0);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const uint32_t valid = __ballot_sync(0xffffffffu, kr >= 0 && vr >= 0) & 0xffffu;     // bit i: key i counts
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        // ---- S = Q K^T
+        float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
+        {
+            const int mi = lane >> 3;
+            const uint32_t q_row = (mi & 1) * 8 + (lane & 7), k_row = (mi >> 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int ks = 0; ks < 16; ks++) {
+                uint32_t a[4], b[4];
+                const uint32_t qc = ks * 2 + (mi >> 1), kc = ks * 2 + (mi & 1);
+                ldsm_x4(a[0], a[1], a[2], a[3], q_base + (qc >> 3) * AM_BOX + swz128(q_row, (qc & 7) * 8));
+                ldsm_x4(b[0], b[1], b[2], b[3], k_base + (kc >> 3) * AM_BOX + swz128(k_row, (kc & 7) * 8));
+                mma_bf16(s[0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                mma_bf16(s[1], a[0], a[1], a[2], a[3], b[2], b[3]);
+            }
+        }
+        uint32_t pa[4];
+        {
+#pragma unroll
+            for (int n = 0; n < 2; n++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int key = n * 8 + tig * 2 + (e & 1);
+                    s[n][e] = (valid >> key & 1u) ? s[n][e] * sc2 : -INFINITY;
+                }
+            float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+            float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+            if (st != s0 + warp) {                              // a later step of this warp: what it holds moves to the new maxima
+                const float f0 = ex2(m0 - n0), f1 = ex2(m1 - n1);
+                l0 *= f0; l1 *= f1;
+#pragma unroll
+                for (int n = 0; n < 32; n++) { o[n][0] *= f0; o[n][1] *= f0; o[n][2] *= f1; o[n][3] *= f1; }
+            }
+            m0 = n0; m1 = n1;
+            const float p00 = ex2(s[0][0] - m0), p01 = ex2(s[0][1] - m0), p02 = ex2(s[0][2] - m1), p03 = ex2(s[0][3] - m1);
+            const float p10 = ex2(s[1][0] - m0), p11 = ex2(s[1][1] - m0), p12 = ex2(s[1][2] - m1), p13 = ex2(s[1][3] - m1);
+            l0 += (p00 + p01) + (p10 + p11); l1 += (p02 + p03) + (p12 + p13);
+            pa[0] = pack_bf16(p00, p01); pa[1] = pack_bf16(p02, p03); pa[2] = pack_bf16(p10, p11); pa[3] = pack_bf16(p12, p13);
+        }
+        // ---- O += P V
+        {
+            const int mi = lane >> 3;
+            const uint32_t v_row = (mi & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int np = 0; np < 16; np++) {
+                uint32_t b[4];
+                const uint32_t vc = np * 2 + (mi >> 1);
+                ldsm_x4_t(b[0], b[1], b[2], b[3], v_base + (vc >> 3) * AM_BOX + swz128(v_row, (vc & 7) * 8));
+                mma_bf16(o[np * 2], pa[0], pa[1], pa[2], pa[3], b[0], b[1]);
+                mma_bf16(o[np * 2 + 1], pa[0], pa[1], pa[2], pa[3], b[2], b[3]);
+            }
+        }
+        __syncwarp();                                           // the buffer may be gathered into again
+    }
+    // ---- the CTA's warps add up: maxima first, then every warp leaves its O, moved to the CTA's maxima, in its buffer
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    if (tig == 0) { sm_m[warp * 16 + gid] = m0; sm_m[warp * 16 + gid + 8] = m1; }
+    __syncthreads();
+    float M0 = NEG_BIG, M1 = NEG_BIG;
+#pragma unroll
+    for (int w = 0; w < AC_WARPS; w++) { M0 = fmaxf(M0, sm_m[w * 16 + gid]); M1 = fmaxf(M1, sm_m[w * 16 + gid + 8]); }
+    const bool has_steps = s0 + warp < s1;
+    {
+        const float f0 = ex2(m0 - M0), f1 = ex2(m1 - M1);
+        if (tig == 0) { sm_l[warp * 16 + gid] = l0 * f0; sm_l[warp * 16 + gid + 8] = l1 * f1; }
+        if (has_steps) {
+            // [16 rows][128 float2], the float2 index xor-ed with (row & 3) << 2: the eight rows of a store then
+            // meet no more bank conflicts than 256 bytes per request cost anyway
+            float2 *w_o = reinterpret_cast<float2 *>(smem + AC_OFF_KV + warp * 16384);
+            const int x0 = (gid & 3) << 2;
+            if (gid < gqa) {                                    // (only the rows that exist: this phase is shared-memory bandwidth)
+#pragma unroll
+                for (int n = 0; n < 32; n++) w_o[gid * 128 + ((n * 4 + tig) ^ x0)] = make_float2(o[n][0] * f0, o[n][1] * f0);
+            }
+            if (gid + 8 < gqa) {
+#pragma unroll
+                for (int n = 0; n < 32; n++) w_o[(gid + 8) * 128 + ((n * 4 + tig) ^ x0)] = make_float2(o[n][2] * f1, o[n][3] * f1);
+            }
+        }
+    }
+    __syncthreads();
+    const int live_warps = min(AC_WARPS, max(s1 - s0, 0));       // warps 0 .. live_warps - 1 hold something
+    for (int idx = threadIdx.x; idx < gqa * 64; idx += AC_WARPS * 32) {
+        const int row = idx >> 6, c4 = idx & 63;
+        const int p4 = c4 ^ ((row & 3) << 1);                    // (the float2 swizzle, in float4 units)
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int w = 0; w < live_warps; w++) {
+            const float4 a = *reinterpret_cast<const float4 *>(smem + AC_OFF_KV + w * 16384 + (row * 64 + p4) * 16);
+            acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+        }
+        *reinterpret_cast<float4 *>(cta_acc + row * 256 + c4 * 4) = acc;
+    }
+    if (threadIdx.x < 16) {
+        float mm = NEG_BIG, ll = 0.0f;
+        for (int w = 0; w < AC_WARPS; w++) { mm = fmaxf(mm, sm_m[w * 16 + threadIdx.x]); ll += sm_l[w * 16 + threadIdx.x]; }
+        cta_ml[threadIdx.x] = mm; cta_ml[16 + threadIdx.x] = ll;
+    }
+    cluster.sync();                                             // every CTA's (max, sum, O) is in its shared memory
+    // ---- the cluster adds up: CTA `rank` finishes its slice of the gqa x 64 float4 of the output
+    {
+        const int total = gqa * 64, per = (total + C - 1) / C;
+        const int idx = rank * per + threadIdx.x;
+        if (threadIdx.x < per && idx < total) {
+            const int row = idx >> 6, c4 = idx & 63;
+            // all remote reads are issued before the first is used (one after the other they were 2 x C round trips
+            // between SMs on the op's critical path)
+            float mq[16], lq[16];
+            float4 aq[16];
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+                mq[q] = NEG_BIG; lq[q] = 0.0f; aq[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (q < C) {
+                    const float *ml = cluster.map_shared_rank(cta_ml, q);
+                    mq[q] = ml[row]; lq[q] = ml[16 + row];
+                    aq[q] = *reinterpret_cast<const float4 *>(cluster.map_shared_rank(cta_acc, q) + row * 256 + c4 * 4);
+                }
+            }
+            float M = NEG_BIG;
+#pragma unroll
+            for (int q = 0; q < 16; q++) M = fmaxf(M, mq[q]);
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            float den = 0.0f;
+#pragma unroll
+            for (int q = 0; q < 16; q++) {
+                const float f = ex2(mq[q] - M);
+                acc.x = fmaf(aq[q].x, f, acc.x); acc.y = fmaf(aq[q].y, f, acc.y); acc.z = fmaf(aq[q].z, f, acc.z); acc.w = fmaf(aq[q].w, f, acc.w);
+                den = fmaf(lq[q], f, den);
+            }
+            const float inv = den > 0.0f ? 1.0f / den : 0.0f;
+            acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+            const size_t rh = (size_t)r * q_heads + h * gqa + row;
+            if (gate) {
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(gate + rh * gate_stride + c4 * 4));
+                acc.x *= sigmoidf(g.x); acc.y *= sigmoidf(g.y); acc.z *= sigmoidf(g.z); acc.w *= sigmoidf(g.w);
+            }
+            *reinterpret_cast<float4 *>(out + rh * 256 + c4 * 4) = acc;
+        }
+    }
+    cluster.sync();                                             // no CTA leaves while another may still read its shared memory
+}
+
 }  // namespace
 
 unsigned long long g_launches = 0;
@@ -1299,6 +1526,49 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
 // Masked attention of `rows` rows over their position lists on tensor ops: n_chunks = ceil(cap / 64)
 // partials per (row, head) into pacc [n_chunks, rows * q_heads, 256] / pstat, for launch_merge_parts.
 int attn_masked_chunks(int cap) { return (cap + AM_KEYS - 1) / AM_KEYS; }
+// The cluster form of the masked attention (fp32 rows in and out, at most 16 q heads per KV head); false where it
+// does not apply or a cluster cannot be placed, and the caller then takes the two-launch path.
+bool launch_attn_masked_cluster(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
+                                int list_stride, float *out, const float *gate, int gate_stride) {
+    static int cluster_size[64] = {0};                          // per device: 0 not tried, -1 unavailable, else CTAs per cluster
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return false;
+    const int gqa = q_heads / kv_heads;
+    if (gqa > 16 || (gate && ((reinterpret_cast<uintptr_t>(gate) & 15) || (gate_stride & 3)))) return false;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[2];
+    cfg.blockDim = dim3(AC_WARPS * 32); cfg.dynamicSmemBytes = AC_SMEM; cfg.stream = s;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    if (cluster_size[dev] == 0) {
+        cluster_size[dev] = -1;
+        if (cudaFuncSetAttribute(attn_masked_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AC_SMEM) == cudaSuccess) {
+            cudaFuncSetAttribute(attn_masked_cluster_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            for (int c : {16, 8}) {                             // the largest cluster this device can place
+                int n = 0;
+                cfg.gridDim = dim3(c, 1, 1); attr[0].val.clusterDim.x = c; cfg.numAttrs = 1;
+                if (cudaOccupancyMaxActiveClusters(&n, attn_masked_cluster_kernel, &cfg) == cudaSuccess && n >= 1) { cluster_size[dev] = c; break; }
+            }
+            cudaGetLastError();
+        }
+    }
+    const int C = cluster_size[dev];
+    if (C <= 0) return false;
+    cfg.gridDim = dim3((unsigned)C, (unsigned)kv_heads, (unsigned)seq.rows);
+    attr[0].val.clusterDim.x = C;
+    cfg.numAttrs = g_tune_pdl ? 2 : 1;
+    if (cudaLaunchKernelEx(&cfg, attn_masked_cluster_kernel, seq, q_heads, kv_heads, gqa, scale, list, list_stride, out, gate, gate_stride) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    g_launches++;
+    return true;
+}
+
+
 void launch_attn_masked_mma(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
                             int list_stride, float *pacc, float *pstat) {
     static bool configured[64] = {false};

@@ -163,6 +163,8 @@ int attn_per_query_splits(int rows, int q_heads, int n_keys);
 // Masked attention on tensor ops over each row's position list (q f32; grouping <= 16): one partial
 // per 64 list entries into pacc [chunks, rows * q_heads, 256] / pstat [chunks, rows * q_heads, 2].
 int attn_masked_chunks(int cap);
+bool launch_attn_masked_cluster(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
+                                int list_stride, float *out, const float *gate, int gate_stride);
 void launch_attn_masked_mma(cudaStream_t s, const AttnSeq &seq, int q_heads, int kv_heads, float scale, const uint32_t *list,
                             int list_stride, float *pacc, float *pstat);
 

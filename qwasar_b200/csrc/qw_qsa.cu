@@ -69,6 +69,79 @@ __global__ void __launch_bounds__(256) qsa_pool_kernel(float *__restrict__ pool,
         if (k < (d >> 5)) pool[(size_t)b * d + lane + 32 * k] = x[k];
 }
 
+// Scores, a LANE per block key.  A warp takes 32 consecutive block keys: their d floats travel into shared
+// memory with 16-byte asynchronous copies, 32 dims at a time in two stages (rows padded by 4 floats, so a
+// lane reading its own row 16 bytes at a time meets no bank conflict), and each lane then walks its key
+// once with one multiply-add chain per index head, the queries read from shared memory as broadcasts.
+// About 25 instructions per key instead of 320: the kernel with a warp per key reloaded the queries and
+// ran a five-step shuffle sum for every (key, head), and sat at 88 % issue utilisation at 1.3 TB/s.
+// Used when d is a multiple of 32; the sums run over d in index order in both scoring ops, so scores from
+// stored block keys still equal scores from raw keys bit for bit.
+constexpr int SCL_WARPS = 4, SCL_CH = 32, SCL_LD = SCL_CH + 4, SCL_HB = 4, SCL_PIECES = SCL_CH / 4;
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *src, bool valid) {
+    const int n = valid ? 16 : 0;                                 // 0: the 16 bytes are filled with zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(src), "r"(n) : "memory");
+}
+__global__ void __launch_bounds__(SCL_WARPS * 32) qsa_scores_lane_kernel(float *__restrict__ scores, const float *__restrict__ qn,
+                                                                         const float *__restrict__ pool, int nq, int d, int ratio,
+                                                                         int base_pos, int max_blocks) {
+    extern __shared__ __align__(16) float scl_smem[];             // [nq][d] queries | per warp [2 stages][32 keys][SCL_LD]
+    const int r = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_blocks = min((base_pos + r + 1) / ratio, max_blocks);
+    const int b0 = (blockIdx.x * SCL_WARPS + warp) * 32;
+    float *qs = scl_smem, *ks = scl_smem + nq * d + (size_t)warp * 2 * 32 * SCL_LD;
+    for (int i = threadIdx.x * 4; i < nq * d; i += SCL_WARPS * 32 * 4)
+        *reinterpret_cast<float4 *>(qs + i) = __ldg(reinterpret_cast<const float4 *>(qn + (size_t)r * nq * d + i));
+    const int n_ch = d / SCL_CH;
+    // step t of the walk = (pass over four index heads, chunk of SCL_CH dims): chunk t % n_ch into stage t & 1; the
+    // lanes share out the 16-byte pieces of the warp's 32 rows
+    const int passes = (nq + SCL_HB - 1) / SCL_HB, steps = passes * n_ch;
+    auto stage = [&](int t) {
+        float *dst = ks + (size_t)(t & 1) * 32 * SCL_LD;
+        const int c = t % n_ch;
+#pragma unroll
+        for (int i = lane; i < 32 * SCL_PIECES; i += 32) {
+            const int row = i / SCL_PIECES, piece = i % SCL_PIECES, b = b0 + row;
+            cp_async16(dst + row * SCL_LD + piece * 4, pool + (size_t)min(b, max_blocks - 1) * d + c * SCL_CH + piece * 4, b < n_blocks);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (b0 < n_blocks) stage(0);
+    __syncthreads();                                              // the queries are in place
+    if (b0 >= n_blocks) return;
+    float total = 0.0f;
+    float acc[SCL_HB] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int t = 0; t < steps; t++) {
+        const int c = t % n_ch, h0 = (t / n_ch) * SCL_HB;
+        if (t + 1 < steps) { stage(t + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        const float *krow = ks + (size_t)(t & 1) * 32 * SCL_LD + lane * SCL_LD;
+        const float *q = qs + (size_t)h0 * d + c * SCL_CH;
+#pragma unroll 4
+        for (int j = 0; j < SCL_CH; j += 4) {
+            const float4 k4 = *reinterpret_cast<const float4 *>(krow + j);
+#pragma unroll
+            for (int h = 0; h < SCL_HB; h++) {
+                if (h0 + h < nq) {
+                    const float4 q4 = *reinterpret_cast<const float4 *>(q + (size_t)h * d + j);
+                    acc[h] = fmaf(k4.w, q4.w, fmaf(k4.z, q4.z, fmaf(k4.y, q4.y, fmaf(k4.x, q4.x, acc[h]))));
+                }
+            }
+        }
+        __syncwarp();                                             // the stage may be written again
+        if (c == n_ch - 1) {                                      // a pass is complete: its heads join the sum
+#pragma unroll
+            for (int h = 0; h < SCL_HB; h++) {
+                if (h0 + h < nq && acc[h] > 0.0f) total = __fadd_rn(total, acc[h]);
+                acc[h] = 0.0f;
+            }
+        }
+    }
+    const int b = b0 + lane;
+    if (b < n_blocks) scores[(size_t)r * max_blocks + b] = __fdiv_rn(total, sqrtf((float)d));
+}
+
 // one warp per (row, block): grid (ceil(max visible blocks / 8), rows)
 __global__ void __launch_bounds__(256) qsa_scores_kernel(float *__restrict__ scores, const float *__restrict__ qn,
                                                          const float *__restrict__ pool, int nq, int d, int ratio, int base_pos,
@@ -281,20 +354,25 @@ __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__rest
 // for rows of thousands of blocks, where one CTA sweeping the row six times from L2 is all latency:
 // 65 536 scores took 67 us.  Here a cluster of SC_CTAS CTAs (distributed shared memory) takes one row;
 // CTA q reads its contiguous share of the scores ONCE, as order-preserving keys into shared memory
-// (0 = not selectable), and every later pass runs from there.  A radix pass builds a 256-bin
-// histogram per CTA (warp-aggregated adds), the cluster synchronises, every CTA sums the eight
-// histograms through distributed shared memory and takes the same decision; the ordered passes need
-// only each CTA's counts of larger and equal keys, read the same way.  The mask is cleared and the
-// list written by the CTAs in parallel, each for its own stretch of blocks.
+// (0 = not selectable), and every later pass runs from there.  Three radix passes (11, 11 and 10 bits)
+// each build a histogram per CTA (warp-aggregated adds) in a buffer of their own, so the cluster
+// synchronises ONCE per pass: every CTA then sums the eight histograms through distributed shared
+// memory and takes the same decision with a block-wide scan from the top bin down.  (Four 8-bit
+// passes with two cluster barriers each took 26 us on 65 536 scores, nearly all of it waiting at
+// barriers.)  The ordered passes need only each CTA's counts of larger and equal keys, read the same
+// way.  The mask is cleared and the list written by the CTAs in parallel, each for its own stretch.
 namespace cg = cooperative_groups;
-constexpr int SC_CTAS = 8, SC_THREADS = 1024, SC_WARPS = SC_THREADS / 32;
+constexpr int SC_CTAS = 8, SC_THREADS = 1024, SC_WARPS = SC_THREADS / 32, SC_BINS = 2048, SC_REP = 8, SC_PRE = 8;
+static_assert(SC_BINS == 2 * SC_THREADS, "the scan gives every thread two bins");
 
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
 qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ list, const float *__restrict__ scores, int ratio,
                           int base_pos, int block_topk, int max_ctx, int max_blocks, int list_stride, int per_cta) {
     extern __shared__ uint32_t keys[];                            // per_cta keys of this CTA's blocks
-    __shared__ int hist[256];
-    __shared__ int tot[256];
+    int (*hist)[SC_BINS] = reinterpret_cast<int (*)[SC_BINS]>(keys + per_cta);     // one histogram per pass (dynamic, behind the keys)
+    int (*rep0)[SC_BINS] = hist + 3;                              // pass 0 counts into SC_REP copies (hist[0] is the first)
+    __shared__ int tot[SC_BINS];
+    __shared__ int w_sum[SC_WARPS], w_off[SC_WARPS], s_all;
     __shared__ int w_gt[SC_WARPS], w_eq[SC_WARPS];
     __shared__ int cta_cnt[2];                                    // this CTA's blocks with a larger / an equal key
     __shared__ uint32_t s_prefix;
@@ -310,6 +388,14 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
     const int tail0 = n_blocks * ratio;
     const int lo = min(rank * per_cta, n_blocks), hi = min(lo + per_cta, n_blocks);
 
+    // the scores of this CTA's blocks are asked for first (up to SC_PRE per thread stay in registers), so that their
+    // trip to memory runs under the clearing of the mask and of the histograms
+    float pre[SC_PRE];
+#pragma unroll
+    for (int j = 0; j < SC_PRE; j++) {
+        const int b = lo + tid + j * SC_THREADS;
+        pre[j] = b < hi ? sc[b] : -FLT_MAX;
+    }
     // this CTA's share of the mask, [m_lo, m_hi): 0 over the blocks, 1 over the tail; 16 bytes per
     // store where the addresses allow (shares are cut at multiples of 16 bytes of the row's address)
     {
@@ -326,72 +412,111 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
         for (int t = head + 16 * tid; t < vec_end; t += 16 * SC_THREADS) *reinterpret_cast<uint4 *>(m + t) = make_uint4(0, 0, 0, 0);
         for (int t = vec_end + tid; t < m_hi; t += SC_THREADS) m[t] = t >= tail0;
     }
-    // the scores of this CTA's blocks, once, as keys
-    for (int i = tid; i < per_cta; i += SC_THREADS) {
+    // ... and go to shared memory as keys
+#pragma unroll
+    for (int j = 0; j < SC_PRE; j++) {
+        const int i = tid + j * SC_THREADS;
+        uint32_t key = 0, k2;
+        if (i < per_cta) { if (sel_key(pre[j], k2)) key = k2; keys[i] = key; }
+    }
+    for (int i = tid + SC_PRE * SC_THREADS; i < per_cta; i += SC_THREADS) {
         uint32_t key = 0;
         const int b = lo + i;
         if (b < hi) { uint32_t k2; if (sel_key(sc[b], k2)) key = k2; }
         keys[i] = key;
     }
+    for (int i = tid; i < 3 * SC_BINS; i += SC_THREADS) (&hist[0][0])[i] = 0;
+    for (int i = tid; i < (SC_REP - 1) * SC_BINS; i += SC_THREADS) (&rep0[0][0])[i] = 0;
     if (tid == 0) { s_prefix = 0; s_remaining = 0; s_take = 0; }
     __syncthreads();
 
-    for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) hist[tid] = 0;
-        __syncthreads();
-        const uint32_t prefix = s_prefix, high = shift == 24 ? 0u : 0xFFFFFFFFu << (shift + 8);
-        for (int i = tid; i < per_cta; i += SC_THREADS) {        // the same trip count on every lane
+    for (int pass = 0; pass < 3; pass++) {
+        const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0, nbits = pass == 2 ? 10 : 11;
+        const uint32_t prefix = s_prefix, high = pass == 0 ? 0u : 0xFFFFFFFFu << (shift + nbits), bmask = (1u << nbits) - 1u;
+        int want = s_remaining;                                   // (read before this pass's decision is written)
+        // The first pass sees every key, and the top bits of a row's scores take a handful of values: its adds go to
+        // one of SC_REP copies by warp (same-address adds in shared memory queue up: with one copy this pass took
+        // 5 us of the kernel's 26), folded into one histogram before the cluster looks at it.
+        int *h = pass == 0 && (warp % SC_REP) ? rep0[warp % SC_REP - 1] : hist[pass];
+        // One add per key, no aggregation inside the warp: matching the lanes' bins first (match.any) costs a round per
+        // distinct value, and with a few dozen distinct bins per warp that was 4 of the first pass's 5 us; the later
+        // passes only add the few keys that share the prefix.
+        for (int i = tid; i < per_cta; i += SC_THREADS) {
             const uint32_t key = keys[i];
-            const bool in = key != 0u && (key & high) == prefix;
-            const int bin = in ? (int)((key >> shift) & 0xFF) : -1;
-            // lanes of one bin add once: scores of a row mostly share their top bytes
-            const uint32_t same = __match_any_sync(0xffffffffu, bin);
-            if (in && (same & below) == 0u) atomicAdd(&hist[bin], __popc(same));
+            if (key != 0u && (key & high) == prefix) atomicAdd(&h[(key >> shift) & bmask], 1);
         }
-        cluster.sync();                                           // every CTA's histogram is complete
-        if (tid < 256) {
-            int sum = 0;
+        if (pass == 0) {
+            __syncthreads();
 #pragma unroll
-            for (int q = 0; q < SC_CTAS; q++) sum += cluster.map_shared_rank(hist, q)[tid];
-            tot[tid] = sum;
+            for (int j = 0; j < 2; j++) {
+                const int bin = tid + j * SC_THREADS;
+                int sum = hist[0][bin];
+#pragma unroll
+                for (int q = 0; q < SC_REP - 1; q++) sum += rep0[q][bin];
+                hist[0][bin] = sum;
+            }
         }
+        cluster.sync();                                           // every CTA's histogram of this pass is complete
+        // CTA q adds up its eighth of the bins over the eight CTAs and stores the sums into every CTA's `tot`
+        // (each CTA pulling all eight histograms moved four times the bytes between the SMs and took 2 us a pass)
+        {
+            const int bins = 1 << nbits, per = bins / SC_CTAS;
+            if (tid < per) {
+                const int bin = rank * per + tid;
+                int v[SC_CTAS];
+#pragma unroll
+                for (int q = 0; q < SC_CTAS; q++) v[q] = cluster.map_shared_rank(hist[pass], q)[bin];
+                int sum = 0;
+#pragma unroll
+                for (int q = 0; q < SC_CTAS; q++) sum += v[q];
+#pragma unroll
+                for (int q = 0; q < SC_CTAS; q++) cluster.map_shared_rank(tot, q)[bin] = sum;
+            }
+            if (bins < SC_BINS) for (int bin = bins + tid; bin < SC_BINS; bin += SC_THREADS) tot[bin] = 0;
+        }
+        cluster.sync();                                           // every CTA's `tot` is complete
+        // From the top bin down, the first bin at which the running count reaches `want` holds the key looked
+        // for; every CTA computes the same.  Thread t owns bins B - 1 - 2t and B - 2 - 2t.
+        const int bhi = SC_BINS - 1 - 2 * tid;
+        const int c0 = tot[bhi], c1 = tot[bhi - 1], mine = c0 + c1;
+        int incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        if (lane == 31) w_sum[warp] = incl;
         __syncthreads();
-        // as in qsa_select_kernel: walking down from bin 255, the first bin at which the count reaches
-        // `want` holds the key looked for (every CTA computes the same)
         if (warp == 0) {
-            int want = s_remaining;
-            __syncwarp();
-            int h[8], mine = 0;
-#pragma unroll
-            for (int j = 0; j < 8; j++) { h[j] = tot[255 - 8 * lane - j]; mine += h[j]; }
-            int incl = mine;
+            const int v = w_sum[lane];
+            int iv = v;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= o) incl += up;
+                const int up = __shfl_up_sync(0xffffffffu, iv, o);
+                if (lane >= o) iv += up;
             }
-            const int all = __shfl_sync(0xffffffffu, incl, 31);
-            if (shift == 24) {
-                want = min(min(block_topk, n_blocks), all);
-                if (lane == 0) s_take = want;
-            }
-            const uint32_t reached = __ballot_sync(0xffffffffu, incl >= want);
-            if (reached == 0u) {
-                if (lane == 31) { s_remaining = want - (all - h[7]); s_prefix = prefix; }
-            } else if (lane == __ffs(reached) - 1) {
-                int run = incl - mine, bin = 0, rem = 0;
-                bool done = false;
-#pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    if (!done && (run + h[j] >= want || 8 * lane + j == 255)) { bin = 255 - 8 * lane - j; rem = want - run; done = true; }
-                    run += h[j];
-                }
-                s_remaining = rem;
-                s_prefix = prefix | ((uint32_t)bin << shift);
+            w_off[lane] = iv - v;
+            if (lane == 31) s_all = iv;
+        }
+        __syncthreads();
+        incl += w_off[warp];
+        const int excl = incl - mine, all = s_all;
+        if (pass == 0) {
+            want = min(min(block_topk, n_blocks), all);
+            if (tid == 0) s_take = want;
+        }
+        if (want > 0) {
+            if (excl < want && want <= incl) {
+                const bool first = excl + c0 >= want;
+                s_prefix = prefix | ((uint32_t)(first ? bhi : bhi - 1) << shift);
+                s_remaining = first ? want - excl : want - excl - c0;
+            } else if (all < want && tid == SC_THREADS - 1) {     // (cannot happen: the prefix bin held at least `want`)
+                s_prefix = prefix;
+                s_remaining = want - (all - c1);
             }
         }
-        cluster.sync();                                           // all have read the histograms; the decision is visible
-        if (s_take <= 0) break;                                   // (the same on every CTA)
+        __syncthreads();                                          // the decision is visible
+        if (want <= 0) break;                                     // (the same on every CTA)
     }
     const int take = s_take;
     const uint32_t kth = s_prefix;
@@ -420,9 +545,15 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
     int eq_before = 0, out_before = 0, total_taken = 0;
     {
         int e_run = 0, o_run = 0;
-        for (int q = 0; q < SC_CTAS; q++) {
+        int gq[SC_CTAS], eq_q[SC_CTAS];
+#pragma unroll
+        for (int q = 0; q < SC_CTAS; q++) {                       // (all the remote reads in flight together)
             const int *cnt = cluster.map_shared_rank(cta_cnt, q);
-            const int g = cnt[0], e = cnt[1];
+            gq[q] = cnt[0]; eq_q[q] = cnt[1];
+        }
+#pragma unroll
+        for (int q = 0; q < SC_CTAS; q++) {
+            const int g = gq[q], e = eq_q[q];
             if (q == rank) { eq_before = e_run; out_before = o_run; }
             o_run += g + min(max(need_eq - e_run, 0), e);
             e_run += e;
@@ -444,9 +575,15 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
             const uint32_t t_bits = __ballot_sync(0xffffffffu, taken);
             if (taken) {
                 const int pos = (at + __popc(t_bits & below)) * ratio;
-                for (int t = 0; t < ratio; t++) {
-                    m[b * ratio + t] = 1;
-                    l[1 + pos + t] = (uint32_t)(b * ratio + t);
+                if (ratio == 4 && (((uintptr_t)m) & 3) == 0) {    // the usual block of four tokens: one store for its mask bytes
+                    *reinterpret_cast<uint32_t *>(m + b * 4) = 0x01010101u;
+                    const uint32_t p0 = (uint32_t)(b * 4);
+                    l[1 + pos] = p0; l[2 + pos] = p0 + 1; l[3 + pos] = p0 + 2; l[4 + pos] = p0 + 3;
+                } else {
+                    for (int t = 0; t < ratio; t++) {
+                        m[b * ratio + t] = 1;
+                        l[1 + pos + t] = (uint32_t)(b * ratio + t);
+                    }
                 }
             }
             eq_rank += __popc(eq_bits);
@@ -473,6 +610,19 @@ void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const flo
                        int base_pos, int max_blocks) {
     const int most = std::min((base_pos + rows) / ratio, max_blocks);
     if (most <= 0 || rows <= 0) return;
+    const size_t smem = ((size_t)nq * d + (size_t)SCL_WARPS * 2 * 32 * SCL_LD) * sizeof(float);
+    if (d % SCL_CH == 0 && ((reinterpret_cast<uintptr_t>(pool) | reinterpret_cast<uintptr_t>(qn)) & 15) == 0 && smem <= 200 * 1024) {
+        static bool configured[16] = {false};
+        int dev = 0; cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 16 && !configured[dev]) {
+            cudaFuncSetAttribute(qsa_scores_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            configured[dev] = true;
+        }
+        qsa_scores_lane_kernel<<<dim3((most + SCL_WARPS * 32 - 1) / (SCL_WARPS * 32), rows), SCL_WARPS * 32, smem, s>>>(
+            scores, qn, pool, nq, d, ratio, base_pos, max_blocks);
+        g_launches++;
+        return;
+    }
     qsa_scores_kernel<<<dim3((most + 7) / 8, rows), 256, 0, s>>>(scores, qn, pool, nq, d, ratio, base_pos, max_blocks);
     g_launches++;
 }
@@ -482,15 +632,15 @@ void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const floa
     // long rows: a cluster of eight CTAs per row with the row's keys resident in their shared memory
     const int most = std::min((base_pos + rows) / ratio, max_blocks);
     const int per_cta = ((most + SC_CTAS - 1) / SC_CTAS + 1023) / 1024 * 1024;
-    if (most >= 8192 && per_cta * 4 <= 200 * 1024) {
+    if (most >= 8192 && per_cta * 4 <= 120 * 1024) {
         static bool configured[64] = {false};
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !configured[dev]) {
-            cudaFuncSetAttribute(qsa_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            cudaFuncSetAttribute(qsa_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
             configured[dev] = true;
         }
-        qsa_select_cluster_kernel<<<rows * SC_CTAS, SC_THREADS, (size_t)per_cta * 4, s>>>(mask, list, scores, ratio, base_pos, block_topk,
+        qsa_select_cluster_kernel<<<rows * SC_CTAS, SC_THREADS, (size_t)per_cta * 4 + (size_t)(3 + SC_REP - 1) * SC_BINS * 4, s>>>(mask, list, scores, ratio, base_pos, block_topk,
                                                                                          max_ctx, max_blocks, 1 + block_topk * ratio + ratio,
                                                                                          per_cta);
         g_launches++;

@@ -784,7 +784,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_tc") && (value == 0 || value == 1)) { qw::g_tune_prefill_tc = value; return true; }
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
-    if (knob && !strcmp(knob, "masked_tc") && (value == 0 || value == 1)) { qw::g_tune_masked_tc = value; return true; }
+    if (knob && !strcmp(knob, "masked_tc") && value >= 0 && value <= 2) { qw::g_tune_masked_tc = value; return true; }
     if (knob && !strcmp(knob, "qmv_tc") && (value == 0 || value == 1)) { qw::g_tune_qmv_tc = value; return true; }
     return false;
 }
@@ -1503,7 +1503,12 @@ static void attn_masked(qw_cmd c, qw_ref out, qw_ref gate, qw_ref q, qw_ref kcac
     if (!sq.q || !po || !pl || (gate.buf && !pg)) return;
     sq.rows = rows; sq.base_pos = base_pos; sq.key_lo = 0; sq.key_hi = base_pos + rows;
     if (g_tune_masked_tc && q_heads / kv_heads <= 16) {
-        // tensor ops over the gathered rows: a partial per 64 list entries, then the merge (and gate)
+        // one launch on a cluster where one can be placed; else tensor ops over the gathered rows with a partial per
+        // 64 list entries, then the merge (and gate)
+        if (g_tune_masked_tc == 1 && launch_attn_masked_cluster(c->stream, sq, q_heads, kv_heads, scale, pl, 1 + cap, (float *)po, (const float *)pg, 256)) {
+            cuda_ok(c, cudaGetLastError(), "attn_masked launch");
+            return;
+        }
         const int chunks = attn_masked_chunks(cap);
         float *scr = (float *)cmd_scratch(c, attn_per_query_scratch_bytes(rows, q_heads, chunks));
         if (!scr) return;

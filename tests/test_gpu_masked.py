@@ -38,9 +38,10 @@ def make_lists(rows, base, cap, seed=5):
     return lists
 
 
-@pytest.fixture(params=["fp32", "tensor"])
+@pytest.fixture(params=["fp32", "tensor", "tensor_two_launches"])
 def form(request, be):
-    assert be.tune("masked_tc", 1 if request.param == "tensor" else 0)
+    # 1: tensor ops, one launch on a thread-block cluster (default); 2: tensor ops, partials + merge; 0: the fp32 kernel
+    assert be.tune("masked_tc", {"fp32": 0, "tensor": 1, "tensor_two_launches": 2}[request.param])
     yield request.param
     be.tune("masked_tc", 1)
 

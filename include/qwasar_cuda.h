@@ -242,7 +242,9 @@ uint64_t    qw_gpu_launch_count(void);
  * plain stream order; "masked_tc" = 1 | 2 | 0, attention over a gathered row list on tensor-op tiles
  * (bf16 operands) as one launch on a thread-block cluster (default), as partials plus a merge launch, or on
  * the fp32 kernel; "qmv_tc" = 1 | 0, the one- and two-token 4-bit
- * product on the integer tensor path (default) or on the fp32 kernel.  Returns false for an unknown
+ * product on the integer tensor path (default) or on the fp32 kernel; "qmm_tc" = 1 | 0, the product for
+ * 16 tokens and more (groups of 64, k a multiple of 512 from 2048 up) on the tcgen05 GEMM with fp16 operands (default;
+ * the reference's tensor form and its 5e-5 bound) or on the fp32 kernel.  Returns false for an unknown
  * knob or value. */
 bool        qw_gpu_tune(const char *knob, int32_t value);
 /* How the split-KV decode kernel divides a launch of n_seq sequences (n_keys[i] keys each, kv_heads

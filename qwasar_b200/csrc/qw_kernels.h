@@ -189,6 +189,19 @@ struct QmvMulti {
 };
 void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m, int *status);
 
+// ---- the 4-bit product for many tokens on tcgen05 (qw_qgemm.cu) --------------------------------
+struct QgemmParams {
+    CUtensorMap map_x;       // fp16 [rows, k] (elements of every 8 in the order 0 4 1 5 2 6 3 7), boxes 64 x 128, SWIZZLE_128B
+    CUtensorMap map_w;       // u32 [n, k / 8], boxes 8 x 256
+    CUtensorMap map_s, map_b;  // bf16 [n, k / 64], boxes 8 x 256
+    float *y;                // [rows, n]
+    int *status;
+    int32_t rows, n, k;
+};
+size_t qgemm_scratch_bytes(int rows, int k);
+bool launch_qgemm_q4(cudaStream_t s, const QgemmParams &p, const float *x, void *x16);
+extern int g_tune_qmm_tc;
+
 // ---- QSA indexer (qw_qsa.cu) ----------------------------------------------------------------
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
                      int b0, int b1, float eps);

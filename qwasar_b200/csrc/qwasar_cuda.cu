@@ -243,6 +243,21 @@ bool encode_tile_map(CUtensorMap *m, const void *base, int dtype, uint64_t row_e
     return true;
 }
 
+// A row-major 2-D tensor [rows][inner] of el-byte elements with a row pitch in bytes, as boxes of box_inner x box_rows.
+bool encode_2d_map(CUtensorMap *m, const void *base, CUtensorMapDataType type, uint32_t el, uint64_t inner, uint64_t pitch_bytes,
+                   uint64_t rows, uint32_t box_inner, uint32_t box_rows, bool swizzle128) {
+    (void)el;
+    cuuint64_t dims[2] = {inner, rows};
+    cuuint64_t strides[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = G.encodeTiled(m, type, 2, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return false; }
+    return true;
+}
+
 bool pool_grow(Pool *a) {
     if (a->mapped_pages >= a->max_pages) { set_error("page pool exhausted (%lld pages)", (long long)a->max_pages); return false; }
     const int64_t first = a->mapped_pages;
@@ -786,6 +801,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     if (knob && !strcmp(knob, "masked_tc") && value >= 0 && value <= 2) { qw::g_tune_masked_tc = value; return true; }
     if (knob && !strcmp(knob, "qmv_tc") && (value == 0 || value == 1)) { qw::g_tune_qmv_tc = value; return true; }
+    if (knob && !strcmp(knob, "qmm_tc") && (value == 0 || value == 1)) { qw::g_tune_qmm_tc = value; return true; }
     return false;
 }
 // How the split-KV kernel would divide a launch: pure host arithmetic, no device needed.
@@ -1373,6 +1389,22 @@ static bool qmat_q4(qw_cmd c, const char *op, qw_ref y, qw_ref x, qw_ref w, qw_r
     const uint16_t *ps = (const uint16_t *)dev_range(c, scales, (size_t)n * (k / group) * 2, false, 2);
     const uint16_t *pb = (const uint16_t *)dev_range(c, biases, (size_t)n * (k / group) * 2, false, 2);
     if (!py || !px || !pw || !ps || !pb) return false;
+    // many tokens: the tcgen05 GEMM with the weights dequantised to fp16 in shared memory (fp16 operands, fp32
+    // accumulation: the reference's tensor form and its bound, tests/test_qmv.c:117-131 -- a bound met from k = 2048
+    // up, the shapes the reference tests it on: the rounding of the operands averages out with the square root of k)
+    if (rows >= 16 && group == 64 && (k & 511) == 0 && k >= 2048 && (n & 7) == 0 && g_tune_qmm_tc &&
+        ((reinterpret_cast<uintptr_t>(py) | reinterpret_cast<uintptr_t>(pw) | reinterpret_cast<uintptr_t>(ps) | reinterpret_cast<uintptr_t>(pb)) & 15) == 0) {
+        void *x16 = cmd_scratch(c, qgemm_scratch_bytes(rows, k));
+        QgemmParams gp;
+        if (x16 && encode_2d_map(&gp.map_x, x16, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)k, (uint64_t)k * 2, (uint64_t)rows, 64, 128, true) &&
+            encode_2d_map(&gp.map_w, pw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)k / 8, (uint64_t)k / 2, (uint64_t)n, 8, 256, false) &&
+            encode_2d_map(&gp.map_s, ps, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)k / 64, (uint64_t)k / 32, (uint64_t)n, 8, 256, false) &&
+            encode_2d_map(&gp.map_b, pb, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)k / 64, (uint64_t)k / 32, (uint64_t)n, 8, 256, false)) {
+            gp.y = py; gp.status = cmd_status(c); gp.rows = rows; gp.n = n; gp.k = k;
+            if (launch_qgemm_q4(c->stream, gp, px, x16)) return cuda_ok(c, cudaGetLastError(), "qgemm_q4 launch");
+            cudaGetLastError();
+        }
+    }
     launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group, cmd_status(c));
     return cuda_ok(c, cudaGetLastError(), "qmat_q4 launch");
 }

@@ -621,7 +621,21 @@ def next_rows_extra(be, torch, peaks, device):
                              "frac_of_hbm": round(per / 1e9 / (ms * 1e-3) / peaks["hbm"], 4), "peak": peaks["which"]}
     for b in (bw, bs, bb, bx, by):
         be.buf_free(b)
-    del w, sc, bi
+    # ---- q4 product, many tokens (a prefill-side q_proj): the tcgen05 GEMM with the weights dequantised on their way
+    rows_p = 4096
+    xp = torch.randn((rows_p, k), generator=g, device=device, dtype=torch.float32)
+    yp = torch.empty((rows_p, n), device=device, dtype=torch.float32)
+    bxp, byp, bw0, bs0, bb0 = wrap(xp), wrap(yp), wrap(w[0]), wrap(sc[0]), wrap(bi[0])
+    def q4p(c):
+        be.op_qmm_q4(c, QwRef(byp, 0), QwRef(bxp, 0), QwRef(bw0, 0), QwRef(bs0, 0), QwRef(bb0, 0), k, n, rows_p, group)
+    ms = time_device(be, torch, q4p, 5, 3, lambda: None)[0]
+    tf = 2.0 * rows_p * k * n / (ms * 1e-3) / 1e12
+    out["qmm_q4_prefill"] = {"k": k, "n": n, "rows": rows_p, "group": group, "ms": round(ms, 4), "tflops": round(tf, 1),
+                             "frac_of_bf16_peak": round(tf / peaks["tf"], 4), "peak": peaks["which"],
+                             "operands": "fp16 (x converted, weights dequantised in shared memory), fp32 accumulate"}
+    for b in (bxp, byp, bw0, bs0, bb0):
+        be.buf_free(b)
+    del w, sc, bi, xp, yp
     # ---- one QSA step at 262 144 positions
     ctx, ratio, topk, nq, d, qh, kvh = 262144 + 64, 4, 512, 4, 128, 16, 2
     base, max_blocks, cap = 262144, (262144 + 64) // 4, 512 * 4 + 4

@@ -6,19 +6,24 @@
 // flight during this step's matmul).  Operands are fp16, accumulation fp32; the reference bounds
 // that form at 5e-5 of the sum of absolute terms (tests/test_qmv.c:117-131).
 //
-// One persistent CTA per SM walks tiles of 128 tokens x 256 weight rows; K advances one
-// quantisation group (64) per step.  Roles, 14 warps:
-//   warp 0      TMA: the step's X tile (fp16, 128 x 64, SWIZZLE_128B), its 256 x 32 bytes of packed
+// One persistent CTA per SM walks tiles of 256 tokens x 256 weight rows (two 128-token halves that share
+// every dequantised weight tile: the dequantisation costs as many issue slots per weight as the tensor
+// core spends clocks on it at 128 tokens, and a 128 x 256 tile pulled 94 bytes per clock from L2 -- with
+// both halves one stage of weights feeds twice the arithmetic); K advances one quantisation group (64)
+// per step.  Roles, 14 warps:
+//   warp 0      TMA: the step's two X tiles (fp16, 128 x 64 each, SWIZZLE_128B), its 256 x 32 bytes of packed
 //               weights, and every eighth step the next 8 groups' scales and biases of the 256 rows
 //   warps 2-9   dequantisation, a thread per weight row: 8 packed words -> 64 fp16 = scale * nibble +
 //               bias (one fused multiply-add in half2, one rounding), written as the tensor core's
 //               K-major SWIZZLE_128B tile; a packed word yields its nibbles in the order 0 4 1 5 2 6 3 7
 //               (two masks instead of eight shifts), and X is laid out in that same order by the
 //               conversion pass, so no lane ever permutes anything
-//   warp 1      one thread issues 4 tcgen05.mma (M128 N256 K16, A and B from shared memory, D in tensor
-//               memory) per step and commits the stage back to the producer
-//   warps 10-13 epilogue: tensor memory -> registers -> y (fp32), on the accumulator that is not being
-//               written: the 512 TMEM columns hold two 128 x 256 fp32 accumulators
+//   warp 1      one thread issues 8 tcgen05.mma (M128 N256 K16, A and B from shared memory, D in tensor
+//               memory) per step and commits the stage back to the producer and the weight buffer back
+//               to the dequantisers
+//   warps 10-13 epilogue: tensor memory -> registers -> y (fp32); the 512 TMEM columns hold the two
+//               halves' 128 x 256 fp32 accumulators, so the epilogue of a tile (a twelfth of its K loop)
+//               is not overlapped
 // Every mbarrier wait is bounded (a timeout raises the CTA's abort flag and reports through the
 // command's status word; control flow never depends on it), tensor memory is always released.
 #include <algorithm>
@@ -28,9 +33,9 @@ namespace qw {
 
 namespace {
 
-constexpr int GM = 128, GN = 256, GK = 64, G_NS = 3;
-constexpr int G_A_BYTES = GM * GK * 2, G_B_BYTES = GN * GK * 2, G_W_BYTES = GN * (GK / 2), G_S_BYTES = GN * 16;
-constexpr int G_OFF_A = 0, G_OFF_B = G_OFF_A + G_NS * G_A_BYTES, G_OFF_W = G_OFF_B + G_NS * G_B_BYTES;
+constexpr int GM = 128, GH = 2, GN = 256, GK = 64, G_NS = 3, G_NB = 2;   // GH halves of GM tokens; TMA stages; weight buffers
+constexpr int G_AH_BYTES = GM * GK * 2, G_A_BYTES = GH * G_AH_BYTES, G_B_BYTES = GN * GK * 2, G_W_BYTES = GN * (GK / 2), G_S_BYTES = GN * 16;
+constexpr int G_OFF_A = 0, G_OFF_B = G_OFF_A + G_NS * G_A_BYTES, G_OFF_W = G_OFF_B + G_NB * G_B_BYTES;
 constexpr int G_OFF_S = G_OFF_W + G_NS * G_W_BYTES;           // [2 slots][scales 256 x 16 B | biases 256 x 16 B]
 constexpr int G_OFF_BAR = G_OFF_S + 2 * 2 * G_S_BYTES;
 constexpr int G_SMEM = G_OFF_BAR + 256;
@@ -93,18 +98,21 @@ __global__ void __launch_bounds__(256) qgemm_x16_kernel(uint4 *__restrict__ x16,
 __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_constant__ QgemmParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + G_OFF_BAR);
-    uint64_t *full_a = bars, *deq = bars + G_NS, *empty = bars + 2 * G_NS;             // per stage
-    uint64_t *sc_full = bars + 3 * G_NS, *sc_empty = sc_full + 2;                      // per scale slot
-    uint64_t *acc_full = sc_empty + 2, *acc_empty = acc_full + 2;                      // per accumulator
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    uint64_t *full_a = bars, *empty = bars + G_NS;                                     // per TMA stage
+    uint64_t *deq = bars + 2 * G_NS, *bq_free = deq + G_NB;                            // per weight buffer
+    uint64_t *sc_full = bq_free + G_NB, *sc_empty = sc_full + 2;                       // per scale slot
+    uint64_t *acc_full = sc_empty + 2, *acc_empty = acc_full + 1;                      // the accumulators
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 1);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool smem_ok = (smem_u32(smem) & 1023u) == 0;          // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) {
         *abort_flag = smem_ok ? 0 : 1;
         if (!smem_ok) report(p.status, QW_ST_BAD_SMEM);
-        for (int i = 0; i < G_NS; i++) { mbar_init(&full_a[i], 1); mbar_init(&deq[i], 8); mbar_init(&empty[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 8); mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }
+        for (int i = 0; i < G_NS; i++) { mbar_init(&full_a[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < G_NB; i++) { mbar_init(&deq[i], 8); mbar_init(&bq_free[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 8); }
+        mbar_init(acc_full, 1); mbar_init(acc_empty, 4);
         mbar_fence_init();
     }
     if (warp == G_W_MMA) g_tmem_alloc(tmem_slot, 512);
@@ -115,7 +123,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
     pdl_wait();                                                   // x16 comes from the kernel in front
     pdl_launch_next();
 
-    const int m_tiles = (p.rows + GM - 1) / GM, n_tiles = (p.n + GN - 1) / GN, tiles = m_tiles * n_tiles;
+    const int gh = p.halves;                                      // 128-token halves per tile: 2, or 1 where that fills the SMs better
+    const int m_tiles = (p.rows + gh * GM - 1) / (gh * GM), n_tiles = (p.n + GN - 1) / GN, tiles = m_tiles * n_tiles;
     const int KS = p.k / GK;                                      // K steps per tile (a multiple of 8)
     const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
 
@@ -133,8 +142,10 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
                         tma_load_2d(smem + G_OFF_S + slot * 2 * G_S_BYTES + G_S_BYTES, &p.map_b, ks, n_t * GN, &sc_full[slot]);
                     }
                     if (g >= G_NS) mbar_wait(&empty[s], ((g / G_NS) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
-                    mbar_expect_tx(&full_a[s], G_A_BYTES + G_W_BYTES);
-                    tma_load_2d(smem + G_OFF_A + s * G_A_BYTES, &p.map_x, ks * GK, m_t * GM, &full_a[s]);
+                    const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;      // a last tile of at most 128 tokens: one half
+                    mbar_expect_tx(&full_a[s], halves * G_AH_BYTES + G_W_BYTES);
+                    for (int h = 0; h < halves; h++)
+                        tma_load_2d(smem + G_OFF_A + s * G_A_BYTES + h * G_AH_BYTES, &p.map_x, ks * GK, (m_t * gh + h) * GM, &full_a[s]);
                     tma_load_2d(smem + G_OFF_W + s * G_W_BYTES, &p.map_w, ks * (GK / 8), n_t * GN, &full_a[s]);
                 }
             }
@@ -142,24 +153,26 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
     } else if (warp == G_W_MMA) {
         if (lane == 0 && smem_ok) {
             for (int it = 0; it < my_tiles; it++) {
-                const int b = it & 1;
-                if (it >= 2) mbar_wait(&acc_empty[b], ((it >> 1) - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+                const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles;
+                const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;
+                if (it >= 1) mbar_wait(acc_empty, (it - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the epilogue has read the last tile
                 g_fence_after();
-                const uint32_t d = tmem + b * GN;
                 for (int ks = 0; ks < KS; ks++) {
-                    const int g = it * KS + ks, s = g % G_NS;
-                    const uint32_t ph = (g / G_NS) & 1;
-                    mbar_wait_hot(&full_a[s], ph, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
-                    mbar_wait_hot(&deq[s], ph, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
+                    const int g = it * KS + ks, s = g % G_NS, bq = g % G_NB;
+                    mbar_wait_hot(&full_a[s], (g / G_NS) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                    mbar_wait_hot(&deq[bq], (g / G_NB) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
                     g_fence_after();
-                    const uint32_t a_lo = g_desc_lo(smem_u32(smem + G_OFF_A + s * G_A_BYTES));
-                    const uint32_t b_lo = g_desc_lo(smem_u32(smem + G_OFF_B + s * G_B_BYTES));
+                    const uint32_t b_lo = g_desc_lo(smem_u32(smem + G_OFF_B + bq * G_B_BYTES));
+                    for (int h = 0; h < halves; h++) {
+                        const uint32_t a_lo = g_desc_lo(smem_u32(smem + G_OFF_A + s * G_A_BYTES + h * G_AH_BYTES));
 #pragma unroll
-                    for (int kk = 0; kk < GK / 16; kk++)
-                        g_mma_ss(d, a_lo + kk * 2, G_DESC_HI, b_lo + kk * 2, G_DESC_HI, G_IDESC, (ks | kk) ? 1u : 0u);
-                    g_commit(&empty[s]);                          // the stage is free once these have read it
+                        for (int kk = 0; kk < GK / 16; kk++)
+                            g_mma_ss(tmem + h * GN, a_lo + kk * 2, G_DESC_HI, b_lo + kk * 2, G_DESC_HI, G_IDESC, (ks | kk) ? 1u : 0u);
+                    }
+                    g_commit(&empty[s]);                          // the stage is free once these have read it,
+                    g_commit(&bq_free[bq]);                       // and so is the weight buffer
                 }
-                g_commit(&acc_full[b]);                           // the tile's accumulator is complete
+                g_commit(acc_full);                               // the tile's accumulators are complete
             }
         }
     } else if (warp < G_W_EPI0) {
@@ -168,16 +181,17 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
         const uint32_t row_off = (uint32_t)t * 128u, sw = (uint32_t)(t & 7);
         for (int it = 0; it < my_tiles; it++) {
             for (int ks = 0; ks < KS; ks++) {
-                const int g = it * KS + ks, s = g % G_NS, slot = (g >> 3) & 1;
+                const int g = it * KS + ks, s = g % G_NS, bq = g % G_NB, slot = (g >> 3) & 1;
                 if ((ks & 7) == 0) mbar_wait(&sc_full[slot], (g >> 4) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
                 mbar_wait(&full_a[s], (g / G_NS) & 1, abort_flag, p.status, QW_ST_TMA_TIMEOUT);
+                if (g >= G_NB) mbar_wait(&bq_free[bq], ((g / G_NB) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
                 const uint16_t sb = *reinterpret_cast<const uint16_t *>(smem + G_OFF_S + slot * 2 * G_S_BYTES + t * 16 + (ks & 7) * 2);
                 const uint16_t bb = *reinterpret_cast<const uint16_t *>(smem + G_OFF_S + slot * 2 * G_S_BYTES + G_S_BYTES + t * 16 + (ks & 7) * 2);
                 const __half2 sc = __float2half2_rn(bf16_bits_to_f32(sb)), bi = __float2half2_rn(bf16_bits_to_f32(bb));
                 const uint4 w0 = *reinterpret_cast<const uint4 *>(smem + G_OFF_W + s * G_W_BYTES + t * 32);
                 const uint4 w1 = *reinterpret_cast<const uint4 *>(smem + G_OFF_W + s * G_W_BYTES + t * 32 + 16);
                 const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                uint8_t *brow = smem + G_OFF_B + s * G_B_BYTES + row_off;
+                uint8_t *brow = smem + G_OFF_B + bq * G_B_BYTES + row_off;
                 const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
@@ -195,7 +209,7 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
                 fence_proxy_async();                              // these writes, before the tensor core's reads
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(&deq[s]);
+                    mbar_arrive(&deq[bq]);
                     if ((ks & 7) == 7) mbar_arrive(&sc_empty[slot]);
                 }
             }
@@ -204,28 +218,31 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
         // ---- epilogue: this warp reads the TMEM lanes of its quarter (warp index mod 4), a lane = a token
         const int q = warp & 3;
         for (int it = 0; it < my_tiles; it++) {
-            const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles, n_t = tile / m_tiles, b = it & 1;
-            mbar_wait(&acc_full[b], (it >> 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
+            const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles, n_t = tile / m_tiles;
+            const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;
+            mbar_wait(acc_full, it & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             g_fence_after();
-            const int row = m_t * GM + q * 32 + lane;
-            float *yrow = p.y + (size_t)row * p.n + (size_t)n_t * GN;
+            for (int h = 0; h < halves; h++) {
+                const int row = (m_t * gh + h) * GM + q * 32 + lane;
+                float *yrow = p.y + (size_t)row * p.n + (size_t)n_t * GN;
 #pragma unroll 1
-            for (int c = 0; c < GN / 32; c++) {
-                uint32_t r[32];
-                g_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + b * GN + c * 32, r);
-                g_tmem_wait_ld();
-                if (row < p.rows && !*abort_flag) {
-                    const int col0 = n_t * GN + c * 32;
+                for (int c = 0; c < GN / 32; c++) {
+                    uint32_t r[32];
+                    g_tmem_ld32(tmem + ((uint32_t)(q * 32) << 16) + h * GN + c * 32, r);
+                    g_tmem_wait_ld();
+                    if (row < p.rows && !*abort_flag) {
+                        const int col0 = n_t * GN + c * 32;
 #pragma unroll
-                    for (int v = 0; v < 8; v++)
-                        if (col0 + v * 4 < p.n)                   // (n is a multiple of 4)
-                            *reinterpret_cast<float4 *>(yrow + c * 32 + v * 4) =
-                                make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                        for (int v = 0; v < 8; v++)
+                            if (col0 + v * 4 < p.n)               // (n is a multiple of 4)
+                                *reinterpret_cast<float4 *>(yrow + c * 32 + v * 4) =
+                                    make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
                 }
             }
             g_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[b]);
+            if (lane == 0) mbar_arrive(acc_empty);
         }
     }
     g_fence_before();
@@ -256,9 +273,15 @@ bool launch_qgemm_q4(cudaStream_t s, const QgemmParams &p, const float *x, void 
     cfg.gridDim = dim3((unsigned)std::min<size_t>((chunks + 255) / 256, (size_t)sm_count() * 8)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0;
     if (cudaLaunchKernelEx(&cfg, qgemm_x16_kernel, reinterpret_cast<uint4 *>(x16), x, chunks) != cudaSuccess) return false;
     g_launches++;
-    const int tiles = ((p.rows + GM - 1) / GM) * ((p.n + GN - 1) / GN);
-    cfg.gridDim = dim3((unsigned)std::min(tiles, sm_count())); cfg.blockDim = dim3(G_THREADS); cfg.dynamicSmemBytes = G_SMEM;
-    if (cudaLaunchKernelEx(&cfg, qgemm_q4_kernel, p) != cudaSuccess) return false;
+    // Two halves per tile cost a step 512 tensor-core clocks, one half about 340 (bound by the dequantisation; measured 730 against 950 TFLOP/s on a large product):
+    // whichever gets through its rounds over the SMs sooner
+    const int n_tiles = (p.n + GN - 1) / GN, sms = sm_count();
+    const int t2 = ((p.rows + 2 * GM - 1) / (2 * GM)) * n_tiles, t1 = ((p.rows + GM - 1) / GM) * n_tiles;
+    QgemmParams q = p;
+    q.halves = (long long)((t2 + sms - 1) / sms) * 512 <= (long long)((t1 + sms - 1) / sms) * 340 ? 2 : 1;
+    const int tiles = q.halves == 2 ? t2 : t1;
+    cfg.gridDim = dim3((unsigned)std::min(tiles, sms)); cfg.blockDim = dim3(G_THREADS); cfg.dynamicSmemBytes = G_SMEM;
+    if (cudaLaunchKernelEx(&cfg, qgemm_q4_kernel, q) != cudaSuccess) return false;
     g_launches++;
     return true;
 }

@@ -98,7 +98,10 @@ constexpr int SEG_COST = QW_SEG_COST;
 __host__ __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
     if (cta >= p.n_cta) return p.total_tiles;
     const int64_t v_total = (int64_t)p.total_tiles + (int64_t)SEG_COST * p.n_seq * p.kv_heads;
-    const int64_t v = ((int64_t)cta * v_total) / p.n_cta;
+    // (32-bit division where the product fits, which is every realistic launch: a 64-bit one is a hundred instructions
+    // at the head of every CTA)
+    const int64_t v = (v_total * p.n_cta) >> 31 ? ((int64_t)cta * v_total) / p.n_cta
+                                                  : (int64_t)(((uint32_t)cta * (uint32_t)v_total) / (uint32_t)p.n_cta);
     int s = 0, e = p.n_seq - 1;
     while (s < e) {
         const int m = (s + e + 1) >> 1;
@@ -106,7 +109,7 @@ __host__ __device__ __forceinline__ int share_lo(const AttnParams &p, int cta) {
     }
     const int64_t rel = v - ((int64_t)p.seq[s].cum_tiles + (int64_t)SEG_COST * s * p.kv_heads);
     const int per = p.seq[s].n_tiles + SEG_COST;
-    int h = (int)(rel / per);
+    int h = rel >> 31 ? (int)(rel / per) : (int)((uint32_t)rel / (uint32_t)per);
     if (h > p.kv_heads - 1) h = p.kv_heads - 1;
     int o = (int)(rel - (int64_t)h * per) - SEG_COST;
     if (o < 0) o = 0;
@@ -532,6 +535,32 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 const bool v0 = mt * 16 + gid < valid_rows, v1 = mt * 16 + gid + 8 < valid_rows;
                 float2 *r0 = reinterpret_cast<float2 *>(red + (size_t)(mt * 16 + gid) * RED_LD + tig * 2);
                 float2 *r1 = r0 + 8 * (RED_LD / 2);
+                const bool two_chains = MT == 1 && KG >= 2 && valid_rows <= 8;
+                if (two_chains) {
+                    // At most 8 valid rows (a decode step): rows 8-15 of `red` are free, so the odd key groups add
+                    // up there while the even ones use rows 0-7 -- half the rounds; the reader adds the two halves.
+                    float2 *rr = (kg & 1) ? r1 : r0;
+                    const int lrow = mt * 16 + gid + ((kg & 1) ? 8 : 0);
+#pragma unroll 1
+                    for (int round = 0; round < (KG + 1) / 2; round++) {
+                        if ((kg >> 1) == round) {
+                            if (v0) {
+                                if (round == 0) {
+#pragma unroll
+                                    for (int n = 0; n < 32; n++) rr[n * 4] = make_float2(o[n][0] * f0, o[n][1] * f0);
+                                } else {
+#pragma unroll
+                                    for (int n = 0; n < 32; n++) {
+                                        const float2 t = rr[n * 4];
+                                        rr[n * 4] = make_float2(fmaf(o[n][0], f0, t.x), fmaf(o[n][1], f0, t.y));
+                                    }
+                                }
+                            }
+                            if (tig == 0) sm_l[lrow] = (round ? sm_l[lrow] : 0.0f) + l0 * f0;
+                        }
+                        asm volatile("bar.sync 1, %0;" ::"n"(NW * 32) : "memory");
+                    }
+                } else
 #pragma unroll 1
                 for (int round = 0; round < KG; round++) {
                     if (kg == round) {
@@ -575,7 +604,12 @@ __global__ void __maxnreg__((SplitCfg<MT, KG_>::MAXREG)) qw_attn_split_kernel(co
                 float Mrow = NEG_BIG;
 #pragma unroll
                 for (int g2 = 0; g2 < KG; g2++) Mrow = fmaxf(Mrow, sm_m[((row >> 4) * KG + g2) * 16 + (row & 15)]);
-                const float L = sm_l[row];
+                float L = sm_l[row];
+                if (MT == 1 && KG >= 2 && valid_rows <= 8) {       // (the odd key groups' half, see above)
+                    const float4 hi = *reinterpret_cast<const float4 *>(red + (size_t)(row + 8) * RED_LD + d4);
+                    acc.x += hi.x; acc.y += hi.y; acc.z += hi.z; acc.w += hi.w;
+                    L += sm_l[row + 8];
+                }
                 if (whole) {
                     const int r = row / p.gqa, g = row - r * p.gqa;
                     const size_t oi = ((size_t)r * p.q_heads + head0 + g) * 256 + d4;
@@ -754,6 +788,15 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
         for (int i = 0; i < 4; i++) gate4[i] = load_gate(sq.gate, gi + i, p.gate_dtype);
     }
     pdl_wait();
+    // the first accumulators of this thread's quarter are asked for together with the (max, sum) pairs: their
+    // weights are not needed until they arrive, and one trip to L2 is saved
+    const int quarter = tid >> 6, d4 = (tid & 63) * 4;
+    const float *base = p.pacc + pi0 * 256 + d4;
+    const size_t step = (size_t)(MT * 16) * 256;
+    float4 first[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++)
+        first[u] = quarter + 4 * u < parts ? *reinterpret_cast<const float4 *>(base + (size_t)(quarter + 4 * u) * step) : make_float4(0.f, 0.f, 0.f, 0.f);
     // max over the non-empty partials, then each partial's weight and the denominator
     float mq = -3.0e38f, lq = 0.0f;
     if (tid < parts) {
@@ -776,11 +819,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) qw_attn_merge_kernel(const __gr
 #pragma unroll
     for (int i = 0; i < MERGE_THREADS / 32; i++) den += red_s[1][i];
 
-    const int quarter = tid >> 6, d4 = (tid & 63) * 4;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float *base = p.pacc + pi0 * 256 + d4;
-    const size_t step = (size_t)(MT * 16) * 256;
-    int q = quarter;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const float w = quarter + 4 * u < parts ? w_s[quarter + 4 * u] : 0.0f;
+        acc.x += first[u].x * w; acc.y += first[u].y * w; acc.z += first[u].z * w; acc.w += first[u].w * w;
+    }
+    int q = quarter + 16;
     for (; q + 12 < parts; q += 16) {
         float4 a[4];
 #pragma unroll

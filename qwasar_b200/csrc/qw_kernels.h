@@ -198,6 +198,7 @@ struct QgemmParams {
     int *status;
     int32_t rows, n, k;
     int32_t halves;          // 128-token halves per tile (set by the launcher)
+    int32_t split_from;      // tiles from this one on run as two entries of one half each (set by the launcher)
 };
 size_t qgemm_scratch_bytes(int rows, int k);
 bool launch_qgemm_q4(cudaStream_t s, const QgemmParams &p, const float *x, void *x16);

@@ -126,12 +126,24 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
     const int gh = p.halves;                                      // 128-token halves per tile: 2, or 1 where that fills the SMs better
     const int m_tiles = (p.rows + gh * GM - 1) / (gh * GM), n_tiles = (p.n + GN - 1) / GN, tiles = m_tiles * n_tiles;
     const int KS = p.k / GK;                                      // K steps per tile (a multiple of 8)
-    const int my_tiles = (int)blockIdx.x < tiles ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    // The list of work: tiles [0, split_from) whole, each later tile as two entries of one half (the launcher splits the
+    // tiles of a last, partly filled round over the SMs so that the round costs a half tile's time).
+    const int entries = p.split_from + 2 * (tiles - p.split_from);
+    const int my_tiles = (int)blockIdx.x < entries ? (entries - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    auto entry = [&](int it, int &m_t, int &n_t, int &h0, int &halves) {
+        const int e = blockIdx.x + it * gridDim.x;
+        int tile = e;
+        h0 = 0;
+        if (e >= p.split_from) { const int j = e - p.split_from; tile = p.split_from + (j >> 1); h0 = j & 1; }
+        m_t = tile % m_tiles; n_t = tile / m_tiles;
+        halves = e >= p.split_from ? 1 : (p.rows - m_t * gh * GM > GM ? gh : 1);   // (a last tile of at most 128 tokens: one half)
+    };
 
     if (warp == G_W_TMA) {
         if (lane == 0 && smem_ok) {
             for (int it = 0; it < my_tiles; it++) {
-                const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles, n_t = tile / m_tiles;
+                int m_t, n_t, h0, halves;
+                entry(it, m_t, n_t, h0, halves);
                 for (int ks = 0; ks < KS; ks++) {
                     const int g = it * KS + ks, s = g % G_NS;
                     if ((ks & 7) == 0) {
@@ -142,10 +154,9 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
                         tma_load_2d(smem + G_OFF_S + slot * 2 * G_S_BYTES + G_S_BYTES, &p.map_b, ks, n_t * GN, &sc_full[slot]);
                     }
                     if (g >= G_NS) mbar_wait(&empty[s], ((g / G_NS) - 1) & 1, abort_flag, p.status, QW_ST_SLOT_TIMEOUT);
-                    const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;      // a last tile of at most 128 tokens: one half
                     mbar_expect_tx(&full_a[s], halves * G_AH_BYTES + G_W_BYTES);
                     for (int h = 0; h < halves; h++)
-                        tma_load_2d(smem + G_OFF_A + s * G_A_BYTES + h * G_AH_BYTES, &p.map_x, ks * GK, (m_t * gh + h) * GM, &full_a[s]);
+                        tma_load_2d(smem + G_OFF_A + s * G_A_BYTES + h * G_AH_BYTES, &p.map_x, ks * GK, (m_t * gh + h0 + h) * GM, &full_a[s]);
                     tma_load_2d(smem + G_OFF_W + s * G_W_BYTES, &p.map_w, ks * (GK / 8), n_t * GN, &full_a[s]);
                 }
             }
@@ -153,8 +164,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
     } else if (warp == G_W_MMA) {
         if (lane == 0 && smem_ok) {
             for (int it = 0; it < my_tiles; it++) {
-                const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles;
-                const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;
+                int m_t, n_t, h0, halves;
+                entry(it, m_t, n_t, h0, halves);
                 if (it >= 1) mbar_wait(acc_empty, (it - 1) & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);   // the epilogue has read the last tile
                 g_fence_after();
                 for (int ks = 0; ks < KS; ks++) {
@@ -218,12 +229,12 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
         // ---- epilogue: this warp reads the TMEM lanes of its quarter (warp index mod 4), a lane = a token
         const int q = warp & 3;
         for (int it = 0; it < my_tiles; it++) {
-            const int tile = blockIdx.x + it * gridDim.x, m_t = tile % m_tiles, n_t = tile / m_tiles;
-            const int halves = p.rows - m_t * gh * GM > GM ? gh : 1;
+            int m_t, n_t, h0, halves;
+            entry(it, m_t, n_t, h0, halves);
             mbar_wait(acc_full, it & 1, abort_flag, p.status, QW_ST_MMA_TIMEOUT);
             g_fence_after();
             for (int h = 0; h < halves; h++) {
-                const int row = (m_t * gh + h) * GM + q * 32 + lane;
+                const int row = (m_t * gh + h0 + h) * GM + q * 32 + lane;
                 float *yrow = p.y + (size_t)row * p.n + (size_t)n_t * GN;
 #pragma unroll 1
                 for (int c = 0; c < GN / 32; c++) {
@@ -279,7 +290,12 @@ bool launch_qgemm_q4(cudaStream_t s, const QgemmParams &p, const float *x, void 
     const int t2 = ((p.rows + 2 * GM - 1) / (2 * GM)) * n_tiles, t1 = ((p.rows + GM - 1) / GM) * n_tiles;
     QgemmParams q = p;
     q.halves = (long long)((t2 + sms - 1) / sms) * 512 <= (long long)((t1 + sms - 1) / sms) * 340 ? 2 : 1;
-    const int tiles = q.halves == 2 ? t2 : t1;
+    int tiles = q.halves == 2 ? t2 : t1;
+    q.split_from = tiles;
+    if (q.halves == 2 && (p.rows % (2 * GM) == 0 || p.rows % (2 * GM) > GM)) {       // every tile has both halves
+        const int rem = tiles % sms;                            // tiles of the last, partly filled round
+        if (rem > 0 && 2 * rem <= sms) { q.split_from = tiles - rem; tiles += rem; }
+    }
     cfg.gridDim = dim3((unsigned)std::min(tiles, sms)); cfg.blockDim = dim3(G_THREADS); cfg.dynamicSmemBytes = G_SMEM;
     if (cudaLaunchKernelEx(&cfg, qgemm_q4_kernel, q) != cudaSuccess) return false;
     g_launches++;

@@ -157,6 +157,43 @@ constexpr int PRE_ROWS = QW_PRE_ROWS;
 // rows of other blocks stream under them.
 constexpr int PRE_WARPS = 4;
 static_assert(PRE_WARPS >= PRE_ROWS, "a block's first PRE_ROWS warps work out the rows' angles");
+// cosf / sinf of an fp32 angle as the correctly rounded float (what the CPU statement gets from libm,
+// qwasar_cpu.c:312-315): evaluated in double to about 2e-16 and rounded once.  The angle is reduced by
+// multiples of pi / 2 in two fused steps (pi / 2 as a double and its residual; angles here stay below 2^19, so
+// the product is exact to far below the result's last bit), sine and cosine of the remainder on [-pi / 4, pi / 4] are
+// their Taylor sums to r^17 and r^16 (remainders below 1e-19 and 2e-18), the quadrant picks and signs them.
+// About 60 instructions; the library's double sincos, which is accurate over the whole double range, cost 700 --
+// two fifths of this kernel's instructions at 4096 tokens.
+__device__ __forceinline__ void sincos_rounded(float ang, float &sn, float &cs) {
+    const double x = (double)ang;
+    const double k = rint(x * 0.63661977236758134308);
+    double r = fma(-k, 1.57079632679489655800, x);
+    r = fma(-k, 6.12323399573676603587e-17, r);
+    const double r2 = r * r;
+    double s = 1.0 / 355687428096000.0;                  // 1 / 17!
+    s = fma(s, r2, -1.0 / 1307674368000.0);              // -1 / 15!
+    s = fma(s, r2, 1.0 / 6227020800.0);                  // 1 / 13!
+    s = fma(s, r2, -1.0 / 39916800.0);                   // -1 / 11!
+    s = fma(s, r2, 1.0 / 362880.0);                      // 1 / 9!
+    s = fma(s, r2, -1.0 / 5040.0);
+    s = fma(s, r2, 1.0 / 120.0);
+    s = fma(s, r2, -1.0 / 6.0);
+    s = fma(s * r2, r, r);                               // r + r^3 (...)
+    double c = 1.0 / 20922789888000.0;                   // 1 / 16!
+    c = fma(c, r2, -1.0 / 87178291200.0);                // -1 / 14!
+    c = fma(c, r2, 1.0 / 479001600.0);                   // 1 / 12!
+    c = fma(c, r2, -1.0 / 3628800.0);                    // -1 / 10!
+    c = fma(c, r2, 1.0 / 40320.0);
+    c = fma(c, r2, -1.0 / 720.0);
+    c = fma(c, r2, 1.0 / 24.0);
+    c = fma(c, r2, -0.5);
+    c = fma(c, r2, 1.0);
+    const int q = (int)(long long)k & 3;
+    const double ss = (q & 1) ? c : s, cc = (q & 1) ? s : c;
+    sn = (float)((q & 2) ? -ss : ss);
+    cs = (float)(((q + 1) & 2) ? -cc : cc);
+}
+
 __global__ void __launch_bounds__(PRE_WARPS * 32, 6) preop_kernel(const __grid_constant__ PreopParams p) {
     __shared__ float cs_s[PRE_ROWS][64];                 // per token: cos[32], sin[32]
     // squares of the key rows, [key warps of the block][PRE_ROWS][260] (row stride 260: lanes on
@@ -216,9 +253,8 @@ __global__ void __launch_bounds__(PRE_WARPS * 32, 6) preop_kernel(const __grid_c
             const float ang = __fmul_rn((float)(ax == 0 ? p0 : ax == 1 ? p1 : p2), p.inv_freq[lane]);
             // cosf / sinf of the fp32 angle (qwasar_cpu.c:312-315), correctly rounded: the double
             // functions are exact far beyond float precision, so one rounding gives the float result
-            double snd, csd;
-            sincos((double)ang, &snd, &csd);
-            const float sn = (float)snd, cs = (float)csd;
+            float sn, cs;
+            sincos_rounded(ang, sn, cs);
             cs_s[warp][lane] = cs; cs_s[warp][32 + lane] = sn;
             if (s.cs_out && slot0 <= qs && qs < slot0 + PRE_WARPS) {          // the block with key head 0 publishes the table
                 s.cs_out[(size_t)r * 64 + lane] = cs; s.cs_out[(size_t)r * 64 + 32 + lane] = sn;

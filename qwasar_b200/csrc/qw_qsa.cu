@@ -166,8 +166,9 @@ __global__ void __launch_bounds__(256) qsa_scores_kernel(float *__restrict__ sco
     if (lane == 0) scores[(size_t)r * max_blocks + b] = __fdiv_rn(s, sqrtf((float)d));
 }
 
-// One CTA per row.  The reference finds the block_topk best blocks one at a time (the largest score
-// above -FLT_MAX, the lowest index among equals): that is the first `take` blocks in the order
+// One CTA per row.  The reference's CPU statement finds the block_topk best blocks one at a time (the
+// largest score above -FLT_MAX, the lowest index among equals, qwasar_flash_cpu.c:345-418); its GPU
+// kernel is qw_qsa_select, metal/sparse.metal:958-1049.  Both pick the first `take` blocks in the order
 // (score descending, index ascending).  Found here without sorting: the scores map to unsigned
 // keys that order the same way (-0 and +0 share a key, as they compare equal), a radix select of
 // four 8-bit passes finds the key of the take-th best, every block with a larger key is taken, and

@@ -69,6 +69,8 @@ struct qw_cmd_s {
     int parallel;
     std::vector<Touch> touched;
     cudaEvent_t uploaded = nullptr; // last first-touch upload on the copy stream (see dev_range)
+    cudaEvent_t written = nullptr, downloaded = nullptr;   // early copy-back at qw_cmd_flush (see there)
+    bool early_down = false;
     std::vector<Scratch> scratch;   // last one is current; earlier ones may still be in flight
     std::vector<Mark> marks;
     std::vector<KTime> ktimes;
@@ -113,6 +115,7 @@ struct Globals {
     std::vector<Scratch> scratch_pool;
     std::vector<cudaStream_t> stream_pool;    // streams of freed command buffers, reused
     cudaStream_t copy_stream = nullptr;       // first-touch uploads of shared buffers, see dev_range
+    cudaStream_t down_stream = nullptr;       // copy-back of written ranges started at qw_cmd_flush
     std::map<std::pair<uintptr_t, uint64_t>, CUtensorMap> map_cache;   // linear caches: (base, rows * 128 + box rows) -> map
 };
 Globals g_devs[MAX_DEVICES];
@@ -701,6 +704,7 @@ static bool init_device(int dev, char *err, size_t errcap) {
     memset(g.status_host, 0, st_bytes);
     g.status_used = 1;
     if (cudaStreamCreateWithFlags(&g.copy_stream, cudaStreamNonBlocking) != cudaSuccess) g.copy_stream = nullptr;
+    if (cudaStreamCreateWithFlags(&g.down_stream, cudaStreamNonBlocking) != cudaSuccess) g.down_stream = nullptr;
     g.up = true;
     return true;
 }
@@ -781,6 +785,7 @@ extern "C" void qw_gpu_shutdown(void) {
         for (auto &st : g.stream_pool) cudaStreamDestroy(st);
         g.stream_pool.clear();
         if (g.copy_stream) { cudaStreamDestroy(g.copy_stream); g.copy_stream = nullptr; }
+        if (g.down_stream) { cudaStreamDestroy(g.down_stream); g.down_stream = nullptr; }
         g.map_cache.clear();
         if (g.status_host) cudaFreeHost(g.status_host);
         g.status_host = g.status_dev = nullptr;
@@ -1126,7 +1131,29 @@ extern "C" qw_cmd qw_cmd_begin_on_stream(void *cuda_stream) {
     return cmd_new(reinterpret_cast<cudaStream_t>(cuda_stream), false);
 }
 extern "C" void qw_cmd_commit(qw_cmd c) { if (c) cudaStreamQuery(c->stream); }
-extern "C" void qw_cmd_flush(qw_cmd c) { if (c) cudaStreamQuery(c->stream); }
+// qw_cmd_flush: "what is encoded so far may start" (qwasar_gpu.h:60-64; the reference's forward flushes every few
+// layers, qwasar_flash_graph.c:657).  Ops launch as they are encoded here, so
+// the hint is used for the other direction: the shared ranges written so far start their way back to the host on a
+// stream of their own, behind an event on the command's stream, and qw_cmd_wait finds them done -- the outputs of
+// a layer travel while the next layers run.  (A range written again later is simply copied again at the wait.)
+extern "C" void qw_cmd_flush(qw_cmd c) {
+    if (!c) return;
+    use_device(c->device);
+    bool any = false;
+    for (auto &t : c->touched) any |= t.whi > t.wlo;
+    if (!any || !G.down_stream) { cudaStreamQuery(c->stream); return; }
+    if (!c->written && cudaEventCreateWithFlags(&c->written, cudaEventDisableTiming) != cudaSuccess) { c->written = nullptr; return; }
+    if (!c->downloaded && cudaEventCreateWithFlags(&c->downloaded, cudaEventDisableTiming) != cudaSuccess) { c->downloaded = nullptr; return; }
+    if (!cuda_ok(c, cudaEventRecord(c->written, c->stream), "flush event") ||
+        !cuda_ok(c, cudaStreamWaitEvent(G.down_stream, c->written, 0), "flush wait")) return;
+    for (auto &t : c->touched)
+        if (t.whi > t.wlo) {
+            cuda_ok(c, cudaMemcpyAsync((char *)t.b->host + t.wlo, (char *)t.b->dev + t.wlo, t.whi - t.wlo, cudaMemcpyDeviceToHost, G.down_stream), "download");
+            t.wlo = t.whi = 0;
+        }
+    cuda_ok(c, cudaEventRecord(c->downloaded, G.down_stream), "download event");
+    c->early_down = true;
+}
 extern "C" void qw_cmd_parallel(qw_cmd c, bool on) { if (c) c->parallel += on ? 1 : (c->parallel > 0 ? -1 : 0); }
 
 extern "C" void qw_cmd_wait(qw_cmd c) {
@@ -1137,6 +1164,7 @@ extern "C" void qw_cmd_wait(qw_cmd c) {
             cuda_ok(c, cudaMemcpyAsync((char *)t.b->host + t.wlo, (char *)t.b->dev + t.wlo, t.whi - t.wlo, cudaMemcpyDeviceToHost, c->stream), "download");
     c->touched.clear();
     cudaError_t e = cudaStreamSynchronize(c->stream);
+    if (e == cudaSuccess && c->early_down) { e = cudaEventSynchronize(c->downloaded); c->early_down = false; }
     if (e != cudaSuccess) cmd_fail(c, "GPU fault: %s", cudaGetErrorString(e));
     if (G.status_host) {
         volatile int *st = G.status_host + (size_t)c->status_slot * STATUS_STRIDE;
@@ -1174,6 +1202,8 @@ extern "C" void qw_cmd_free(qw_cmd c) {
     if (!c->touched.empty() || !c->scratch.empty()) cudaStreamSynchronize(c->stream);
     for (auto &s : c->scratch) G.scratch_pool.push_back(s);
     if (c->uploaded) cudaEventDestroy(c->uploaded);
+    if (c->written) cudaEventDestroy(c->written);
+    if (c->downloaded) cudaEventDestroy(c->downloaded);
     for (auto &m : c->marks) cudaEventDestroy(m.ev);
     for (auto &k : c->ktimes) { cudaEventDestroy(k.t0); cudaEventDestroy(k.t1); }
     if (c->own_stream) {

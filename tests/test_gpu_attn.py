@@ -193,3 +193,24 @@ def test_copy_reads_what_an_earlier_op_wrote(be):
         want = x * (1.0 / (1.0 + np.exp(-0.5)))
         assert np.allclose(np.array(dv), want, rtol=1e-6)
         assert np.array_equal(np.array(dv), np.array(yv))
+
+
+def test_flush_starts_the_copy_back_and_later_writes_still_arrive(be):
+    """qw_cmd_flush (the reference flushes between layers, qwasar_flash_graph.c:657) lets what was written so far
+    start its way back to the host; a range that a later op of the same command buffer writes again, and a buffer
+    first written after the flush, must still hold their final values after qw_cmd_wait."""
+    x = np.linspace(-2, 2, 4096).astype(np.float32)
+    g = np.full(4096, 0.25, np.float32)
+    sg = 1.0 / (1.0 + np.exp(-0.25))
+    with Bufs(be) as B:
+        ab, av = B.shared(x.copy()); bb, bv = B.shared(x.copy()); gb, _ = B.shared(g)
+        c = be.cmd_begin()
+        be.op_mul_sigmoid(c, QwRef(ab, 0), QwRef(gb, 0), 4096)          # a *= s
+        be.cmd_flush(c)
+        be.op_mul_sigmoid(c, QwRef(ab, 0), QwRef(gb, 0), 4096)          # a *= s again, after its first copy-back began
+        be.op_mul_sigmoid(c, QwRef(bb, 0), QwRef(gb, 0), 4096)          # b first written after the flush
+        be.cmd_flush(c)
+        be.cmd_flush(c)                                                 # nothing new: a no-op
+        be.cmd_wait(c); be.cmd_free(c)
+        assert np.allclose(np.array(av), x * sg * sg, rtol=2e-6)
+        assert np.allclose(np.array(bv), x * sg, rtol=2e-6)

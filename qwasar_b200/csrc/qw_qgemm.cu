@@ -10,10 +10,10 @@
 // every dequantised weight tile: the dequantisation costs as many issue slots per weight as the tensor
 // core spends clocks on it at 128 tokens, and a 128 x 256 tile pulled 94 bytes per clock from L2 -- with
 // both halves one stage of weights feeds twice the arithmetic); K advances one quantisation group (64)
-// per step.  Roles, 22 warps:
+// per step.  Roles, 14 warps:
 //   warp 0      TMA: the step's two X tiles (fp16, 128 x 64 each, SWIZZLE_128B), its 256 x 32 bytes of packed
 //               weights, and every eighth step the next 8 groups' scales and biases of the 256 rows
-//   warps 2-17  dequantisation, two threads per weight row: 8 packed words -> 64 fp16 = scale * nibble +
+//   warps 2-9   dequantisation, a thread per weight row: 8 packed words -> 64 fp16 = scale * nibble +
 //               bias (one fused multiply-add in half2, one rounding), written as the tensor core's
 //               K-major SWIZZLE_128B tile; a packed word yields its nibbles in the order 0 4 1 5 2 6 3 7
 //               (two masks instead of eight shifts), and X is laid out in that same order by the
@@ -21,7 +21,7 @@
 //   warp 1      one thread issues 8 tcgen05.mma (M128 N256 K16, A and B from shared memory, D in tensor
 //               memory) per step and commits the stage back to the producer and the weight buffer back
 //               to the dequantisers
-//   warps 18-21 epilogue: tensor memory -> registers -> y (fp32); the 512 TMEM columns hold the two
+//   warps 10-13 epilogue: tensor memory -> registers -> y (fp32); the 512 TMEM columns hold the two
 //               halves' 128 x 256 fp32 accumulators, so the epilogue of a tile (a twelfth of its K loop)
 //               is not overlapped
 // Every mbarrier wait is bounded (a timeout raises the CTA's abort flag and reports through the
@@ -39,10 +39,8 @@ constexpr int G_OFF_A = 0, G_OFF_B = G_OFF_A + G_NS * G_A_BYTES, G_OFF_W = G_OFF
 constexpr int G_OFF_S = G_OFF_W + G_NS * G_W_BYTES;           // [2 slots][scales 256 x 16 B | biases 256 x 16 B]
 constexpr int G_OFF_BAR = G_OFF_S + 2 * 2 * G_S_BYTES;
 constexpr int G_SMEM = G_OFF_BAR + 256;
-constexpr int G_DEQ_WARPS = 16;                                // two threads per weight row
-constexpr int G_W_TMA = 0, G_W_MMA = 1, G_W_DEQ0 = 2, G_W_EPI0 = G_W_DEQ0 + G_DEQ_WARPS;
-constexpr int G_THREADS = (G_W_EPI0 + 4) * 32;
-static_assert(G_W_EPI0 % 4 == 2, "the epilogue warps' TMEM quarters are their warp indices mod 4");
+constexpr int G_THREADS = 14 * 32;
+constexpr int G_W_TMA = 0, G_W_MMA = 1, G_W_DEQ0 = 2, G_W_EPI0 = 10;
 
 __device__ __forceinline__ void g_tmem_alloc(uint32_t *slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
@@ -112,8 +110,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
         *abort_flag = smem_ok ? 0 : 1;
         if (!smem_ok) report(p.status, QW_ST_BAD_SMEM);
         for (int i = 0; i < G_NS; i++) { mbar_init(&full_a[i], 1); mbar_init(&empty[i], 1); }
-        for (int i = 0; i < G_NB; i++) { mbar_init(&deq[i], G_DEQ_WARPS); mbar_init(&bq_free[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], G_DEQ_WARPS); }
+        for (int i = 0; i < G_NB; i++) { mbar_init(&deq[i], 8); mbar_init(&bq_free[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&sc_full[i], 1); mbar_init(&sc_empty[i], 8); }
         mbar_init(acc_full, 1); mbar_init(acc_empty, 4);
         mbar_fence_init();
     }
@@ -189,8 +187,8 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
             }
         }
     } else if (warp < G_W_EPI0) {
-        // ---- dequantisation: two threads per weight row of the tile, four packed words (32 weights) each
-        const int t = (threadIdx.x - G_W_DEQ0 * 32) >> 1, half = threadIdx.x & 1;
+        // ---- dequantisation: thread t owns weight row t of the tile
+        const int t = threadIdx.x - G_W_DEQ0 * 32;
         const uint32_t row_off = (uint32_t)t * 128u, sw = (uint32_t)(t & 7);
         for (int it = 0; it < my_tiles; it++) {
             for (int ks = 0; ks < KS; ks++) {
@@ -201,22 +199,23 @@ __global__ void __launch_bounds__(G_THREADS, 1) qgemm_q4_kernel(const __grid_con
                 const uint16_t sb = *reinterpret_cast<const uint16_t *>(smem + G_OFF_S + slot * 2 * G_S_BYTES + t * 16 + (ks & 7) * 2);
                 const uint16_t bb = *reinterpret_cast<const uint16_t *>(smem + G_OFF_S + slot * 2 * G_S_BYTES + G_S_BYTES + t * 16 + (ks & 7) * 2);
                 const __half2 sc = __float2half2_rn(bf16_bits_to_f32(sb)), bi = __float2half2_rn(bf16_bits_to_f32(bb));
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(smem + G_OFF_W + s * G_W_BYTES + t * 32 + half * 16);
-                const uint32_t ww[4] = {w0.x, w0.y, w0.z, w0.w};
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(smem + G_OFF_W + s * G_W_BYTES + t * 32);
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(smem + G_OFF_W + s * G_W_BYTES + t * 32 + 16);
+                const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
                 uint8_t *brow = smem + G_OFF_B + bq * G_B_BYTES + row_off;
                 const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
-                for (int jj = 0; jj < 4; jj++) {
+                for (int j = 0; j < 8; j++) {
                     // 0x6400 | nibble is the fp16 number 1024 + nibble: two nibbles per instruction, then minus 1024
                     // (exact) and one fused multiply-add
                     uint32_t h[4];
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        const uint32_t bits = ((ww[jj] >> (4 * q)) & 0x000F000Fu) | 0x64006400u;
+                        const uint32_t bits = ((ww[j] >> (4 * q)) & 0x000F000Fu) | 0x64006400u;
                         const __half2 v = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1024), sc, bi);
                         h[q] = *reinterpret_cast<const uint32_t *>(&v);
                     }
-                    *reinterpret_cast<uint4 *>(brow + (((uint32_t)(half * 4 + jj) ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+                    *reinterpret_cast<uint4 *>(brow + (((uint32_t)j ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
                 }
                 fence_proxy_async();                              // these writes, before the tensor core's reads
                 __syncwarp();

@@ -54,7 +54,7 @@ from qwasar_b200 import sharding, synth  # noqa: E402
 METRIC = "attn decode KV-read GB/s @32K ctx"
 UNIT = "GB/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one qw_attn_split_kernel launch, as a
-# multiple of the launch's algorithmic K+V bytes: 1.075368 GB read + 4.56 MB written against
+# multiple of the launch's algorithmic K+V bytes: 1.0755 GB read + 4.2 to 4.7 MB written against
 # 1.073775 GB (profiles/qw_attn_split_kernel__c3_27b_decode_32k_batch8.md).
 TRAFFIC_RATIO = 1.0057
 

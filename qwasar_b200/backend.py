@@ -11,7 +11,7 @@ import os
 import subprocess
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libqwasar_cuda.so")
+LIB_PATH = os.environ.get("QWASAR_CUDA_LIB") or os.path.join(HERE, "libqwasar_cuda.so")   # (the override: for comparing two builds)
 HEADER = os.path.join(os.path.dirname(HERE), "include", "qwasar_cuda.h")
 
 F32, BF16 = 0, 1

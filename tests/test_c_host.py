@@ -41,7 +41,8 @@ def test_header_compiles_as_c99_and_every_entry_point_links(attn_node):
     assert "device:" in r.stdout or "qw_gpu_init:" in r.stdout    # a device, or the library's refusal without one
 
 
-REF_HEADER = os.path.join(os.environ.get("QWASAR_REF", "/root/reference"), "qwasar_gpu.h")
+# the reference checkout: $QWASAR_REF, or beside this repository as oracle/Makefile assumes
+REF_HEADER = os.path.join(os.environ.get("QWASAR_REF") or os.path.join(os.path.dirname(ROOT), "reference"), "qwasar_gpu.h")
 
 
 @pytest.mark.skipif(not os.path.exists(REF_HEADER), reason="the reference checkout is not present on this machine")

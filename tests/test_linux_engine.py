@@ -9,7 +9,7 @@ import subprocess
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("QWASAR_REF", "/root/reference")
+REF = os.environ.get("QWASAR_REF") or os.path.join(os.path.dirname(ROOT), "reference")   # beside this repository, as oracle/Makefile assumes
 FIXTURE = os.path.join(REF, "tests", "fixtures", "flashnext-tiny-q4")
 EXE = os.path.join(ROOT, "oracle", "_ref", "flash_toy_cpu")
 

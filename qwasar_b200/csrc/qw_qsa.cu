@@ -363,7 +363,7 @@ __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__rest
 // barriers.)  The ordered passes need only each CTA's counts of larger and equal keys, read the same
 // way.  The mask is cleared and the list written by the CTAs in parallel, each for its own stretch.
 namespace cg = cooperative_groups;
-constexpr int SC_CTAS = 8, SC_THREADS = 1024, SC_WARPS = SC_THREADS / 32, SC_BINS = 2048, SC_REP = 8, SC_PRE = 8;
+constexpr int SC_CTAS = 8, SC_THREADS = 1024, SC_WARPS = SC_THREADS / 32, SC_BINS = 2048, SC_REP = 2, SC_PRE = 8;
 static_assert(SC_BINS == 2 * SC_THREADS, "the scan gives every thread two bins");
 
 __global__ void __cluster_dims__(SC_CTAS, 1, 1) __launch_bounds__(SC_THREADS)
@@ -436,12 +436,15 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
         const uint32_t prefix = s_prefix, high = pass == 0 ? 0u : 0xFFFFFFFFu << (shift + nbits), bmask = (1u << nbits) - 1u;
         int want = s_remaining;                                   // (read before this pass's decision is written)
         // The first pass sees every key, and the top bits of a row's scores take a handful of values: its adds go to
-        // one of SC_REP copies by warp (same-address adds in shared memory queue up: with one copy this pass took
-        // 5 us of the kernel's 26), folded into one histogram before the cluster looks at it.
+        // one of SC_REP copies by warp, folded into one histogram before the cluster looks at it (two copies measured
+        // best: 20.3 us for the whole selection against 21.7 with eight, whose clearing and folding cost more than
+        // they save).
         int *h = pass == 0 && (warp % SC_REP) ? rep0[warp % SC_REP - 1] : hist[pass];
         // One add per key, no aggregation inside the warp: matching the lanes' bins first (match.any) costs a round per
-        // distinct value, and with a few dozen distinct bins per warp that was 4 of the first pass's 5 us; the later
-        // passes only add the few keys that share the prefix.
+        // distinct value, and with a few dozen distinct bins per warp that was 4 of the first pass's 5 us; electing the
+        // two most common bins of a warp was slower too (24.5 against 21 us), and rows of equal scores (all zero, nine in
+        // ten zero) cost plain adds nothing extra: the hardware folds a warp's adds to one address.  The later passes only
+        // add the few keys that share the prefix.
         for (int i = tid; i < per_cta; i += SC_THREADS) {
             const uint32_t key = keys[i];
             if (key != 0u && (key & high) == prefix) atomicAdd(&h[(key >> shift) & bmask], 1);

@@ -111,6 +111,23 @@ def test_select_rows_of_thousands_of_blocks(be, oracle, rows, ratio, base, topk)
     check_select(be, oracle, scores, rows, ratio, base, topk, max_ctx)
 
 
+@pytest.mark.parametrize("kind", ["all_zero", "mostly_zero", "two_values"])
+def test_select_long_rows_of_mostly_equal_scores(be, oracle, kind):
+    """The distributions a histogram pass likes least: every score equal (all zero: index heads that all came out
+    negative), nine in ten equal, and two values only -- the lowest indices among the equals win."""
+    rng = np.random.default_rng(7)
+    rows, ratio, base, topk = 2, 4, 50000, 300
+    max_ctx = base + rows + 3
+    nb = max_ctx // ratio
+    if kind == "all_zero":
+        scores = np.zeros((rows, nb), np.float32)
+    elif kind == "mostly_zero":
+        scores = np.where(rng.random((rows, nb)) < 0.9, 0.0, np.abs(rng.standard_normal((rows, nb)))).astype(np.float32)
+    else:
+        scores = np.where(rng.random((rows, nb)) < 0.5, 1.25, 2.5).astype(np.float32)
+    check_select(be, oracle, scores, rows, ratio, base, topk, max_ctx)
+
+
 def test_scores_select_attend_chain(be, oracle):
     """Raw index keys -> scores -> selection -> masked attention, every stage on the device, against
     the oracle's chain fed with the device's scores (so that a last-bit difference of a score cannot

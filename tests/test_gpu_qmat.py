@@ -34,7 +34,7 @@ def worst_rel_err(got, x, deq):
 @pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (8192, 70, 2, 64), (5120, 33, 1, 32), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32),
                                               (5120, 12288, 1, 64), (5120, 1000, 2, 64), (12288, 500, 1, 64), (4096, 257, 2, 64), (128, 16, 1, 64),
                                               (640, 1, 1, 64), (16384, 40, 2, 64),
-                                              (2048, 256, 16, 64), (1024, 520, 200, 64), (5120, 768, 300, 64), (2048, 1000, 129, 64), (2560, 8, 16, 64), (6144, 264, 64, 64)])
+                                              (2048, 256, 16, 64), (1024, 520, 200, 64), (5120, 768, 300, 64), (2048, 1000, 129, 64), (2560, 8, 16, 64), (6144, 264, 64, 64), (2048, 100, 15, 64), (1024, 72, 7, 64)])
 def test_q4_product(be, oracle, op, k, n, rows, group):
     rng = np.random.default_rng(k + n + rows)
     w, sc, bi = q4_weights(rng, n, k, group)

@@ -810,6 +810,8 @@ def seq_split_extra(be, torch, dist, world, rank, device, barrier, peaks, layers
             "gbs": round(total / 1e9 / (res["exchange"] * 1e-3), 1),
             "per_gpu_frac_of_hbm": round(total / ss / 1e9 / (res["exchange"] * 1e-3) / peaks["hbm"], 4),
             "kernels_only_per_gpu_frac_of_hbm": round(total / ss / 1e9 / (res["kernels_only"] * 1e-3) / peaks["hbm"], 4)}
+        if nb > 1:      # (why this figure can exceed the step with the exchange)
+            out[f"batch{nb}"]["kernels_only_path"] = "qw_op_attn_partial + qw_op_attn_merge once per sequence: the batched form exists only with the exchange"
         for b in (bqg, bk, bv, bpos, bqn, bo, bpa):
             be.buf_free(b)
         be.xchg_free(x)

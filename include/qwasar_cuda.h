@@ -241,8 +241,10 @@ uint64_t    qw_gpu_launch_count(void);
  * decode chain start under the kernel in front of them (programmatic dependent launch, default) or in
  * plain stream order; "masked_tc" = 1 | 2 | 0, attention over a gathered row list on tensor-op tiles
  * (bf16 operands) as one launch on a thread-block cluster (default), as partials plus a merge launch, or on
- * the fp32 kernel; "qmv_tc" = 1 | 0, the one- and two-token 4-bit
- * product on the integer tensor path (default) or on the fp32 kernel; "qmm_tc" = 1 | 0, the product for
+ * the fp32 kernel; "qmv_tc" = 1 | 0, the 4-bit product of up to 15 tokens
+ * on the integer tensor path (default; four tokens to a pass over the weights) or on the fp32 kernel; "qmv_pre" = 1 | 0 | 2, the
+ * integer path's digits of x are cut once by a kernel ahead of the product from three tokens on (default), never
+ * (every block of the product cuts its own), or for one and two tokens as well; "qmm_tc" = 1 | 0, the product for
  * 16 tokens and more (groups of 64, k a multiple of 512 from 2048 up) on the tcgen05 GEMM with fp16 operands (default;
  * the reference's tensor form and its 5e-5 bound) or on the fp32 kernel.  Returns false for an unknown
  * knob or value. */

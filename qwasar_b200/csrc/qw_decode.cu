@@ -1492,6 +1492,7 @@ int g_tune_prefill_fuse_q = 1;
 int g_tune_pdl = 1;
 int g_tune_masked_tc = 1;
 int g_tune_qmv_tc = 1;
+int g_tune_qmv_pre = 1;
 
 int sm_count() {
     static int n[64] = {0};                    // per device

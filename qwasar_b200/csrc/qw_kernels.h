@@ -175,8 +175,11 @@ void launch_merge_parts(cudaStream_t s, void *out, int out_dtype, const float *p
                         float *pacc_out, float *pstat_out, size_t acc_stride = 0, size_t stat_stride = 0);
 
 // ---- 4-bit affine product (qw_qmat.cu): y [rows, n] = x [rows, k] . dequant(w [n, k/8])^T ----
+// `xq`: qmv_scratch_bytes(rows, k, group) bytes of scratch for the digits of x (0: none wanted), or null (the kernel's blocks
+// then cut the digits themselves).
+size_t qmv_scratch_bytes(int rows, int k, int group);
 void launch_qmat_q4(cudaStream_t s, float *y, const float *x, const uint32_t *w, const uint16_t *scales, const uint16_t *biases, int k,
-                    int n, int rows, int group, int *status);
+                    int n, int rows, int group, int *status, void *xq);
 
 // Up to four one-token products sharing x (and k, group) in one launch; w rows 16-byte aligned.
 struct QmvMulti {
@@ -187,7 +190,7 @@ struct QmvMulti {
     int32_t n[4], blocks[4];
     int32_t count, k, group;
 };
-void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m, int *status);
+void launch_qmv_q4_multi(cudaStream_t s, QmvMulti m, int *status, void *xq);
 
 // ---- the 4-bit product for many tokens on tcgen05 (qw_qgemm.cu) --------------------------------
 struct QgemmParams {
@@ -230,5 +233,6 @@ extern int g_tune_pdl;
 extern int g_tune_masked_tc;
 // 1: a one-token 4-bit product keeps x in registers (qmv1_q4_kernel); 0: the shared-memory kernel.
 extern int g_tune_qmv_tc;
+extern int g_tune_qmv_pre;
 
 }  // namespace qw

@@ -806,6 +806,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     if (knob && !strcmp(knob, "masked_tc") && value >= 0 && value <= 2) { qw::g_tune_masked_tc = value; return true; }
     if (knob && !strcmp(knob, "qmv_tc") && (value == 0 || value == 1)) { qw::g_tune_qmv_tc = value; return true; }
+    if (knob && !strcmp(knob, "qmv_pre") && value >= 0 && value <= 2) { qw::g_tune_qmv_pre = value; return true; }
     if (knob && !strcmp(knob, "qmm_tc") && (value == 0 || value == 1)) { qw::g_tune_qmm_tc = value; return true; }
     return false;
 }
@@ -1435,7 +1436,8 @@ static bool qmat_q4(qw_cmd c, const char *op, qw_ref y, qw_ref x, qw_ref w, qw_r
             cudaGetLastError();
         }
     }
-    launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group, cmd_status(c));
+    const size_t xq_bytes = qmv_scratch_bytes(rows, k, group);
+    launch_qmat_q4(c->stream, py, px, pw, ps, pb, k, n, rows, group, cmd_status(c), xq_bytes ? cmd_scratch(c, xq_bytes) : nullptr);
     return cuda_ok(c, cudaGetLastError(), "qmat_q4 launch");
 }
 extern "C" void qw_op_qmat_q4(qw_cmd c, qw_ref y, qw_ref x, qw_ref w, qw_ref scales, qw_ref biases, int32_t k, int32_t n, int32_t rows,
@@ -1471,9 +1473,10 @@ extern "C" bool qw_op_qmv_q4_multi(qw_cmd c, qw_ref x, int32_t k, int32_t group,
         aligned = aligned && ((uintptr_t)m.w[i] & 15) == 0;
     }
     if (aligned) {
-        launch_qmv_q4_multi(c->stream, m, cmd_status(c));               // one dispatch for all parts
+        const size_t xq_bytes = qmv_scratch_bytes(1, k, group);
+        launch_qmv_q4_multi(c->stream, m, cmd_status(c), xq_bytes ? cmd_scratch(c, xq_bytes) : nullptr);   // one dispatch for all parts
     } else {
-        for (int32_t i = 0; i < count; i++) launch_qmat_q4(c->stream, m.y[i], m.x, m.w[i], m.scales[i], m.biases[i], k, m.n[i], 1, group, cmd_status(c));
+        for (int32_t i = 0; i < count; i++) launch_qmat_q4(c->stream, m.y[i], m.x, m.w[i], m.scales[i], m.biases[i], k, m.n[i], 1, group, cmd_status(c), nullptr);
     }
     return cuda_ok(c, cudaGetLastError(), "qmv_q4_multi launch");
 }

@@ -34,7 +34,9 @@ def worst_rel_err(got, x, deq):
 @pytest.mark.parametrize("k,n,rows,group", [(64, 3, 1, 64), (4096, 48, 1, 64), (8192, 70, 2, 64), (5120, 33, 1, 32), (2048, 1000, 5, 64), (1024, 100, 17, 32), (256, 9, 8, 32),
                                               (5120, 12288, 1, 64), (5120, 1000, 2, 64), (12288, 500, 1, 64), (4096, 257, 2, 64), (128, 16, 1, 64),
                                               (640, 1, 1, 64), (16384, 40, 2, 64),
-                                              (2048, 256, 16, 64), (1024, 520, 200, 64), (5120, 768, 300, 64), (2048, 1000, 129, 64), (2560, 8, 16, 64), (6144, 264, 64, 64), (2048, 100, 15, 64), (1024, 72, 7, 64)])
+                                              (2048, 256, 16, 64), (1024, 520, 200, 64), (5120, 768, 300, 64), (2048, 1000, 129, 64), (2560, 8, 16, 64), (6144, 264, 64, 64), (2048, 100, 15, 64), (1024, 72, 7, 64),
+                                              (5120, 1000, 3, 64), (5120, 2000, 4, 64), (6144, 264, 4, 64), (512, 50, 3, 64), (7168, 40, 4, 64), (8192, 70, 4, 64),
+                                              (3072, 17, 4, 64), (5120, 300, 11, 64)])
 def test_q4_product(be, oracle, op, k, n, rows, group):
     rng = np.random.default_rng(k + n + rows)
     w, sc, bi = q4_weights(rng, n, k, group)
@@ -58,20 +60,21 @@ def test_q4_product(be, oracle, op, k, n, rows, group):
         assert np.allclose(got, want, rtol=0, atol=(1e-3 if tensor_form else 2e-5) * np.abs(want).max() + 1e-6)
 
 
+@pytest.mark.parametrize("rows", [2, 4, 3])
 @pytest.mark.parametrize("kind", ["positive", "outlier", "tiny", "huge", "zero", "nan"])
-def test_q4_product_input_ranges(be, kind):
-    """The one- and two-token product turns x into scaled integers: inputs that stress the scale --
-    one-signed (nothing cancels in the sums), a 1e4 outlier over unit noise, magnitudes near the
-    ends of the fp32 range, all zeros -- stay inside the reference's bound; a NaN in one token
-    poisons that token's outputs and leaves the other token's alone."""
-    k, n, rows, group = 5120, 300, 2, 64
+def test_q4_product_input_ranges(be, kind, rows):
+    """The product of up to four tokens turns x into scaled integers, each token by its own scale:
+    inputs that stress the scale -- one-signed (nothing cancels in the sums), a 1e4 outlier over unit
+    noise, magnitudes near the ends of the fp32 range, all zeros -- stay inside the reference's
+    bound; a NaN in one token poisons that token's outputs and leaves the other tokens' alone."""
+    k, n, group = 5120, 300, 64
     rng = np.random.default_rng(len(kind))
     w, sc, bi = q4_weights(rng, n, k, group)
     x = rng.standard_normal((rows, k)).astype(np.float32)
     if kind == "positive":
         x = np.abs(x) + 1.0
     elif kind == "outlier":
-        x[0, 77] = 1.0e4; x[1, 4000] = -3.0e4
+        x[0, 77] = 1.0e4; x[1, 4000] = -3.0e4; x[rows - 1, 5119] = 2.0e4
     elif kind == "tiny":
         x *= np.float32(1e-30)
     elif kind == "huge":
@@ -89,8 +92,9 @@ def test_q4_product_input_ranges(be, kind):
         got = np.array(yv)
     deq = dequant(w, sc, bi, k, group)
     if kind == "nan":
-        assert np.all(np.isnan(got[1])) and np.all(np.isfinite(got[0]))
-        assert worst_rel_err(got[:1], x[:1], deq) < 2e-6
+        keep = [r for r in range(rows) if r != 1]
+        assert np.all(np.isnan(got[1])) and np.all(np.isfinite(got[keep]))
+        assert worst_rel_err(got[keep], x[keep], deq) < 2e-6
         return
     assert np.all(np.isfinite(got))
     if kind == "zero":

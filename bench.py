@@ -659,13 +659,21 @@ def next_rows_extra(be, torch, peaks, device):
         "attend_us": lambda c: be.op_attn_masked(c, QwRef(bo, 0), QwRef(bqq, 0), QwRef(bk, 0), QwRef(bv, 0), QwRef(bl, 0), 1, qh, kvh, 256,
                                                  ctx, base, 0.0625, topk, ratio),
     }
-    step = {}
+    # Each figure is per launch over `reps` back-to-back launches per timed step (like the eight weight sets of the
+    # product above): the event the timer records after a step keeps the next launch from starting under the
+    # last one, which is how the layers of a decode step follow one another.
+    step, reps = {}, 4
     for name, fn in stages.items():
-        step[name] = round(time_device(be, torch, fn, 10, 3, lambda: None)[0] * 1e3, 2)
+        def repeated(c, fn=fn):
+            for _ in range(reps):
+                fn(c)
+        step[name] = round(time_device(be, torch, repeated, 10, 3, lambda: None)[0] * 1e3 / reps, 2)
     def chain(c):                      # the three stages back to back, as a decode step encodes them
-        for fn in stages.values():
-            fn(c)
-    step["chain_us"] = round(time_device(be, torch, chain, 10, 3, lambda: None)[0] * 1e3, 2)
+        for _ in range(reps):
+            for fn in stages.values():
+                fn(c)
+    step["chain_us"] = round(time_device(be, torch, chain, 10, 3, lambda: None)[0] * 1e3 / reps, 2)
+    step["launches_per_timed_step"] = reps
     step["listed_kv_bytes"] = int(lst[0, 0].item()) * kvh * 1024
     out["qsa_step_262k"] = step
     for b in bufs:

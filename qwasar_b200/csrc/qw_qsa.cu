@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(SCL_WARPS * 32) qsa_scores_lane_kernel(float *
     const int n_blocks = min((base_pos + r + 1) / ratio, max_blocks);
     const int b0 = (blockIdx.x * SCL_WARPS + warp) * 32;
     float *qs = scl_smem, *ks = scl_smem + nq * d + (size_t)warp * 2 * 32 * SCL_LD;
+    pdl_wait();                                                   // the queries and the pool may come from the kernel before
+    pdl_launch_next();
     for (int i = threadIdx.x * 4; i < nq * d; i += SCL_WARPS * 32 * 4)
         *reinterpret_cast<float4 *>(qs + i) = __ldg(reinterpret_cast<const float4 *>(qn + (size_t)r * nq * d + i));
     const int n_ch = d / SCL_CH;
@@ -389,8 +391,14 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
     const int tail0 = n_blocks * ratio;
     const int lo = min(rank * per_cta, n_blocks), hi = min(lo + per_cta, n_blocks);
 
+    // under the kernel before (programmatic dependent launch): the histograms are cleared; then it has completed
+    for (int i = tid; i < 3 * SC_BINS; i += SC_THREADS) (&hist[0][0])[i] = 0;
+    for (int i = tid; i < (SC_REP - 1) * SC_BINS; i += SC_THREADS) (&rep0[0][0])[i] = 0;
+    if (tid == 0) { s_prefix = 0; s_remaining = 0; s_take = 0; }
+    pdl_wait();
+    pdl_launch_next();
     // the scores of this CTA's blocks are asked for first (up to SC_PRE per thread stay in registers), so that their
-    // trip to memory runs under the clearing of the mask and of the histograms
+    // trip to memory runs under the clearing of the mask
     float pre[SC_PRE];
 #pragma unroll
     for (int j = 0; j < SC_PRE; j++) {
@@ -426,9 +434,6 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
         if (b < hi) { uint32_t k2; if (sel_key(sc[b], k2)) key = k2; }
         keys[i] = key;
     }
-    for (int i = tid; i < 3 * SC_BINS; i += SC_THREADS) (&hist[0][0])[i] = 0;
-    for (int i = tid; i < (SC_REP - 1) * SC_BINS; i += SC_THREADS) (&rep0[0][0])[i] = 0;
-    if (tid == 0) { s_prefix = 0; s_remaining = 0; s_take = 0; }
     __syncthreads();
 
     for (int pass = 0; pass < 3; pass++) {
@@ -604,6 +609,12 @@ qsa_select_cluster_kernel(uint8_t *__restrict__ mask, uint32_t *__restrict__ lis
 
 }  // namespace
 
+// The launch may start under the kernel in front of it on the stream; the kernel orders itself with pdl_wait().
+static void pdl_attr(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, cudaStream_t s) {
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_tune_pdl ? 1 : 0; cfg.stream = s;
+}
+
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
                      int b0, int b1, float eps) {
     if (b1 <= b0) return;
@@ -622,9 +633,11 @@ void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const flo
             cudaFuncSetAttribute(qsa_scores_lane_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
             configured[dev] = true;
         }
-        qsa_scores_lane_kernel<<<dim3((most + SCL_WARPS * 32 - 1) / (SCL_WARPS * 32), rows), SCL_WARPS * 32, smem, s>>>(
-            scores, qn, pool, nq, d, ratio, base_pos, max_blocks);
-        g_launches++;
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        pdl_attr(cfg, attr, s);
+        cfg.gridDim = dim3((most + SCL_WARPS * 32 - 1) / (SCL_WARPS * 32), rows); cfg.blockDim = dim3(SCL_WARPS * 32); cfg.dynamicSmemBytes = smem;
+        if (cudaLaunchKernelEx(&cfg, qsa_scores_lane_kernel, scores, qn, pool, nq, d, ratio, base_pos, max_blocks) == cudaSuccess) g_launches++;
         return;
     }
     qsa_scores_kernel<<<dim3((most + 7) / 8, rows), 256, 0, s>>>(scores, qn, pool, nq, d, ratio, base_pos, max_blocks);
@@ -644,10 +657,12 @@ void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const floa
             cudaFuncSetAttribute(qsa_select_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
             configured[dev] = true;
         }
-        qsa_select_cluster_kernel<<<rows * SC_CTAS, SC_THREADS, (size_t)per_cta * 4 + (size_t)(3 + SC_REP - 1) * SC_BINS * 4, s>>>(mask, list, scores, ratio, base_pos, block_topk,
-                                                                                         max_ctx, max_blocks, 1 + block_topk * ratio + ratio,
-                                                                                         per_cta);
-        g_launches++;
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute attr[1];
+        pdl_attr(cfg, attr, s);
+        cfg.gridDim = dim3(rows * SC_CTAS); cfg.blockDim = dim3(SC_THREADS); cfg.dynamicSmemBytes = (size_t)per_cta * 4 + (size_t)(3 + SC_REP - 1) * SC_BINS * 4;
+        if (cudaLaunchKernelEx(&cfg, qsa_select_cluster_kernel, mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
+                               1 + block_topk * ratio + ratio, per_cta) == cudaSuccess) g_launches++;
         return;
     }
     qsa_select_kernel<<<rows, SEL_THREADS, 0, s>>>(mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,

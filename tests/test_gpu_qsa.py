@@ -161,3 +161,36 @@ def test_scores_select_attend_chain(be, oracle):
         assert int(lists[r, 0]) == n and np.array_equal(lists[r, 1:1 + n], want_list[r, 1:1 + n])
     want = oracle.attn_masked(q, kc, vc, want_list, rows, qh, kvh, 256, max_ctx, 0.0625)
     assert rel_l2(got, want) < 5e-3          # the masked attention's tensor-op form (bf16 q and weights)
+
+
+def test_long_row_stages_back_to_back_on_the_same_buffers(be, oracle):
+    """Scoring and selection of a long row (the thread-block-cluster selection) launched several times in
+    a row on the same score, mask and list buffers, with two different queries: each launch may
+    start under the one before it, and the buffers must come out as the LAST pair leaves them."""
+    rng = np.random.default_rng(77)
+    rows, nq, d, ratio, base, topk = 1, 4, 128, 4, 40001, 256
+    max_ctx = base + 63; max_blocks = max_ctx // ratio; cap = topk * ratio + ratio
+    pool = rng.standard_normal((max_blocks, d)).astype(np.float32)
+    qa = rng.standard_normal((rows, nq, d)).astype(np.float32); qb_ = rng.standard_normal((rows, nq, d)).astype(np.float32)
+    with Bufs(be) as B:
+        pb, _ = B.shared(pool); q1, _ = B.shared(qa); q2, _ = B.shared(qb_)
+        sb, sv = B.shared_empty((rows, max_blocks), np.float32, fill=np.float32(0.0))
+        mb, mv = B.shared_empty((rows, max_ctx), np.uint8, fill=255)
+        lb, lv = B.shared_empty((rows, 1 + cap), np.uint32, fill=0xFFFFFFF0)
+
+        def stages(c):
+            for qx in (q1, q2, q1, q2):
+                be.op_qsa_scores_pooled(c, QwRef(sb, 0), QwRef(qx, 0), QwRef(pb, 0), rows, nq, d, ratio, base, max_blocks)
+                be.op_qsa_select(c, QwRef(mb, 0), QwRef(lb, 0), QwRef(sb, 0), rows, ratio, base, topk, max_ctx, max_blocks)
+                be.op_qsa_select(c, QwRef(mb, 0), QwRef(lb, 0), QwRef(sb, 0), rows, ratio, base, topk, max_ctx, max_blocks)
+        run(be, stages)
+        scores, mask, lists = np.array(sv), np.array(mv), np.array(lv)
+
+        def last_alone(c):
+            be.op_qsa_scores_pooled(c, QwRef(sb, 0), QwRef(q2, 0), QwRef(pb, 0), rows, nq, d, ratio, base, max_blocks)
+        run(be, last_alone)
+        assert np.array_equal(scores, np.array(sv)), "the last scoring's output differs from the same scoring run alone"
+    want_mask, want_list = oracle.qsa_select(scores, rows, ratio, base, topk, max_ctx)
+    n_keys, n = base + 1, int(want_list[0, 0])
+    assert np.array_equal(mask[0, :n_keys] != 0, want_mask[0, :n_keys] != 0)
+    assert int(lists[0, 0]) == n and np.array_equal(lists[0, 1:1 + n], want_list[0, 1:1 + n])

@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(256) qsa_pool_kernel(float *__restrict__ pool,
                                                        const uint16_t *__restrict__ k_norm, const float *__restrict__ inv_freq,
                                                        int d, int ratio, int b0, int b1, float eps) {
     const int b = b0 + blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_wait();                                                   // the index keys may come from the kernel before
+    pdl_launch_next();
     if (b >= b1) return;
     float x[8];
     block_key(x, ikeys, k_norm, inv_freq, d, ratio, b, eps, lane);
@@ -150,6 +152,8 @@ __global__ void __launch_bounds__(256) qsa_scores_kernel(float *__restrict__ sco
                                                          int max_blocks) {
     const int r = blockIdx.y, b = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     const int n_blocks = (base_pos + r + 1) / ratio;
+    pdl_wait();
+    pdl_launch_next();
     if (b >= n_blocks || b >= max_blocks) return;
     const int nk = d >> 5;
     float key[8];
@@ -202,6 +206,8 @@ __global__ void __launch_bounds__(SEL_THREADS) qsa_select_kernel(uint8_t *__rest
     const float *sc = scores + (size_t)r * max_blocks;
     uint8_t *m = mask + (size_t)r * max_ctx;
     uint32_t *l = list + (size_t)r * list_stride;
+    pdl_wait();                                                   // (the kernel before may still read the mask and the list)
+    pdl_launch_next();
     // the mask starts as 0 over the blocks and 1 over the tail; 16 bytes per store where the row allows
     const int tail0 = n_blocks * ratio;
     const int head = min((int)((16 - ((uintptr_t)m & 15)) & 15), n_keys);
@@ -618,8 +624,11 @@ static void pdl_attr(cudaLaunchConfig_t &cfg, cudaLaunchAttribute *attr, cudaStr
 void launch_qsa_pool(cudaStream_t s, float *pool, const float *ikeys, const uint16_t *k_norm, const float *inv_freq, int d, int ratio,
                      int b0, int b1, float eps) {
     if (b1 <= b0) return;
-    qsa_pool_kernel<<<(b1 - b0 + 7) / 8, 256, 0, s>>>(pool, ikeys, k_norm, inv_freq, d, ratio, b0, b1, eps);
-    g_launches++;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    pdl_attr(cfg, attr, s);
+    cfg.gridDim = dim3((b1 - b0 + 7) / 8); cfg.blockDim = dim3(256);
+    if (cudaLaunchKernelEx(&cfg, qsa_pool_kernel, pool, ikeys, k_norm, inv_freq, d, ratio, b0, b1, eps) == cudaSuccess) g_launches++;
 }
 void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const float *pool, int rows, int nq, int d, int ratio,
                        int base_pos, int max_blocks) {
@@ -640,8 +649,11 @@ void launch_qsa_scores(cudaStream_t s, float *scores, const float *qn, const flo
         if (cudaLaunchKernelEx(&cfg, qsa_scores_lane_kernel, scores, qn, pool, nq, d, ratio, base_pos, max_blocks) == cudaSuccess) g_launches++;
         return;
     }
-    qsa_scores_kernel<<<dim3((most + 7) / 8, rows), 256, 0, s>>>(scores, qn, pool, nq, d, ratio, base_pos, max_blocks);
-    g_launches++;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    pdl_attr(cfg, attr, s);
+    cfg.gridDim = dim3((most + 7) / 8, rows); cfg.blockDim = dim3(256);
+    if (cudaLaunchKernelEx(&cfg, qsa_scores_kernel, scores, qn, pool, nq, d, ratio, base_pos, max_blocks) == cudaSuccess) g_launches++;
 }
 void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const float *scores, int rows, int ratio, int base_pos,
                        int block_topk, int max_ctx, int max_blocks) {
@@ -665,9 +677,12 @@ void launch_qsa_select(cudaStream_t s, uint8_t *mask, uint32_t *list, const floa
                                1 + block_topk * ratio + ratio, per_cta) == cudaSuccess) g_launches++;
         return;
     }
-    qsa_select_kernel<<<rows, SEL_THREADS, 0, s>>>(mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
-                                                      1 + block_topk * ratio + ratio);
-    g_launches++;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    pdl_attr(cfg, attr, s);
+    cfg.gridDim = dim3(rows); cfg.blockDim = dim3(SEL_THREADS);
+    if (cudaLaunchKernelEx(&cfg, qsa_select_kernel, mask, list, scores, ratio, base_pos, block_topk, max_ctx, max_blocks,
+                           1 + block_topk * ratio + ratio) == cudaSuccess) g_launches++;
 }
 
 }  // namespace qw

@@ -696,7 +696,52 @@ def small_decode_extra(be, torch, peaks, device, name, layers):
         res["kernel_us"] = round(k_ms / k_n * 1e3, 2)
         res["kernel_frac_of_hbm"] = round(per_layer / 1e9 / (k_ms / k_n * 1e-3) / peaks["hbm"], 4)
     b.free()
+    if name == "c1_9b_decode_4k":
+        res["reference_op_order"] = unfused_layer_extra(be, torch, wl, device, layers)
     return res
+
+
+def unfused_layer_extra(be, torch, wl, device, layers):
+    """The same layer as the graph encodes it op by op (qwasar_graph.c:630-659: split, two norms, two
+    rotations, cache write, attention, gate -- eight calls through the C ABI, fp32 activations, a
+    caller-owned bf16 cache per layer) beside the one fused call the figure above times."""
+    from qwasar_b200.backend import QwRef
+    rows, qh, kvh, base = wl["rows"], wl["q_heads"], wl["kv_heads"], wl["base_pos"]
+    ctx = base + rows + 56
+    g = torch.Generator(device=device); g.manual_seed(wl["seed"] + 100)
+    wrap = lambda t: be.buf_wrap_device(t.data_ptr(), t.numel() * t.element_size())
+    qg = torch.randn((rows, qh, 512), generator=g, device=device, dtype=torch.float32)
+    k = torch.randn((rows, kvh, 256), generator=g, device=device, dtype=torch.float32)
+    v = torch.randn((rows, kvh, 256), generator=g, device=device, dtype=torch.float32)
+    kn = torch.empty_like(k)
+    q = torch.empty((rows, qh, 256), device=device, dtype=torch.float32); gate = torch.empty_like(q); out = torch.empty_like(q)
+    pos = torch.arange(base, base + rows, device=device, dtype=torch.int32).repeat(3, 1).contiguous()
+    kc = torch.randn((layers, kvh, ctx, 256), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    vc = torch.randn((layers, kvh, ctx, 256), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
+    keep = (qg, k, v, kn, q, gate, out, pos, kc, vc)
+    bqg, bk, bv, bkn, bq, bg, bo, bp, bkc, bvc = [wrap(t) for t in keep]
+    tab = rope_tab(be)
+    layer_bytes = kvh * ctx * 512
+
+    def encode(c):
+        for l in range(layers):
+            be.op_split_heads2(c, QwRef(bq, 0), QwRef(bg, 0), QwRef(bqg, 0), rows, qh, 256)
+            be.op_rms_norm(c, QwRef(bq, 0), QwRef(bq, 0), QwRef(tab, 512), 256, rows * qh, synth.EPS, 1.0)
+            be.op_rms_norm(c, QwRef(bkn, 0), QwRef(bk, 0), QwRef(tab, 512), 256, rows * kvh, synth.EPS, 1.0)
+            be.op_rope_partial(c, QwRef(bq, 0), QwRef(bp, 0), QwRef(tab, 0), QwRef(tab, 128), rows, qh, 256, 64)
+            be.op_rope_partial(c, QwRef(bkn, 0), QwRef(bp, 0), QwRef(tab, 0), QwRef(tab, 128), rows, kvh, 256, 64)
+            be.op_kv_write(c, QwRef(bkc, l * layer_bytes), QwRef(bvc, l * layer_bytes), QwRef(bkn, 0), QwRef(bv, 0), rows, kvh, 256, ctx, base)
+            be.op_attn(c, QwRef(bo, 0), QwRef(bq, 0), QwRef(bkc, l * layer_bytes), QwRef(bvc, l * layer_bytes), rows, qh, kvh, 256, ctx,
+                       base, synth.SCALE)
+            be.op_mul_sigmoid(c, QwRef(bo, 0), QwRef(bg, 0), rows * qh * 256)
+    n0 = be.launch_count()
+    ms, each = time_device(be, torch, encode, 30, 5, lambda: None)
+    launches = (be.launch_count() - n0) // (35 * layers)
+    for b in (bqg, bk, bv, bkn, bq, bg, bo, bp, bkc, bvc, tab):
+        be.buf_free(b)
+    del keep
+    return {"us_per_layer": round(ms * 1e3 / layers, 2), "us_per_layer_median": round(statistics.median(each) * 1e3 / layers, 2),
+            "calls_per_layer": 8, "kernels_per_layer": int(launches), "activations": "fp32", "cache": "caller-owned bf16, one per layer"}
 
 
 def strong_extra(be, torch, dist, world, rank, device, wl, layers, barrier, peaks, headline):

@@ -23,6 +23,8 @@ namespace {
 __global__ void split_heads2_kernel(float *__restrict__ a, float *__restrict__ b, const float *__restrict__ src,
                                     int64_t n_rh, int dim) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over n_rh * dim
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (i >= n_rh * dim) return;
     const int64_t rh = i / dim;
     const int d = (int)(i - rh * dim);
@@ -35,6 +37,8 @@ __global__ void rms_norm_kernel(float *__restrict__ y, const float *__restrict__
                                 int dim, int rows, float eps, float out_scale) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (row >= rows) return;
     const float *xr = x + (size_t)row * dim;
     float *yr = y + (size_t)row * dim;
@@ -53,6 +57,8 @@ __global__ void rope_partial_kernel(float *__restrict__ x, const int32_t *__rest
                                     const uint8_t *__restrict__ axis, const float *__restrict__ inv_freq,
                                     int rows, int heads, int head_dim, int half) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // over rows*heads*half
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (i >= (int64_t)rows * heads * half) return;
     const int j = (int)(i % half);
     const int64_t rh = i / half;
@@ -71,6 +77,8 @@ __global__ void kv_write_kernel(KvLayer kc, KvLayer vc, const float *__restrict_
                                 int rows, int kv_heads, int base_pos) {
     const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (w >= rows * kv_heads) return;
     const int r = w / kv_heads, h = w % kv_heads;
     const float4 *ks = reinterpret_cast<const float4 *>(k + (size_t)w * 256) + lane * 2;
@@ -87,12 +95,16 @@ __global__ void kv_write_kernel(KvLayer kc, KvLayer vc, const float *__restrict_
 
 __global__ void mul_sigmoid_kernel(float *__restrict__ y, const float *__restrict__ g, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (i < n) y[i] = __fmul_rn(y[i], __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g[i]))));
 }
 
 // dst[r, 0:len] = src[r, offset:offset+len] over rows of src_stride floats (qwasar_gpu.h:387-389)
 __global__ void slice_rows_kernel(float *__restrict__ dst, const float *__restrict__ src, int64_t n, int src_stride, int offset, int len) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (i >= n) return;
     const int64_t r = i / len;
     dst[i] = src[r * src_stride + offset + (i - r * len)];
@@ -100,6 +112,8 @@ __global__ void slice_rows_kernel(float *__restrict__ dst, const float *__restri
 
 __global__ void f32_to_bf16_kernel(__nv_bfloat16 *__restrict__ dst, const float *__restrict__ src, int64_t n) {
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    pdl_wait();                                                   // (programmatic dependent launch, qw_common.cuh)
+    pdl_launch_next();
     if (i + 3 < n) {
         const float4 v = *reinterpret_cast<const float4 *>(src + i);
         uint2 o;
@@ -369,48 +383,50 @@ void launch_kv_pack(cudaStream_t s, KvLayer kc, KvLayer vc, void *packed, int kv
     kv_pack_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(kc, vc, reinterpret_cast<uint4 *>(packed), kv_heads, n_tokens, unpack);
     g_launches++;
 }
+// The small ops start under the kernel in front of them on the stream (each waits for it before it touches memory):
+// in the graph's own sequence of eight ops per layer the gaps between launches outweigh the kernels.
+template <typename... Params, typename... Args>
+static void launch_small(void (*kernel)(Params...), unsigned grid, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(256); cfg.stream = s; cfg.attrs = attr; cfg.numAttrs = g_tune_pdl ? 1 : 0;
+    if (cudaLaunchKernelEx(&cfg, kernel, Params(args)...) == cudaSuccess) g_launches++;
+}
 void launch_split_heads2(cudaStream_t s, float *a, float *b, const float *src, int rows, int heads, int dim) {
     const int64_t n = (int64_t)rows * heads * dim;
     if (n <= 0) return;
-    split_heads2_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(a, b, src, (int64_t)rows * heads, dim);
-    g_launches++;
+    launch_small(split_heads2_kernel, (unsigned)((n + 255) / 256), s, a, b, src, (int64_t)rows * heads, dim);
 }
 void launch_rms_norm(cudaStream_t s, float *y, const float *x, const uint16_t *w, int dim, int rows, float eps,
                      float out_scale) {
     if (rows <= 0) return;
-    rms_norm_kernel<<<(rows + 7) / 8, 256, 0, s>>>(y, x, w, dim, rows, eps, out_scale);
-    g_launches++;
+    launch_small(rms_norm_kernel, (unsigned)((rows + 7) / 8), s, y, x, w, dim, rows, eps, out_scale);
 }
 void launch_rope_partial(cudaStream_t s, float *x, const int32_t *pos, const uint8_t *axis, const float *inv_freq,
                          int rows, int heads, int head_dim, int rotary_dim) {
     const int64_t n = (int64_t)rows * heads * (rotary_dim / 2);
     if (n <= 0) return;
-    rope_partial_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(x, pos, axis, inv_freq, rows, heads, head_dim,
-                                                                     rotary_dim / 2);
-    g_launches++;
+    launch_small(rope_partial_kernel, (unsigned)((n + 255) / 256), s, x, pos, axis, inv_freq, rows, heads, head_dim, rotary_dim / 2);
 }
 void launch_kv_write(cudaStream_t s, KvLayer kc, KvLayer vc, const float *k, const float *v, int rows, int kv_heads,
                      int base_pos) {
     const int n = rows * kv_heads;
     if (n <= 0) return;
-    kv_write_kernel<<<(n + 7) / 8, 256, 0, s>>>(kc, vc, k, v, rows, kv_heads, base_pos);
-    g_launches++;
+    launch_small(kv_write_kernel, (unsigned)((n + 7) / 8), s, kc, vc, k, v, rows, kv_heads, base_pos);
 }
 void launch_mul_sigmoid(cudaStream_t s, float *y, const float *gate, int64_t n) {
     if (n <= 0) return;
-    mul_sigmoid_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(y, gate, n);
-    g_launches++;
+    launch_small(mul_sigmoid_kernel, (unsigned)((n + 255) / 256), s, y, gate, n);
 }
 void launch_slice_rows(cudaStream_t s, float *dst, const float *src, int rows, int src_stride, int offset, int len) {
     const int64_t n = (int64_t)rows * len;
     if (n <= 0) return;
-    slice_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(dst, src, n, src_stride, offset, len);
-    g_launches++;
+    launch_small(slice_rows_kernel, (unsigned)((n + 255) / 256), s, dst, src, n, src_stride, offset, len);
 }
 void launch_f32_to_bf16(cudaStream_t s, __nv_bfloat16 *dst, const float *src, int64_t n) {
     if (n <= 0) return;
-    f32_to_bf16_kernel<<<(unsigned)((n + 1023) / 1024), 256, 0, s>>>(dst, src, n);
-    g_launches++;
+    launch_small(f32_to_bf16_kernel, (unsigned)((n + 1023) / 1024), s, dst, src, n);
 }
 void launch_preop(cudaStream_t s, const PreopParams &p, int max_rows) {
     const int slots = (p.skip_q ? 0 : p.q_heads) + 2 * p.kv_heads;

@@ -622,8 +622,20 @@ def next_rows_extra(be, torch, peaks, device):
     per = w_bytes + 2 * s_bytes
     out["qmat_q4_decode"] = {"k": k, "n": n, "group": group, "us": round(ms * 1e3, 2), "weight_gbs": round(per / 1e9 / (ms * 1e-3), 1),
                              "frac_of_hbm": round(per / 1e9 / (ms * 1e-3) / peaks["hbm"], 4), "peak": peaks["which"]}
-    for b in (bw, bs, bb, bx, by):
+    # ---- the same product for the four rows of a speculative verify: one pass over the weights
+    x4 = torch.randn((4, k), generator=g, device=device, dtype=torch.float32)
+    y4 = torch.empty((4, n), device=device, dtype=torch.float32)
+    bx4, by4 = wrap(x4), wrap(y4)
+
+    def q4v(c):
+        for i in range(sets):
+            be.op_qmat_q4(c, QwRef(by4, 0), QwRef(bx4, 0), QwRef(bw, i * w_bytes), QwRef(bs, i * s_bytes), QwRef(bb, i * s_bytes), k, n, 4, group)
+    ms4 = time_device(be, torch, q4v, 5, 3, lambda: None)[0] / sets
+    out["qmat_q4_verify"] = {"k": k, "n": n, "rows": 4, "group": group, "us": round(ms4 * 1e3, 2), "weight_gbs": round(per / 1e9 / (ms4 * 1e-3), 1),
+                             "frac_of_hbm": round(per / 1e9 / (ms4 * 1e-3) / peaks["hbm"], 4), "peak": peaks["which"]}
+    for b in (bw, bs, bb, bx, by, bx4, by4):
         be.buf_free(b)
+    del x4, y4
     # ---- q4 product, many tokens (a prefill-side q_proj): the tcgen05 GEMM with the weights dequantised on their way
     rows_p = 4096
     xp = torch.randn((rows_p, k), generator=g, device=device, dtype=torch.float32)

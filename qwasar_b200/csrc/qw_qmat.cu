@@ -570,7 +570,12 @@ __global__ void __launch_bounds__(NB == 1 ? (QI_MAXW + 2) * 32 : (QI_MAXW4 + 2) 
     fence_proxy_async();                                           // (our reads of it, before the bulk copies' writes)
     asm volatile("bar.arrive 3, %0;" ::"r"(CT + 32) : "memory");     // the borrowed stage may be loaded
     const uint32_t a_stage = smem_u32(stage0);
-    const uint32_t o_w = (uint32_t)(gid >> 1) * job.w_stride + (gid & 1) * w_bytes + tig * 8 + g0 * 32, o_s = 8u * job.w_stride + (uint32_t)gid * s_bytes + g0 * 2;
+    // Rows of the instruction -> rows of the tile: lanes 0-15 (the half of a warp an 8-byte read is served by at a time)
+    // hold instruction rows 0-3, which are the first rows of the tile's first four pairs -- 8 banks apart, all 32 banks
+    // between them; lanes 16-31 the pairs' second rows.  (Instruction row = tile row put a pair's two rows, which lie
+    // a multiple of 32 banks apart, into the same half: every read took four passes instead of two.)
+    const int trow = 2 * (gid & 3) + (gid >> 2);
+    const uint32_t o_w = (uint32_t)(gid & 3) * job.w_stride + (gid >> 2) * w_bytes + tig * 8 + g0 * 32, o_s = 8u * job.w_stride + (uint32_t)trow * s_bytes + g0 * 2;
     const uint32_t d_w = 4u * job.w_stride, d_s = 8u * s_bytes, d_b = 16u * s_bytes;
     for (int it = 0; it < my_tiles; it++) {
         const int st = it % S;
@@ -579,7 +584,7 @@ __global__ void __launch_bounds__(NB == 1 ? (QI_MAXW + 2) * 32 : (QI_MAXW4 + 2) 
         const uint4 sv0 = lds_u4(a_s), sv1 = lds_u4(a_s + d_s), bv0 = lds_u4(a_s + d_b), bv1 = lds_u4(a_s + d_b + d_s);
         const uint32_t s0w[4] = {sv0.x, sv0.y, sv0.z, sv0.w}, s1w[4] = {sv1.x, sv1.y, sv1.z, sv1.w};
         const uint32_t b0w[4] = {bv0.x, bv0.y, bv0.z, bv0.w}, b1w[4] = {bv1.x, bv1.y, bv1.z, bv1.w};
-        float ya0[NB], ya1[NB], yb0 = 0.0f, yb1 = 0.0f;        // rows gid, gid + 8: column-pair sums per block, bias sums (token tig)
+        float ya0[NB], ya1[NB], yb0 = 0.0f, yb1 = 0.0f;        // rows trow, trow + 8: column-pair sums per block, bias sums (token tig)
 #pragma unroll
         for (int u = 0; u < NB; u++) { ya0[u] = 0.0f; ya1[u] = 0.0f; }
 #pragma unroll
@@ -614,8 +619,8 @@ __global__ void __launch_bounds__(NB == 1 ? (QI_MAXW + 2) * 32 : (QI_MAXW4 + 2) 
         if (it >= QI_SLOTS) mbar_wait_hot(&pfree[slot], ((it / QI_SLOTS) - 1) & 1, &s_abort, job.status, QW_ST_SLOT_TIMEOUT);
         float *pp = part + (size_t)(slot * W + warp) * 64 * NB, *pq = pbias + (size_t)(slot * W + warp) * 64;
 #pragma unroll
-        for (int u = 0; u < NB; u++) { pp[gid * 4 * NB + u * 4 + tig] = ya0[u]; pp[(gid + 8) * 4 * NB + u * 4 + tig] = ya1[u]; }
-        pq[gid * 4 + tig] = yb0; pq[(gid + 8) * 4 + tig] = yb1;
+        for (int u = 0; u < NB; u++) { pp[trow * 4 * NB + u * 4 + tig] = ya0[u]; pp[(trow + 8) * 4 * NB + u * 4 + tig] = ya1[u]; }
+        pq[trow * 4 + tig] = yb0; pq[(trow + 8) * 4 + tig] = yb1;
         __syncwarp();
         if (lane == 0) mbar_arrive(&done[slot]);                // partial sums are in place
     }

@@ -36,7 +36,8 @@ def worst_rel_err(got, x, deq):
                                               (640, 1, 1, 64), (16384, 40, 2, 64),
                                               (2048, 256, 16, 64), (1024, 520, 200, 64), (5120, 768, 300, 64), (2048, 1000, 129, 64), (2560, 8, 16, 64), (6144, 264, 64, 64), (2048, 100, 15, 64), (1024, 72, 7, 64),
                                               (5120, 1000, 3, 64), (5120, 2000, 4, 64), (6144, 264, 4, 64), (512, 50, 3, 64), (7168, 40, 4, 64), (8192, 70, 4, 64),
-                                              (3072, 17, 4, 64), (5120, 300, 11, 64)])
+                                              (3072, 17, 4, 64), (5120, 300, 11, 64),
+                                              (4608, 40, 1, 64), (3584, 24, 2, 64), (1536, 33, 1, 64), (5632, 50, 3, 64), (5632, 48, 1, 64)])
 def test_q4_product(be, oracle, op, k, n, rows, group):
     rng = np.random.default_rng(k + n + rows)
     w, sc, bi = q4_weights(rng, n, k, group)

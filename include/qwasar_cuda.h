@@ -238,7 +238,8 @@ uint64_t    qw_gpu_launch_count(void);
  * split-KV kernel; "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
  * split-KV kernel over row chunks; "prefill_fuse_q" = 1 | 0, with bf16 rows the tcgen05 prefill norms and
  * rotates its own query tiles (default) or the pre-op kernel does; "pdl" = 1 | 0, the kernels of the
- * decode chain start under the kernel in front of them (programmatic dependent launch, default) or in
+ * decode chain, of the QSA ops, of the small unfused ops and of the few-token 4-bit product start under the kernel in
+ * front of them (programmatic dependent launch, default: each waits for that kernel before it touches memory) or in
  * plain stream order; "masked_tc" = 1 | 2 | 0, attention over a gathered row list on tensor-op tiles
  * (bf16 operands) as one launch on a thread-block cluster (default), as partials plus a merge launch, or on
  * the fp32 kernel; "qmv_tc" = 1 | 0, the 4-bit product of up to 15 tokens

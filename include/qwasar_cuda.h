@@ -235,7 +235,8 @@ int32_t     qw_gpu_current(void);            /* -1 before init */
 uint64_t    qw_gpu_launch_count(void);
 /* Diagnostic knobs (the counterpart of the reference's QWASAR_ATTN / QWASAR_FA overrides,
  * qwasar_metal.m:1513-1516): "split_kg" = 4 | 6, consumer warps per 16-row tile of the
- * split-KV kernel; "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
+ * split-KV kernel (one row tile: a decode step); "split_kg2" = 3 | 2, the same for two row tiles (17 to 32 query rows
+ * per KV head: a verify step); "prefill_tc" = 1 | 0, many-row attention on the tcgen05 kernel or on the
  * split-KV kernel over row chunks; "prefill_fuse_q" = 1 | 0, with bf16 rows the tcgen05 prefill norms and
  * rotates its own query tiles (default) or the pre-op kernel does; "pdl" = 1 | 0, the kernels of the
  * decode chain, of the QSA ops, of the small unfused ops and of the few-token 4-bit product start under the kernel in

@@ -41,7 +41,7 @@ template <int MT, int KG_>
 struct SplitCfg {
     static constexpr int KG = KG_;
     static constexpr int NW = MT * KG;                    // consumer warps
-    static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? 5 : 3);
+    static constexpr int NST = (MT == 1) ? 6 : (MT == 2 ? (KG_ == 3 ? 3 : 5) : 3);
     static constexpr int THREADS = (NW + 1) * 32;         // + the TMA producer warp
     static_assert(THREADS <= 256, "warps are allocated in fours: 9 warps would be budgeted as 12");
     // a warp must take part in every phase of each stage it ever waits on (a parity wait is only
@@ -1492,6 +1492,7 @@ int g_tune_prefill_fuse_q = 1;
 int g_tune_pdl = 1;
 int g_tune_masked_tc = 1;
 int g_tune_qmv_tc = 1;
+int g_tune_split_kg2 = 3;
 int g_tune_qmv_pre = 1;
 
 int sm_count() {
@@ -1520,7 +1521,10 @@ void launch_attn_split(cudaStream_t s, const AttnParams &p, int max_rows) {
             if (g_tune_split_kg == 4) launch_split_t<1, 4>(s, p);
             else launch_split_t<1, 6>(s, p);
             break;
-        case 2: launch_split_t<2, 2>(s, p); break;
+        case 2:
+            if (g_tune_split_kg2 == 3) launch_split_t<2, 3>(s, p);
+            else launch_split_t<2, 2>(s, p);
+            break;
         default: launch_split_t<4, 1>(s, p); break;
     }
 }

@@ -233,6 +233,7 @@ extern int g_tune_pdl;
 extern int g_tune_masked_tc;
 // 1: a one-token 4-bit product keeps x in registers (qmv1_q4_kernel); 0: the shared-memory kernel.
 extern int g_tune_qmv_tc;
+extern int g_tune_split_kg2;
 extern int g_tune_qmv_pre;
 
 }  // namespace qw

@@ -805,6 +805,7 @@ extern "C" bool qw_gpu_tune(const char *knob, int32_t value) {
     if (knob && !strcmp(knob, "prefill_fuse_q") && (value == 0 || value == 1)) { qw::g_tune_prefill_fuse_q = value; return true; }
     if (knob && !strcmp(knob, "pdl") && (value == 0 || value == 1)) { qw::g_tune_pdl = value; return true; }
     if (knob && !strcmp(knob, "masked_tc") && value >= 0 && value <= 2) { qw::g_tune_masked_tc = value; return true; }
+    if (knob && !strcmp(knob, "split_kg2") && (value == 2 || value == 3)) { qw::g_tune_split_kg2 = value; return true; }
     if (knob && !strcmp(knob, "qmv_tc") && (value == 0 || value == 1)) { qw::g_tune_qmv_tc = value; return true; }
     if (knob && !strcmp(knob, "qmv_pre") && value >= 0 && value <= 2) { qw::g_tune_qmv_pre = value; return true; }
     if (knob && !strcmp(knob, "qmm_tc") && (value == 0 || value == 1)) { qw::g_tune_qmm_tc = value; return true; }

@@ -674,7 +674,7 @@ def next_rows_extra(be, torch, peaks, device):
     # Each figure is per launch over `reps` back-to-back launches per timed step (like the eight weight sets of the
     # product above): the event the timer records after a step keeps the next launch from starting under the
     # last one, which is how the layers of a decode step follow one another.
-    step, reps = {}, 4
+    step, reps = {}, 8
     for name, fn in stages.items():
         def repeated(c, fn=fn):
             for _ in range(reps):

@@ -76,3 +76,26 @@ def test_no_device_means_loud_failure():
     assert lib.qw_kv_arena_alloc(1, 1, 64, 256) is None
     with pytest.raises(RuntimeError):
         qwasar_b200.Backend()
+
+
+def test_documented_knobs_are_the_accepted_ones():
+    """Every knob the header documents (`"name" = a | b | c` in the comment above qw_gpu_tune) is
+    accepted with each value it lists and refused with another; an unknown knob is refused.  Host
+    state only: no device is touched.  The defaults are restored."""
+    text = open(os.path.join(ROOT, "include", "qwasar_cuda.h")).read()
+    doc = text[text.index("/* Diagnostic knobs"):text.index("qw_gpu_tune(const char *knob")]
+    doc = re.sub(r"\n \* ?", " ", doc)
+    knobs = {m.group(1): [int(v) for v in re.findall(r"\d+", m.group(2))]
+             for m in re.finditer(r'"([a-z0-9_]+)" = (\d+(?: \| \d+)+)', doc)}
+    assert set(knobs) >= {"split_kg", "split_kg2", "prefill_tc", "prefill_fuse_q", "pdl", "masked_tc", "qmv_tc", "qmv_pre", "qmm_tc"}
+    lib = backend.load_library()
+    try:
+        for name, values in knobs.items():
+            for v in values:
+                assert lib.qw_gpu_tune(name.encode(), v), f'{name} = {v} is documented but refused'
+            assert not lib.qw_gpu_tune(name.encode(), 97), f"{name} accepts a value the header does not list"
+        assert not lib.qw_gpu_tune(b"no_such_knob", 1)
+        assert not lib.qw_gpu_tune(None, 1)
+    finally:
+        for name, values in knobs.items():                      # back to the defaults: the first value listed, split_kg 6
+            lib.qw_gpu_tune(name.encode(), 6 if name == "split_kg" else values[0])
